@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the forward-Laplacian hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One JSON line on stdout (rank 0).  A "step" is one pass of the hot path over one batch of
+synthetic triplets; `value` is samples (walker-Laplacians) per second over all ranks with the
+inputs already in HBM; `e2e` is the same through host buffers (H2D of the inputs and D2H of the
+result inside the timed region).  `--impl reference` times the CPU restatement of the reference's
+rules (the reference itself is pure Python on JAX, which is not installed on these machines).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = 'walker_laplacians_per_sec'
+UNIT = 'walker-Laplacians/s'
+
+
+def load_peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {'hbm_gbs': p['hbm_gbs'], 'bf16_tflops': p['bf16_tflops'], 'source': 'measured'}
+    return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'source': 'fallback'}
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,'
+              'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,'
+              'clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples: list[list[str]] = []
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ['nvidia-smi', f'--query-gpu={self.FIELDS}', '--format=csv,noheader,nounits',
+                     '-i', str(self.index)], capture_output=True, text=True, timeout=5).stdout
+                row = [c.strip() for c in out.strip().split(',')]
+                if len(row) == 6:
+                    self.samples.append(row)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self):
+        if not self.samples:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['unsampled']}
+        sm = [float(s[0]) for s in self.samples if s[0].replace('.', '').isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace('.', '').isdigit()]
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith('active') for s in self.samples)]
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': reasons, 'samples': len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------
+# workload: operator microbench (BASELINE.json configs[1])
+# ------------------------------------------------------------------------------------------
+B, D, F, KS = 4096, 96, 256, 3  # samples, dense Jacobian rows, features, sparse rows per position
+
+
+def make_host_inputs(seed: int, n_samples: int = B):
+    g = torch.Generator().manual_seed(seed)
+    mk = lambda *s: torch.randn(*s, generator=g)
+    return {
+        'dense': (mk(n_samples, F), mk(D, n_samples, F), mk(n_samples, F)),
+        'sparse': (mk(n_samples, F), mk(KS, n_samples, F), mk(n_samples, F)),
+        'W': mk(F, F) / F**0.5,
+        'bias': mk(F) * 0.1,
+    }
+
+
+def chain_device(kernels, a, W, bias, timers=None):
+    """dot_general(+bias) -> tanh -> silu -> LayerNorm on one triplet; optional per-kernel events."""
+    def run(name, fn):
+        if timers is None:
+            return fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        timers.append((name, e0, e1))
+        return out
+
+    tag = 'dense' if a.jacobian.data.shape[0] > KS else 'sparse'
+    h = run(f'dot_general/{tag}', lambda: kernels.dot_general(a, W, bias))
+    h = run(f'tanh/{tag}', lambda: kernels.elementwise('tanh', h))
+    h = run(f'silu/{tag}', lambda: kernels.elementwise('silu', h))
+    h = run(f'layernorm/{tag}', lambda: kernels.layernorm(h, None, None, 1e-6))
+    return h
+
+
+def chain_oracle(rules, t, W, bias):
+    t = rules.dot_general(t, W, bias)
+    t = rules.elementwise('tanh', t)
+    t = rules.elementwise('silu', t)
+    return rules.layernorm(t, None, None, 1e-6)
+
+
+def algorithmic(name: str):
+    """(bytes, flops) one launch of the named kernel moves / computes (fp32, algorithmic)."""
+    kind, tag = name.split('/')
+    K = D if tag == 'dense' else KS
+    rows = (K + 2) * B
+    if kind == 'dot_general':
+        return 4 * (rows * (F + F) + F * F + F), 2 * rows * F * F
+    return 8 * rows * F, 0
+
+
+def run_ours(args, rank, world, device):
+    from folx_b200 import kernels, lib
+
+    lib.load()
+    host = make_host_inputs(seed=rank)
+    pinned = {k: tuple(t.pin_memory() for t in host[k]) for k in ('dense', 'sparse')}
+    W = host['W'].to(device)
+    bias = host['bias'].to(device)
+
+    def upload(kind):
+        x, J, lap = pinned[kind]
+        a = kernels.alloc_triplet(J.shape[0], x.shape, device)
+        a.x.copy_(x, non_blocking=True)
+        a.jacobian.data.copy_(J, non_blocking=True)
+        a.laplacian.copy_(lap, non_blocking=True)
+        return a
+
+    dense, sparse = upload('dense'), upload('sparse')
+    torch.cuda.synchronize(device)
+
+    def step(timers=None):
+        chain_device(kernels, dense, W, bias, timers)
+        chain_device(kernels, sparse, W, bias, timers)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    kernels.check_gemm_status(device)
+
+    # ---- device-resident timing ----
+    timers: list = []
+    barrier()
+    with ClockSampler(device.index or 0) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step(timers)
+        e1.record()
+        barrier()
+        # keep sampling long enough for at least a couple of nvidia-smi readings
+        total_ms = e0.elapsed_time(e1)
+        if total_ms < 800:
+            t_end = time.time() + 0.8
+            while time.time() < t_end:
+                step()
+            torch.cuda.synchronize(device)
+    kernels.check_gemm_status(device)
+    launches = 8 * args.steps
+
+    # ---- end to end through host buffers ----
+    out_host = {k: tuple(torch.empty_like(t).pin_memory() for t in host[k]) for k in ('dense', 'sparse')}
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        for kind in ('dense', 'sparse'):
+            a = upload(kind)
+            h = chain_device(kernels, a, W, bias)
+            ox, oj, ol = out_host[kind]
+            ox.copy_(h.x, non_blocking=True)
+            oj.copy_(h.jacobian.data, non_blocking=True)
+            ol.copy_(h.laplacian, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    g1.record()
+    barrier()
+    e2e_ms = max(g0.elapsed_time(g1), (time.perf_counter() - t0) * 1e3 * 0.0) / e2e_steps
+    io_bytes = sum(t.numel() * 4 for k in ('dense', 'sparse') for t in host[k])
+
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms], device=device, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        total_ms, e2e_ms = float(t[0]), float(t[1])
+
+    # ---- per-kernel roofline from the events recorded inside the timed region ----
+    per_kernel: dict[str, list[float]] = {}
+    for name, a, b in timers:
+        per_kernel.setdefault(name, []).append(a.elapsed_time(b))
+    peaks = load_peaks()
+    tf32_peak = peaks['bf16_tflops'] / 2.0  # dense TF32 is half the bf16 rate
+    kern = {}
+    for name, ts in per_kernel.items():
+        ms = sum(ts) / len(ts)
+        nbytes, flops = algorithmic(name)
+        kern[name] = {'ms': round(ms, 4), 'share': None, 'GBps': round(nbytes / ms / 1e6, 1),
+                      'frac_hbm': round(nbytes / ms / 1e6 / peaks['hbm_gbs'], 3)}
+        if flops:
+            kern[name]['TFLOPs_fp32_equiv'] = round(flops / ms / 1e9, 1)
+    tot = sum(v['ms'] for v in kern.values())
+    for v in kern.values():
+        v['share'] = round(v['ms'] / tot, 3)
+    dominant = max(kern, key=lambda n: kern[n]['ms'])
+    nbytes, flops = algorithmic(dominant)
+    ms = kern[dominant]['ms']
+    if dominant.startswith('dot_general'):
+        achieved = flops / ms / 1e9
+        roofline = {'kernel': dominant, 'bound': 'tensor', 'achieved': round(achieved, 1),
+                    'peak': round(tf32_peak, 1), 'unit': 'TFLOP/s', 'frac': round(achieved / tf32_peak, 3),
+                    'traffic': None,
+                    'note': 'achieved = fp32-equivalent (algorithmic) flops; the 3xTF32 split executes 3x '
+                            'that on the tensor pipe, so the ceiling is peak/3; peak = measured bf16 / 2 '
+                            f'({peaks["source"]})',
+                    'frac_of_3xtf32_ceiling': round(3 * achieved / tf32_peak, 3),
+                    'hbm_frac': kern[dominant]['frac_hbm']}
+    else:
+        achieved = nbytes / ms / 1e6
+        roofline = {'kernel': dominant, 'bound': 'hbm', 'achieved': round(achieved, 1),
+                    'peak': peaks['hbm_gbs'], 'unit': 'GB/s', 'frac': round(achieved / peaks['hbm_gbs'], 3),
+                    'traffic': None, 'note': f'peak {peaks["source"]}'}
+
+    result = {
+        'metric': METRIC, 'value': world * B * args.steps / (total_ms / 1e3), 'unit': UNIT,
+        'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3),
+        'ms_per_step': total_ms / args.steps, 'higher_is_better': True, 'scaling': 'weak',
+        'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': 'operator-microbench (BASELINE configs[1]): per step, on B=4096 samples, '
+                               'dot_general(256x256)+bias -> tanh -> silu -> LayerNorm on a dense J (d=96) '
+                               'and on a sparse J (3 rows per position)',
+                   'samples_per_gpu': B, 'jac_rows_dense': D, 'jac_rows_sparse': KS, 'features': F,
+                   'l2': 'dense triplet is 411 MB per tensor (> 126 MB L2); every kernel streams it'},
+        'clocks': clocks.summary(),
+        'e2e': {'value': world * B / (e2e_ms / 1e3), 'unit': UNIT, 'h2d_bytes_per_step': io_bytes,
+                'd2h_bytes_per_step': io_bytes, 'ms_per_step': e2e_ms},
+        'gpu_launches': launches,
+        'roofline': roofline,
+        'kernels': kern,
+    }
+    return result
+
+
+def cpu_baseline(sample: int, repeats: int = 3):
+    """Times the CPU restatement (oracle, torch fp32, all host threads) on `sample` samples."""
+    from oracle import rules
+
+    host = make_host_inputs(seed=0, n_samples=sample)
+    W, bias = host['W'], host['bias']
+    chain_oracle(rules, host['sparse'], W, bias)  # warm-up
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        chain_oracle(rules, host['dense'], W, bias)
+        chain_oracle(rules, host['sparse'], W, bias)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return {'value': sample / t, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
+            'sample': f'{sample} of {B} samples of the same step (dense d=96 chain + sparse chain), torch-CPU fp32, '
+                      f'median of {repeats}; host has {os.cpu_count()} logical cores',
+            'seconds': t}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return None
+    times = []
+    sample = 256
+    from oracle import rules
+
+    host = make_host_inputs(seed=0, n_samples=sample)
+    W, bias = host['W'], host['bias']
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        chain_oracle(rules, host['dense'], W, bias)
+        chain_oracle(rules, host['sparse'], W, bias)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = sample * args.steps / total
+    return {
+        'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': total / args.steps * 1e3,
+        'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
+        'data': 'synthetic',
+        'config': {'workload': 'operator-microbench (BASELINE configs[1]); each step is a bounded sample of '
+                               f'{sample} of the 4096 samples', 'note': 'CPU restatement of the reference rules '
+                               '(the reference needs JAX, which is not installed here)'},
+        'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
+                         'sample': f'{sample} of {B} samples per step'},
+        'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    args = ap.parse_args()
+
+    rank = int(os.environ.get('RANK', 0))
+    world = int(os.environ.get('WORLD_SIZE', 1))
+    local = int(os.environ.get('LOCAL_RANK', 0))
+
+    if args.impl == 'reference':
+        res = run_reference(args, rank, world)
+        if res is not None:
+            print(json.dumps(res), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device (there is no CPU fallback for the product path)')
+    device = torch.device('cuda', local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        torch.distributed.init_process_group('nccl', device_id=device)
+    res = run_ours(args, rank, world, device)
+    if rank == 0:
+        res['cpu_baseline'] = cpu_baseline(sample=128) if world == 1 else None
+        print(json.dumps(res), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

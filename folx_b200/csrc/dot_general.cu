@@ -1,0 +1,73 @@
+// dot_general with one constant operand on a stacked triplet: entry points and dispatch between
+// the tensor-core kernel and the CUDA-core kernel (reference: _dot_general_one_constant,
+// folx/wrapped_functions.py:71-171, and the bias `add`, folx/wrapped_functions.py:364-366).
+#include "gemm.cuh"
+
+namespace fl {
+static int g_mode = 0;
+}
+
+extern "C" void fl_dot_general_set_mode(int32_t mode) { fl::g_mode = mode; }
+
+extern "C" int64_t fl_dot_general_workspace_bytes(int64_t F_in, int64_t F_out) {
+  if (F_in <= 0 || F_out <= 0) return 256;
+  return fl::wsplit_geom(F_in, F_out).bytes;
+}
+
+extern "C" int32_t fl_dot_general_prepare(const float* W, int64_t F_in, int64_t F_out,
+                                          void* workspace, int64_t workspace_bytes, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(W && workspace && F_in > 0 && F_out > 0, FL_EBADSHAPE,
+             "fl_dot_general_prepare: bad arguments");
+  FL_REQUIRE(workspace_bytes >= wsplit_geom(F_in, F_out).bytes, FL_EBADSHAPE,
+             "fl_dot_general_prepare: workspace too small (%lld < %lld)", (long long)workspace_bytes,
+             (long long)wsplit_geom(F_in, F_out).bytes);
+  return gemm_tc_prepare(W, F_in, F_out, workspace, (cudaStream_t)stream);
+}
+
+extern "C" int32_t fl_dot_general(const float* x, const float* jac, const float* lap, int64_t P,
+                                  int64_t K, int64_t F_in, int64_t F_out, const float* W,
+                                  const float* bias, const void* workspace,
+                                  int64_t workspace_bytes, float* y, float* jac_y, float* lap_y,
+                                  int32_t* status, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(P >= 0 && K >= 0 && F_in > 0 && F_out > 0, FL_EBADSHAPE,
+             "fl_dot_general: bad sizes P=%lld K=%lld F_in=%lld F_out=%lld", (long long)P,
+             (long long)K, (long long)F_in, (long long)F_out);
+  if (P == 0) return FL_OK;
+  FL_REQUIRE(x && lap && y && lap_y && W && (K == 0 || (jac && jac_y)), FL_EBADSHAPE,
+             "fl_dot_general: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+
+  // Pieces of the stacked operand: x rows, J rows, lap rows.  Adjacent pieces are merged so the
+  // usual stacked layout runs as one launch.
+  struct Piece { const float* a; float* o; int64_t rows; int64_t bias_rows; };
+  Piece pieces[3] = {{x, y, P, bias ? P : 0}, {jac, jac_y, K * P, 0}, {lap, lap_y, P, 0}};
+  Piece merged[3];
+  int n = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (pieces[i].rows == 0) continue;
+    if (n > 0 && merged[n - 1].a + merged[n - 1].rows * F_in == pieces[i].a &&
+        merged[n - 1].o + merged[n - 1].rows * F_out == pieces[i].o) {
+      merged[n - 1].rows += pieces[i].rows;
+    } else {
+      merged[n++] = pieces[i];
+    }
+  }
+
+  bool have_ws = workspace != nullptr && workspace_bytes >= wsplit_geom(F_in, F_out).bytes;
+  for (int i = 0; i < n; ++i) {
+    const Piece& p = merged[i];
+    bool tc_ok = have_ws && gemm_tc_supported(p.a, p.rows, F_in, F_out, p.o) && F_in >= 16 &&
+                 F_out >= 16;
+    bool use_tc = g_mode == 2 ? true : (g_mode == 1 ? false : tc_ok);
+    if (g_mode == 2)
+      FL_REQUIRE(tc_ok, FL_EUNSUPPORTED,
+                 "fl_dot_general: tensor-core kernel forced but shape/workspace unsuitable");
+    int32_t rc = use_tc ? gemm_tc(p.a, p.rows, F_in, F_out, workspace, bias, p.bias_rows, p.o,
+                                  status, st)
+                        : gemm_ffma(p.a, p.rows, F_in, F_out, W, bias, p.bias_rows, p.o, st);
+    if (rc != FL_OK) return rc;
+  }
+  return FL_OK;
+}

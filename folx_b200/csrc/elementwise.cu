@@ -1,0 +1,243 @@
+// Single-pass elementwise forward-Laplacian rules.
+//
+// For y = f(x) applied per element:  J_y[k] = f'(x) J[k],  lap_y = f'(x) lap + f''(x) sum_k J[k]^2
+// (reference: folx/jvp.py:687-697 and 262-272 for the Jacobian part, folx/hessian.py:87-112 for
+// the Hessian part).  The sum over k is per element, so one thread owns a float4 of positions,
+// walks the K Jacobian rows once, and no cross-thread reduction is needed: every byte of the
+// triplet is read once and written once.  The kernel is HBM-bound; algorithmic traffic is
+// 8 (K + 2) N bytes.
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+struct D { float y, d1, d2; };
+
+template <int OP>
+__device__ __forceinline__ D eval(float x, float param) {
+  D r;
+  if constexpr (OP == FL_OP_TANH) {
+    r.y = tanhf(x);
+    r.d1 = 1.0f - r.y * r.y;
+    r.d2 = -2.0f * r.y * r.d1;
+  } else if constexpr (OP == FL_OP_SILU) {
+    float s = 1.0f / (1.0f + expf(-x));
+    r.y = x * s;
+    r.d1 = s * (1.0f + x * (1.0f - s));
+    r.d2 = s * (1.0f - s) * (2.0f + x * (1.0f - 2.0f * s));
+  } else if constexpr (OP == FL_OP_EXP) {
+    r.y = expf(x);
+    r.d1 = r.y;
+    r.d2 = r.y;
+  } else if constexpr (OP == FL_OP_LOG) {
+    float inv = 1.0f / x;
+    r.y = logf(x);
+    r.d1 = inv;
+    r.d2 = -inv * inv;
+  } else if constexpr (OP == FL_OP_SQRT) {
+    r.y = sqrtf(x);
+    r.d1 = 0.5f / r.y;
+    r.d2 = -0.5f * r.d1 / x;
+  } else if constexpr (OP == FL_OP_RSQRT) {
+    r.y = 1.0f / sqrtf(x);
+    float inv = 1.0f / x;
+    r.d1 = -0.5f * r.y * inv;
+    r.d2 = 0.75f * r.y * inv * inv;
+  } else if constexpr (OP == FL_OP_SQUARE) {
+    r.y = x * x;
+    r.d1 = 2.0f * x;
+    r.d2 = 2.0f;
+  } else if constexpr (OP == FL_OP_SIGMOID) {
+    float s = 1.0f / (1.0f + expf(-x));
+    r.y = s;
+    r.d1 = s * (1.0f - s);
+    r.d2 = r.d1 * (1.0f - 2.0f * s);
+  } else if constexpr (OP == FL_OP_SOFTPLUS) {
+    // log(1 + e^x) evaluated without overflow
+    r.y = fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x)));
+    float s = 1.0f / (1.0f + expf(-x));
+    r.d1 = s;
+    r.d2 = s * (1.0f - s);
+  } else if constexpr (OP == FL_OP_INTEGER_POW) {
+    int n = (int)param;
+    // x^(n-2) by repeated multiplication (|n| is small); negative powers through 1/x.
+    int m = n - 2;
+    float base = m >= 0 ? x : 1.0f / x;
+    int e = m >= 0 ? m : -m;
+    float p = 1.0f;
+    float b = base;
+    while (e) {
+      if (e & 1) p *= b;
+      b *= b;
+      e >>= 1;
+    }
+    float xm2 = p;             // x^(n-2)
+    float xm1 = xm2 * x;       // x^(n-1)
+    r.y = xm1 * x;             // x^n
+    r.d1 = (float)n * xm1;
+    r.d2 = (float)n * (float)(n - 1) * xm2;
+  } else if constexpr (OP == FL_OP_SIN) {
+    float s, c;
+    sincosf(x, &s, &c);
+    r.y = s; r.d1 = c; r.d2 = -s;
+  } else if constexpr (OP == FL_OP_COS) {
+    float s, c;
+    sincosf(x, &s, &c);
+    r.y = c; r.d1 = -s; r.d2 = -c;
+  } else if constexpr (OP == FL_OP_NEG) {
+    r.y = -x; r.d1 = -1.0f; r.d2 = 0.0f;
+  } else if constexpr (OP == FL_OP_ABS) {
+    r.y = fabsf(x);
+    r.d1 = x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f);
+    r.d2 = 0.0f;
+  } else if constexpr (OP == FL_OP_SCALE) {
+    r.y = param * x; r.d1 = param; r.d2 = 0.0f;
+  } else if constexpr (OP == FL_OP_SHIFT) {
+    r.y = x + param; r.d1 = 1.0f; r.d2 = 0.0f;
+  } else if constexpr (OP == FL_OP_RECIPROCAL) {
+    float inv = 1.0f / x;
+    r.y = inv;
+    r.d1 = -inv * inv;
+    r.d2 = 2.0f * inv * inv * inv;
+  }
+  return r;
+}
+
+template <int OP>
+constexpr bool is_linear() {
+  return OP == FL_OP_NEG || OP == FL_OP_ABS || OP == FL_OP_SCALE || OP == FL_OP_SHIFT;
+}
+
+constexpr int kUnroll = 8;
+
+// One thread per float4 of positions.
+template <int OP>
+__global__ void __launch_bounds__(256)
+elementwise_vec4(float param, const float4* __restrict__ x, const float4* __restrict__ jac,
+                 const float4* __restrict__ lap, float4* __restrict__ y,
+                 float4* __restrict__ jac_y, float4* __restrict__ lap_y, int K, int64_t n4,
+                 int64_t js4, int64_t jys4) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 xv = ld_stream(x + i);
+  float4 lv = ld_stream(lap + i);
+  D a = eval<OP>(xv.x, param), b = eval<OP>(xv.y, param), c = eval<OP>(xv.z, param),
+    d = eval<OP>(xv.w, param);
+  st_stream(y + i, make_float4(a.y, b.y, c.y, d.y));
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* jp = jac + i;
+  float4* jo = jac_y + i;
+  int k = 0;
+  for (; k + kUnroll <= K; k += kUnroll) {
+    float4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) v[u] = ld_stream(jp + (int64_t)(k + u) * js4);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if constexpr (!is_linear<OP>()) {
+        acc.x = fmaf(v[u].x, v[u].x, acc.x);
+        acc.y = fmaf(v[u].y, v[u].y, acc.y);
+        acc.z = fmaf(v[u].z, v[u].z, acc.z);
+        acc.w = fmaf(v[u].w, v[u].w, acc.w);
+      }
+      st_stream(jo + (int64_t)(k + u) * jys4,
+                make_float4(a.d1 * v[u].x, b.d1 * v[u].y, c.d1 * v[u].z, d.d1 * v[u].w));
+    }
+  }
+  for (; k < K; ++k) {
+    float4 v = ld_stream(jp + (int64_t)k * js4);
+    if constexpr (!is_linear<OP>()) {
+      acc.x = fmaf(v.x, v.x, acc.x);
+      acc.y = fmaf(v.y, v.y, acc.y);
+      acc.z = fmaf(v.z, v.z, acc.z);
+      acc.w = fmaf(v.w, v.w, acc.w);
+    }
+    st_stream(jo + (int64_t)k * jys4, make_float4(a.d1 * v.x, b.d1 * v.y, c.d1 * v.z, d.d1 * v.w));
+  }
+  st_stream(lap_y + i, make_float4(fmaf(a.d2, acc.x, a.d1 * lv.x), fmaf(b.d2, acc.y, b.d1 * lv.y),
+                                   fmaf(c.d2, acc.z, c.d1 * lv.z), fmaf(d.d2, acc.w, d.d1 * lv.w)));
+}
+
+// Scalar variant for sizes / strides / pointers that are not 16-byte friendly.
+template <int OP>
+__global__ void __launch_bounds__(256)
+elementwise_scalar(float param, const float* __restrict__ x, const float* __restrict__ jac,
+                   const float* __restrict__ lap, float* __restrict__ y, float* __restrict__ jac_y,
+                   float* __restrict__ lap_y, int K, int64_t n, int64_t js, int64_t jys) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  D a = eval<OP>(x[i], param);
+  y[i] = a.y;
+  float acc = 0.f;
+  for (int k = 0; k < K; ++k) {
+    float v = jac[(int64_t)k * js + i];
+    if constexpr (!is_linear<OP>()) acc = fmaf(v, v, acc);
+    jac_y[(int64_t)k * jys + i] = a.d1 * v;
+  }
+  lap_y[i] = fmaf(a.d2, acc, a.d1 * lap[i]);
+}
+
+template <int OP>
+int32_t launch(float param, const float* x, const float* jac, const float* lap, float* y,
+               float* jac_y, float* lap_y, int64_t K, int64_t N, int64_t js, int64_t jys,
+               cudaStream_t st) {
+  bool vec = (N % 4 == 0) && (js % 4 == 0) && (jys % 4 == 0) && aligned16(x) && aligned16(lap) &&
+             aligned16(y) && aligned16(lap_y) && (K == 0 || (aligned16(jac) && aligned16(jac_y)));
+  if (vec) {
+    int64_t n4 = N / 4;
+    int64_t blocks = (n4 + 255) / 256;
+    elementwise_vec4<OP><<<(unsigned)blocks, 256, 0, st>>>(
+        param, (const float4*)x, (const float4*)jac, (const float4*)lap, (float4*)y,
+        (float4*)jac_y, (float4*)lap_y, (int)K, n4, js / 4, jys / 4);
+  } else {
+    int64_t blocks = (N + 255) / 256;
+    elementwise_scalar<OP><<<(unsigned)blocks, 256, 0, st>>>(param, x, jac, lap, y, jac_y, lap_y,
+                                                             (int)K, N, js, jys);
+  }
+  FL_CHECK_LAUNCH("fl_elementwise launch");
+  return FL_OK;
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_elementwise(int32_t op, float param, const float* x, const float* jac,
+                                  const float* lap, float* y, float* jac_y, float* lap_y,
+                                  int64_t K, int64_t N, int64_t jac_stride, int64_t jac_y_stride,
+                                  void* stream) {
+  using namespace fl;
+  FL_REQUIRE(op >= 0 && op < FL_OP_COUNT_, FL_EUNSUPPORTED, "fl_elementwise: unknown op %d", op);
+  FL_REQUIRE(K >= 0 && N >= 0 && K < (1ll << 31), FL_EBADSHAPE,
+             "fl_elementwise: bad sizes K=%lld N=%lld", (long long)K, (long long)N);
+  FL_REQUIRE(K == 0 || (jac_stride >= N && jac_y_stride >= N), FL_EBADSHAPE,
+             "fl_elementwise: Jacobian row stride smaller than N");
+  FL_REQUIRE((N + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_elementwise: N too large");
+  if (N == 0) return FL_OK;
+  FL_REQUIRE(x && lap && y && lap_y && (K == 0 || (jac && jac_y)), FL_EBADSHAPE,
+             "fl_elementwise: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+#define FL_CASE(OP) \
+  case OP:          \
+    return launch<OP>(param, x, jac, lap, y, jac_y, lap_y, K, N, jac_stride, jac_y_stride, st);
+  switch (op) {
+    FL_CASE(FL_OP_TANH)
+    FL_CASE(FL_OP_SILU)
+    FL_CASE(FL_OP_EXP)
+    FL_CASE(FL_OP_LOG)
+    FL_CASE(FL_OP_SQRT)
+    FL_CASE(FL_OP_RSQRT)
+    FL_CASE(FL_OP_SQUARE)
+    FL_CASE(FL_OP_SIGMOID)
+    FL_CASE(FL_OP_SOFTPLUS)
+    FL_CASE(FL_OP_INTEGER_POW)
+    FL_CASE(FL_OP_SIN)
+    FL_CASE(FL_OP_COS)
+    FL_CASE(FL_OP_NEG)
+    FL_CASE(FL_OP_ABS)
+    FL_CASE(FL_OP_SCALE)
+    FL_CASE(FL_OP_SHIFT)
+    FL_CASE(FL_OP_RECIPROCAL)
+  }
+#undef FL_CASE
+  return FL_EUNSUPPORTED;
+}

@@ -1,0 +1,33 @@
+// Internal interface between the dot_general entry points and the two GEMM implementations.
+#pragma once
+
+#include "common.cuh"
+
+namespace fl {
+
+// Geometry of the split-W workspace produced by fl_dot_general_prepare:
+//   [ W_hi^T | W_lo^T ], each n_chunks * n_tile rows of k_pad fp32 (K-major, zero padded).
+struct WSplitGeom {
+  int64_t k_pad;     // F_in rounded up to the K block of the tensor-core kernel
+  int64_t n_tile;    // rows of W^T one CTA tile covers (multiple of 16, <= 256)
+  int64_t n_chunks;  // number of such tiles along F_out
+  int64_t bytes;     // total workspace bytes
+};
+
+WSplitGeom wsplit_geom(int64_t F_in, int64_t F_out);
+
+// CUDA-core fp32 kernel: Y = A W (+ bias on rows < bias_rows).
+int32_t gemm_ffma(const float* A, int64_t M, int64_t Kc, int64_t N, const float* W,
+                  const float* bias, int64_t bias_rows, float* Y, cudaStream_t st);
+
+// Can the tensor-core kernel take this problem (alignment / size rules of TMA and tcgen05)?
+bool gemm_tc_supported(const float* A, int64_t M, int64_t Kc, int64_t N, const float* Y);
+
+// tcgen05 3xTF32 kernel reading the split W from `workspace`.
+int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* workspace,
+                const float* bias, int64_t bias_rows, float* Y, int32_t* status, cudaStream_t st);
+
+// Splits W into TF32 head/tail, transposed and padded, into `workspace`.
+int32_t gemm_tc_prepare(const float* W, int64_t Kc, int64_t N, void* workspace, cudaStream_t st);
+
+}  // namespace fl

@@ -1,0 +1,497 @@
+// Stacked-triplet GEMM on the sm_100a tensor cores in split-fp32 (3xTF32) arithmetic.
+//
+//   Y[M, N] = A[M, Kc] W[Kc, N]  (+ bias on the first bias_rows rows)
+//
+// A is the stacked triplet [x; J_1..J_K; lap] viewed as (K+2) P rows; the reference computes the
+// same three products with separate lax.dot_general calls (folx/wrapped_functions.py:159-171).
+//
+// fp32 accuracy on TF32 tensor cores: every operand v is split as v = hi + lo with
+// hi = tf32(v) and lo = tf32(v - hi); the product keeps hi*hi + lo*hi + hi*lo, accumulated in fp32
+// in tensor memory.  The dropped lo*lo term is ~2^-22 relative.  W is constant, so its split is
+// done once (gemm_tc_prepare) into a K-major, zero-padded workspace; A is split on the fly in
+// shared memory by converter warps.
+//
+// Kernel structure (one persistent CTA per SM, 320 threads):
+//   warp 4      TMA producer: A tile (128 x 32 fp32) + W_hi^T, W_lo^T tiles (n_tile x 32) per stage,
+//               128-byte swizzle, completion on an mbarrier
+//   warps 6-9   converters: A -> (A_hi in place, A_lo) in shared memory
+//   warp 5      MMA issuer: 3 tcgen05.mma (kind::tf32, M = 128, N = n_tile, K = 8) per K slice
+//               into one of two TMEM accumulators (2 x 256 columns)
+//   warps 0-3   epilogue: tcgen05.ld -> registers -> (+bias) -> swizzled staging -> TMA store,
+//               overlapping the next tile's main loop through the second accumulator
+// Every mbarrier wait is bounded; when one runs out the CTA raises a shared abort flag, all
+// roles drain, tensor memory is released and a status word is written for the host.
+#include <cuda.h>
+
+#include "gemm.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int BLOCK_M = 128;
+constexpr int BLOCK_K = 32;  // fp32 elements = one 128-byte swizzle row
+constexpr int UMMA_K = 8;    // K of one tcgen05.mma kind::tf32
+constexpr int STAGES = 2;
+constexpr int MAX_N = 256;
+constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
+constexpr int W_TILE_BYTES = MAX_N * BLOCK_K * 4;
+constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * W_TILE_BYTES;
+constexpr int EPI_WARPS = 4;
+constexpr int EPI_BUF_BYTES = 32 * 32 * 4;
+constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
+constexpr int CTRL_BYTES = 256;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
+constexpr int NUM_THREADS = 320;
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t SPIN_LIMIT = 1u << 22;
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false (and raises the abort flag) when the limit is reached or
+// another thread of the CTA has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    if (it > 64) {
+      if (*abort_flag) return false;
+      __nanosleep(40);
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float tf32_rna(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return __uint_as_float(r);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one 128-byte swizzle span:
+// 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1, SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
+struct Ctrl {
+  uint64_t full[STAGES];
+  uint64_t conv[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tfull[2];
+  uint64_t tempty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmWhi,
+               const __grid_constant__ CUtensorMap tmWlo, const __grid_constant__ CUtensorMap tmY,
+               const float* __restrict__ bias, int64_t bias_rows, int num_m_tiles, int num_k_steps,
+               int n_tile, int n_chunks, int n_total, int32_t* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* epi = smem + STAGES * STAGE_BYTES;
+  Ctrl* ctrl = (Ctrl*)(epi + EPI_BYTES);
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_tiles = num_m_tiles * n_chunks;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->conv[s]), 128);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&ctrl->tfull[a]), 1);
+      mbar_init(smem_u32(&ctrl->tempty[a]), 128);
+    }
+    ctrl->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&ctrl->tmem_base)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  const uint32_t stage_bytes_tx = (uint32_t)(A_TILE_BYTES + 2 * n_tile * BLOCK_K * 4);
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m_tile = t / n_chunks, n_chunk = t % n_chunks;
+        for (int ks = 0; ks < num_k_steps; ++ks) {
+          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sb = smem + stage * STAGE_BYTES;
+          const uint32_t bar = smem_u32(&ctrl->full[stage]);
+          mbar_expect_tx(bar, stage_bytes_tx);
+          tma_load_2d(smem_u32(sb), &tmA, ks * BLOCK_K, m_tile * BLOCK_M, bar);
+          tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES), &tmWhi, ks * BLOCK_K, n_chunk * n_tile, bar);
+          tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES), &tmWlo, ks * BLOCK_K,
+                      n_chunk * n_tile, bar);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) {
+        // Drain: give copies that are still in flight a bounded chance to land before the CTA
+        // releases its shared memory.
+        for (int s = 0; s < STAGES; ++s)
+          for (uint32_t it = 0; it < (1u << 16); ++it) {
+            if (mbar_try(smem_u32(&ctrl->full[s]), 0) || mbar_try(smem_u32(&ctrl->full[s]), 1)) break;
+            __nanosleep(100);
+          }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      // kind::tf32 instruction descriptor: D = fp32, A = B = TF32, both K-major, M = 128, N = n_tile.
+      const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_tile >> 3) << 17) |
+                             ((uint32_t)(BLOCK_M >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(smem_u32(&ctrl->tempty[acc]), acc_phase ^ 1, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MAX_N);
+        for (int ks = 0; ks < num_k_steps; ++ks) {
+          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag) ||
+              !mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          uint8_t* sb = smem + stage * STAGE_BYTES;
+          const uint64_t d_ahi = smem_desc_sw128(smem_u32(sb));
+          const uint64_t d_alo = smem_desc_sw128(smem_u32(sb + A_TILE_BYTES));
+          const uint64_t d_whi = smem_desc_sw128(smem_u32(sb + 2 * A_TILE_BYTES));
+          const uint64_t d_wlo = smem_desc_sw128(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES));
+#pragma unroll
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            // advance inside the 128-byte swizzle row: 8 fp32 = 32 bytes = 2 descriptor units
+            const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
+            umma_tf32(tmem_d, d_alo + off, d_whi + off, idesc, (ks | kk) != 0);
+            umma_tf32(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
+            umma_tf32(tmem_d, d_ahi + off, d_whi + off, idesc, 1);
+          }
+          umma_commit(smem_u32(&ctrl->empty[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(smem_u32(&ctrl->tfull[acc]));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else if (warp >= 6) {
+    // ---------------- converters: A -> (A_hi, A_lo) ----------------
+    const int ct = threadIdx.x - 6 * 32;  // 0..127
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int ks = 0; ks < num_k_steps; ++ks) {
+        if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag)) { ok = false; break; }
+        float4* a4 = (float4*)(smem + stage * STAGE_BYTES);
+        float4* lo4 = (float4*)(smem + stage * STAGE_BYTES + A_TILE_BYTES);
+#pragma unroll
+        for (int j = 0; j < A_TILE_BYTES / 16 / 128; ++j) {
+          const int i = ct + 128 * j;
+          float4 v = a4[i];
+          float4 h, l;
+          h.x = tf32_rna(v.x); h.y = tf32_rna(v.y); h.z = tf32_rna(v.z); h.w = tf32_rna(v.w);
+          l.x = tf32_rna(v.x - h.x); l.y = tf32_rna(v.y - h.y);
+          l.z = tf32_rna(v.z - h.z); l.w = tf32_rna(v.w - h.w);
+          a4[i] = h;
+          lo4[i] = l;
+        }
+        fence_proxy_async();
+        mbar_arrive(smem_u32(&ctrl->conv[stage]));
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 0-3; warp w owns TMEM lanes 32 w .. 32 w + 31) ----------------
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint8_t* my_buf = epi + warp * 2 * EPI_BUF_BYTES;
+    int buf = 0;
+    const int chunks = (n_tile + 31) / 32;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const int m_tile = t / n_chunks, n_chunk = t % n_chunks;
+      if (!mbar_wait(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int64_t row = (int64_t)m_tile * BLOCK_M + warp * 32 + lane;
+      const bool add_bias = bias != nullptr && row < bias_rows;
+      for (int c = 0; c < chunks; ++c) {
+        const int col0 = n_chunk * n_tile + c * 32;
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(acc * MAX_N + c * 32), v);
+        tmem_ld_wait();
+        if (c == chunks - 1) {
+          // accumulator fully read: hand it back to the MMA warp
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ctrl->tempty[acc]));
+        }
+        if (col0 >= n_total) continue;
+        if (add_bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = col0 + j;
+            if (col < n_total) v[j] = __float_as_uint(__uint_as_float(v[j]) + __ldg(bias + col));
+          }
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+        uint8_t* dst = my_buf + buf * EPI_BUF_BYTES + lane * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *(uint4*)(dst + ((j ^ (lane & 7)) * 16)) =
+              make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&tmY, smem_u32(my_buf + buf * EPI_BUF_BYTES), col0,
+                       m_tile * BLOCK_M + warp * 32);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+        buf ^= 1;
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+  if (threadIdx.x == 0 && ctrl->abort_flag && status) atomicExch(status, FL_ETIMEOUT);
+}
+
+// W [Kc][N] row-major -> W_hi^T, W_lo^T [rows = n_chunks * n_tile][k_pad], zero padded.
+__global__ void wsplit_kernel(const float* __restrict__ W, int Kc, int N, float* __restrict__ whi,
+                              float* __restrict__ wlo, int rows, int k_pad) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)rows * k_pad) return;
+  int n = (int)(i / k_pad), k = (int)(i % k_pad);
+  float v = (n < N && k < Kc) ? W[(int64_t)k * N + n] : 0.f;
+  float h = tf32_rna(v);
+  whi[i] = h;
+  wlo[i] = tf32_rna(v - h);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 2-D fp32 row-major tensor map with 128-byte swizzle; the box is 32 columns wide.
+int32_t make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t row_stride,
+                 int box_rows, const char* what) {
+  EncodeTiledFn enc = get_encode();
+  FL_REQUIRE(enc != nullptr, FL_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)row_stride * 4};
+  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FL_REQUIRE(r == CUDA_SUCCESS, FL_ECUDA, "cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
+  return FL_OK;
+}
+
+}  // namespace
+
+WSplitGeom wsplit_geom(int64_t F_in, int64_t F_out) {
+  WSplitGeom g;
+  g.k_pad = (F_in + BLOCK_K - 1) / BLOCK_K * BLOCK_K;
+  int64_t n16 = (F_out + 15) / 16 * 16;
+  if (n16 <= MAX_N) {
+    g.n_chunks = 1;
+    g.n_tile = n16;
+  } else {
+    g.n_chunks = (F_out + MAX_N - 1) / MAX_N;
+    int64_t per = (F_out + g.n_chunks - 1) / g.n_chunks;
+    g.n_tile = (per + 31) / 32 * 32;
+  }
+  g.bytes = 2 * g.n_chunks * g.n_tile * g.k_pad * 4;
+  if (g.bytes < 256) g.bytes = 256;
+  return g;
+}
+
+bool gemm_tc_supported(const float* A, int64_t M, int64_t Kc, int64_t N, const float* Y) {
+  return M > 0 && Kc >= 4 && N >= 4 && Kc % 4 == 0 && N % 4 == 0 && aligned16(A) && aligned16(Y) &&
+         M < (1ll << 31) - BLOCK_M && Kc < (1 << 20) && N < (1 << 20);
+}
+
+int32_t gemm_tc_prepare(const float* W, int64_t Kc, int64_t N, void* workspace, cudaStream_t st) {
+  WSplitGeom g = wsplit_geom(Kc, N);
+  int64_t rows = g.n_chunks * g.n_tile;
+  int64_t total = rows * g.k_pad;
+  float* whi = (float*)workspace;
+  float* wlo = whi + total;
+  wsplit_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(W, (int)Kc, (int)N, whi, wlo,
+                                                                 (int)rows, (int)g.k_pad);
+  FL_CHECK_LAUNCH("wsplit launch");
+  return FL_OK;
+}
+
+int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* workspace,
+                const float* bias, int64_t bias_rows, float* Y, int32_t* status, cudaStream_t st) {
+  FL_REQUIRE(gemm_tc_supported(A, M, Kc, N, Y), FL_EUNSUPPORTED,
+             "tensor-core GEMM needs F_in %% 4 == 0, F_out %% 4 == 0 and 16-byte aligned buffers");
+  FL_REQUIRE(aligned16(workspace), FL_EBADSHAPE, "dot_general workspace must be 16-byte aligned");
+  static bool attr_set = false;
+  if (!attr_set) {
+    FL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 SMEM_BYTES));
+    attr_set = true;
+  }
+  WSplitGeom g = wsplit_geom(Kc, N);
+  const int64_t wrows = g.n_chunks * g.n_tile;
+  const float* whi = (const float*)workspace;
+  const float* wlo = whi + wrows * g.k_pad;
+  CUtensorMap tmA, tmWhi, tmWlo, tmY;
+  int32_t rc;
+  if ((rc = make_map(&tmA, A, M, Kc, Kc, BLOCK_M, "A")) != FL_OK) return rc;
+  if ((rc = make_map(&tmWhi, whi, wrows, g.k_pad, g.k_pad, (int)g.n_tile, "W_hi")) != FL_OK) return rc;
+  if ((rc = make_map(&tmWlo, wlo, wrows, g.k_pad, g.k_pad, (int)g.n_tile, "W_lo")) != FL_OK) return rc;
+  if ((rc = make_map(&tmY, Y, M, N, N, 32, "Y")) != FL_OK) return rc;
+  const int num_m_tiles = (int)((M + BLOCK_M - 1) / BLOCK_M);
+  const int64_t tiles = (int64_t)num_m_tiles * g.n_chunks;
+  int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+  gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(
+      tmA, tmWhi, tmWlo, tmY, bias, bias_rows, num_m_tiles, (int)(g.k_pad / BLOCK_K),
+      (int)g.n_tile, (int)g.n_chunks, (int)N, status);
+  FL_CHECK_LAUNCH("gemm_tc launch");
+  return FL_OK;
+}
+
+}  // namespace fl

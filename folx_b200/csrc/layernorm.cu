@@ -1,0 +1,252 @@
+// One-pass LayerNorm forward-Laplacian rule over the feature axis.
+//
+// The reference evaluates LayerNorm as a chain of registry rules (reduce_sum, sub, square, add,
+// rsqrt, mul, div: folx/wrapped_functions.py:364-391, 409 with folx/custom_hessian.py:35-59 for
+// the division), each a full pass over the Jacobian.  Their composition has the closed form
+//   c = x - mean(x), r = (mean(c^2) + eps)^-1/2, z = c r,
+//   u_k = r (J_k - mean(J_k)), b_k = mean(z u_k), lc = lap - mean(lap),
+//   Jz_k  = u_k - z b_k,
+//   lap_z = r (lc - z mean(z lc)) + sum_k [ -2 b_k u_k + z (3 b_k^2 - mean(u_k^2)) ],
+//   y = gamma z + beta, J_y = gamma Jz, lap_y = gamma lap_z,
+// with all means taken over the F features of one position.  One warp owns one position: the
+// feature reductions are warp shuffles, the K Jacobian rows stream through registers once.
+// HBM-bound; algorithmic traffic 8 (K + 2) P F bytes.
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+constexpr int kRowUnroll = 4;
+
+__device__ __forceinline__ float hsum(float4 v) { return (v.x + v.y) + (v.z + v.w); }
+__device__ __forceinline__ float hdot(float4 a, float4 b) {
+  return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
+}
+
+// F == 128 * VPL: lane l holds float4 number l + 32 j of the row, j < VPL.
+template <int VPL>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
+               const float4* __restrict__ lap, const float4* __restrict__ gamma,
+               const float4* __restrict__ beta, float eps, float4* __restrict__ y,
+               float4* __restrict__ jy, float4* __restrict__ ly, int64_t P, int K, int64_t js4,
+               int64_t jys4) {
+  const int lane = threadIdx.x & 31;
+  const int64_t p = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (p >= P) return;
+  constexpr int F4 = 32 * VPL;
+  const float invF = 1.0f / (float)(F4 * 4);
+  const int64_t row = p * F4;
+
+  float4 z[VPL], g[VPL];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    z[j] = ld_stream(x + row + lane + 32 * j);
+    s += hsum(z[j]);
+    g[j] = gamma ? __ldg(gamma + lane + 32 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
+  }
+  const float mean = warp_sum(s) * invF;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    z[j].x -= mean; z[j].y -= mean; z[j].z -= mean; z[j].w -= mean;
+    q += hdot(z[j], z[j]);
+  }
+  const float r = rsqrtf(warp_sum(q) * invF + eps);
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    z[j].x *= r; z[j].y *= r; z[j].z *= r; z[j].w *= r;
+    float4 bt = beta ? __ldg(beta + lane + 32 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    st_stream(y + row + lane + 32 * j,
+              make_float4(fmaf(g[j].x, z[j].x, bt.x), fmaf(g[j].y, z[j].y, bt.y),
+                          fmaf(g[j].z, z[j].z, bt.z), fmaf(g[j].w, z[j].w, bt.w)));
+  }
+
+  float4 s1[VPL];  // sum_k b_k u_k
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) s1[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+  float s2 = 0.f;  // sum_k (3 b_k^2 - mean(u_k^2))
+
+  auto process = [&](float4 (&v)[VPL], int64_t k) {
+    float t = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) t += hsum(v[j]);
+    const float m = warp_sum(t) * invF;
+    float tb = 0.f, tq = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      v[j].x = r * (v[j].x - m); v[j].y = r * (v[j].y - m);
+      v[j].z = r * (v[j].z - m); v[j].w = r * (v[j].w - m);
+      tb += hdot(z[j], v[j]);
+      tq += hdot(v[j], v[j]);
+    }
+    const float b = warp_sum(tb) * invF;
+    const float uu = warp_sum(tq) * invF;
+    s2 += 3.0f * b * b - uu;
+    float4* out = jy + k * jys4 + row + lane;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      s1[j].x = fmaf(b, v[j].x, s1[j].x); s1[j].y = fmaf(b, v[j].y, s1[j].y);
+      s1[j].z = fmaf(b, v[j].z, s1[j].z); s1[j].w = fmaf(b, v[j].w, s1[j].w);
+      st_stream(out + 32 * j, make_float4(g[j].x * (v[j].x - z[j].x * b), g[j].y * (v[j].y - z[j].y * b),
+                                          g[j].z * (v[j].z - z[j].z * b), g[j].w * (v[j].w - z[j].w * b)));
+    }
+  };
+
+  int k = 0;
+  for (; k + kRowUnroll <= K; k += kRowUnroll) {
+    float4 v[kRowUnroll][VPL];
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; ++u)
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) v[u][j] = ld_stream(jac + (int64_t)(k + u) * js4 + row + lane + 32 * j);
+#pragma unroll
+    for (int u = 0; u < kRowUnroll; ++u) process(v[u], k + u);
+  }
+  for (; k < K; ++k) {
+    float4 v[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) v[j] = ld_stream(jac + (int64_t)k * js4 + row + lane + 32 * j);
+    process(v, k);
+  }
+
+  float4 l[VPL];
+  float t = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    l[j] = ld_stream(lap + row + lane + 32 * j);
+    t += hsum(l[j]);
+  }
+  const float lm = warp_sum(t) * invF;
+  float tz = 0.f;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    l[j].x -= lm; l[j].y -= lm; l[j].z -= lm; l[j].w -= lm;
+    tz += hdot(z[j], l[j]);
+  }
+  const float zl = warp_sum(tz) * invF;
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    float4 o;
+    o.x = g[j].x * (r * (l[j].x - z[j].x * zl) - 2.0f * s1[j].x + z[j].x * s2);
+    o.y = g[j].y * (r * (l[j].y - z[j].y * zl) - 2.0f * s1[j].y + z[j].y * s2);
+    o.z = g[j].z * (r * (l[j].z - z[j].z * zl) - 2.0f * s1[j].z + z[j].z * s2);
+    o.w = g[j].w * (r * (l[j].w - z[j].w * zl) - 2.0f * s1[j].w + z[j].w * s2);
+    st_stream(ly + row + lane + 32 * j, o);
+  }
+}
+
+// Any F: lanes stride over the features; z and the running sums live in shared memory.
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+layernorm_rows_generic(const float* __restrict__ x, const float* __restrict__ jac,
+                       const float* __restrict__ lap, const float* __restrict__ gamma,
+                       const float* __restrict__ beta, float eps, float* __restrict__ y,
+                       float* __restrict__ jy, float* __restrict__ ly, int64_t P, int F, int K,
+                       int64_t js, int64_t jys) {
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31;
+  const int w = threadIdx.x >> 5;
+  const int64_t p = (int64_t)blockIdx.x * kWarpsPerBlock + w;
+  if (p >= P) return;
+  float* z = smem + (size_t)w * 2 * F;
+  float* s1 = z + F;
+  const float invF = 1.0f / (float)F;
+  const int64_t row = p * F;
+  float s = 0.f;
+  for (int f = lane; f < F; f += 32) s += x[row + f];
+  const float mean = warp_sum(s) * invF;
+  float q = 0.f;
+  for (int f = lane; f < F; f += 32) {
+    float c = x[row + f] - mean;
+    q = fmaf(c, c, q);
+  }
+  const float r = rsqrtf(warp_sum(q) * invF + eps);
+  for (int f = lane; f < F; f += 32) {
+    float zz = (x[row + f] - mean) * r;
+    z[f] = zz;
+    s1[f] = 0.f;
+    y[row + f] = fmaf(gamma ? gamma[f] : 1.f, zz, beta ? beta[f] : 0.f);
+  }
+  float s2 = 0.f;
+  for (int k = 0; k < K; ++k) {
+    const float* jr = jac + (int64_t)k * js + row;
+    float t = 0.f;
+    for (int f = lane; f < F; f += 32) t += jr[f];
+    const float m = warp_sum(t) * invF;
+    float tb = 0.f, tq = 0.f;
+    for (int f = lane; f < F; f += 32) {
+      float u = r * (jr[f] - m);
+      tb = fmaf(z[f], u, tb);
+      tq = fmaf(u, u, tq);
+    }
+    const float b = warp_sum(tb) * invF;
+    const float uu = warp_sum(tq) * invF;
+    s2 += 3.0f * b * b - uu;
+    float* out = jy + (int64_t)k * jys + row;
+    for (int f = lane; f < F; f += 32) {
+      float u = r * (jr[f] - m);
+      s1[f] = fmaf(b, u, s1[f]);
+      out[f] = (gamma ? gamma[f] : 1.f) * (u - z[f] * b);
+    }
+  }
+  float t = 0.f;
+  for (int f = lane; f < F; f += 32) t += lap[row + f];
+  const float lm = warp_sum(t) * invF;
+  float tz = 0.f;
+  for (int f = lane; f < F; f += 32) tz = fmaf(z[f], lap[row + f] - lm, tz);
+  const float zl = warp_sum(tz) * invF;
+  for (int f = lane; f < F; f += 32) {
+    float lc = lap[row + f] - lm;
+    ly[row + f] = (gamma ? gamma[f] : 1.f) * (r * (lc - z[f] * zl) - 2.0f * s1[f] + z[f] * s2);
+  }
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_layernorm(const float* x, const float* jac, const float* lap,
+                                const float* gamma, const float* beta, float eps, float* y,
+                                float* jac_y, float* lap_y, int64_t P, int64_t F, int64_t K,
+                                int64_t jac_stride, int64_t jac_y_stride, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(P >= 0 && F > 0 && K >= 0 && K < (1ll << 31) && F < (1ll << 20), FL_EBADSHAPE,
+             "fl_layernorm: bad sizes P=%lld F=%lld K=%lld", (long long)P, (long long)F, (long long)K);
+  FL_REQUIRE(K == 0 || (jac_stride >= P * F && jac_y_stride >= P * F), FL_EBADSHAPE,
+             "fl_layernorm: Jacobian row stride smaller than P*F");
+  if (P == 0) return FL_OK;
+  FL_REQUIRE(x && lap && y && lap_y && (K == 0 || (jac && jac_y)), FL_EBADSHAPE,
+             "fl_layernorm: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t blocks = (P + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_layernorm: P too large");
+  bool vec = (F % 128 == 0) && F <= 1024 && (jac_stride % 4 == 0) && (jac_y_stride % 4 == 0) &&
+             aligned16(x) && aligned16(lap) && aligned16(y) && aligned16(lap_y) &&
+             (K == 0 || (aligned16(jac) && aligned16(jac_y))) && (!gamma || aligned16(gamma)) &&
+             (!beta || aligned16(beta));
+  if (vec) {
+#define FL_LN(V)                                                                                  \
+  case V:                                                                                         \
+    layernorm_rows<V><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, st>>>(                          \
+        (const float4*)x, (const float4*)jac, (const float4*)lap, (const float4*)gamma,           \
+        (const float4*)beta, eps, (float4*)y, (float4*)jac_y, (float4*)lap_y, P, (int)K,          \
+        jac_stride / 4, jac_y_stride / 4);                                                        \
+    break;
+    switch ((int)(F / 128)) {
+      FL_LN(1) FL_LN(2) FL_LN(3) FL_LN(4) FL_LN(5) FL_LN(6) FL_LN(7) FL_LN(8)
+    }
+#undef FL_LN
+  } else {
+    size_t smem = (size_t)kWarpsPerBlock * 2 * F * sizeof(float);
+    FL_REQUIRE(smem <= 200 * 1024, FL_EUNSUPPORTED, "fl_layernorm: F=%lld too wide", (long long)F);
+    if (smem > 48 * 1024)
+      FL_CUDA(cudaFuncSetAttribute(layernorm_rows_generic,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    layernorm_rows_generic<<<(unsigned)blocks, kWarpsPerBlock * 32, smem, st>>>(
+        x, jac, lap, gamma, beta, eps, y, jac_y, lap_y, P, (int)F, (int)K, jac_stride,
+        jac_y_stride);
+  }
+  FL_CHECK_LAUNCH("fl_layernorm launch");
+  return FL_OK;
+}

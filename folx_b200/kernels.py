@@ -1,0 +1,210 @@
+"""Torch-tensor front of the C ABI: allocates outputs (stacked triplets) and launches kernels.
+
+Storage convention: a triplet of ``N`` positions with ``K`` Jacobian rows is ONE buffer
+``T[K + 2, N]`` -- row 0 is ``x``, rows ``1..K`` are ``J``, row ``K + 1`` is the Laplacian -- and
+``x``, ``jacobian.data``, ``laplacian`` are views into it.  The stacked ``[x; J; lap]`` operand
+of the dot_general rule is therefore a view, not a copy.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import weakref
+
+import numpy as np
+import torch
+
+from . import lib
+from .api import FwdJacobian, FwdLaplArray
+
+
+def _ptr(t: torch.Tensor | None):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _require_cuda(*ts: torch.Tensor):
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                'folx_b200 kernels run on CUDA tensors only (there is no CPU fallback); '
+                f'got a tensor on {t.device}'
+            )
+        if t.dtype != torch.float32:
+            raise TypeError(f'folx_b200 kernels are fp32; got {t.dtype}')
+
+
+def alloc_triplet(K: int, shape, device, x0_idx: np.ndarray | None = None) -> FwdLaplArray:
+    """Uninitialised stacked triplet with ``K`` Jacobian rows over positions of ``shape``."""
+    shape = tuple(int(s) for s in shape)
+    buf = torch.empty((K + 2, *shape), dtype=torch.float32, device=device)
+    return FwdLaplArray(buf[0], FwdJacobian(buf[1 : K + 1], x0_idx), buf[K + 1])
+
+
+def as_contiguous(a: FwdLaplArray) -> FwdLaplArray:
+    """Triplet whose three fields are dense row-major tensors (copying only when needed)."""
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    if x.is_contiguous() and l.is_contiguous() and _rows_contiguous(j):
+        return a
+    K = j.shape[0]
+    out = alloc_triplet(K, x.shape, x.device, a.jacobian.x0_idx)
+    out.x.copy_(x)
+    out.jacobian.data.copy_(j.expand(K, *x.shape) if j.shape[1:] != x.shape else j)
+    out.laplacian.copy_(l)
+    return out
+
+
+def _rows_contiguous(j: torch.Tensor) -> bool:
+    """Each Jacobian row is dense row-major (the row stride itself may be anything >= N)."""
+    if j.shape[0] == 0:
+        return True
+    return j[0].is_contiguous() and (j.shape[0] == 1 or j.stride(0) >= j[0].numel())
+
+
+def _jac_stride(j: torch.Tensor) -> int:
+    return j.stride(0) if j.shape[0] > 1 else max(j[0].numel() if j.shape[0] else 0, 1)
+
+
+def elementwise(op: str, a: FwdLaplArray, param: float = 0.0) -> FwdLaplArray:
+    """y = f(x) applied per element; the index map is unchanged (folx/jvp.py:294-297)."""
+    a = as_contiguous(a)
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    _require_cuda(x, j, l)
+    K, N = j.shape[0], x.numel()
+    out = alloc_triplet(K, x.shape, x.device, a.jacobian.x0_idx)
+    lib.call(
+        'fl_elementwise', lib.ELEMENTWISE_OPS[op], float(param), _ptr(x), _ptr(j), _ptr(l),
+        _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), K, N, _jac_stride(j),
+        _jac_stride(out.jacobian.data), _stream(x.device),
+    )
+    return out
+
+
+def binary(op: str, a, b, x0_idx: np.ndarray | None = None) -> FwdLaplArray:
+    """y = a (op) b for triplets with aligned Jacobian rows; either side may be a plain tensor.
+
+    ``b`` may be smaller than ``a`` when its shape equals the trailing part of ``a``'s shape
+    (broadcast over the leading positions).
+    """
+    a_t, b_t = isinstance(a, FwdLaplArray), isinstance(b, FwdLaplArray)
+    assert a_t or b_t
+    if a_t:
+        a = as_contiguous(a)
+    if b_t:
+        b = as_contiguous(b)
+    ax = a.x if a_t else a.contiguous()
+    bx = b.x if b_t else b.contiguous()
+    _require_cuda(ax, bx)
+    N, Nb = ax.numel(), bx.numel()
+    if Nb > N or N % max(Nb, 1) != 0:
+        raise ValueError(f'binary: operand b ({tuple(bx.shape)}) does not tile a ({tuple(ax.shape)})')
+    K = a.jacobian.data.shape[0] if a_t else b.jacobian.data.shape[0]
+    if a_t and b_t and b.jacobian.data.shape[0] != K:
+        raise ValueError('binary: operands have different numbers of Jacobian rows')
+    if x0_idx is None:
+        x0_idx = a.jacobian.x0_idx if a_t else b.jacobian.x0_idx
+    out = alloc_triplet(K, ax.shape, ax.device, x0_idx)
+    ja = a.jacobian.data if a_t else None
+    jb = b.jacobian.data if b_t else None
+    lib.call(
+        'fl_binary', lib.BINARY_OPS[op],
+        _ptr(ax), _ptr(ja), _ptr(a.laplacian if a_t else None), _jac_stride(ja) if a_t else 0,
+        _ptr(bx), _ptr(jb), _ptr(b.laplacian if b_t else None), _jac_stride(jb) if b_t else 0,
+        _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), _jac_stride(out.jacobian.data),
+        K, N, Nb, _stream(ax.device),
+    )
+    return out
+
+
+class _WeightCache:
+    """Split-W workspaces keyed by the weight tensor (redone when the tensor is modified)."""
+
+    def __init__(self):
+        self._entries: dict[int, tuple] = {}
+
+    def get(self, W: torch.Tensor) -> torch.Tensor:
+        key = id(W)
+        ent = self._entries.get(key)
+        if ent is not None:
+            ref, version, ptr, ws = ent
+            if ref() is W and version == W._version and ptr == W.data_ptr():
+                return ws
+        F_in, F_out = W.shape
+        nbytes = lib.load().fl_dot_general_workspace_bytes(F_in, F_out)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
+        lib.call('fl_dot_general_prepare', _ptr(W), F_in, F_out, _ptr(ws), nbytes, _stream(W.device))
+        self._entries[key] = (weakref.ref(W, lambda _: self._entries.pop(key, None)), W._version,
+                              W.data_ptr(), ws)
+        return ws
+
+
+_weights = _WeightCache()
+_status: dict[torch.device, torch.Tensor] = {}
+
+
+def gemm_status(device) -> torch.Tensor:
+    """Device status word the tensor-core GEMM raises when one of its bounded waits runs out."""
+    device = torch.device(device)
+    if device not in _status:
+        _status[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[device]
+
+
+def check_gemm_status(device) -> None:
+    """Synchronises and raises if a GEMM launched so far reported a timeout."""
+    st = gemm_status(device)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise lib.FolxB200Error('fl_dot_general', code, 'a bounded wait inside the kernel ran out')
+
+
+def dot_general(a: FwdLaplArray, W: torch.Tensor, bias: torch.Tensor | None = None,
+                x0_idx: np.ndarray | None = None) -> FwdLaplArray:
+    """y = x @ W (+ bias) over the last axis of a triplet (folx/wrapped_functions.py:71-171)."""
+    a = as_contiguous(a)
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    W = W.contiguous()
+    _require_cuda(x, j, l, W, bias)
+    F_in, F_out = W.shape
+    if x.shape[-1] != F_in:
+        raise ValueError(f'dot_general: last axis {x.shape[-1]} != {F_in}')
+    K = j.shape[0]
+    P = x.numel() // F_in
+    if K > 1 and j.stride(0) != x.numel():
+        # the kernel wants the K * P Jacobian rows back to back
+        j = j.contiguous()
+    out = alloc_triplet(K, (*x.shape[:-1], F_out), x.device, x0_idx)
+    ws = _weights.get(W)
+    lib.call(
+        'fl_dot_general', _ptr(x), _ptr(j), _ptr(l), P, K, F_in, F_out, _ptr(W),
+        _ptr(bias.contiguous() if bias is not None else None), _ptr(ws), ws.numel(),
+        _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), _ptr(gemm_status(x.device)),
+        _stream(x.device),
+    )
+    return out
+
+
+def layernorm(a: FwdLaplArray, gamma: torch.Tensor | None, beta: torch.Tensor | None,
+              eps: float = 1e-6) -> FwdLaplArray:
+    """LayerNorm over the last axis of a triplet whose index map is constant along that axis."""
+    a = as_contiguous(a)
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    _require_cuda(x, j, l, gamma, beta)
+    F = x.shape[-1]
+    P = x.numel() // F
+    K = j.shape[0]
+    out = alloc_triplet(K, x.shape, x.device, a.jacobian.x0_idx)
+    lib.call(
+        'fl_layernorm', _ptr(x), _ptr(j), _ptr(l),
+        _ptr(gamma.contiguous() if gamma is not None else None),
+        _ptr(beta.contiguous() if beta is not None else None), float(eps),
+        _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), P, F, K, _jac_stride(j),
+        _jac_stride(out.jacobian.data), _stream(x.device),
+    )
+    return out

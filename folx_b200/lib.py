@@ -1,0 +1,102 @@
+"""ctypes binding of libfolx_b200.so (the C ABI declared in include/folx_b200.h).
+
+The library is the product's only compute path: if it is missing (and cannot be built) or a
+call fails, this module raises -- there is no fallback implementation.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int32, c_int64, c_void_p
+
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG_DIR, 'libfolx_b200.so')
+
+FL_OK = 0
+FL_EBADSHAPE = 1
+FL_EUNSUPPORTED = 2
+FL_ETIMEOUT = 3
+FL_ECUDA = 4
+
+# op codes of fl_elementwise / fl_binary (mirrors include/folx_b200.h)
+ELEMENTWISE_OPS = {
+    'tanh': 0, 'silu': 1, 'exp': 2, 'log': 3, 'sqrt': 4, 'rsqrt': 5, 'square': 6,
+    'sigmoid': 7, 'softplus': 8, 'integer_pow': 9, 'sin': 10, 'cos': 11, 'neg': 12,
+    'abs': 13, 'scale': 14, 'shift': 15, 'reciprocal': 16,
+}
+BINARY_OPS = {'add': 0, 'sub': 1, 'mul': 2, 'div': 3}
+
+
+class FolxB200Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, fn: str, code: int, message: str):
+        super().__init__(f'{fn} failed with status {code}: {message}')
+        self.code = code
+
+
+_f = POINTER(c_float)
+_SIGNATURES = {
+    'fl_version': (c_int32, []),
+    'fl_last_error': (c_char_p, []),
+    'fl_elementwise': (c_int32, [c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    'fl_binary': (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                            c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                            c_int64, c_int64, c_void_p]),
+    'fl_dot_general_workspace_bytes': (c_int64, [c_int64, c_int64]),
+    'fl_dot_general_prepare': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
+    'fl_dot_general': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                 c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
+                                 c_void_p, c_void_p, c_void_p]),
+    'fl_dot_general_set_mode': (None, [c_int32]),
+    'fl_layernorm': (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                               c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                               c_int64, c_void_p]),
+}
+
+_lib = None
+
+
+def exported_symbols() -> list[str]:
+    """Names every build of the library must export (one per declaration in the header)."""
+    return sorted(_SIGNATURES)
+
+
+def load(build_if_missing: bool = True) -> ctypes.CDLL:
+    """Loads (building first if needed and possible) the shared library; raises if unavailable."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if build_if_missing:
+        try:
+            from . import build as _build
+
+            if _build.needs_build():
+                _build.build()
+        except Exception as e:  # no nvcc on this machine: use the shipped binary if there is one
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError(
+                    f'libfolx_b200.so is missing and could not be built: {e}'
+                ) from e
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(f'{LIB_PATH} not found; run `python -m folx_b200.build`')
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here means the binary is stale
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(fn_name: str, code: int) -> None:
+    if code != FL_OK:
+        msg = load().fl_last_error()
+        raise FolxB200Error(fn_name, code, msg.decode() if msg else '')
+
+
+def call(fn_name: str, *args) -> None:
+    """Calls a status-returning entry point and raises FolxB200Error on failure."""
+    check(fn_name, getattr(load(), fn_name)(*args))

@@ -1,0 +1,155 @@
+/*
+ * folx_b200 -- C ABI of the sm_100a forward-Laplacian kernels.
+ *
+ * Every entry point propagates a triplet (x, J, lap) -- the value of a tensor, its Jacobian
+ * with respect to the function's inputs and its Laplacian -- through one operation:
+ *     y = f(x),  J_y = df(x) J,  lap_y = df(x) lap + tr(J^T H_f J)
+ * (reference: README.md:99-109, folx/wrapper.py:120-125).
+ *
+ * Conventions shared by all entry points
+ *   - fp32 data, row-major, the Jacobian axis is outermost (reference: folx/api.py:16, JAC_DIM = 0):
+ *       x, lap : [N]         N = number of scalar positions of the tensor (walkers x shape)
+ *       J      : [K][N]      K = dense input dimension or number of sparse rows; consecutive
+ *                            rows are `jac_stride` elements apart (>= N)
+ *   - all pointers are DEVICE pointers owned by the caller; the library allocates nothing;
+ *     workspace, where needed, is passed in and its size comes from a *_workspace_bytes query
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*); no call synchronises
+ *   - the return value is FL_OK or one of the FL_E* codes; fl_last_error() gives the message of
+ *     the last failure on the calling thread.  No C++ exception crosses the boundary.
+ *   - sparse Jacobians are stored as K rows plus a STATIC host-side index map (x0_idx); the
+ *     map never crosses this boundary except as int32 gather tables (fl_gather_rows) and as
+ *     the operands of the index-set kernels (fl_index_union / fl_index_intersection).
+ */
+#ifndef FOLX_B200_H_
+#define FOLX_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FL_OK 0
+#define FL_EBADSHAPE 1    /* a size, stride or alignment the kernel cannot take */
+#define FL_EUNSUPPORTED 2 /* valid request that this build has no kernel for */
+#define FL_ETIMEOUT 3     /* a bounded device-side wait ran out (reported through a status word) */
+#define FL_ECUDA 4        /* a CUDA runtime / driver call failed */
+
+/* Library identification and error text. */
+int32_t fl_version(void);
+const char* fl_last_error(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Elementwise rules.  Replaces the pair dense_elementwise_jvp / sparse_diag_jvp
+ * (folx/jvp.py:687-697, 256-327) plus elementwise_jhj_trace (folx/hessian.py:87-112) of every
+ * scalar function registered with in_axes=() (folx/wrapped_functions.py:384-431, 553-556):
+ *     y = f(x), J_y[k] = f'(x) J[k], lap_y = f'(x) lap + f''(x) sum_k J[k]^2.
+ * One pass: every input element is read once and every output element written once.
+ * `param` is the exponent of FL_OP_INTEGER_POW and the factor / offset of FL_OP_SCALE /
+ * FL_OP_SHIFT, ignored otherwise.
+ * ------------------------------------------------------------------------------------------- */
+enum {
+  FL_OP_TANH = 0,
+  FL_OP_SILU = 1,
+  FL_OP_EXP = 2,
+  FL_OP_LOG = 3,
+  FL_OP_SQRT = 4,
+  FL_OP_RSQRT = 5,
+  FL_OP_SQUARE = 6,
+  FL_OP_SIGMOID = 7,
+  FL_OP_SOFTPLUS = 8,
+  FL_OP_INTEGER_POW = 9,
+  FL_OP_SIN = 10,
+  FL_OP_COS = 11,
+  FL_OP_NEG = 12,   /* linear: no Hessian term (folx/hessian.py:561-562) */
+  FL_OP_ABS = 13,   /* real abs, linear a.e. (folx/wrapped_functions.py:350-352) */
+  FL_OP_SCALE = 14, /* y = param * x (mul by a constant, folx/hessian.py:563-564) */
+  FL_OP_SHIFT = 15, /* y = x + param (add of a constant, folx/wrapped_functions.py:364-366) */
+  FL_OP_RECIPROCAL = 16,
+  FL_OP_COUNT_ = 17
+};
+
+int32_t fl_elementwise(int32_t op, float param,
+                       const float* x, const float* jac, const float* lap,
+                       float* y, float* jac_y, float* lap_y,
+                       int64_t K, int64_t N, int64_t jac_stride, int64_t jac_y_stride,
+                       void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Binary elementwise rules on two triplets with aligned Jacobian rows (same K, same index map).
+ * Replaces wrap_forward_laplacian(mul | div | add | sub, in_axes=()) with both operands
+ * triplets (folx/wrapped_functions.py:364-383): the jvp of folx/jvp.py:273-317 and the Hessian
+ * terms of folx/hessian.py:177-188 (mul: 2 sum_k Ja_k Jb_k) and folx/custom_hessian.py:35-59
+ * (div: -2/b^2 sum_k Ja_k Jb_k + 2a/b^3 sum_k Jb_k^2).
+ * Broadcasting: operand b may be broadcast along the position axis with period `b_period`
+ * (position i of b is i % b_period; b_period == N means no broadcast); its buffers then hold
+ * b_period positions.
+ * ------------------------------------------------------------------------------------------- */
+enum { FL_BIN_ADD = 0, FL_BIN_SUB = 1, FL_BIN_MUL = 2, FL_BIN_DIV = 3 };
+
+int32_t fl_binary(int32_t op,
+                  const float* a, const float* jac_a, const float* lap_a, int64_t jac_a_stride,
+                  const float* b, const float* jac_b, const float* lap_b, int64_t jac_b_stride,
+                  float* y, float* jac_y, float* lap_y, int64_t jac_y_stride,
+                  int64_t K, int64_t N, int64_t b_period, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * dot_general with one constant operand: y = x W (+ b).  Replaces _dot_general_one_constant
+ * (folx/wrapped_functions.py:71-171, three lax.dot_general calls at 167-169) and the bias
+ * `add` rule that follows a Dense layer (folx/wrapped_functions.py:364-366).
+ *
+ * The triplet is treated as ONE stacked operand T = [x; J_1..J_K; lap] of (K+2)*P rows and F_in
+ * columns; Y = T W, with the bias added to the P rows of x only (J and lap of a constant are 0).
+ * x, jac and lap may live anywhere; when they are adjacent in memory (jac == x + P*F_in,
+ * lap == jac + K*P*F_in, same for the outputs) the whole product is a single launch.
+ *
+ *   W    : [F_in][F_out] row-major (constant operand), bias : [F_out] or NULL
+ *   x/lap: [P][F_in], jac : [K][P][F_in] -> y/lap_y : [P][F_out], jac_y : [K][P][F_out]
+ *
+ * Arithmetic: split-fp32 on the tensor cores (3xTF32: W and T are split into a TF32 head and a
+ * TF32 tail, three tcgen05 MMAs accumulate in fp32 in tensor memory), so the result carries
+ * fp32 accuracy.  The split of W lives in caller-provided workspace:
+ *   fl_dot_general_workspace_bytes(F_in, F_out)  -> bytes needed (0 is never returned)
+ *   fl_dot_general_prepare(W, ...)               -> fills the workspace; redo when W changes
+ * `status` is a device int32 the kernel sets to non-zero if a bounded wait inside it ran out
+ * (the host reads it when it next synchronises); it may be NULL.
+ * ------------------------------------------------------------------------------------------- */
+int64_t fl_dot_general_workspace_bytes(int64_t F_in, int64_t F_out);
+
+int32_t fl_dot_general_prepare(const float* W, int64_t F_in, int64_t F_out,
+                               void* workspace, int64_t workspace_bytes, void* stream);
+
+int32_t fl_dot_general(const float* x, const float* jac, const float* lap,
+                       int64_t P, int64_t K, int64_t F_in, int64_t F_out,
+                       const float* W, const float* bias,
+                       const void* workspace, int64_t workspace_bytes,
+                       float* y, float* jac_y, float* lap_y,
+                       int32_t* status, void* stream);
+
+/* Selects the GEMM implementation: 0 = automatic (tensor-core path when the shape allows),
+ * 1 = force the CUDA-core fp32 kernel, 2 = force the tensor-core kernel (FL_EUNSUPPORTED if the
+ * shape does not fit).  Process-wide; meant for tests and benchmarks. */
+void fl_dot_general_set_mode(int32_t mode);
+
+/* ---------------------------------------------------------------------------------------------
+ * LayerNorm over the last (feature) axis of a triplet, one pass.  In the reference LayerNorm is
+ * a composition of ~10 registry rules (reduce_sum, sub, square/integer_pow, add, rsqrt, mul,
+ * div; folx/wrapped_functions.py:364-391, 409, folx/custom_hessian.py:35-59); this is their
+ * closed form.  With c = x - mean(x), r = (mean(c^2) + eps)^-1/2, z = c r,
+ * u_k = r (J_k - mean(J_k)), b_k = mean(z u_k), lc = lap - mean(lap):
+ *     Jz_k  = u_k - z b_k
+ *     lap_z = r (lc - z mean(z lc)) + sum_k [ -2 b_k u_k + z (3 b_k^2 - mean(u_k^2)) ]
+ *     y = gamma z + beta,  J_y = gamma Jz,  lap_y = gamma lap_z        (means over features)
+ * x/lap : [P][F], jac : [K][P][F] with row stride jac_stride; gamma/beta : [F] or NULL (1 / 0).
+ * ------------------------------------------------------------------------------------------- */
+int32_t fl_layernorm(const float* x, const float* jac, const float* lap,
+                     const float* gamma, const float* beta, float eps,
+                     float* y, float* jac_y, float* lap_y,
+                     int64_t P, int64_t F, int64_t K, int64_t jac_stride, int64_t jac_y_stride,
+                     void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FOLX_B200_H_ */

@@ -1,0 +1,234 @@
+"""Closed-form forward-Laplacian rules on the CPU (torch, any float dtype).
+
+A triplet is a tuple ``(x, J, lap)`` with ``J`` of shape ``(K, *x.shape)`` (Jacobian axis first,
+reference: folx/api.py:16).  Every function restates one rule of the reference and cites it.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+Triplet = tuple[torch.Tensor, torch.Tensor, torch.Tensor]
+
+
+# --------------------------------------------------------------------------------------------
+# elementwise: y = f(x), J_y = f'(x) J, lap_y = f'(x) lap + f''(x) sum_k J_k^2
+# reference: folx/jvp.py:687-697 (jvp part), folx/hessian.py:87-112 (Hessian part)
+# --------------------------------------------------------------------------------------------
+def _derivs(op: str, x: torch.Tensor, param: float = 0.0):
+    if op == 'tanh':
+        y = torch.tanh(x)
+        d1 = 1 - y * y
+        return y, d1, -2 * y * d1
+    if op == 'silu':
+        s = torch.sigmoid(x)
+        return x * s, s * (1 + x * (1 - s)), s * (1 - s) * (2 + x * (1 - 2 * s))
+    if op == 'exp':
+        y = torch.exp(x)
+        return y, y, y
+    if op == 'log':
+        return torch.log(x), 1 / x, -1 / (x * x)
+    if op == 'sqrt':
+        y = torch.sqrt(x)
+        return y, 0.5 / y, -0.25 / (x * y)
+    if op == 'rsqrt':
+        y = torch.rsqrt(x)
+        return y, -0.5 * y / x, 0.75 * y / (x * x)
+    if op == 'square':
+        return x * x, 2 * x, torch.full_like(x, 2.0)
+    if op == 'sigmoid':
+        s = torch.sigmoid(x)
+        d1 = s * (1 - s)
+        return s, d1, d1 * (1 - 2 * s)
+    if op == 'softplus':
+        s = torch.sigmoid(x)
+        return torch.nn.functional.softplus(x), s, s * (1 - s)
+    if op == 'integer_pow':
+        n = int(param)
+        return x**n, n * x ** (n - 1), n * (n - 1) * x ** (n - 2)
+    if op == 'sin':
+        return torch.sin(x), torch.cos(x), -torch.sin(x)
+    if op == 'cos':
+        return torch.cos(x), -torch.sin(x), -torch.cos(x)
+    if op == 'neg':
+        return -x, -torch.ones_like(x), torch.zeros_like(x)
+    if op == 'abs':
+        return torch.abs(x), torch.sign(x), torch.zeros_like(x)
+    if op == 'scale':
+        return param * x, torch.full_like(x, param), torch.zeros_like(x)
+    if op == 'shift':
+        return x + param, torch.ones_like(x), torch.zeros_like(x)
+    if op == 'reciprocal':
+        inv = 1 / x
+        return inv, -inv * inv, 2 * inv**3
+    raise KeyError(op)
+
+
+def elementwise(op: str, t: Triplet, param: float = 0.0) -> Triplet:
+    x, J, lap = t
+    y, d1, d2 = _derivs(op, x, param)
+    return y, d1 * J, d1 * lap + d2 * (J * J).sum(0)
+
+
+# --------------------------------------------------------------------------------------------
+# binary ops on aligned Jacobians
+# mul: folx/wrapped_functions.py:375-377 + folx/hessian.py:177-188 (2 sum_k Ja_k Jb_k)
+# div: folx/wrapped_functions.py:378-383 + folx/custom_hessian.py:35-59
+# add/sub: folx/wrapped_functions.py:364-369 (linear)
+# --------------------------------------------------------------------------------------------
+def binary(op: str, a: Triplet, b: Triplet) -> Triplet:
+    ax, aJ, al = a
+    bx, bJ, bl = b
+    if op == 'add':
+        return ax + bx, aJ + bJ, al + bl
+    if op == 'sub':
+        return ax - bx, aJ - bJ, al - bl
+    if op == 'mul':
+        return ax * bx, aJ * bx + ax * bJ, al * bx + ax * bl + 2 * (aJ * bJ).sum(0)
+    if op == 'div':
+        y = ax / bx
+        J = aJ / bx - ax * bJ / bx**2
+        lap = (al / bx - ax * bl / bx**2 - 2 / bx**2 * (aJ * bJ).sum(0)
+               + 2 * ax / bx**3 * (bJ * bJ).sum(0))
+        return y, J, lap
+    raise KeyError(op)
+
+
+def constant(x: torch.Tensor, K: int) -> Triplet:
+    """A constant seen as a triplet: zero Jacobian and Laplacian."""
+    return x, torch.zeros((K, *x.shape), dtype=x.dtype), torch.zeros_like(x)
+
+
+# --------------------------------------------------------------------------------------------
+# dot_general with a constant right operand, plus the bias add
+# reference: folx/wrapped_functions.py:159-171 (three products), 364-366 (bias is a constant:
+# it shifts x only)
+# --------------------------------------------------------------------------------------------
+def dot_general(t: Triplet, W: torch.Tensor, bias: torch.Tensor | None = None) -> Triplet:
+    x, J, lap = t
+    y = x @ W
+    if bias is not None:
+        y = y + bias
+    return y, J @ W, lap @ W
+
+
+# --------------------------------------------------------------------------------------------
+# reductions (linear): folx/wrapped_functions.py:387-391, dense path folx/jvp.py:676-684
+# --------------------------------------------------------------------------------------------
+def reduce_sum(t: Triplet, axes, keepdim: bool = False) -> Triplet:
+    x, J, lap = t
+    axes = tuple(a % x.ndim for a in (axes if isinstance(axes, (tuple, list)) else (axes,)))
+    jaxes = tuple(a + 1 for a in axes)
+    return x.sum(axes, keepdim=keepdim), J.sum(jaxes, keepdim=keepdim), lap.sum(axes, keepdim=keepdim)
+
+
+def reduce_mean(t: Triplet, axes, keepdim: bool = False) -> Triplet:
+    x = t[0]
+    axes_t = axes if isinstance(axes, (tuple, list)) else (axes,)
+    n = math.prod(x.shape[a] for a in axes_t)
+    return elementwise('scale', reduce_sum(t, axes, keepdim), 1.0 / n)
+
+
+# --------------------------------------------------------------------------------------------
+# LayerNorm as the reference evaluates it: a chain of registry rules
+# (reduce_sum, sub, square, add eps, rsqrt, mul; folx/wrapped_functions.py:364-391, 409).
+# --------------------------------------------------------------------------------------------
+def layernorm(t: Triplet, gamma: torch.Tensor | None, beta: torch.Tensor | None,
+              eps: float = 1e-6) -> Triplet:
+    K = t[1].shape[0]
+    mean = reduce_mean(t, -1, keepdim=True)
+    c = binary('sub', t, tuple(torch.broadcast_to(m, s.shape) for m, s in zip(mean, t)))
+    var = reduce_mean(elementwise('square', c), -1, keepdim=True)
+    r = elementwise('rsqrt', elementwise('shift', var, eps))
+    z = binary('mul', c, tuple(torch.broadcast_to(m, s.shape) for m, s in zip(r, c)))
+    if gamma is not None:
+        z = binary('mul', z, constant(torch.broadcast_to(gamma, z[0].shape), K))
+    if beta is not None:
+        z = binary('add', z, constant(torch.broadcast_to(beta, z[0].shape), K))
+    return z
+
+
+# --------------------------------------------------------------------------------------------
+# slogdet of a batch of square matrices with a dense Jacobian
+# reference: folx/slogdet.py:296-317: M_k = A^-1 dA_k, J_k = tr M_k,
+#            lap = tr(A^-1 lapA) - sum_k tr(M_k M_k)
+# x: (..., n, n), J: (K, ..., n, n)
+# --------------------------------------------------------------------------------------------
+def slogdet(t: Triplet):
+    A, J, lap = t
+    sign, logdet = torch.linalg.slogdet(A)
+    A_inv = torch.linalg.inv(A)
+    M = torch.einsum('...ij,k...jd->k...id', A_inv, J)
+    jac = torch.einsum('k...ii->k...', M)
+    lapl = torch.einsum('...ji,...ij->...', A_inv, lap) - torch.einsum('k...id,k...di->...', M, M)
+    return sign, (logdet, jac, lapl)
+
+
+# --------------------------------------------------------------------------------------------
+# Multi-head self attention on triplets, compact form.
+# reference: the kernel body folx/experimental/pallas/attention/forward_laplacian.py:387-487
+# (same terms, regrouped) with the masking of lines 389-407, 421-424 and `big_number`
+# (folx/experimental/pallas/attention/utils.py:210-220).
+# q, k, v: (B, n, H, d); *_J: (R, B, n, H, d); mask: (B, n) bool; input_mask: (R, B) bool.
+# --------------------------------------------------------------------------------------------
+def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: torch.Tensor) -> Triplet:
+    qx, qJ, ql = q
+    kx, kJ, kl = k
+    vx, vJ, vl = v
+    dt = qx.dtype
+    big = 1e20 if dt == torch.float32 else 1e40
+    m = mask.to(dt)
+    row = m[:, :, None, None]  # (B, n, 1, 1)
+    ql, kl, vl = ql * row, kl * row, vl * row
+    qJ, kJ, vJ = qJ * row, kJ * row, vJ * row
+    sq = (mask[:, :, None] & mask[:, None, :])  # (B, n, n)
+    # scores (B, H, n, n)
+    s = torch.einsum('bihd,bjhd->bhij', qx, kx)
+    s = torch.where(sq[:, None], s, torch.full_like(s, -big))
+    p = torch.softmax(s, dim=-1)
+    o = torch.einsum('bhij,bjhd->bihd', p, vx)
+
+    def rs(a):  # row sums of a (.., i, j) -> (.., i, 1)
+        return a.sum(-1, keepdim=True)
+
+    def pv(a, val):  # (b h i j) x (b j h d) -> (b i h d)
+        return torch.einsum('bhij,bjhd->bihd', a, val)
+
+    def bihd(a):  # (b h i 1) -> (b i h 1)
+        return a.permute(0, 2, 1, 3)
+
+    # Laplacian, linear part: s_D = q k_D^T + q_D k^T
+    sD = torch.einsum('bihd,bjhd->bhij', qx, kl) + torch.einsum('bihd,bjhd->bhij', ql, kx)
+    psD = p * sD
+    o_lap = pv(psD, vx) - bihd(rs(psD)) * o + pv(p, vl)
+
+    R = qJ.shape[0]
+    o_J = torch.empty_like(qJ)
+    for r in range(R):
+        qr_k = torch.einsum('bihd,bjhd->bhij', qJ[r], kx)
+        q_kr = torch.einsum('bihd,bjhd->bhij', qx, kJ[r])
+        sr = qr_k + q_kr
+        psr = p * sr
+        cr_sum = rs(psr)
+        pr = psr - p * cr_sum  # d p / d x_r
+        pvr = pv(p, vJ[r])
+        o_J[r] = pv(pr, vx) + pvr
+        # Hessian part
+        qr_kr = torch.einsum('bihd,bjhd->bhij', qJ[r], kJ[r])
+        cr = sr - cr_sum
+        term_v = pr * cr + p * (2 * qr_kr - rs(pr * sr) - rs(p * 2 * qr_kr))
+        contrib = pv(term_v, vx) + 2 * pv(pr, vJ[r])
+        w = input_mask[r].to(dt)[:, None, None, None]
+        o_lap = o_lap + w * contrib
+    return o, o_J, o_lap
+
+
+# --------------------------------------------------------------------------------------------
+# initial state: identity Jacobian, zero Laplacian (reference: folx/interpreter.py:267-298)
+# --------------------------------------------------------------------------------------------
+def init_dense(x: torch.Tensor) -> Triplet:
+    n = x.numel()
+    J = torch.eye(n, dtype=x.dtype).reshape(n, *x.shape)
+    return x, J, torch.zeros_like(x)

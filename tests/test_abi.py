@@ -1,0 +1,33 @@
+"""The C-ABI library builds, loads and exports every symbol the header declares (no GPU needed)."""
+
+import os
+import re
+
+from folx_b200 import lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, 'include', 'folx_b200.h')).read()
+    text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    return sorted(set(re.findall(r'\b(fl_[a-z0-9_]+)\s*\(', text)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    handle = lib.load()
+    declared = _declared_symbols()
+    assert declared, 'no declarations found in the header'
+    for name in declared:
+        assert hasattr(handle, name), f'{name} is declared in the header but not exported'
+    assert sorted(lib.exported_symbols()) == declared
+    assert handle.fl_version() >= 100
+
+
+def test_error_text_is_available_without_a_gpu():
+    handle = lib.load()
+    # an argument check that fails before any CUDA call
+    rc = handle.fl_elementwise(999, 0.0, None, None, None, None, None, None, 0, 4, 4, 4, None)
+    assert rc == lib.FL_EUNSUPPORTED
+    assert b'unknown op' in handle.fl_last_error()
+    assert handle.fl_dot_general_workspace_bytes(256, 256) == 2 * 256 * 256 * 4

@@ -1,0 +1,201 @@
+"""GPU parity of the dense rules (elementwise, binary, dot_general, LayerNorm) against the oracle.
+
+All calls go through the C ABI (folx_b200.kernels -> ctypes -> libfolx_b200.so).
+"""
+
+import pytest
+import torch
+
+from folx_b200 import kernels, lib
+from oracle import rules
+
+from gpu_util import assert_close, seeded_triplet, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+
+POSITIVE = {'log', 'sqrt', 'rsqrt', 'reciprocal'}
+
+
+@pytest.mark.parametrize('op', sorted(set(lib.ELEMENTWISE_OPS) - {'integer_pow', 'scale', 'shift'}))
+@pytest.mark.parametrize('K,shape', [(0, (5,)), (1, (7, 3)), (9, (4, 8)), (17, (3, 5, 16))])
+def test_elementwise(cuda_device, op, K, shape):
+    t = seeded_triplet(K, shape, seed=1, positive=op in POSITIVE)
+    got = kernels.elementwise(op, to_device(t, cuda_device))
+    assert_close(to_host(got), rules.elementwise(op, t))
+
+
+@pytest.mark.parametrize('op,param', [('integer_pow', 2), ('integer_pow', 3), ('integer_pow', -1),
+                                      ('integer_pow', -2), ('scale', 0.37), ('shift', -1.5)])
+def test_elementwise_param(cuda_device, op, param):
+    t = seeded_triplet(6, (10, 12), seed=2, positive=True)
+    got = kernels.elementwise(op, to_device(t, cuda_device), param)
+    assert_close(to_host(got), rules.elementwise(op, t, param))
+
+
+def test_elementwise_unstacked_and_empty(cuda_device):
+    t = seeded_triplet(3, (6, 5), seed=3)
+    got = kernels.elementwise('tanh', to_device(t, cuda_device, stacked=False))
+    assert_close(to_host(got), rules.elementwise('tanh', t))
+    empty = seeded_triplet(3, (0, 4), seed=3)
+    out = kernels.elementwise('tanh', to_device(empty, cuda_device))
+    assert out.x.shape == (0, 4) and out.jacobian.data.shape == (3, 0, 4)
+
+
+def test_elementwise_bench_shape_properties(cuda_device):
+    """Operator-microbench size (B=4096, d=96, F=256): sum-of-squares identity on the device."""
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    K, P, F = 96, 4096, 256
+    a = kernels.alloc_triplet(K, (P, F), cuda_device)
+    a.x.normal_(generator=g); a.jacobian.data.normal_(generator=g); a.laplacian.normal_(generator=g)
+    out = kernels.elementwise('tanh', a)
+    y = torch.tanh(a.x)
+    d1 = 1 - y * y
+    torch.testing.assert_close(out.x, y, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(out.jacobian.data, d1 * a.jacobian.data, rtol=1e-5, atol=1e-6)
+    want = d1 * a.laplacian - 2 * y * d1 * (a.jacobian.data.double() ** 2).sum(0).float()
+    torch.testing.assert_close(out.laplacian, want, rtol=1e-4, atol=1e-3)
+    # linearity in (J, lap): doubling both doubles J_y and changes lap_y by the known amount
+    b = kernels.alloc_triplet(K, (P, F), cuda_device)
+    b.x.copy_(a.x); b.jacobian.data.copy_(2 * a.jacobian.data); b.laplacian.copy_(2 * a.laplacian)
+    out2 = kernels.elementwise('tanh', b)
+    torch.testing.assert_close(out2.jacobian.data, 2 * out.jacobian.data, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div'])
+@pytest.mark.parametrize('K,shape', [(0, (4,)), (5, (6, 7)), (12, (3, 4, 8))])
+def test_binary(cuda_device, op, K, shape):
+    a = seeded_triplet(K, shape, seed=4)
+    b = seeded_triplet(K, shape, seed=5, positive=True)
+    got = kernels.binary(op, to_device(a, cuda_device), to_device(b, cuda_device))
+    assert_close(to_host(got), rules.binary(op, a, b))
+
+
+@pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div'])
+def test_binary_constant_and_broadcast(cuda_device, op):
+    K, shape = 5, (6, 8)
+    a = seeded_triplet(K, shape, seed=6, positive=True)
+    c = seeded_triplet(0, (8,), seed=7, positive=True)[0]
+    cb = torch.broadcast_to(c, shape)
+    # triplet (op) broadcast constant
+    got = kernels.binary(op, to_device(a, cuda_device), c.float().to(cuda_device))
+    assert_close(to_host(got), rules.binary(op, a, rules.constant(cb, K)))
+    # constant (op) triplet
+    got = kernels.binary(op, cb.float().contiguous().to(cuda_device), to_device(a, cuda_device))
+    assert_close(to_host(got), rules.binary(op, rules.constant(cb, K), a))
+    # triplet (op) broadcast triplet
+    b = seeded_triplet(K, (8,), seed=8, positive=True)
+    bb = tuple(torch.broadcast_to(u, (*u.shape[:-1], *shape)) for u in b)
+    got = kernels.binary(op, to_device(a, cuda_device), to_device(b, cuda_device))
+    assert_close(to_host(got), rules.binary(op, a, bb))
+
+
+GEMM_SHAPES = [
+    # (K, P, F_in, F_out)
+    (0, 1, 4, 4), (3, 5, 8, 12), (2, 130, 32, 16), (7, 33, 64, 48), (5, 200, 100, 100),
+    (3, 129, 256, 256), (4, 64, 56, 256), (2, 40, 36, 260), (1, 300, 256, 512), (6, 17, 30, 10),
+]
+
+
+@pytest.mark.parametrize('mode', [1, 0])
+@pytest.mark.parametrize('K,P,F_in,F_out', GEMM_SHAPES)
+@pytest.mark.parametrize('with_bias', [False, True])
+def test_dot_general(cuda_device, mode, K, P, F_in, F_out, with_bias):
+    t = seeded_triplet(K, (P, F_in), seed=9)
+    g = torch.Generator().manual_seed(10)
+    W = (torch.randn(F_in, F_out, generator=g, dtype=torch.float64) / F_in**0.5).float().double()
+    b = (torch.randn(F_out, generator=g, dtype=torch.float64) * 0.1).float().double() if with_bias else None
+    lib.load().fl_dot_general_set_mode(mode)
+    try:
+        got = kernels.dot_general(to_device(t, cuda_device), W.float().to(cuda_device),
+                                  b.float().to(cuda_device) if with_bias else None)
+        kernels.check_gemm_status(cuda_device)
+    finally:
+        lib.load().fl_dot_general_set_mode(0)
+    assert_close(to_host(got), rules.dot_general(t, W, b))
+
+
+def test_dot_general_unstacked_inputs(cuda_device):
+    t = seeded_triplet(4, (70, 64), seed=11)
+    W = torch.randn(64, 32, dtype=torch.float64).float().double()
+    got = kernels.dot_general(to_device(t, cuda_device, stacked=False), W.float().to(cuda_device))
+    kernels.check_gemm_status(cuda_device)
+    assert_close(to_host(got), rules.dot_general(t, W))
+
+
+def test_dot_general_accuracy_is_fp32_class(cuda_device):
+    """3xTF32 must be as accurate as an fp32 product: error << TF32's 1e-3."""
+    K, P, F = 6, 512, 256
+    t = seeded_triplet(K, (P, F), seed=12)
+    W = (torch.randn(F, F, dtype=torch.float64) / 16).float().double()
+    got = to_host(kernels.dot_general(to_device(t, cuda_device), W.float().to(cuda_device)))
+    kernels.check_gemm_status(cuda_device)
+    want = rules.dot_general(t, W)
+    for g, w in zip(got, want):
+        err = (g - w).abs().max() / w.abs().max()
+        assert float(err) < 5e-6, float(err)
+
+
+def test_dot_general_bench_shape_linearity(cuda_device):
+    """Full operator-microbench size: Y(T1 + T2) == Y(T1) + Y(T2) and a sampled fp64 check."""
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    K, P, F = 96, 4096, 256
+    W = torch.randn(F, F, device=cuda_device, generator=g) / 16
+    bias = torch.randn(F, device=cuda_device, generator=g) * 0.1
+    a = kernels.alloc_triplet(K, (P, F), cuda_device)
+    a.x.normal_(generator=g); a.jacobian.data.normal_(generator=g); a.laplacian.normal_(generator=g)
+    ya = kernels.dot_general(a, W, bias)
+    kernels.check_gemm_status(cuda_device)
+    rows = torch.randint(0, P, (64,), device=cuda_device, generator=g)
+    Wd = W.double()
+    torch.testing.assert_close(ya.x[rows].double(), a.x[rows].double() @ Wd + bias.double(), rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(ya.laplacian[rows].double(), a.laplacian[rows].double() @ Wd, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(ya.jacobian.data[:, rows].double(), a.jacobian.data[:, rows].double() @ Wd,
+                               rtol=1e-4, atol=1e-5)
+    # linearity of the Jacobian part
+    b = kernels.alloc_triplet(K, (P, F), cuda_device)
+    b.x.copy_(a.x); b.jacobian.data.copy_(-a.jacobian.data); b.laplacian.copy_(a.laplacian)
+    yb = kernels.dot_general(b, W, bias)
+    kernels.check_gemm_status(cuda_device)
+    assert float((ya.jacobian.data + yb.jacobian.data).abs().max()) == 0.0
+    assert torch.equal(ya.x, yb.x)
+
+
+@pytest.mark.parametrize('K,P,F', [(0, 3, 128), (5, 9, 256), (3, 17, 1024), (4, 6, 100), (2, 5, 7),
+                                   (7, 33, 384)])
+@pytest.mark.parametrize('affine', [False, True])
+def test_layernorm(cuda_device, K, P, F, affine):
+    t = seeded_triplet(K, (P, F), seed=13)
+    g = torch.Generator().manual_seed(14)
+    gamma = torch.randn(F, generator=g, dtype=torch.float64).float().double() if affine else None
+    beta = torch.randn(F, generator=g, dtype=torch.float64).float().double() if affine else None
+    got = kernels.layernorm(to_device(t, cuda_device),
+                            gamma.float().to(cuda_device) if affine else None,
+                            beta.float().to(cuda_device) if affine else None, 1e-6)
+    assert_close(to_host(got), rules.layernorm(t, gamma, beta, 1e-6))
+
+
+def test_layernorm_bench_shape_properties(cuda_device):
+    """Full size: outputs are normalised; J_y and lap_y sum to ~0 over features (mean removed)."""
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    K, P, F = 96, 4096, 256
+    a = kernels.alloc_triplet(K, (P, F), cuda_device)
+    a.x.normal_(generator=g); a.jacobian.data.normal_(generator=g); a.laplacian.normal_(generator=g)
+    out = kernels.layernorm(a, None, None, 1e-6)
+    assert float(out.x.mean(-1).abs().max()) < 1e-5
+    torch.testing.assert_close(out.x.pow(2).mean(-1), torch.ones(P, device=cuda_device), rtol=1e-4, atol=1e-4)
+    assert float(out.jacobian.data.sum(-1).abs().max()) < 1e-3
+    # sampled rows against the oracle
+    rows = torch.arange(0, P, 512)
+    t = (a.x[rows].double().cpu(), a.jacobian.data[:, rows].double().cpu(), a.laplacian[rows].double().cpu())
+    want = rules.layernorm(t, None, None, 1e-6)
+    got = (out.x[rows].double().cpu(), out.jacobian.data[:, rows].double().cpu(), out.laplacian[rows].double().cpu())
+    assert_close(got, want)
+
+
+def test_errors_are_reported_not_swallowed(cuda_device):
+    a = to_device(seeded_triplet(2, (4, 8), seed=15), cuda_device)
+    with pytest.raises(lib.FolxB200Error):
+        lib.call('fl_elementwise', 999, 0.0, None, None, None, None, None, None, 0, 4, 4, 4, None)
+    with pytest.raises(RuntimeError):
+        kernels.elementwise('tanh', to_device(seeded_triplet(2, (4,), seed=1), 'cpu', stacked=False))
+    assert a.x.is_cuda

@@ -1,0 +1,159 @@
+"""Pins the CPU oracle: every closed-form rule must equal brute-force AD (fp64).
+
+The reference has no stored float vectors; its tests assert exactly this identity
+(test/laplacian_testcase.py:22-49), so this is the float-path pin of the oracle.
+"""
+
+import pytest
+import torch
+
+from oracle import brute, rules
+
+torch.manual_seed(0)
+DT = torch.float64
+
+
+def rand_triplet(K, shape, positive=False, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(shape, dtype=DT, generator=g)
+    if positive:
+        x = x.abs() + 0.5
+    J = torch.randn((K, *shape), dtype=DT, generator=g)
+    lap = torch.randn(shape, dtype=DT, generator=g)
+    return x, J, lap
+
+
+def assert_triplet_close(a, b, rtol=1e-9, atol=1e-10):
+    for u, v, name in zip(a, b, ('x', 'jacobian', 'laplacian')):
+        torch.testing.assert_close(u, v, rtol=rtol, atol=atol, msg=lambda m: f'{name}: {m}')
+
+
+ELEMENTWISE = {
+    'tanh': (torch.tanh, False), 'silu': (torch.nn.functional.silu, False),
+    'exp': (torch.exp, False), 'log': (torch.log, True), 'sqrt': (torch.sqrt, True),
+    'rsqrt': (torch.rsqrt, True), 'square': (torch.square, False),
+    'sigmoid': (torch.sigmoid, False), 'softplus': (torch.nn.functional.softplus, False),
+    'sin': (torch.sin, False), 'cos': (torch.cos, False), 'neg': (torch.neg, False),
+    'abs': (torch.abs, False), 'reciprocal': (torch.reciprocal, True),
+}
+
+
+@pytest.mark.parametrize('op', sorted(ELEMENTWISE))
+def test_elementwise_matches_brute_force(op):
+    fn, positive = ELEMENTWISE[op]
+    t = rand_triplet(5, (3, 4), positive)
+    assert_triplet_close(rules.elementwise(op, t), brute.propagate(fn, [t]))
+
+
+@pytest.mark.parametrize('n', [-2, -1, 2, 3])
+def test_integer_pow(n):
+    t = rand_triplet(4, (6,), positive=True)
+    assert_triplet_close(rules.elementwise('integer_pow', t, n), brute.propagate(lambda x: x**n, [t]))
+
+
+def test_scale_shift():
+    t = rand_triplet(4, (6,))
+    assert_triplet_close(rules.elementwise('scale', t, 2.5), brute.propagate(lambda x: 2.5 * x, [t]))
+    assert_triplet_close(rules.elementwise('shift', t, 2.5), brute.propagate(lambda x: x + 2.5, [t]))
+
+
+@pytest.mark.parametrize('op,fn', [('add', torch.add), ('sub', torch.sub), ('mul', torch.mul),
+                                   ('div', torch.div)])
+def test_binary_matches_brute_force(op, fn):
+    a = rand_triplet(5, (3, 4), seed=1)
+    b = rand_triplet(5, (3, 4), positive=True, seed=2)
+    assert_triplet_close(rules.binary(op, a, b), brute.propagate(fn, [a, b]))
+
+
+def test_dot_general_matches_brute_force():
+    t = rand_triplet(4, (3, 6))
+    W = torch.randn(6, 5, dtype=DT)
+    b = torch.randn(5, dtype=DT)
+    assert_triplet_close(rules.dot_general(t, W, b), brute.propagate(lambda x: x @ W + b, [t]))
+
+
+def test_layernorm_matches_brute_force():
+    t = rand_triplet(6, (2, 8))
+    gamma = torch.randn(8, dtype=DT)
+    beta = torch.randn(8, dtype=DT)
+    f = lambda x: torch.nn.functional.layer_norm(x, (8,), gamma, beta, eps=1e-6)
+    assert_triplet_close(rules.layernorm(t, gamma, beta, 1e-6), brute.propagate(f, [t]), rtol=1e-8)
+
+
+def test_layernorm_closed_form_used_by_kernel():
+    """The fused formula documented in include/folx_b200.h equals the rule chain."""
+    x, J, lap = rand_triplet(6, (3, 16))
+    eps = 1e-6
+    mean = lambda a: a.mean(-1, keepdim=True)
+    c = x - mean(x)
+    r = (mean(c * c) + eps) ** -0.5
+    z = c * r
+    u = r * (J - mean(J))
+    b = mean(z * u)
+    lc = lap - mean(lap)
+    Jz = u - z * b
+    lap_z = r * (lc - z * mean(z * lc)) + (-2 * b * u + z * (3 * b * b - mean(u * u))).sum(0)
+    assert_triplet_close((z, Jz, lap_z), rules.layernorm((x, J, lap), None, None, eps), rtol=1e-9)
+
+
+@pytest.mark.parametrize('n', [1, 3, 5])
+def test_slogdet_matches_brute_force(n):
+    t = rand_triplet(4, (2, n, n), seed=3)
+    sign, out = rules.slogdet(t)
+    ref = brute.propagate(lambda a: torch.linalg.slogdet(a)[1], [t])
+    assert_triplet_close(out, ref, rtol=1e-8)
+    torch.testing.assert_close(sign, torch.linalg.slogdet(t[0])[0])
+
+
+def _attention(q, k, v, mask):
+    s = torch.einsum('bihd,bjhd->bhij', q, k)
+    sq = mask[:, :, None] & mask[:, None, :]
+    s = torch.where(sq[:, None], s, torch.full_like(s, -1e40))
+    return torch.einsum('bhij,bjhd->bihd', torch.softmax(s, -1), v)
+
+
+@pytest.mark.parametrize('masked', [False, True])
+def test_mhsa_matches_brute_force(masked):
+    B, n, H, d, R = 2, 4, 2, 3, 5
+    q = rand_triplet(R, (B, n, H, d), seed=4)
+    k = rand_triplet(R, (B, n, H, d), seed=5)
+    v = rand_triplet(R, (B, n, H, d), seed=6)
+    mask = torch.ones(B, n, dtype=torch.bool)
+    if masked:
+        mask[0, 3] = False
+        mask[1, 2:] = False
+        # masked electrons carry no derivatives (the kernel zeroes them, reference lines 392-423)
+        zero = lambda t: (t[0], t[1] * mask[None, :, :, None, None], t[2] * mask[:, :, None, None])
+        q, k, v = zero(q), zero(k), zero(v)
+    input_mask = torch.ones(R, B, dtype=torch.bool)
+    out = rules.mhsa(q, k, v, mask, input_mask)
+    ref = brute.propagate(lambda a, b, c: _attention(a, b, c, mask), [q, k, v])
+    # rows of masked electrons are "don't care": the reference's tests blank them before
+    # comparing (test/experimental/pallas/test_attention.py:341-386, mask_fwd_lapl_array)
+    keep = lambda t: (t[0] * mask[:, :, None, None], t[1] * mask[None, :, :, None, None],
+                      t[2] * mask[:, :, None, None])
+    assert_triplet_close(keep(out), keep(ref), rtol=1e-8, atol=1e-9)
+
+
+def test_mhsa_input_mask_drops_hessian_terms_of_masked_coordinates():
+    B, n, H, d, R = 1, 3, 1, 2, 4
+    q = rand_triplet(R, (B, n, H, d), seed=7)
+    k = rand_triplet(R, (B, n, H, d), seed=8)
+    v = rand_triplet(R, (B, n, H, d), seed=9)
+    mask = torch.ones(B, n, dtype=torch.bool)
+    input_mask = torch.ones(R, B, dtype=torch.bool)
+    input_mask[2] = False
+    # zeroing the masked coordinate's Jacobian rows must give the same Laplacian
+    z = lambda t: (t[0], torch.cat([t[1][:2], torch.zeros_like(t[1][2:3]), t[1][3:]]), t[2])
+    a = rules.mhsa(q, k, v, mask, input_mask)
+    b = rules.mhsa(z(q), z(k), z(v), mask, torch.ones(R, B, dtype=torch.bool))
+    torch.testing.assert_close(a[2], b[2], rtol=1e-10, atol=1e-12)
+
+
+def test_reduce_sum_and_init():
+    t = rand_triplet(3, (4, 5))
+    assert_triplet_close(rules.reduce_sum(t, -1), brute.propagate(lambda x: x.sum(-1), [t]))
+    x = torch.randn(2, 3, dtype=DT)
+    _, J, lap = rules.init_dense(x)
+    assert J.shape == (6, 2, 3) and float(lap.abs().sum()) == 0.0
+    assert torch.equal(J.reshape(6, 6), torch.eye(6, dtype=DT))
