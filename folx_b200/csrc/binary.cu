@@ -8,7 +8,7 @@
 //        (reference: folx/wrapped_functions.py:378-383, folx/custom_hessian.py:35-59)
 //   add/sub: linear in both operands, no Hessian term (folx/wrapped_functions.py:364-369).
 //
-// Either operand may be a constant array (its jac and lap pointers are NULL): then its Jacobian
+// Either operand may be a constant array (its lap pointer, and jac pointer, are NULL): then its Jacobian
 // and Laplacian are zero.  Operand b may be periodic along the position axis (broadcast).
 // HBM-bound, one pass; algorithmic traffic 4 (K + 2) (N_a + N_b + N) bytes.
 #include "common.cuh"
@@ -71,7 +71,7 @@ int32_t dispatch(const float* a, const float* ja, const float* la, int64_t jas, 
                  const float* jb, const float* lb, int64_t jbs, float* y, float* jy, float* ly,
                  int64_t jys, int64_t K, int64_t N, int64_t b_period, cudaStream_t st) {
   unsigned blocks = (unsigned)((N + 255) / 256);
-  bool at = ja != nullptr, bt = jb != nullptr;
+  bool at = la != nullptr, bt = lb != nullptr;
 #define FL_LAUNCH(AT, BT)                                                                     \
   binary_kernel<OP, AT, BT><<<blocks, 256, 0, st>>>(a, ja, la, jas, b, jb, lb, jbs, y, jy, ly, \
                                                     jys, (int)K, N, b_period)
@@ -100,7 +100,10 @@ extern "C" int32_t fl_binary(int32_t op, const float* a, const float* jac_a, con
   FL_REQUIRE(b_period > 0 && b_period <= N && N % b_period == 0, FL_EBADSHAPE,
              "fl_binary: b_period %lld does not divide N %lld", (long long)b_period, (long long)N);
   FL_REQUIRE(a && b && y && lap_y && (K == 0 || jac_y), FL_EBADSHAPE, "fl_binary: null pointer");
-  FL_REQUIRE((jac_a == nullptr) == (lap_a == nullptr) && (jac_b == nullptr) == (lap_b == nullptr),
+  // an operand is a triplet iff its lap pointer is given; its jac may be NULL only when K == 0
+  FL_REQUIRE((lap_a != nullptr || jac_a == nullptr) && (lap_b != nullptr || jac_b == nullptr) &&
+                 (K == 0 || ((lap_a == nullptr) == (jac_a == nullptr) &&
+                             (lap_b == nullptr) == (jac_b == nullptr))),
              FL_EBADSHAPE, "fl_binary: jac and lap of an operand must both be given or both NULL");
   cudaStream_t st = (cudaStream_t)stream;
   switch (op) {

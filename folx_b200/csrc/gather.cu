@@ -1,0 +1,137 @@
+// Static gather / segment-sum of Jacobian rows driven by host-built int32 tables.
+//
+// Moving a sparse Jacobian into another row frame -- densifying it, aligning it to the union
+// frame of a reduction or of a binary op, summing rows of a reduced axis -- is always
+//     out[o, pos] = sum_s in[take[o, s, class(pos)], in_pos(pos)]        (take < 0: empty slot)
+// with a table that depends only on the index maps.  The reference does this with
+// take_along_axis + masked sum (materialize_by_gather, folx/utils.py:71-114, called from
+// folx/api.py:58-118 and folx/jvp.py:37-86, 164-171) or a runtime segment_sum; here the table is
+// uploaded once per traced function and one kernel applies it: pure gather, deterministic
+// (fixed slot order, no atomics), coalesced along the innermost axis.
+// HBM-bound; algorithmic traffic 4 (rows_read + k_out) N bytes plus the table.
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kMaxDims = FL_GATHER_MAX_DIMS;
+
+struct GatherGeom {
+  int ndim;
+  int64_t shape[kMaxDims];         // output position shape (row-major)
+  int64_t in_stride[kMaxDims];     // element stride of each axis inside one input row (0: broadcast)
+  int64_t table_stride[kMaxDims];  // stride of each axis in the table (0: table constant along it)
+};
+
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const float* __restrict__ in, int64_t in_row_stride,
+                   const int32_t* __restrict__ take, int64_t table_positions, int k_out,
+                   int n_slots, float* __restrict__ out, int64_t out_row_stride, int64_t N,
+                   GatherGeom g) {
+  int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (pos >= N) return;
+  int64_t rem = pos, in_off = 0, t_off = 0;
+#pragma unroll
+  for (int d = kMaxDims - 1; d >= 0; --d) {
+    if (d < g.ndim) {
+      int64_t i = rem % g.shape[d];
+      rem /= g.shape[d];
+      in_off += i * g.in_stride[d];
+      t_off += i * g.table_stride[d];
+    }
+  }
+  for (int o = 0; o < k_out; ++o) {
+    float acc = 0.f;
+    for (int s = 0; s < n_slots; ++s) {
+      int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
+      if (r >= 0) acc += __ldg(in + (int64_t)r * in_row_stride + in_off);
+    }
+    __stcs(out + (int64_t)o * out_row_stride + pos, acc);
+  }
+}
+
+// Innermost axis contiguous in the input, table constant along it, everything 16-byte friendly:
+// one thread moves a float4.
+__global__ void __launch_bounds__(256)
+gather_rows_vec4(const float4* __restrict__ in, int64_t in_row_stride4,
+                 const int32_t* __restrict__ take, int64_t table_positions, int k_out, int n_slots,
+                 float4* __restrict__ out, int64_t out_row_stride4, int64_t N4, GatherGeom g) {
+  int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (pos >= N4) return;
+  // g.shape[last] and g.in_stride are already expressed in float4 units by the host
+  int64_t rem = pos, in_off = 0, t_off = 0;
+#pragma unroll
+  for (int d = kMaxDims - 1; d >= 0; --d) {
+    if (d < g.ndim) {
+      int64_t i = rem % g.shape[d];
+      rem /= g.shape[d];
+      in_off += i * g.in_stride[d];
+      t_off += i * g.table_stride[d];
+    }
+  }
+  for (int o = 0; o < k_out; ++o) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_slots; ++s) {
+      int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
+      if (r >= 0) {
+        float4 v = __ldg(in + (int64_t)r * in_row_stride4 + in_off);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    st_stream(out + (int64_t)o * out_row_stride4 + pos, acc);
+  }
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_gather_rows(const float* jac_in, int64_t k_in, int64_t in_row_stride,
+                                  const int32_t* take, int64_t k_out, int64_t n_slots,
+                                  float* jac_out, int64_t out_row_stride, int32_t ndim,
+                                  const int64_t* shape, const int64_t* in_strides,
+                                  const int64_t* table_strides, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(ndim >= 0 && ndim <= kMaxDims, FL_EBADSHAPE, "fl_gather_rows: ndim %d not in [0, %d]",
+             ndim, kMaxDims);
+  FL_REQUIRE(k_in >= 0 && k_out >= 0 && n_slots >= 0 && k_out < (1ll << 31) && n_slots < (1ll << 31),
+             FL_EBADSHAPE, "fl_gather_rows: bad row counts");
+  GatherGeom g;
+  g.ndim = ndim;
+  int64_t N = 1, T = 1;
+  for (int d = 0; d < kMaxDims; ++d) {
+    g.shape[d] = d < ndim ? shape[d] : 1;
+    g.in_stride[d] = d < ndim ? in_strides[d] : 0;
+    g.table_stride[d] = d < ndim ? table_strides[d] : 0;
+    FL_REQUIRE(g.shape[d] >= 0, FL_EBADSHAPE, "fl_gather_rows: negative extent");
+    N *= g.shape[d];
+  }
+  // number of distinct table positions = 1 + max offset
+  for (int d = 0; d < ndim; ++d)
+    if (g.shape[d] > 0) T += (g.shape[d] - 1) * g.table_stride[d];
+  if (N == 0 || k_out == 0) return FL_OK;
+  FL_REQUIRE(jac_out && (n_slots == 0 || (take && jac_in)), FL_EBADSHAPE,
+             "fl_gather_rows: null pointer");
+  FL_REQUIRE(out_row_stride >= N, FL_EBADSHAPE, "fl_gather_rows: output row stride smaller than N");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int last = ndim - 1;
+  bool vec = ndim >= 1 && g.shape[last] % 4 == 0 && g.table_stride[last] == 0 &&
+             g.in_stride[last] == 1 && in_row_stride % 4 == 0 && out_row_stride % 4 == 0 &&
+             aligned16(jac_in) && aligned16(jac_out);
+  for (int d = 0; vec && d < last; ++d) vec = g.in_stride[d] % 4 == 0;
+  if (vec) {
+    GatherGeom g4 = g;
+    g4.shape[last] /= 4;
+    for (int d = 0; d < last; ++d) g4.in_stride[d] /= 4;
+    int64_t N4 = N / 4;
+    FL_REQUIRE((N4 + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_gather_rows: too many positions");
+    gather_rows_vec4<<<(unsigned)((N4 + 255) / 256), 256, 0, st>>>(
+        (const float4*)jac_in, in_row_stride / 4, take, T, (int)k_out, (int)n_slots,
+        (float4*)jac_out, out_row_stride / 4, N4, g4);
+  } else {
+    FL_REQUIRE((N + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_gather_rows: too many positions");
+    gather_rows_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(
+        jac_in, in_row_stride, take, T, (int)k_out, (int)n_slots, jac_out, out_row_stride, N, g);
+  }
+  FL_CHECK_LAUNCH("fl_gather_rows launch");
+  return FL_OK;
+}

@@ -43,7 +43,7 @@ constexpr int CTRL_BYTES = 256;
 constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
 constexpr int NUM_THREADS = 320;
 constexpr int TMEM_COLS = 512;
-constexpr uint32_t SPIN_LIMIT = 1u << 22;
+constexpr uint32_t SPIN_LIMIT = 1u << 20;  // probes of <= ~2 us each: a wait gives up after ~2 s
 
 // ---- PTX wrappers -------------------------------------------------------------------------
 
@@ -68,10 +68,10 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(2000u)  // suspend-time hint in ns: one probe stays short
       : "memory");
   return ok != 0;
 }
@@ -81,10 +81,7 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
     if (mbar_try(bar, parity)) return true;
-    if (it > 64) {
-      if (*abort_flag) return false;
-      __nanosleep(40);
-    }
+    if (it > 16 && *abort_flag) return false;
   }
   *abort_flag = 1;
   return false;

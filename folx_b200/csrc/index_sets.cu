@@ -1,0 +1,112 @@
+// Per-position index-set algebra on the device: sorted-unique union and intersection of the
+// sparse-Jacobian index maps (find_out_idx, folx/hessian.py:288-340; the per-position helpers
+// at 234-285).  Integer work, bit-exact: the host NumPy implementation is the default for the
+// small static maps of a traced function; this kernel serves large maps and is validated
+// against it value for value.
+//
+// One thread owns one position: it sorts its (<= FL_INDEX_SET_MAX) candidates in registers /
+// local memory (insertion sort -- the lists are short), removes duplicates and negatives, and
+// writes the ascending set padded with -1.  For the intersection every input list is first
+// deduplicated, so a value belongs to all n inputs iff it occurs n times in the merged list.
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kMaxSet = FL_INDEX_SET_MAX;
+
+__device__ __forceinline__ void insertion_sort(int32_t* v, int n) {
+  for (int i = 1; i < n; ++i) {
+    int32_t key = v[i];
+    int j = i - 1;
+    while (j >= 0 && v[j] > key) {
+      v[j + 1] = v[j];
+      --j;
+    }
+    v[j + 1] = key;
+  }
+}
+
+// in-place sorted unique of the non-negative entries; returns the count
+__device__ __forceinline__ int sorted_unique(int32_t* v, int n) {
+  insertion_sort(v, n);
+  int m = 0;
+  for (int i = 0; i < n; ++i)
+    if (v[i] >= 0 && (m == 0 || v[i] != v[m - 1])) v[m++] = v[i];
+  return m;
+}
+
+__global__ void __launch_bounds__(128)
+index_union_kernel(const int32_t* __restrict__ in, int64_t S, int K, int32_t* __restrict__ out,
+                   int m_cap, int32_t* __restrict__ counts) {
+  int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= S) return;
+  int32_t v[kMaxSet];
+  for (int k = 0; k < K; ++k) v[k] = in[s * K + k];
+  int m = sorted_unique(v, K);
+  counts[s] = m;
+  for (int j = 0; j < m_cap; ++j) out[s * m_cap + j] = j < m ? v[j] : -1;
+}
+
+__global__ void __launch_bounds__(128)
+index_intersection_kernel(const int32_t* __restrict__ in, int64_t S, int K_total, int n_inputs,
+                          const int32_t* __restrict__ seg_offsets, int32_t* __restrict__ out,
+                          int m_cap, int32_t* __restrict__ counts) {
+  int64_t s = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (s >= S) return;
+  int32_t v[kMaxSet];
+  int total = 0;
+  for (int i = 0; i < n_inputs; ++i) {
+    int b = seg_offsets[i], e = seg_offsets[i + 1];
+    int32_t* seg = v + total;
+    for (int k = b; k < e; ++k) seg[k - b] = in[s * K_total + k];
+    total += sorted_unique(seg, e - b);
+  }
+  insertion_sort(v, total);
+  int m = 0;
+  for (int i = 0; i + n_inputs <= total; ++i) {
+    if (v[i] == v[i + n_inputs - 1] && (i == 0 || v[i] != v[i - 1])) {
+      if (m < m_cap) out[s * m_cap + m] = v[i];
+      ++m;
+    }
+  }
+  counts[s] = m;
+  for (int j = m; j < m_cap; ++j) out[s * m_cap + j] = -1;
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_index_union(const int32_t* idx, int64_t S, int64_t K, int32_t* out,
+                                  int64_t m_cap, int32_t* counts, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(S >= 0 && K >= 0 && m_cap >= 0, FL_EBADSHAPE, "fl_index_union: bad sizes");
+  FL_REQUIRE(K <= kMaxSet, FL_EUNSUPPORTED, "fl_index_union: %lld candidates per position (max %d)",
+             (long long)K, kMaxSet);
+  if (S == 0) return FL_OK;
+  FL_REQUIRE((K == 0 || idx) && counts && (m_cap == 0 || out), FL_EBADSHAPE,
+             "fl_index_union: null pointer");
+  index_union_kernel<<<(unsigned)((S + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+      idx, S, (int)K, out, (int)m_cap, counts);
+  FL_CHECK_LAUNCH("fl_index_union launch");
+  return FL_OK;
+}
+
+extern "C" int32_t fl_index_intersection(const int32_t* idx, int64_t S, int64_t K_total,
+                                         int32_t n_inputs, const int32_t* seg_offsets,
+                                         int32_t* out, int64_t m_cap, int32_t* counts,
+                                         void* stream) {
+  using namespace fl;
+  FL_REQUIRE(S >= 0 && K_total >= 0 && m_cap >= 0 && n_inputs >= 1, FL_EBADSHAPE,
+             "fl_index_intersection: bad sizes");
+  FL_REQUIRE(K_total <= kMaxSet, FL_EUNSUPPORTED,
+             "fl_index_intersection: %lld candidates per position (max %d)", (long long)K_total,
+             kMaxSet);
+  if (S == 0) return FL_OK;
+  FL_REQUIRE((K_total == 0 || idx) && counts && seg_offsets && (m_cap == 0 || out), FL_EBADSHAPE,
+             "fl_index_intersection: null pointer");
+  index_intersection_kernel<<<(unsigned)((S + 127) / 128), 128, 0, (cudaStream_t)stream>>>(
+      idx, S, (int)K_total, n_inputs, seg_offsets, out, (int)m_cap, counts);
+  FL_CHECK_LAUNCH("fl_index_intersection launch");
+  return FL_OK;
+}

@@ -54,6 +54,12 @@ _SIGNATURES = {
     'fl_layernorm': (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_void_p]),
+    'fl_gather_rows': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
+                                 c_int64, c_int32, POINTER(c_int64), POINTER(c_int64),
+                                 POINTER(c_int64), c_void_p]),
+    'fl_index_union': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
+    'fl_index_intersection': (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p,
+                                        c_int64, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -1,0 +1,260 @@
+"""Host-side algebra of the sparse-Jacobian index maps (``x0_idx``), in NumPy.
+
+Index maps are static: they depend on the traced function, never on the data, so they are
+computed once on the host and only the resulting gather tables go to the device
+(reference: "we always compute sparsity patterns at compile time", folx/api.py:31-32).
+Every function here reproduces the integer results of a reference helper bit for bit and cites
+it; the algorithms themselves are this module's own.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import numpy as np
+
+from .api import JAC_DIM, FunctionFlags
+
+
+# ------------------------------------------------------------------------------------------
+# small shape helpers
+# ------------------------------------------------------------------------------------------
+def broadcast_except(arrs: Sequence[np.ndarray], axis: int = JAC_DIM) -> list[np.ndarray]:
+    """Broadcasts arrays against each other on every axis but ``axis`` (folx/utils.py:406-429)."""
+    nd = arrs[0].ndim
+    axis %= nd
+    pre = np.broadcast_shapes(*[a.shape[:axis] for a in arrs])
+    post = np.broadcast_shapes(*[a.shape[axis + 1 :] for a in arrs])
+    return [np.broadcast_to(a, (*pre, a.shape[axis], *post)) for a in arrs]
+
+
+def compact_repeated_dims_except(arr: np.ndarray, axis: int | None):
+    """Collapses to size 1 every axis (other than ``axis``) along which ``arr`` is constant.
+
+    Returns ``(arr, compacted_axes)``; reference: folx/utils.py:484-496.
+    """
+    skip = set() if axis is None else {axis % arr.ndim}
+    done = []
+    for d in range(arr.ndim):
+        if d in skip:
+            continue
+        head = np.take(arr, [0], axis=d)
+        if (head == arr).all():
+            arr = head
+            done.append(d)
+    return arr, tuple(done)
+
+
+def has_duplicate_x0_idx(x0_idx: np.ndarray | None) -> bool:
+    """True iff some position lists the same non-negative input twice (folx/hessian.py:71-84)."""
+    if x0_idx is None or x0_idx.shape[JAC_DIM] <= 1:
+        return False
+    s = np.sort(x0_idx, axis=JAC_DIM)
+    return bool(((s[1:] == s[:-1]) & (s[1:] >= 0)).any())
+
+
+def mask_varies_along(x0_idx: np.ndarray, axes: Sequence[int]) -> bool:
+    """Does the index map change along any of the given data axes? (folx/wrapped_functions.py:118-123)"""
+    for ax in axes:
+        if x0_idx.shape[ax] > 1 and not (np.take(x0_idx, [0], axis=ax) == x0_idx).all():
+            return True
+    return False
+
+
+# ------------------------------------------------------------------------------------------
+# per-position index sets
+# ------------------------------------------------------------------------------------------
+def per_position_sorted_unique(arr: np.ndarray) -> np.ndarray:
+    """Sorted unique non-negative values along the last axis, ``-1`` padded to the widest set.
+
+    ``arr``: ``(*S, K)`` -> ``(*S, M)``; same result as folx/hessian.py:234-258.
+    """
+    lead = arr.shape[:-1]
+    K = arr.shape[-1]
+    if K == 0:
+        return np.full((*lead, 0), -1, dtype=arr.dtype)
+    flat = np.sort(arr.reshape(-1, K), axis=-1)
+    first = flat >= 0
+    first[:, 1:] &= flat[:, 1:] != flat[:, :-1]
+    rank = np.cumsum(first, axis=-1) - 1
+    counts = first.sum(-1)
+    M = int(counts.max()) if counts.size else 0
+    out = np.full((flat.shape[0], M), -1, dtype=arr.dtype)
+    rows = np.broadcast_to(np.arange(flat.shape[0])[:, None], flat.shape)
+    out[rows[first], rank[first]] = flat[first]
+    return out.reshape(*lead, M)
+
+
+def per_position_intersection(masks: Sequence[np.ndarray]) -> np.ndarray:
+    """Sorted values present in EVERY input's set at a position, ``-1`` padded.
+
+    Inputs ``(*S, K_i)``; same result as folx/hessian.py:261-285.
+    """
+    n = len(masks)
+    uniq = [per_position_sorted_unique(m) for m in masks]
+    allv = np.concatenate(uniq, axis=-1)
+    lead = allv.shape[:-1]
+    T = allv.shape[-1]
+    if T < n:
+        return np.full((*lead, 0), -1, dtype=allv.dtype)
+    flat = np.sort(allv.reshape(-1, T), axis=-1)
+    # after per-input deduplication a value is common to all inputs iff it fills a run of n
+    hit = (flat[:, : T - n + 1] == flat[:, n - 1 :]) & (flat[:, : T - n + 1] >= 0)
+    rank = np.cumsum(hit, axis=-1) - 1
+    counts = hit.sum(-1)
+    M = int(counts.max()) if counts.size else 0
+    out = np.full((flat.shape[0], M), -1, dtype=allv.dtype)
+    rows = np.broadcast_to(np.arange(flat.shape[0])[:, None], hit.shape)
+    out[rows[hit], rank[hit]] = flat[:, : T - n + 1][hit]
+    return out.reshape(*lead, M)
+
+
+def find_out_idx(masks: Sequence[np.ndarray | None], x_shapes: Sequence[tuple[int, ...]],
+                 in_axes: Sequence[tuple[int, ...]], flags: FunctionFlags, threshold: int,
+                 dense_rows: Sequence[int] | None = None):
+    """Per-output-position input dependency set of an operation on sparse triplets.
+
+    ``masks[i]`` is argument i's index map ``(K_i, *x_shape_i)`` (broadcastable) or ``None`` for a
+    dense Jacobian with ``dense_rows[i]`` rows; ``in_axes[i]`` are the axes of argument i that the
+    operation consumes (empty for elementwise ops).  Returns ``(idx, dense_out)``: ``idx`` has shape
+    ``(M, *frame)`` where ``frame`` is the broadcast of the arguments' shapes without their
+    consumed axes and with axes that have size 1 in every argument dropped; it lists the sorted
+    union (intersection when the op is linear in one argument) of the inputs each position
+    depends on.  Reference: folx/hessian.py:288-340 (same outputs).
+    """
+    if all(m is None for m in masks):
+        return None, True
+    full = []
+    for i, (m, shp) in enumerate(zip(masks, x_shapes)):
+        if m is None:
+            k = dense_rows[i]
+            m = np.arange(k, dtype=np.int32).reshape(k, *([1] * len(shp)))
+        full.append(np.broadcast_to(m, (m.shape[0], *shp)))
+    max_size = max(int(np.sum(np.unique(m) >= 0)) for m in full)
+
+    # per argument: consumed axes join the Jacobian axis, the others are position axes
+    pos_parts, flat_parts = [], []
+    for m, shp, axes in zip(full, x_shapes, in_axes):
+        nd = len(shp)
+        axes = tuple(a % nd for a in axes) if nd else ()
+        keep = [a for a in range(nd) if a not in axes]
+        t = np.transpose(m, [1 + a for a in keep] + [0] + [1 + a for a in axes])
+        pshape = tuple(shp[a] for a in keep)
+        flat_parts.append(t.reshape(*pshape, -1))
+        pos_parts.append(pshape)
+    nd_pos = max(len(p) for p in pos_parts)
+    padded = [(1,) * (nd_pos - len(p)) + p for p in pos_parts]
+    frame_full = np.broadcast_shapes(*padded)
+    keep_dims = [d for d in range(nd_pos) if any(p[d] != 1 for p in padded)]
+    aligned = []
+    for t, p in zip(flat_parts, padded):
+        t = t.reshape(*p, t.shape[-1])
+        aligned.append(np.broadcast_to(t, (*frame_full, t.shape[-1])))
+
+    if FunctionFlags.LINEAR_IN_ONE in flags:
+        idx = per_position_intersection(aligned)
+    else:
+        idx = per_position_sorted_unique(np.concatenate(aligned, axis=-1))
+    idx = idx.reshape(*[frame_full[d] for d in keep_dims], idx.shape[-1])
+    idx = np.moveaxis(idx, -1, JAC_DIM).astype(np.int64)
+    M = idx.shape[JAC_DIM]
+    return idx, bool(M >= max_size or M > threshold)
+
+
+# ------------------------------------------------------------------------------------------
+# matching stored rows to a target frame, and the gather tables the device consumes
+# ------------------------------------------------------------------------------------------
+def get_index_mask(mask: np.ndarray, outputs: np.ndarray) -> np.ndarray:
+    """For each stored row and position, the slot of ``outputs`` holding the row's input, else -1.
+
+    ``mask``: ``(K, ...)``, ``outputs``: ``(M, ...)`` broadcastable; result ``(K, *broadcast)``.
+    The first matching slot wins; a ``-1`` row matches a ``-1`` padding slot exactly as in the
+    reference (folx/api.py:120-159: ``argmax`` over ``mask[..., None] == out_mask``).
+    """
+    outputs, mask = broadcast_except([np.asarray(outputs), np.asarray(mask)], JAC_DIM)
+    M = outputs.shape[0]
+    if M == 0:
+        return np.full(mask.shape, -1, dtype=np.int64)
+    eq = mask[:, None] == outputs[None, :]  # (K, M, ...)
+    first = eq.argmax(axis=1)
+    return np.where(eq.any(axis=1), first, -1).astype(np.int64)
+
+
+def gather_table(idx: np.ndarray, max_idx: int):
+    """Static gather table summing source rows into target rows.
+
+    ``idx``: ``(p, k)`` target row of every source row at every position (``-1``: drop).  Returns
+    ``take`` of shape ``(p, max_idx, n_slots)`` with source-row numbers (``-1``: empty slot): target
+    row t at position q is ``sum_s x[q, take[q, t, s]]``.  Rows sharing a target keep their source
+    order across the slots, which is the table of folx/utils.py:87-109.
+    """
+    p, k = idx.shape
+    if k == 0 or max_idx == 0:
+        return np.full((p, max_idx, 0), -1, dtype=np.int64)
+    valid = idx >= 0
+    # occurrence number of each row among earlier rows with the same target at its position
+    order = np.argsort(idx, axis=1, kind='stable')
+    st = np.take_along_axis(idx, order, axis=1)
+    new_run = np.ones((p, k), dtype=bool)
+    new_run[:, 1:] = st[:, 1:] != st[:, :-1]
+    start = np.maximum.accumulate(np.where(new_run, np.arange(k)[None, :], 0), axis=1)
+    slot_sorted = np.arange(k)[None, :] - start
+    ok = st >= 0
+    n_slots = int(slot_sorted[ok].max()) + 1 if ok.any() else 0
+    take = np.full((p, max_idx, n_slots), -1, dtype=np.int64)
+    rows = np.broadcast_to(np.arange(p)[:, None], (p, k))
+    take[rows[ok], st[ok], slot_sorted[ok]] = order[ok]
+    del valid
+    return take
+
+
+def reduction_frame(masks: Sequence[np.ndarray], axes: Sequence[int]):
+    """Union frame of a reduction over ``axes`` (data axes, shared by all arguments).
+
+    ``masks[i]``: ``(K_i, *shape)``.  Returns ``(out_mask, per_arg_targets)``: ``out_mask`` is
+    ``(M, *kept_shape)`` -- per kept position the sorted unique inputs any reduced element depends
+    on, ``-1`` padded -- and ``per_arg_targets[i]`` is ``(K_i, *shape)``, the row of ``out_mask`` each
+    stored row maps to.  Reference: folx/utils.py:499-588 (mask part).
+    """
+    masks = broadcast_except(list(masks), JAC_DIM)
+    nd = masks[0].ndim - 1
+    axes = tuple(sorted(a % nd for a in axes))
+    kept = [a for a in range(nd) if a not in axes]
+    kept_shape = tuple(masks[0].shape[1 + a] for a in kept)
+    cols = []
+    for m in masks:
+        t = np.transpose(m, [1 + a for a in kept] + [1 + a for a in axes] + [0])
+        cols.append(t.reshape(*kept_shape, -1))
+    union = per_position_sorted_unique(np.concatenate(cols, axis=-1))  # (*kept, M)
+    out_mask = np.moveaxis(union, -1, 0)
+    # frame with size-1 reduced axes so that it broadcasts against every argument
+    frame_shape = [1] * nd
+    for a, s in zip(kept, kept_shape):
+        frame_shape[a] = s
+    frame = out_mask.reshape(out_mask.shape[0], *frame_shape)
+    targets = [get_index_mask(m, frame) for m in masks]
+    return out_mask, targets
+
+
+def sum_outdeps(x0_idx: np.ndarray, axes: Sequence[int]):
+    """Output index map of ``sum`` over ``axes`` of a sparse triplet (folx/jvp.py:116-146).
+
+    ``x0_idx``: ``(K, *shape)``.  Returns ``(idx_out, targets)`` with ``idx_out``: ``(M, *kept_shape)``
+    sorted unique per kept position (``-1`` padded) and ``targets``: ``(K, *shape)`` the row of
+    ``idx_out`` every stored row is summed into.
+    """
+    out_mask, (targets,) = reduction_frame([x0_idx], axes)
+    return out_mask, targets
+
+
+def union_rows(masks: Sequence[np.ndarray]):
+    """Row-wise union used when sparse operands of an elementwise op are merged.
+
+    Concatenates the index maps along the Jacobian axis and keeps the distinct ROWS (whole
+    slices), in the lexicographic order ``np.unique(axis=0)`` produces; returns ``(result_mask,
+    inverse)`` where ``inverse[r]`` is the output row of concatenated input row ``r``.
+    Reference: folx/jvp.py:299-308.
+    """
+    cat = np.concatenate(broadcast_except(list(masks), JAC_DIM), axis=JAC_DIM)
+    result, inv = np.unique(cat, axis=JAC_DIM, return_inverse=True)
+    return result, inv.reshape(-1)

@@ -1,0 +1,161 @@
+"""Device side of the sparse-Jacobian bookkeeping: applying static gather tables.
+
+The index maps themselves are handled on the host (``masks.py``); this module turns them into
+int32 tables, uploads each table once (they are static per traced function) and launches
+``fl_gather_rows``.  Reference behaviour restated here: ``FwdJacobian.materialize_for_idx`` and
+``__add__`` (folx/api.py:58-118, 230-249).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import hashlib
+
+import numpy as np
+import torch
+
+from . import lib, masks
+from .api import JAC_DIM, FwdJacobian
+from .kernels import _ptr, _require_cuda, _stream
+
+_table_cache: dict[tuple, torch.Tensor] = {}
+
+
+def _device_table(take: np.ndarray, device) -> torch.Tensor:
+    """Uploads an int32 table once per (content, device)."""
+    arr = np.ascontiguousarray(take, dtype=np.int32)
+    key = (hashlib.blake2b(arr.tobytes(), digest_size=16).digest(), arr.shape, str(device))
+    t = _table_cache.get(key)
+    if t is None:
+        t = torch.from_numpy(arr).to(device)
+        _table_cache[key] = t
+    return t
+
+
+def _i64(vals):
+    return (ctypes.c_int64 * len(vals))(*[int(v) for v in vals])
+
+
+def gather_rows(data: torch.Tensor, take: np.ndarray, out_shape: tuple[int, ...],
+                table_shape: tuple[int, ...]) -> torch.Tensor:
+    """``out[o, pos] = sum_s data[take[o, s, tpos(pos)], pos]``.
+
+    ``data``: ``(k_in, *in_shape)`` broadcastable to ``out_shape``; ``take``: ``(k_out, n_slots,
+    *table_shape)`` with ``table_shape`` broadcastable to ``out_shape`` (size-1 axes: constant).
+    Returns ``(k_out, *out_shape)``.
+    """
+    _require_cuda(data)
+    nd = len(out_shape)
+    k_in = data.shape[0]
+    k_out, n_slots = take.shape[0], take.shape[1]
+    in_shape = (1,) * (nd - (data.ndim - 1)) + tuple(data.shape[1:])
+    tshape = (1,) * (nd - len(table_shape)) + tuple(table_shape)
+    if k_in > 0:
+        row = data[0].reshape(in_shape) if data[0].is_contiguous() else None
+        if row is None or (k_in > 1 and data.stride(0) < row.numel()):
+            data = data.contiguous()
+            row = data[0].reshape(in_shape)
+        in_strides = [0 if in_shape[d] == 1 else row.stride(d) for d in range(nd)]
+        in_row_stride = data.stride(0) if k_in > 1 else max(row.numel(), 1)
+    else:
+        in_strides, in_row_stride = [0] * nd, 1
+    # row-major strides of the table's position box; constant axes get stride 0
+    tstrides, acc = [0] * nd, 1
+    for d in range(nd - 1, -1, -1):
+        if tshape[d] != 1:
+            tstrides[d] = acc
+            acc *= tshape[d]
+    # merge axes beyond the kernel's limit is not needed for the shapes used here
+    if nd > 6:
+        raise ValueError('gather_rows: more than 6 position axes')
+    out = torch.empty((k_out, *out_shape), dtype=torch.float32, device=data.device)
+    N = int(np.prod(out_shape, dtype=np.int64))
+    table = _device_table(take.reshape(k_out, n_slots, -1), data.device)
+    lib.call('fl_gather_rows', _ptr(data), k_in, in_row_stride, _ptr(table), k_out, n_slots,
+             _ptr(out), max(N, 1), nd, _i64(out_shape), _i64(in_strides), _i64(tstrides),
+             _stream(data.device))
+    return out
+
+
+def materialize_for_idx(jac: FwdJacobian, idx: np.ndarray, max_idx: int | None = None) -> torch.Tensor:
+    """Rows of a sparse Jacobian summed into the frame ``idx`` (reference: folx/api.py:58-118).
+
+    ``idx[k, pos]`` is the target row of stored row ``k`` at ``pos`` (``-1``: drop); the result has
+    ``max_idx`` rows over the broadcast of ``data``'s and ``idx``'s positions.
+    """
+    assert jac.weak
+    idx = np.asarray(idx)
+    if max_idx is None:
+        max_idx = int(idx.max()) + 1
+    data = jac.data
+    k = data.shape[JAC_DIM]
+    idx_c, _ = masks.compact_repeated_dims_except(idx, JAC_DIM)
+    out_shape = tuple(np.broadcast_shapes(tuple(data.shape[1:]), idx.shape[1:]))
+    tshape = idx_c.shape[1:]
+    p = int(np.prod(tshape, dtype=np.int64))
+    flat = np.broadcast_to(idx_c, (k, *tshape)).reshape(k, p).T  # (p, k)
+    take = masks.gather_table(flat, max_idx)  # (p, max_idx, n_slots)
+    take = np.transpose(take, (1, 2, 0)).reshape(max_idx, take.shape[2], *tshape)
+    return gather_rows(data, take, out_shape, tshape)
+
+
+def dense_from_sparse(jac: FwdJacobian) -> torch.Tensor:
+    """Dense Jacobian with ``max_n + 1`` rows (reference: folx/api.py:182-190)."""
+    return jac.dense_array
+
+
+def _pad_rows(a: torch.Tensor, rows: int) -> torch.Tensor:
+    if a.shape[0] == rows:
+        return a
+    pad = torch.zeros((rows - a.shape[0], *a.shape[1:]), dtype=a.dtype, device=a.device)
+    return torch.cat([a, pad], dim=0)
+
+
+def add_jacobians(a: FwdJacobian, b: FwdJacobian) -> FwdJacobian:
+    """``a + b`` with the reference's rules (folx/api.py:230-249): dense if either is dense (the
+    shorter one zero-padded), data added when the index maps are equal, rows concatenated
+    otherwise (which is where duplicate indices at a position come from)."""
+    if not a.weak or not b.weak:
+        da, db = a.dense_array, b.dense_array
+        rows = max(da.shape[0], db.shape[0])
+        return FwdJacobian(_pad_rows(da, rows) + _pad_rows(db, rows))
+    if a.x0_idx.shape[JAC_DIM] == b.x0_idx.shape[JAC_DIM] and bool((a.x0_idx == b.x0_idx).all()):
+        return FwdJacobian(a.data + b.data, np.broadcast_arrays(a.x0_idx, b.x0_idx)[0])
+    shape = torch.broadcast_shapes(a.data.shape[1:], b.data.shape[1:])
+    da = a.data.expand(a.data.shape[0], *shape)
+    db = b.data.expand(b.data.shape[0], *shape)
+    ma, mb = masks.broadcast_except([a.x0_idx, b.x0_idx], JAC_DIM)
+    return FwdJacobian(torch.cat([da, db], dim=0), np.concatenate([ma, mb], axis=JAC_DIM))
+
+
+def index_union_device(idx: np.ndarray, device) -> np.ndarray:
+    """``masks.per_position_sorted_unique`` computed by the device kernel (same result)."""
+    lead, K = idx.shape[:-1], idx.shape[-1]
+    S = int(np.prod(lead, dtype=np.int64))
+    if K == 0:
+        return np.full((*lead, 0), -1, dtype=idx.dtype)
+    d_in = torch.from_numpy(np.ascontiguousarray(idx.reshape(S, K), dtype=np.int32)).to(device)
+    d_out = torch.empty((S, K), dtype=torch.int32, device=device)
+    d_cnt = torch.empty((S,), dtype=torch.int32, device=device)
+    lib.call('fl_index_union', _ptr(d_in), S, K, _ptr(d_out), K, _ptr(d_cnt), _stream(device))
+    M = int(d_cnt.max().item()) if S else 0
+    return d_out[:, :M].cpu().numpy().astype(idx.dtype).reshape(*lead, M)
+
+
+def index_intersection_device(parts: list[np.ndarray], device) -> np.ndarray:
+    """``masks.per_position_intersection`` computed by the device kernel (same result)."""
+    lead = parts[0].shape[:-1]
+    S = int(np.prod(lead, dtype=np.int64))
+    offs = np.cumsum([0] + [p.shape[-1] for p in parts]).astype(np.int32)
+    K = int(offs[-1])
+    if K < len(parts):
+        return np.full((*lead, 0), -1, dtype=parts[0].dtype)
+    cat = np.concatenate([p.reshape(S, -1) for p in parts], axis=-1)
+    d_in = torch.from_numpy(np.ascontiguousarray(cat, dtype=np.int32)).to(device)
+    d_off = torch.from_numpy(offs).to(device)
+    d_out = torch.empty((S, K), dtype=torch.int32, device=device)
+    d_cnt = torch.empty((S,), dtype=torch.int32, device=device)
+    lib.call('fl_index_intersection', _ptr(d_in), S, K, len(parts), _ptr(d_off), _ptr(d_out), K,
+             _ptr(d_cnt), _stream(device))
+    M = int(d_cnt.max().item()) if S else 0
+    return d_out[:, :M].cpu().numpy().astype(parts[0].dtype).reshape(*lead, M)

@@ -81,6 +81,7 @@ int32_t fl_elementwise(int32_t op, float param,
  * triplets (folx/wrapped_functions.py:364-383): the jvp of folx/jvp.py:273-317 and the Hessian
  * terms of folx/hessian.py:177-188 (mul: 2 sum_k Ja_k Jb_k) and folx/custom_hessian.py:35-59
  * (div: -2/b^2 sum_k Ja_k Jb_k + 2a/b^3 sum_k Jb_k^2).
+ * Either operand may be a constant array: pass NULL for its jac and lap (zero derivatives).
  * Broadcasting: operand b may be broadcast along the position axis with period `b_period`
  * (position i of b is i % b_period; b_period == N means no broadcast); its buffers then hold
  * b_period positions.
@@ -147,6 +148,51 @@ int32_t fl_layernorm(const float* x, const float* jac, const float* lap,
                      float* y, float* jac_y, float* lap_y,
                      int64_t P, int64_t F, int64_t K, int64_t jac_stride, int64_t jac_y_stride,
                      void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sparse Jacobians: moving rows into another row frame with a static table.
+ *     out[o, pos] = sum_{s < n_slots} in[take[o, s, tpos(pos)], ipos(pos)]      (take < 0: nothing)
+ * This one operation replaces materialize_by_gather / segment_sum (folx/utils.py:71-114), i.e.
+ * FwdJacobian.materialize_for_idx and dense_array (folx/api.py:58-118, 182-190), the row
+ * alignment of reductions (get_jacobian_for_reduction, folx/utils.py:499-588), the sparse sum
+ * (sparse_sum_jvp and _factorized_dense_row_sum, folx/jvp.py:37-176) and the merge of rows that
+ * share an index map (folx/jvp.py:305-317).  The table is built on the host from the static
+ * index maps (folx_b200/masks.py) and uploaded once.
+ *
+ *   positions form an `ndim`-dimensional row-major box `shape` (ndim <= FL_GATHER_MAX_DIMS);
+ *   ipos(pos) = sum_d i_d * in_strides[d]   (stride 0: the input is broadcast along axis d)
+ *   tpos(pos) = sum_d i_d * table_strides[d] (stride 0: the table is constant along axis d)
+ *   jac_in : k_in rows, in_row_stride apart;  jac_out : k_out rows of prod(shape), out_row_stride apart
+ *   take   : int32 [k_out][n_slots][table positions], DEVICE pointer
+ *   shape / in_strides / table_strides : HOST pointers to `ndim` int64 values
+ * ------------------------------------------------------------------------------------------- */
+#define FL_GATHER_MAX_DIMS 6
+
+int32_t fl_gather_rows(const float* jac_in, int64_t k_in, int64_t in_row_stride,
+                       const int32_t* take, int64_t k_out, int64_t n_slots,
+                       float* jac_out, int64_t out_row_stride,
+                       int32_t ndim, const int64_t* shape, const int64_t* in_strides,
+                       const int64_t* table_strides, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Index-set algebra of find_out_idx on the device (folx/hessian.py:234-340), bit-exact.
+ *   fl_index_union:        per position, the ascending distinct non-negative values of its K
+ *                          candidates (_per_position_sorted_unique, folx/hessian.py:234-258)
+ *   fl_index_intersection: per position, the ascending values present in every one of n_inputs
+ *                          candidate lists (_per_position_intersection, folx/hessian.py:261-285);
+ *                          list i occupies columns seg_offsets[i] .. seg_offsets[i+1]-1
+ * idx : int32 [S][K] (device); out : int32 [S][m_cap], -1 padded (sets wider than m_cap are
+ * truncated); counts : int32 [S], the true size of every set (the caller takes M = max(counts)
+ * and re-runs with a larger m_cap if M > m_cap).  K (K_total) <= FL_INDEX_SET_MAX.
+ * ------------------------------------------------------------------------------------------- */
+#define FL_INDEX_SET_MAX 256
+
+int32_t fl_index_union(const int32_t* idx, int64_t S, int64_t K,
+                       int32_t* out, int64_t m_cap, int32_t* counts, void* stream);
+
+int32_t fl_index_intersection(const int32_t* idx, int64_t S, int64_t K_total, int32_t n_inputs,
+                              const int32_t* seg_offsets, int32_t* out, int64_t m_cap,
+                              int32_t* counts, void* stream);
 
 #ifdef __cplusplus
 }

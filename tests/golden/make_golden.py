@@ -1,0 +1,144 @@
+"""Generates the committed golden fixtures of the integer (index-map) paths.
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+Part 1 runs the reference's own pure-NumPy helpers (loaded by ``oracle.refmasks`` from the
+reference checkout, nothing copied) on seeded inputs and stores inputs and outputs in
+``index_helpers.npz``.  Part 2 writes ``find_out_idx_cases.json``: the literal known-answer cases
+of the reference's test/test_find_out_idx.py:58-235 (inputs and expected outputs as data).
+The tests read only the two generated files.
+"""
+
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from oracle import refmasks  # noqa: E402
+
+
+def helper_fixtures(ref):
+    rng = np.random.default_rng(20240611)
+    out = {}
+    # sorted unique
+    shapes = [((5, 7), 9), ((3, 4, 6), 5), ((1, 3), 4), ((6, 0), 3), ((4, 8), 2), ((2, 2, 2, 5), 20)]
+    for i, (shape, vmax) in enumerate(shapes):
+        a = rng.integers(-1, vmax, size=shape).astype(np.int32)
+        out[f'su{i}_in'] = a
+        out[f'su{i}_out'] = ref._per_position_sorted_unique(a)
+    a = -np.ones((3, 4), dtype=np.int32)
+    out['su_neg_in'] = a
+    out['su_neg_out'] = ref._per_position_sorted_unique(a)
+    # intersection
+    cases = [((4, 5), [3, 4], 6), ((2, 3, 2), [2, 2, 3], 4), ((6,), [5, 1], 3), ((3, 3), [2, 0], 5)]
+    for i, (lead, ks, vmax) in enumerate(cases):
+        ms = [rng.integers(-1, vmax, size=(*lead, k)).astype(np.int32) for k in ks]
+        for j, m in enumerate(ms):
+            out[f'is{i}_in{j}'] = m
+        out[f'is{i}_n'] = np.array(len(ms))
+        out[f'is{i}_out'] = ref._per_position_intersection(ms)
+    # duplicates
+    for i in range(6):
+        a = rng.integers(-1, 6, size=(rng.integers(1, 4), 5, 3)).astype(np.int32)
+        out[f'dup{i}_in'] = a
+        out[f'dup{i}_out'] = np.array(ref._has_duplicate_x0_idx(a))
+    # compaction of repeated axes
+    base = rng.integers(0, 9, size=(3, 1, 4, 1)).astype(np.int32)
+    arrs = [np.broadcast_to(base, (3, 5, 4, 2)).copy(), rng.integers(0, 3, size=(2, 3, 4)).astype(np.int32),
+            np.zeros((4, 2, 2), dtype=np.int32)]
+    for i, a in enumerate(arrs):
+        c, axes = ref.compact_repeated_dims_except(a, 0)
+        out[f'cr{i}_in'] = a
+        out[f'cr{i}_out'] = c
+        out[f'cr{i}_axes'] = np.array(axes, dtype=np.int64)
+    # static gather: inputs, targets and the summed result (or "no table" when the reference
+    # prefers a runtime scatter)
+    for i, (p, k, mx, r) in enumerate([(4, 6, 3, 5), (3, 5, 8, 2), (2, 9, 2, 3), (5, 3, 3, 1), (3, 4, 40, 2)]):
+        x = rng.standard_normal((p, k, r))
+        idx = rng.integers(-1, mx, size=(p, k)).astype(np.int64)
+        res = ref.materialize_by_gather(x, idx, mx)
+        out[f'mg{i}_x'] = x
+        out[f'mg{i}_idx'] = idx
+        out[f'mg{i}_max'] = np.array(mx)
+        out[f'mg{i}_none'] = np.array(res is None)
+        # the defining sum, for the cases the reference hands to segment_sum instead
+        want = np.zeros((p, mx, r))
+        for q in range(p):
+            for kk in range(k):
+                if idx[q, kk] >= 0:
+                    want[q, idx[q, kk]] += x[q, kk]
+        if res is not None:
+            np.testing.assert_allclose(res, want, atol=1e-12)
+        out[f'mg{i}_out'] = want
+    # mask alignment used by find_out_idx
+    m = rng.integers(-1, 7, size=(2, 4, 3)).astype(np.int32)
+    out['al0_in'] = m
+    out['al0_out'] = ref._align_mask_for_broadcast(m, [1, 1], 2)
+    out['al1_out'] = ref._align_mask_for_broadcast(m, [None, 2], 2)
+    # slogdet factor tables (shape and cost are what the reference's tests pin)
+    mask = np.full((3, 4, 4), -1, dtype=np.int64)
+    for e in range(4):
+        mask[:, e, :] = 3 * e + np.arange(3)[:, None]
+    for per_entry in (False, True):
+        cost, (take, cols, rows, coords, pe) = ref._factor_tables(mask, per_entry)
+        tag = 'pe' if per_entry else 'row'
+        out[f'ft_{tag}_mask'] = mask
+        out[f'ft_{tag}_cost'] = np.array(cost)
+        out[f'ft_{tag}_take'] = take
+        out[f'ft_{tag}_cols'] = cols
+        out[f'ft_{tag}_rows'] = rows
+        out[f'ft_{tag}_coords'] = coords
+    return out
+
+
+# Known-answer cases of the reference's test/test_find_out_idx.py (line numbers in `src`).
+FIND_OUT_IDX_CASES = [
+    {'src': '65-70', 'masks': [[[0, 1, 2], [3, 4, -1]]], 'in_axes': [[]], 'flags': 'GENERAL', 'threshold': 100,
+     'expected': [[0, 1, 2], [3, 4, -1]], 'dense': False},
+    {'src': '73-84', 'masks': [[[0, 1, 2], [3, 4, -1]], [[0, 1, 5], [6, 4, -1]]], 'in_axes': [[], []],
+     'flags': 'GENERAL', 'threshold': 100, 'expected': [[0, 1, 2], [3, 4, 5], [6, -1, -1]], 'dense': False},
+    {'src': '87-100', 'masks': [[[0, 1, 2], [3, 4, -1]], [[0, 1, 5], [6, 4, -1]]], 'in_axes': [[], []],
+     'flags': 'LINEAR_IN_ONE', 'threshold': 100, 'expected': [[0, 1, -1], [-1, 4, -1]], 'dense': False},
+    {'src': '103-112', 'masks': [[[[0, 1, 2], [10, 11, 12]], [[3, 4, -1], [13, 14, -1]]]], 'in_axes': [[]],
+     'flags': 'GENERAL', 'threshold': 100,
+     'expected': [[[0, 1, 2], [10, 11, 12]], [[3, 4, -1], [13, 14, -1]]], 'dense': False},
+    {'src': '115-132', 'masks': [[[[0], [1], [2]], [[3], [4], [-1]]], [[[5, 6, 7]], [[-1, 8, 9]]]],
+     'in_axes': [[], []], 'flags': 'GENERAL', 'threshold': 100, 'expected_shape_tail': [3, 3],
+     'expected_sets': {'0,0': [0, 3, 5], '2,2': [2, 7, 9]}, 'dense': False},
+    {'src': '135-142', 'masks': [[[0, 1], [2, 3]]], 'in_axes': [[]], 'flags': 'GENERAL', 'threshold': 1,
+     'expected_rows': 2, 'dense': True},
+    {'src': '145-157', 'masks': [[[0, 0, 0, 0], [1, 1, 1, 1], [2, 2, 2, 2], [3, 3, 3, 3]]], 'in_axes': [[]],
+     'flags': 'GENERAL', 'threshold': 100, 'expected_rows': 4, 'dense': True},
+    {'src': '160-167', 'masks': [[[-1, -1, -1], [-1, -1, -1]]], 'in_axes': [[]], 'flags': 'GENERAL',
+     'threshold': 100, 'expected_shape': [0, 3], 'dense': True},
+    {'src': '170-176', 'masks': [[[0, 1, 2], [0, 1, 2]]], 'in_axes': [[]], 'flags': 'GENERAL', 'threshold': 100,
+     'expected': [[0, 1, 2]], 'dense': False},
+    {'src': '179-194', 'arange_mask': [2, 4, 3], 'x_shapes': [[4, 3]], 'in_axes': [[0]], 'flags': 'GENERAL',
+     'threshold': 100, 'expected_shape': [8, 3], 'expected_col0': [0, 3, 6, 9, 12, 15, 18, 21], 'dense': False},
+    {'src': '197-212', 'masks': [[[0, 1], [2, -1]], [[1, 3], [4, -1]], [[5, 1], [-1, -1]]],
+     'in_axes': [[], [], []], 'flags': 'GENERAL', 'threshold': 100,
+     'expected': [[0, 1], [1, 3], [2, -1], [4, -1], [5, -1]], 'dense': True},
+    {'src': '215-227', 'masks': [[[0, 1], [2, -1]], [[1, 3], [0, -1]], [[5, 1], [0, -1]]],
+     'in_axes': [[], [], []], 'flags': 'LINEAR_IN_ONE', 'threshold': 100, 'expected': [[0, -1]], 'dense': False},
+    {'src': '230-242', 'masks': [[[0, 1], [2, 3]], [[10, 11], [12, 13], [-1, -1]]], 'in_axes': [[], []],
+     'flags': 'GENERAL', 'threshold': 100, 'expected': [[0, 1], [2, 3], [10, 11], [12, 13]], 'dense': True},
+]
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    ref = refmasks.load(ref_root)
+    np.savez_compressed(os.path.join(HERE, 'index_helpers.npz'), **helper_fixtures(ref))
+    with open(os.path.join(HERE, 'find_out_idx_cases.json'), 'w') as f:
+        json.dump({'source': 'test/test_find_out_idx.py of the reference (known-answer cases)',
+                   'cases': FIND_OUT_IDX_CASES}, f, indent=1)
+    print('wrote index_helpers.npz and find_out_idx_cases.json')
+
+
+if __name__ == '__main__':
+    main()
