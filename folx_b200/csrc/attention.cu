@@ -1,0 +1,396 @@
+// Fused forward-Laplacian rule of multi-head self attention.
+//
+// One CTA owns one (walker, head): q, k, v (n x d each), the softmax matrix p (n x n) and the
+// Laplacian accumulator stay on chip while the R Jacobian rows of q, k, v stream through shared
+// memory once (cp.async, double buffered) and the R rows of the output Jacobian are written once.
+// The reference does the same walk inside a Pallas/Triton program per (batch, q-block, head)
+// (mhsa_forward_laplacian_kernel, folx/experimental/pallas/attention/forward_laplacian.py:349-487);
+// the terms below are its terms regrouped around p_r = dp/dx_r:
+//     s_r = q_r k^T + q k_r^T,  c_r = s_r - rowsum(p s_r),  p_r = p c_r,
+//     o_r = p_r v + p v_r
+//     lap_o = [same formula with the Laplacian rows in place of the Jacobian rows]
+//           + sum_r m_r { [p_r c_r + p (2 q_r k_r^T - rowsum(p_r s_r) - rowsum(2 p q_r k_r^T))] v + 2 p_r v_r }
+// Masking follows the reference (lines 389-407, 421-424): scores of masked pairs are -1e20,
+// Jacobian / Laplacian rows of masked electrons are read as zero, m_r = input_mask[r, walker]
+// gates the Hessian term of coordinate r only.
+// Per Jacobian row: three n x n x d and four n x d x n contractions on the CUDA cores (fp32).
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int DP = 68;        // smem pitch of an (n x 64) tile, floats
+constexpr int DMAX = 64;      // largest head dimension
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  int sz = valid ? 16 : 0;  // size 0: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ float dot4(float4 a, float4 b) {
+  return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
+}
+
+__device__ __forceinline__ float half_warp_sum(float v) {
+  // the 16 threads that share a score row sit in one half-warp
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float half_warp_max(float v) {
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+struct Args {
+  const float *q, *qj, *ql, *k, *kj, *kl, *v, *vj, *vl;
+  const uint8_t *mask, *input_mask;
+  float *o, *oj, *ol;
+  int B, n, H, d, R;
+  int64_t qjs, kjs, vjs, ojs;
+};
+
+// Loads one (n x d) tile of a (B, n, H, d) tensor into smem rows [NP][DP]; rows >= n, columns >= d
+// and rows whose electron is masked (when zero_masked) are zero.  VEC: 16-byte cp.async.
+template <int NP, bool VEC>
+__device__ __forceinline__ void load_tile(float* dst, const float* src, const Args& a, int b, int h,
+                                          const uint8_t* rowmask, bool zero_masked) {
+  const int64_t row_stride = (int64_t)a.H * a.d;
+  const float* base = src + ((int64_t)b * a.n * a.H + h) * a.d;
+  if constexpr (VEC) {
+    for (int e = threadIdx.x; e < NP * (DMAX / 4); e += kThreads) {
+      int i = e / (DMAX / 4), c = (e % (DMAX / 4)) * 4;
+      bool ok = i < a.n && c < a.d && !(zero_masked && rowmask && !rowmask[i]);
+      cp_async16(dst + i * DP + c, ok ? base + i * row_stride + c : src, ok);
+    }
+  } else {
+    for (int e = threadIdx.x; e < NP * DMAX; e += kThreads) {
+      int i = e / DMAX, c = e % DMAX;
+      bool ok = i < a.n && c < a.d && !(zero_masked && rowmask && !rowmask[i]);
+      dst[i * DP + c] = ok ? base[i * row_stride + c] : 0.f;
+    }
+  }
+}
+
+template <int NP, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+mhsa_kernel(Args a) {
+  constexpr int T = NP / 16;  // per-thread tile edge in the score phase
+  constexpr int PP = NP + 1;  // pitch of the n x n matrices
+  extern __shared__ __align__(16) float smem[];
+  float* Q = smem;                 // [NP][DP]
+  float* Kx = Q + NP * DP;
+  float* V = Kx + NP * DP;
+  float* buf = V + NP * DP;        // 2 x {QR, KR, VR}
+  float* Pm = buf + 6 * NP * DP;   // [NP][PP]
+  float* PR = Pm + NP * PP;
+  float* TV = PR + NP * PP;
+  __shared__ uint8_t rowmask_s[64];
+
+  const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
+  const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
+  const int n = a.n, d = a.d;
+
+  if (threadIdx.x < NP)
+    rowmask_s[threadIdx.x] = threadIdx.x < n ? (a.mask ? a.mask[(int64_t)b * n + threadIdx.x] : 1) : 0;
+  __syncthreads();
+
+  load_tile<NP, VEC>(Q, a.q, a, b, h, rowmask_s, false);
+  load_tile<NP, VEC>(Kx, a.k, a, b, h, rowmask_s, false);
+  load_tile<NP, VEC>(V, a.v, a, b, h, rowmask_s, false);
+  // first streamed row: the Laplacians (treated like a Jacobian row without a Hessian term)
+  load_tile<NP, VEC>(buf + 0 * NP * DP, a.ql, a, b, h, rowmask_s, true);
+  load_tile<NP, VEC>(buf + 1 * NP * DP, a.kl, a, b, h, rowmask_s, true);
+  load_tile<NP, VEC>(buf + 2 * NP * DP, a.vl, a, b, h, rowmask_s, true);
+  if constexpr (VEC) { cp_async_commit(); cp_async_wait<0>(); }
+  __syncthreads();
+
+  // ---------------- softmax matrix p (kept in registers in the score layout and in smem) --------
+  float p[T][T];
+  {
+    float s[T][T];
+#pragma unroll
+    for (int x = 0; x < T; ++x)
+#pragma unroll
+      for (int y = 0; y < T; ++y) s[x][y] = 0.f;
+    for (int l = 0; l < DMAX; l += 4) {
+      float4 qv[T], kv[T];
+#pragma unroll
+      for (int x = 0; x < T; ++x) qv[x] = *reinterpret_cast<const float4*>(Q + (ty + 16 * x) * DP + l);
+#pragma unroll
+      for (int y = 0; y < T; ++y) kv[y] = *reinterpret_cast<const float4*>(Kx + (tx + 16 * y) * DP + l);
+#pragma unroll
+      for (int x = 0; x < T; ++x)
+#pragma unroll
+        for (int y = 0; y < T; ++y) s[x][y] += dot4(qv[x], kv[y]);
+    }
+#pragma unroll
+    for (int x = 0; x < T; ++x) {
+      const int i = ty + 16 * x;
+      float mx = -3.0e38f;
+#pragma unroll
+      for (int y = 0; y < T; ++y) {
+        const int j = tx + 16 * y;
+        if (j < n) {
+          if (!(rowmask_s[i] && rowmask_s[j])) s[x][y] = -1e20f;
+          mx = fmaxf(mx, s[x][y]);
+        }
+      }
+      mx = half_warp_max(mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int y = 0; y < T; ++y) {
+        const int j = tx + 16 * y;
+        p[x][y] = j < n ? expf(s[x][y] - mx) : 0.f;
+        sum += p[x][y];
+      }
+      sum = half_warp_sum(sum);
+      const float inv = 1.0f / sum;
+#pragma unroll
+      for (int y = 0; y < T; ++y) {
+        p[x][y] *= inv;
+        Pm[i * PP + tx + 16 * y] = p[x][y];
+      }
+    }
+  }
+  __syncthreads();
+
+  // o = p v, in the output layout: rows ty + 16 x, columns 4 tx .. 4 tx + 3
+  {
+    float4 acc[T];
+#pragma unroll
+    for (int x = 0; x < T; ++x) acc[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < n; ++j) {
+      const float4 vv = *reinterpret_cast<const float4*>(V + j * DP + 4 * tx);
+#pragma unroll
+      for (int x = 0; x < T; ++x) {
+        const float pv = Pm[(ty + 16 * x) * PP + j];
+        acc[x].x = fmaf(pv, vv.x, acc[x].x); acc[x].y = fmaf(pv, vv.y, acc[x].y);
+        acc[x].z = fmaf(pv, vv.z, acc[x].z); acc[x].w = fmaf(pv, vv.w, acc[x].w);
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < T; ++x) {
+      const int i = ty + 16 * x;
+      if (i < n) {
+        float* dst = a.o + (((int64_t)b * n + i) * a.H + h) * d + 4 * tx;
+        const float vals[4] = {acc[x].x, acc[x].y, acc[x].z, acc[x].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (4 * tx + c < d) dst[c] = vals[c];
+      }
+    }
+  }
+
+  float4 lap_acc[T];
+#pragma unroll
+  for (int x = 0; x < T; ++x) lap_acc[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+  // ---------------- stream the Laplacian row (it == 0) and the R Jacobian rows -------------------
+  for (int it = 0; it <= a.R; ++it) {
+    const int cur = it & 1;
+    if (it < a.R) {
+      // prefetch Jacobian row r = it into the other buffer
+      float* nb = buf + (cur ^ 1) * 3 * NP * DP;
+      load_tile<NP, VEC>(nb + 0 * NP * DP, a.qj + (int64_t)it * a.qjs, a, b, h, rowmask_s, true);
+      load_tile<NP, VEC>(nb + 1 * NP * DP, a.kj + (int64_t)it * a.kjs, a, b, h, rowmask_s, true);
+      load_tile<NP, VEC>(nb + 2 * NP * DP, a.vj + (int64_t)it * a.vjs, a, b, h, rowmask_s, true);
+      if constexpr (VEC) cp_async_commit();
+    }
+    if constexpr (VEC) {
+      if (it < a.R) cp_async_wait<1>(); else cp_async_wait<0>();
+    }
+    __syncthreads();
+    const float* QR = buf + cur * 3 * NP * DP;
+    const float* KR = QR + NP * DP;
+    const float* VR = KR + NP * DP;
+    const bool hess = it > 0;
+
+    // ---- score phase: q_r k^T, q k_r^T, q_r k_r^T ----
+    {
+      float s1[T][T], s2[T][T], s3[T][T];
+#pragma unroll
+      for (int x = 0; x < T; ++x)
+#pragma unroll
+        for (int y = 0; y < T; ++y) { s1[x][y] = 0.f; s2[x][y] = 0.f; s3[x][y] = 0.f; }
+      for (int l = 0; l < DMAX; l += 4) {
+        float4 qv[T], qrv[T], kv[T], krv[T];
+#pragma unroll
+        for (int x = 0; x < T; ++x) {
+          qv[x] = *reinterpret_cast<const float4*>(Q + (ty + 16 * x) * DP + l);
+          qrv[x] = *reinterpret_cast<const float4*>(QR + (ty + 16 * x) * DP + l);
+        }
+#pragma unroll
+        for (int y = 0; y < T; ++y) {
+          kv[y] = *reinterpret_cast<const float4*>(Kx + (tx + 16 * y) * DP + l);
+          krv[y] = *reinterpret_cast<const float4*>(KR + (tx + 16 * y) * DP + l);
+        }
+#pragma unroll
+        for (int x = 0; x < T; ++x)
+#pragma unroll
+          for (int y = 0; y < T; ++y) {
+            s1[x][y] += dot4(qrv[x], kv[y]);
+            s2[x][y] += dot4(qv[x], krv[y]);
+            if (hess) s3[x][y] += dot4(qrv[x], krv[y]);
+          }
+      }
+#pragma unroll
+      for (int x = 0; x < T; ++x) {
+        const int i = ty + 16 * x;
+        float sr[T], r1 = 0.f;
+#pragma unroll
+        for (int y = 0; y < T; ++y) {
+          sr[y] = s1[x][y] + s2[x][y];
+          r1 = fmaf(p[x][y], sr[y], r1);
+        }
+        r1 = half_warp_sum(r1);  // rowsum(p s_r)
+        float pr[T], r2 = 0.f, r3 = 0.f;
+#pragma unroll
+        for (int y = 0; y < T; ++y) {
+          pr[y] = p[x][y] * (sr[y] - r1);
+          r2 = fmaf(pr[y], sr[y], r2);
+          r3 = fmaf(p[x][y], 2.0f * s3[x][y], r3);
+        }
+        if (hess) {
+          r2 = half_warp_sum(r2);  // rowsum(p_r s_r)
+          r3 = half_warp_sum(r3);  // rowsum(2 p q_r k_r^T)
+        }
+#pragma unroll
+        for (int y = 0; y < T; ++y) {
+          const int j = tx + 16 * y;
+          PR[i * PP + j] = pr[y];
+          if (hess) TV[i * PP + j] = pr[y] * (sr[y] - r1) + p[x][y] * (2.0f * s3[x][y] - r2 - r3);
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- value phase: o_r = p_r v + p v_r ; hessian term = tv v + 2 p_r v_r ----
+    {
+      float4 oj[T], ct[T];
+#pragma unroll
+      for (int x = 0; x < T; ++x) {
+        oj[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+        ct[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      for (int j = 0; j < n; ++j) {
+        const float4 vv = *reinterpret_cast<const float4*>(V + j * DP + 4 * tx);
+        const float4 vr = *reinterpret_cast<const float4*>(VR + j * DP + 4 * tx);
+#pragma unroll
+        for (int x = 0; x < T; ++x) {
+          const int i = ty + 16 * x;
+          const float prv = PR[i * PP + j], pv = Pm[i * PP + j];
+          oj[x].x = fmaf(prv, vv.x, fmaf(pv, vr.x, oj[x].x));
+          oj[x].y = fmaf(prv, vv.y, fmaf(pv, vr.y, oj[x].y));
+          oj[x].z = fmaf(prv, vv.z, fmaf(pv, vr.z, oj[x].z));
+          oj[x].w = fmaf(prv, vv.w, fmaf(pv, vr.w, oj[x].w));
+          if (hess) {
+            const float tv = TV[i * PP + j], p2 = 2.0f * prv;
+            ct[x].x = fmaf(tv, vv.x, fmaf(p2, vr.x, ct[x].x));
+            ct[x].y = fmaf(tv, vv.y, fmaf(p2, vr.y, ct[x].y));
+            ct[x].z = fmaf(tv, vv.z, fmaf(p2, vr.z, ct[x].z));
+            ct[x].w = fmaf(tv, vv.w, fmaf(p2, vr.w, ct[x].w));
+          }
+        }
+      }
+      if (!hess) {
+#pragma unroll
+        for (int x = 0; x < T; ++x) lap_acc[x] = oj[x];
+      } else {
+        const int r = it - 1;
+        const float m = a.input_mask ? (a.input_mask[(int64_t)r * a.B + b] ? 1.f : 0.f) : 1.f;
+#pragma unroll
+        for (int x = 0; x < T; ++x) {
+          lap_acc[x].x = fmaf(m, ct[x].x, lap_acc[x].x); lap_acc[x].y = fmaf(m, ct[x].y, lap_acc[x].y);
+          lap_acc[x].z = fmaf(m, ct[x].z, lap_acc[x].z); lap_acc[x].w = fmaf(m, ct[x].w, lap_acc[x].w);
+          const int i = ty + 16 * x;
+          if (i < n) {
+            float* dst = a.oj + (int64_t)r * a.ojs + (((int64_t)b * n + i) * a.H + h) * d + 4 * tx;
+            if (VEC) {
+              if (4 * tx < d) __stcs(reinterpret_cast<float4*>(dst), oj[x]);
+            } else {
+              const float vals[4] = {oj[x].x, oj[x].y, oj[x].z, oj[x].w};
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                if (4 * tx + c < d) dst[c] = vals[c];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int x = 0; x < T; ++x) {
+    const int i = ty + 16 * x;
+    if (i < n) {
+      float* dst = a.ol + (((int64_t)b * n + i) * a.H + h) * d + 4 * tx;
+      const float vals[4] = {lap_acc[x].x, lap_acc[x].y, lap_acc[x].z, lap_acc[x].w};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (4 * tx + c < d) dst[c] = vals[c];
+    }
+  }
+}
+
+template <int NP>
+int32_t launch(const Args& a, bool vec, cudaStream_t st) {
+  constexpr size_t smem = (size_t)(9 * NP * DP + 3 * NP * (NP + 1)) * sizeof(float);
+  auto kv = mhsa_kernel<NP, true>;
+  auto ks = mhsa_kernel<NP, false>;
+  static bool attr = false;
+  if (!attr) {
+    FL_CUDA(cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    FL_CUDA(cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  const int64_t blocks = (int64_t)a.B * a.H;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_mhsa: too many (walker, head) pairs");
+  if (vec) kv<<<(unsigned)blocks, kThreads, smem, st>>>(a);
+  else ks<<<(unsigned)blocks, kThreads, smem, st>>>(a);
+  FL_CHECK_LAUNCH("fl_mhsa launch");
+  return FL_OK;
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_lap, const float* k,
+                           const float* k_jac, const float* k_lap, const float* v,
+                           const float* v_jac, const float* v_lap, const uint8_t* mask,
+                           const uint8_t* input_mask, float* o, float* o_jac, float* o_lap,
+                           int64_t B, int64_t n, int64_t H, int64_t d, int64_t R,
+                           int64_t q_jac_stride, int64_t k_jac_stride, int64_t v_jac_stride,
+                           int64_t o_jac_stride, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(B >= 0 && n >= 1 && H >= 1 && d >= 1 && R >= 0, FL_EBADSHAPE,
+             "fl_mhsa: bad sizes B=%lld n=%lld H=%lld d=%lld R=%lld", (long long)B, (long long)n,
+             (long long)H, (long long)d, (long long)R);
+  FL_REQUIRE(n <= 64 && d <= DMAX, FL_EUNSUPPORTED,
+             "fl_mhsa: sequence length %lld (max 64) or head dim %lld (max %d) not supported",
+             (long long)n, (long long)d, DMAX);
+  if (B == 0) return FL_OK;
+  FL_REQUIRE(q && k && v && q_lap && k_lap && v_lap && o && o_lap &&
+                 (R == 0 || (q_jac && k_jac && v_jac && o_jac)),
+             FL_EBADSHAPE, "fl_mhsa: null pointer");
+  Args a{q, q_jac, q_lap, k, k_jac, k_lap, v, v_jac, v_lap, mask, input_mask, o, o_jac, o_lap,
+         (int)B, (int)n, (int)H, (int)d, (int)R, q_jac_stride, k_jac_stride, v_jac_stride,
+         o_jac_stride};
+  auto al = [](const void* p) { return p == nullptr || aligned16(p); };
+  bool vec = d % 4 == 0 && al(q) && al(k) && al(v) && al(q_jac) && al(k_jac) && al(v_jac) &&
+             al(q_lap) && al(k_lap) && al(v_lap) && al(o_jac) && q_jac_stride % 4 == 0 &&
+             k_jac_stride % 4 == 0 && v_jac_stride % 4 == 0 && o_jac_stride % 4 == 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n <= 16) return launch<16>(a, vec, st);
+  if (n <= 32) return launch<32>(a, vec, st);
+  return launch<64>(a, vec, st);
+}

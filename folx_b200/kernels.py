@@ -208,3 +208,70 @@ def layernorm(a: FwdLaplArray, gamma: torch.Tensor | None, beta: torch.Tensor | 
         _jac_stride(out.jacobian.data), _stream(x.device),
     )
     return out
+
+
+def slogdet(a: FwdLaplArray):
+    """``(sign, triplet of log|det|)`` for matrices in the last two axes (folx/slogdet.py:296-358).
+
+    The Jacobian must be dense (the rule densifies, as the reference does: the determinant
+    depends on every coordinate its matrix depends on, folx/slogdet.py:247, 344).
+    """
+    if a.jacobian.weak:
+        a = a.dense
+    a = as_contiguous(a)
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    _require_cuda(x, j, l)
+    n = x.shape[-1]
+    if x.shape[-2] != n:
+        raise ValueError(f'slogdet: matrices must be square, got {tuple(x.shape[-2:])}')
+    batch = tuple(x.shape[:-2])
+    n_mat = x.numel() // (n * n) if n else 0
+    K = j.shape[0]
+    if K > 1 and j.stride(0) < x.numel():
+        j = j.contiguous()
+    sign = torch.empty(batch, dtype=torch.float32, device=x.device)
+    out = alloc_triplet(K, batch, x.device, None)
+    lib.call(
+        'fl_slogdet', _ptr(x), _ptr(j), _ptr(l), n_mat, n, K, _jac_stride(j), _ptr(sign),
+        _ptr(out.x), _ptr(out.jacobian.data), max(n_mat, 1), _ptr(out.laplacian), _stream(x.device),
+    )
+    return sign, out
+
+
+def mhsa(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, mask: torch.Tensor | None = None,
+         input_mask: torch.Tensor | None = None) -> FwdLaplArray:
+    """Softmax self attention ``o = softmax(q k^T) v`` on triplets of shape ``(B, n, H, d)``.
+
+    Reference: mhsa_forward_laplacian (folx/experimental/pallas/attention/forward_laplacian.py:
+    27-179).  Sparse Jacobians are densified first, as the reference does (lines 164-178);
+    ``mask`` is ``(B, n)`` bool, ``input_mask`` is ``(R, B)`` bool.
+    """
+    trip = []
+    for t in (q, k, v):
+        if t.jacobian.weak:
+            t = t.dense
+        trip.append(as_contiguous(t))
+    R = max(t.jacobian.data.shape[0] for t in trip)
+    fixed = []
+    for t in trip:
+        j = t.jacobian.data
+        if j.shape[0] < R:  # dense Jacobians may be truncated at the highest referenced input
+            j = torch.cat([j, torch.zeros((R - j.shape[0], *j.shape[1:]), dtype=j.dtype, device=j.device)])
+        if R > 1 and j.stride(0) < t.x.numel():
+            j = j.contiguous()
+        fixed.append((t.x, j, t.laplacian))
+    (qx, qj, ql), (kx, kj, kl), (vx, vj, vl) = fixed
+    _require_cuda(qx, qj, ql, kx, kj, kl, vx, vj, vl)
+    B, n, H, d = qx.shape
+    out = alloc_triplet(R, (B, n, H, d), qx.device, None)
+    m8 = mask.to(torch.uint8).contiguous() if mask is not None else None
+    im8 = input_mask.to(torch.uint8).contiguous() if input_mask is not None else None
+    if im8 is not None and tuple(im8.shape) != (R, B):
+        raise ValueError(f'mhsa: input_mask must have shape {(R, B)}, got {tuple(im8.shape)}')
+    lib.call(
+        'fl_mhsa', _ptr(qx), _ptr(qj), _ptr(ql), _ptr(kx), _ptr(kj), _ptr(kl), _ptr(vx), _ptr(vj),
+        _ptr(vl), _ptr(m8), _ptr(im8), _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian),
+        B, n, H, d, R, _jac_stride(qj), _jac_stride(kj), _jac_stride(vj),
+        _jac_stride(out.jacobian.data), _stream(qx.device),
+    )
+    return out

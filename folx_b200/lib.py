@@ -60,6 +60,9 @@ _SIGNATURES = {
     'fl_index_union': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     'fl_index_intersection': (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p,
                                         c_int64, c_void_p, c_void_p]),
+    'fl_slogdet': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                             c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    'fl_mhsa': (c_int32, [c_void_p] * 14 + [c_int64] * 9 + [c_void_p]),
 }
 
 _lib = None

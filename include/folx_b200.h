@@ -194,6 +194,43 @@ int32_t fl_index_intersection(const int32_t* idx, int64_t S, int64_t K_total, in
                               const int32_t* seg_offsets, int32_t* out, int64_t m_cap,
                               int32_t* counts, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * slogdet of a batch of small square matrices with a dense Jacobian.  Replaces dense_slogdet /
+ * _dense_log_det (folx/slogdet.py:296-344) behind the 'slogdet' registry entry
+ * (folx/wrapped_functions.py:557):
+ *     sign, log|det A|,  J_k = tr(A^-1 dA_k),  lap = tr(A^-1 lapA) - sum_k tr(M_k M_k), M_k = A^-1 dA_k
+ * The intermediate M (K x n x n per matrix) is never written to memory.
+ *   A, lap : [n_mat][n][n], jac : [K][n_mat][n][n] (row stride jac_stride), n <= 32
+ *   sign, logdet, lap_out : [n_mat], jac_out : [K][n_mat] (row stride jac_out_stride)
+ * For real matrices the sign carries no derivatives (folx/slogdet.py:58-61).
+ * ------------------------------------------------------------------------------------------- */
+int32_t fl_slogdet(const float* A, const float* jac, const float* lap,
+                   int64_t n_mat, int64_t n, int64_t K, int64_t jac_stride,
+                   float* sign, float* logdet, float* jac_out, int64_t jac_out_stride,
+                   float* lap_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Multi-head self attention on triplets, fused.  Replaces mhsa_forward_laplacian and its Pallas
+ * kernel (folx/experimental/pallas/attention/forward_laplacian.py:27-179, 349-487), registered
+ * in the reference under the jitted name '_multi_head_self_attention'
+ * (folx/experimental/pallas/attention/__init__.py:17-45).  No 1/sqrt(d) scaling is applied
+ * (the caller scales q, as in the reference).
+ *   q, k, v, their lap, o, o_lap : [B][n][H][d];  *_jac, o_jac : [R][B][n][H][d] (row strides given)
+ *   mask       : uint8 [B][n]  (0 = padded electron) or NULL (all valid)
+ *   input_mask : uint8 [R][B]  (0 = padded input coordinate) or NULL (all valid)
+ * Semantics of the masks follow the reference kernel: masked score pairs get -1e20, Jacobian and
+ * Laplacian rows of masked electrons are read as zero, input_mask gates the Hessian
+ * contribution of a coordinate to o_lap.  n <= 64, d <= 64.
+ * ------------------------------------------------------------------------------------------- */
+int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_lap,
+                const float* k, const float* k_jac, const float* k_lap,
+                const float* v, const float* v_jac, const float* v_lap,
+                const uint8_t* mask, const uint8_t* input_mask,
+                float* o, float* o_jac, float* o_lap,
+                int64_t B, int64_t n, int64_t H, int64_t d, int64_t R,
+                int64_t q_jac_stride, int64_t k_jac_stride, int64_t v_jac_stride,
+                int64_t o_jac_stride, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,93 @@
+"""GPU parity of the fused attention-Laplacian kernel against the oracle.
+
+Shapes follow the reference's own test (test/experimental/pallas/test_attention.py:320-386:
+(B, n, H, d) in {(1,1,1,1), (1,16,4,32)} with max_sequence in {16, 4}) plus the PsiFormer sizes.
+Rows of masked electrons are blanked before comparing, as the reference's test does.
+"""
+
+import pytest
+import torch
+
+from folx_b200 import kernels
+from oracle import rules
+
+from gpu_util import assert_close, seeded_triplet, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+def make_inputs(B, n, H, d, R, max_sequence, seed, scale=0.5):
+    q = seeded_triplet(R, (B, n, H, d), seed=seed, scale=scale)
+    k = seeded_triplet(R, (B, n, H, d), seed=seed + 1, scale=scale)
+    v = seeded_triplet(R, (B, n, H, d), seed=seed + 2)
+    mask = torch.zeros(B, n, dtype=torch.bool)
+    mask[:, :max_sequence] = True
+    input_mask = torch.zeros(R, B, dtype=torch.bool)
+    input_mask[: min(R, 3 * max_sequence)] = True
+    # masked electrons / coordinates carry no derivatives
+    def blank(t):
+        x, J, l = t
+        return (x, J * mask[None, :, :, None, None] * input_mask[:, :, None, None, None],
+                l * mask[:, :, None, None])
+    return blank(q), blank(k), blank(v), mask, input_mask
+
+
+def blank_out(t, mask):
+    return (t[0] * mask[:, :, None, None], t[1] * mask[None, :, :, None, None], t[2] * mask[:, :, None, None])
+
+
+@pytest.mark.parametrize('B,n,H,d,R,max_sequence', [
+    (1, 1, 1, 1, 3, 1), (1, 16, 4, 32, 48, 16), (1, 16, 4, 32, 48, 4),
+    (2, 5, 2, 8, 7, 5), (3, 32, 4, 64, 12, 32), (2, 32, 2, 64, 9, 20), (2, 64, 2, 64, 6, 64),
+    (1, 40, 1, 48, 5, 33), (2, 7, 3, 6, 4, 7),
+])
+def test_mhsa_matches_oracle(cuda_device, B, n, H, d, R, max_sequence):
+    q, k, v, mask, input_mask = make_inputs(B, n, H, d, R, max_sequence, seed=B + n + d)
+    got = kernels.mhsa(to_device(q, cuda_device), to_device(k, cuda_device), to_device(v, cuda_device),
+                       mask.to(cuda_device), input_mask.to(cuda_device))
+    want = rules.mhsa(q, k, v, mask, input_mask)
+    # the reference's tolerance for the Laplacian of this kernel is rtol 2e-3 / atol 5e-5
+    # (test_attention.py:365-386); we hold x and J to rtol 1e-4 and the Laplacian to 1e-3
+    g, w = blank_out(to_host(got), mask), blank_out(want, mask)
+    assert_close(g[:2], w[:2], rtol=1e-4, atol_scale=2e-5)
+    assert_close(g[2:], w[2:], rtol=1e-3, atol_scale=5e-5)
+
+
+def test_mhsa_without_masks_and_unstacked(cuda_device):
+    B, n, H, d, R = 2, 16, 2, 32, 10
+    q = seeded_triplet(R, (B, n, H, d), seed=1, scale=0.5)
+    k = seeded_triplet(R, (B, n, H, d), seed=2, scale=0.5)
+    v = seeded_triplet(R, (B, n, H, d), seed=3)
+    got = kernels.mhsa(to_device(q, cuda_device, stacked=False), to_device(k, cuda_device),
+                       to_device(v, cuda_device, stacked=False))
+    want = rules.mhsa(q, k, v, torch.ones(B, n, dtype=torch.bool), torch.ones(R, B, dtype=torch.bool))
+    assert_close(to_host(got)[:2], want[:2], rtol=1e-4, atol_scale=2e-5)
+    assert_close(to_host(got)[2:], want[2:], rtol=1e-3, atol_scale=5e-5)
+
+
+def test_mhsa_psiformer_shape_properties(cuda_device):
+    """PsiFormer layer shape (n=32, H=4, d=64, R=96) on fewer walkers: sampled oracle check and the
+    invariance o(q, k + c) = o(q, k) for a per-head constant row shift of the scores."""
+    B, n, H, d, R = 16, 32, 4, 64, 96
+    g = torch.Generator(device=cuda_device).manual_seed(0)
+    def rand():
+        a = kernels.alloc_triplet(R, (B, n, H, d), cuda_device)
+        a.x.normal_(generator=g).mul_(0.3); a.jacobian.data.normal_(generator=g).mul_(0.3)
+        a.laplacian.normal_(generator=g).mul_(0.3)
+        return a
+    q, k, v = rand(), rand(), rand()
+    out = kernels.mhsa(q, k, v)
+    sel = torch.tensor([0, 7, 15])
+    pick = lambda a: (a.x[sel].double().cpu(), a.jacobian.data[:, sel].double().cpu(), a.laplacian[sel].double().cpu())
+    want = rules.mhsa(pick(q), pick(k), pick(v), torch.ones(3, n, dtype=torch.bool),
+                      torch.ones(R, 3, dtype=torch.bool))
+    got = pick(out)
+    assert_close(got[:2], want[:2], rtol=1e-4, atol_scale=2e-5)
+    assert_close(got[2:], want[2:], rtol=1e-3, atol_scale=5e-5)
+    # adding the same vector to every key shifts each score row by a constant: softmax unchanged
+    shift = torch.randn(d, device=cuda_device, generator=g) * 0.2
+    k2 = kernels.alloc_triplet(R, (B, n, H, d), cuda_device)
+    k2.x.copy_(k.x + shift); k2.jacobian.data.copy_(k.jacobian.data); k2.laplacian.copy_(k.laplacian)
+    out2 = kernels.mhsa(q, k2, v)
+    torch.testing.assert_close(out2.x, out.x, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(out2.jacobian.data, out.jacobian.data, rtol=1e-3, atol=1e-4)
