@@ -11,5 +11,29 @@ from .api import (  # noqa: F401
     FwdLaplArgs,
     FwdLaplArray,
 )
+from .attention import multi_head_self_attention  # noqa: F401
+from .interpreter import LaplTensor, apply_rule, forward_laplacian, vmap  # noqa: F401
+from .operators import (  # noqa: F401
+    ForwardLaplacianOperator,
+    LoopLaplacianOperator,
+    ParallelLaplacianOperator,
+)
+from .registry import (  # noqa: F401
+    deregister_function,
+    get_laplacian,
+    is_registered,
+    register_function,
+    warp_without_fwd_laplacian,
+    wrap_elementwise,
+    wrap_forward_laplacian,
+)
+
+__all__ = [
+    'forward_laplacian', 'vmap', 'ForwardLaplacianOperator', 'LoopLaplacianOperator',
+    'ParallelLaplacianOperator', 'wrap_forward_laplacian', 'warp_without_fwd_laplacian',
+    'wrap_elementwise', 'register_function', 'deregister_function', 'is_registered', 'get_laplacian',
+    'FwdLaplArray', 'FwdJacobian', 'FwdLaplArgs', 'FunctionFlags', 'JAC_DIM',
+    'multi_head_self_attention', 'apply_rule', 'LaplTensor',
+]
 
 __version__ = '0.1.0'

@@ -3,6 +3,8 @@
 // Moving a sparse Jacobian into another row frame -- densifying it, aligning it to the union
 // frame of a reduction or of a binary op, summing rows of a reduced axis -- is always
 //     out[o, pos] = sum_s in[take[o, s, class(pos)], in_pos(pos)]        (take < 0: empty slot)
+// A table entry names a source row and, for reductions, an element of the reduced axis:
+// entry = row * n_reduced + reduced_index (n_reduced == 1 when nothing is reduced).
 // with a table that depends only on the index maps.  The reference does this with
 // take_along_axis + masked sum (materialize_by_gather, folx/utils.py:71-114, called from
 // folx/api.py:58-118 and folx/jvp.py:37-86, 164-171) or a runtime segment_sum; here the table is
@@ -27,7 +29,7 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const float* __restrict__ in, int64_t in_row_stride,
                    const int32_t* __restrict__ take, int64_t table_positions, int k_out,
                    int n_slots, float* __restrict__ out, int64_t out_row_stride, int64_t N,
-                   GatherGeom g) {
+                   int nr, int64_t red_stride, GatherGeom g) {
   int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (pos >= N) return;
   int64_t rem = pos, in_off = 0, t_off = 0;
@@ -44,7 +46,10 @@ gather_rows_kernel(const float* __restrict__ in, int64_t in_row_stride,
     float acc = 0.f;
     for (int s = 0; s < n_slots; ++s) {
       int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
-      if (r >= 0) acc += __ldg(in + (int64_t)r * in_row_stride + in_off);
+      if (r >= 0) {
+        const int row = r / nr, red = r - row * nr;
+        acc += __ldg(in + (int64_t)row * in_row_stride + (int64_t)red * red_stride + in_off);
+      }
     }
     __stcs(out + (int64_t)o * out_row_stride + pos, acc);
   }
@@ -55,7 +60,8 @@ gather_rows_kernel(const float* __restrict__ in, int64_t in_row_stride,
 __global__ void __launch_bounds__(256)
 gather_rows_vec4(const float4* __restrict__ in, int64_t in_row_stride4,
                  const int32_t* __restrict__ take, int64_t table_positions, int k_out, int n_slots,
-                 float4* __restrict__ out, int64_t out_row_stride4, int64_t N4, GatherGeom g) {
+                 float4* __restrict__ out, int64_t out_row_stride4, int64_t N4, int nr,
+                 int64_t red_stride4, GatherGeom g) {
   int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (pos >= N4) return;
   // g.shape[last] and g.in_stride are already expressed in float4 units by the host
@@ -74,7 +80,8 @@ gather_rows_vec4(const float4* __restrict__ in, int64_t in_row_stride4,
     for (int s = 0; s < n_slots; ++s) {
       int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
       if (r >= 0) {
-        float4 v = __ldg(in + (int64_t)r * in_row_stride4 + in_off);
+        const int row = r / nr, red = r - row * nr;
+        float4 v = __ldg(in + (int64_t)row * in_row_stride4 + (int64_t)red * red_stride4 + in_off);
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
     }
@@ -89,8 +96,11 @@ extern "C" int32_t fl_gather_rows(const float* jac_in, int64_t k_in, int64_t in_
                                   const int32_t* take, int64_t k_out, int64_t n_slots,
                                   float* jac_out, int64_t out_row_stride, int32_t ndim,
                                   const int64_t* shape, const int64_t* in_strides,
-                                  const int64_t* table_strides, void* stream) {
+                                  const int64_t* table_strides, int64_t n_reduced,
+                                  int64_t reduced_stride, void* stream) {
   using namespace fl;
+  FL_REQUIRE(n_reduced >= 1 && n_reduced < (1ll << 31), FL_EBADSHAPE,
+             "fl_gather_rows: n_reduced must be >= 1");
   FL_REQUIRE(ndim >= 0 && ndim <= kMaxDims, FL_EBADSHAPE, "fl_gather_rows: ndim %d not in [0, %d]",
              ndim, kMaxDims);
   FL_REQUIRE(k_in >= 0 && k_out >= 0 && n_slots >= 0 && k_out < (1ll << 31) && n_slots < (1ll << 31),
@@ -116,6 +126,7 @@ extern "C" int32_t fl_gather_rows(const float* jac_in, int64_t k_in, int64_t in_
   const int last = ndim - 1;
   bool vec = ndim >= 1 && g.shape[last] % 4 == 0 && g.table_stride[last] == 0 &&
              g.in_stride[last] == 1 && in_row_stride % 4 == 0 && out_row_stride % 4 == 0 &&
+             reduced_stride % 4 == 0 &&
              aligned16(jac_in) && aligned16(jac_out);
   for (int d = 0; vec && d < last; ++d) vec = g.in_stride[d] % 4 == 0;
   if (vec) {
@@ -126,11 +137,12 @@ extern "C" int32_t fl_gather_rows(const float* jac_in, int64_t k_in, int64_t in_
     FL_REQUIRE((N4 + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_gather_rows: too many positions");
     gather_rows_vec4<<<(unsigned)((N4 + 255) / 256), 256, 0, st>>>(
         (const float4*)jac_in, in_row_stride / 4, take, T, (int)k_out, (int)n_slots,
-        (float4*)jac_out, out_row_stride / 4, N4, g4);
+        (float4*)jac_out, out_row_stride / 4, N4, (int)n_reduced, reduced_stride / 4, g4);
   } else {
     FL_REQUIRE((N + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_gather_rows: too many positions");
     gather_rows_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(
-        jac_in, in_row_stride, take, T, (int)k_out, (int)n_slots, jac_out, out_row_stride, N, g);
+        jac_in, in_row_stride, take, T, (int)k_out, (int)n_slots, jac_out, out_row_stride, N,
+        (int)n_reduced, reduced_stride, g);
   }
   FL_CHECK_LAUNCH("fl_gather_rows launch");
   return FL_OK;

@@ -1,0 +1,508 @@
+"""``forward_laplacian``: runs a function on triplets by dispatching every operation to the rule
+registry (reference: folx/interpreter.py:127-352).
+
+The reference traces the function to a jaxpr and walks its equations.  Here the function is a
+PyTorch function; its operations are intercepted as they execute: the arguments are wrapped in
+``LaplTensor`` objects whose ``__torch_function__`` maps each torch call to a registry key
+(``torch.tanh`` -> ``'tanh'``, ``x @ W`` -> ``'dot_general'`` ...), looks the rule up with
+``get_laplacian`` and calls it as ``rule(args, kwargs, sparsity_threshold)`` -- the same contract
+``eval_laplacian`` / ``eval_pjit`` use (folx/interpreter.py:186-216).  Operations whose inputs
+carry no triplet run as ordinary torch calls (folx/interpreter.py:222-245).
+
+Mapping over walkers (``jax.vmap`` in the reference's usage, README.md:43-70) is built in: with
+``batch_dims=1`` every argument has a leading walker axis that the traced function never sees --
+``LaplTensor.shape`` and all axis arguments are per walker -- while the kernels process all
+walkers at once and the index maps stay walker-independent.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Any, Callable, Sequence
+
+import numpy as np
+import torch
+
+from . import registry
+from .api import FwdJacobian, FwdLaplArray
+
+
+def _call(key: str, args: tuple, kwargs: dict, thr: int):
+    rule = registry.get_laplacian(key)
+    if rule is None:
+        raise NotImplementedError(f"no forward-Laplacian rule is registered for '{key}'")
+    return rule(args, kwargs, thr)
+
+
+class BatchedConst(torch.Tensor):
+    """A derivative-free value produced inside a walker-mapped function (``detach()``, the sign of
+    ``slogdet``, a comparison).  It is an ordinary tensor that still carries the hidden walker
+    axes in front; the subclass only marks that fact so that arithmetic with a ``LaplTensor``
+    lines the axes up.  Index its axes from the right (negative ``dim``)."""
+
+
+class LaplTensor:
+    """A tensor seen by the traced function: value, Jacobian and Laplacian travel together."""
+
+    __slots__ = ('arr', 'nb', 'thr')
+
+    def __init__(self, arr: FwdLaplArray, nb: int, thr: int):
+        self.arr, self.nb, self.thr = arr, nb, thr
+
+    # ---- tensor-like attributes (per walker) ----
+    @property
+    def shape(self):
+        return torch.Size(self.arr.x.shape[self.nb:])
+
+    @property
+    def ndim(self):
+        return self.arr.x.ndim - self.nb
+
+    @property
+    def dtype(self):
+        return self.arr.x.dtype
+
+    @property
+    def device(self):
+        return self.arr.x.device
+
+    def dim(self):
+        return self.ndim
+
+    def size(self, d=None):
+        return self.shape if d is None else self.shape[d]
+
+    def numel(self):
+        return math.prod(self.shape)
+
+    def __len__(self):
+        return self.shape[0]
+
+    def __repr__(self):
+        j = self.arr.jacobian
+        kind = f'sparse k={j.data.shape[0]}' if j.weak else f'dense k={j.data.shape[0]}'
+        return f'LaplTensor(shape={tuple(self.shape)}, batch_dims={self.nb}, jacobian={kind})'
+
+    # ---- helpers ----
+    def _wrap(self, out):
+        if isinstance(out, FwdLaplArray):
+            return LaplTensor(out, self.nb, self.thr)
+        if isinstance(out, (tuple, list)):
+            return type(out)(self._wrap(o) for o in out)
+        if torch.is_tensor(out) and self.nb > 0:
+            return out.as_subclass(BatchedConst)
+        return out
+
+    def _axis(self, ax: int, extra: int = 0) -> int:
+        n = self.ndim + extra
+        if not -n <= ax < n:
+            raise IndexError(f'axis {ax} out of range for a {self.ndim}-dimensional tensor')
+        return (ax % n) + self.nb
+
+    def _rank_to(self, rank: int) -> 'LaplTensor':
+        """Inserts size-1 axes after the walker axes so that the per-walker rank is ``rank``."""
+        t = self
+        while t.ndim < rank:
+            t = LaplTensor(_call('expand_dims', (t.arr,), {'dimensions': t.nb}, t.thr), t.nb, t.thr)
+        return t
+
+    # ---- arithmetic ----
+    def _binary(self, op: str, other, reverse: bool = False):
+        a = self
+        if isinstance(other, LaplTensor):
+            rank = max(a.ndim, other.ndim)
+            a, other = a._rank_to(rank), other._rank_to(rank)
+            ob = other.arr
+        elif isinstance(other, BatchedConst):
+            # carries the walker axes already: line up the per-walker ranks
+            ob = other.as_subclass(torch.Tensor)
+            rank_o = ob.ndim - a.nb
+            if rank_o > a.ndim:
+                a = a._rank_to(rank_o)
+            elif rank_o < a.ndim:
+                ob = ob.reshape(*ob.shape[: a.nb], *((1,) * (a.ndim - rank_o)), *ob.shape[a.nb:])
+        else:
+            ob = other
+            if torch.is_tensor(other) and other.ndim > a.ndim:
+                a = a._rank_to(other.ndim)
+        args = (ob, a.arr) if reverse else (a.arr, ob)
+        return a._wrap(_call(op, args, {}, a.thr))
+
+    def __add__(self, o): return self._binary('add', o)
+    def __radd__(self, o): return self._binary('add', o)
+    def __sub__(self, o): return self._binary('sub', o)
+    def __rsub__(self, o): return self._binary('sub', o, reverse=True)
+    def __mul__(self, o): return self._binary('mul', o)
+    def __rmul__(self, o): return self._binary('mul', o)
+    def __truediv__(self, o): return self._binary('div', o)
+    def __rtruediv__(self, o): return self._binary('div', o, reverse=True)
+    def __neg__(self): return self._unary('neg')
+
+    def __pow__(self, p):
+        if isinstance(p, (int, float)) and float(p).is_integer():
+            p = int(p)
+            if p == 2:
+                return self._unary('square')
+            return self._wrap(_call('integer_pow', (self.arr,), {'y': p}, self.thr))
+        if p == 0.5:
+            return self._unary('sqrt')
+        if p == -0.5:
+            return self._unary('rsqrt')
+        raise NotImplementedError(f'power {p} of a triplet is not supported')
+
+    def __matmul__(self, W):
+        if isinstance(W, LaplTensor):
+            return self._wrap(_call('dot_general', (self.arr, W.arr), {}, self.thr))
+        if W.ndim == 1:
+            return (self @ W[:, None]).squeeze(-1)
+        return self._wrap(_call('dot_general', (self.arr, W), {}, self.thr))
+
+    def __rmatmul__(self, W):
+        return self._wrap(_call('dot_general', (W, self.arr), {}, self.thr))
+
+    def _unary(self, key: str):
+        return self._wrap(_call(key, (self.arr,), {}, self.thr))
+
+    def tanh(self): return self._unary('tanh')
+    def exp(self): return self._unary('exp')
+    def log(self): return self._unary('log')
+    def sqrt(self): return self._unary('sqrt')
+    def rsqrt(self): return self._unary('rsqrt')
+    def square(self): return self._unary('square')
+    def sigmoid(self): return self._unary('sigmoid')
+    def sin(self): return self._unary('sin')
+    def cos(self): return self._unary('cos')
+    def abs(self): return self._unary('abs')
+    def neg(self): return self._unary('neg')
+    def reciprocal(self): return self._unary('reciprocal')
+    def pow(self, p): return self.__pow__(p)
+
+    def detach(self):
+        return self._wrap(_call('stop_gradient', (self.arr,), {}, self.thr))
+
+    # comparisons drop the derivatives (folx/wrapped_functions.py:539-551)
+    def _cmp(self, key, o):
+        return self._wrap(_call(key, (self.arr, o.arr if isinstance(o, LaplTensor) else o), {}, self.thr))
+
+    def __lt__(self, o): return self._cmp('lt', o)
+    def __le__(self, o): return self._cmp('le', o)
+    def __gt__(self, o): return self._cmp('gt', o)
+    def __ge__(self, o): return self._cmp('ge', o)
+
+    # ---- reductions ----
+    def sum(self, dim=None, keepdim=False):
+        if dim is None:
+            dim = tuple(range(self.ndim))
+        dims = (dim,) if isinstance(dim, int) else tuple(dim)
+        axes = tuple(self._axis(d) for d in dims)
+        return self._wrap(_call('reduce_sum', (self.arr,), {'axes': axes, 'keepdim': keepdim}, self.thr))
+
+    def mean(self, dim=None, keepdim=False):
+        if dim is None:
+            dim = tuple(range(self.ndim))
+        dims = (dim,) if isinstance(dim, int) else tuple(dim)
+        n = math.prod(self.shape[d] for d in dims)
+        return self.sum(dims, keepdim) * (1.0 / n)
+
+    # ---- indexing ----
+    def reshape(self, *shape):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+            shape = tuple(shape[0])
+        shape = list(shape)
+        if -1 in shape:
+            known = math.prod(s for s in shape if s != -1)
+            shape[shape.index(-1)] = self.numel() // max(known, 1)
+        phys = (*self.arr.x.shape[: self.nb], *shape)
+        return self._wrap(_call('reshape', (self.arr,), {'new_sizes': phys, 'batch_dims': self.nb}, self.thr))
+
+    view = reshape
+
+    def flatten(self, start_dim=0, end_dim=-1):
+        s, e = start_dim % self.ndim, end_dim % self.ndim
+        shp = list(self.shape)
+        return self.reshape(*shp[:s], math.prod(shp[s : e + 1]), *shp[e + 1 :])
+
+    def permute(self, *perm):
+        if len(perm) == 1 and isinstance(perm[0], (tuple, list)):
+            perm = tuple(perm[0])
+        phys = tuple(range(self.nb)) + tuple(self._axis(p) for p in perm)
+        return self._wrap(_call('transpose', (self.arr,), {'permutation': phys}, self.thr))
+
+    def transpose(self, d0, d1):
+        perm = list(range(self.ndim))
+        a, b = d0 % self.ndim, d1 % self.ndim
+        perm[a], perm[b] = perm[b], perm[a]
+        return self.permute(*perm)
+
+    swapaxes = transpose
+
+    @property
+    def T(self):
+        return self.permute(*reversed(range(self.ndim)))
+
+    @property
+    def mT(self):
+        return self.transpose(-1, -2)
+
+    def unsqueeze(self, dim):
+        return self._wrap(_call('expand_dims', (self.arr,), {'dimensions': self._axis(dim, 1)}, self.thr))
+
+    def squeeze(self, dim):
+        return self._wrap(_call('squeeze', (self.arr,), {'dimensions': self._axis(dim)}, self.thr))
+
+    def expand(self, *shape):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+            shape = tuple(shape[0])
+        t = self._rank_to(len(shape))
+        shape = [t.shape[i] if s == -1 else s for i, s in enumerate(shape)]
+        phys = (*t.arr.x.shape[: t.nb], *shape)
+        return t._wrap(_call('broadcast_in_dim', (t.arr,), {'shape': phys}, t.thr))
+
+    def broadcast_to(self, shape):
+        return self.expand(*shape)
+
+    def __getitem__(self, index):
+        if not isinstance(index, tuple):
+            index = (index,)
+        phys = (slice(None),) * self.nb + index
+        return self._wrap(_call('slice', (self.arr,), {'index': phys, 'batch_dims': self.nb}, self.thr))
+
+    # ---- torch.* dispatch ----
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        handler = _TORCH_TABLE.get(func)
+        if handler is None:
+            name = getattr(func, '__name__', str(func))
+            raise NotImplementedError(
+                f'torch function {name} has no forward-Laplacian mapping; register a rule and '
+                'call it through folx_b200.apply_rule, or express it with supported operations')
+        return handler(*args, **kwargs)
+
+
+def _first(args) -> LaplTensor:
+    for a in args:
+        if isinstance(a, LaplTensor):
+            return a
+        if isinstance(a, (tuple, list)):
+            for b in a:
+                if isinstance(b, LaplTensor):
+                    return b
+    raise TypeError('no LaplTensor among the arguments')
+
+
+def _method(name):
+    def h(x, *a, **k):
+        return getattr(x, name)(*a, **k)
+
+    return h
+
+
+def _binary_fn(op):
+    def h(a, b, **k):
+        if isinstance(a, LaplTensor):
+            return a._binary(op, b)
+        return b._binary(op, a, reverse=True)
+
+    return h
+
+
+def _linear(x, weight, bias=None):
+    return x._wrap(_call('dot_general', (x.arr, weight.t()), {'bias': bias}, x.thr))
+
+
+def _matmul(a, b):
+    if isinstance(a, LaplTensor):
+        return a.__matmul__(b)
+    return b.__rmatmul__(a)
+
+
+def _cat(tensors, dim=0):
+    t0 = _first(tensors)
+    rank = max(t.ndim for t in tensors)
+    parts = []
+    for t in tensors:
+        if isinstance(t, LaplTensor):
+            parts.append(t._rank_to(rank).arr)
+        elif isinstance(t, BatchedConst):
+            c = t.as_subclass(torch.Tensor)
+            parts.append(c.reshape(*c.shape[: t0.nb], *((1,) * (rank - (c.ndim - t0.nb))), *c.shape[t0.nb:]))
+        else:
+            # a constant is shared by all walkers: give it the walker axes
+            c = t.reshape((1,) * (t0.nb + rank - t.ndim) + tuple(t.shape))
+            parts.append(c.expand(*t0.arr.x.shape[: t0.nb], *c.shape[t0.nb:]))
+    ax = (dim % rank) + t0.nb
+    return t0._wrap(_call('concatenate', tuple(parts), {'dimension': ax, 'batch_dims': t0.nb}, t0.thr))
+
+
+def _stack(tensors, dim=0):
+    t0 = _first(tensors)
+    rank = t0.ndim + 1
+    d = dim % rank
+    return _cat([t.unsqueeze(d) for t in tensors], d)
+
+
+def _slogdet(x):
+    sign, out = _call('slogdet', (x.arr,), {}, x.thr)
+    return x._wrap(sign), x._wrap(out)
+
+
+def _layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
+    if len(tuple(normalized_shape)) != 1:
+        raise NotImplementedError('layer_norm on triplets normalises the last axis only')
+    return x._wrap(_call('layer_norm', (x.arr, weight, bias), {'eps': eps}, x.thr))
+
+
+def _logsumexp(x, dim, keepdim=False):
+    # the stabilising maximum is a constant (stop_gradient), as in jax.nn.logsumexp
+    phys = x._axis(dim)
+    m = x._wrap(x.arr.x.amax(dim=phys, keepdim=True))
+    out = (x - m).exp().sum(dim, keepdim=True).log() + m
+    return out if keepdim else out.squeeze(dim)
+
+
+def _softmax_unsupported(*a, **k):
+    raise NotImplementedError(
+        'softmax on triplets is only available inside the fused attention rule '
+        '(folx_b200.multi_head_self_attention)')
+
+
+def _pow(x, p):
+    return x.__pow__(p)
+
+
+def _like(fn):
+    def h(x, **k):
+        return fn(x.arr.x[(0,) * x.nb], **k)
+
+    return h
+
+
+_TORCH_TABLE: dict[Any, Callable] = {
+    torch.tanh: _method('tanh'), torch.nn.functional.tanh: _method('tanh'),
+    torch.exp: _method('exp'), torch.log: _method('log'), torch.sqrt: _method('sqrt'),
+    torch.rsqrt: _method('rsqrt'), torch.square: _method('square'), torch.sigmoid: _method('sigmoid'),
+    torch.nn.functional.sigmoid: _method('sigmoid'), torch.sin: _method('sin'), torch.cos: _method('cos'),
+    torch.abs: _method('abs'), torch.neg: _method('neg'), torch.negative: _method('neg'),
+    torch.reciprocal: _method('reciprocal'),
+    torch.nn.functional.silu: lambda x, inplace=False: x._unary('silu'),
+    torch.nn.functional.softplus: lambda x, beta=1.0, threshold=20.0: x._unary('softplus'),
+    torch.add: _binary_fn('add'), torch.sub: _binary_fn('sub'), torch.subtract: _binary_fn('sub'),
+    torch.mul: _binary_fn('mul'), torch.multiply: _binary_fn('mul'), torch.div: _binary_fn('div'),
+    torch.true_divide: _binary_fn('div'), torch.pow: _pow,
+    torch.matmul: _matmul, torch.nn.functional.linear: _linear,
+    torch.sum: _method('sum'), torch.mean: _method('mean'),
+    torch.reshape: _method('reshape'), torch.permute: _method('permute'),
+    torch.transpose: _method('transpose'), torch.swapaxes: _method('transpose'),
+    torch.unsqueeze: _method('unsqueeze'), torch.squeeze: _method('squeeze'),
+    torch.flatten: _method('flatten'), torch.broadcast_to: _method('broadcast_to'),
+    torch.cat: _cat, torch.concatenate: _cat, torch.concat: _cat, torch.stack: _stack,
+    torch.linalg.slogdet: _slogdet, torch.slogdet: _slogdet,
+    torch.nn.functional.layer_norm: _layer_norm, torch.logsumexp: _logsumexp,
+    torch.softmax: _softmax_unsupported, torch.nn.functional.softmax: _softmax_unsupported,
+    torch.detach: _method('detach'),
+    torch.zeros_like: _like(torch.zeros_like), torch.ones_like: _like(torch.ones_like),
+}
+
+
+def apply_rule(key, *args, **kwargs):
+    """Calls the registered rule ``key`` on a mix of ``LaplTensor``s and constants.
+
+    This is how a traced function reaches rules that have no torch spelling -- user-registered
+    ones (``register_function``) and ``'_multi_head_self_attention'`` -- the counterpart of the
+    reference's dispatch on the name of a jitted function (folx/interpreter.py:186-193).
+    """
+    t0 = _first(args)
+    raw = tuple(a.arr if isinstance(a, LaplTensor) else a for a in args)
+    return t0._wrap(_call(key, raw, kwargs, t0.thr))
+
+
+# ------------------------------------------------------------------------------------------
+# initial state and the public transform
+# ------------------------------------------------------------------------------------------
+def init_forward_laplacian_state(xs: Sequence[torch.Tensor], sparsity: bool, weights=1.0,
+                                 batch_dims: int = 0) -> list[FwdLaplArray]:
+    """Identity Jacobian and zero Laplacian for every input (folx/interpreter.py:267-298).
+
+    Sparse mode: one row per element with ``x0_idx = arange(n)`` (lines 286-293); dense mode:
+    ``diag(weights)`` unravelled to ``(n, *shape)`` (lines 295-296).  ``n`` counts the elements of
+    ALL inputs of one walker.
+    """
+    if isinstance(weights, (int, float)):
+        weights = [float(weights)] * len(xs)
+    sizes = [math.prod(x.shape[batch_dims:]) for x in xs]
+    n = sum(sizes)
+    out, off = [], 0
+    for x, w, sz in zip(xs, weights, sizes):
+        bshape, shape = tuple(x.shape[:batch_dims]), tuple(x.shape[batch_dims:])
+        lap = torch.zeros_like(x)
+        if sparsity:
+            data = torch.full((1, *x.shape), float(w), dtype=x.dtype, device=x.device) if not torch.is_tensor(w) \
+                else (torch.ones_like(x) * w)[None]
+            idx = np.arange(off, off + sz, dtype=np.int64).reshape(1, *((1,) * batch_dims), *shape)
+            jac = FwdJacobian(data, idx)
+        else:
+            eye = torch.zeros((n, sz), dtype=x.dtype, device=x.device)
+            eye[off : off + sz] = torch.eye(sz, dtype=x.dtype, device=x.device)
+            eye = eye.reshape(n, *((1,) * batch_dims), *shape)
+            if torch.is_tensor(w) or w != 1.0:
+                eye = eye * w
+            jac = FwdJacobian(eye.expand(n, *bshape, *shape), None)
+        out.append(FwdLaplArray(x, jac, lap))
+        off += sz
+    return out
+
+
+def _tree_map(fn, tree):
+    if isinstance(tree, (tuple, list)):
+        return type(tree)(_tree_map(fn, t) for t in tree)
+    if isinstance(tree, dict):
+        return {k: _tree_map(fn, v) for k, v in tree.items()}
+    return fn(tree)
+
+
+def forward_laplacian(fn: Callable, sparsity_threshold: int | float = 0, disable_jit: bool = False,
+                      batch_dims: int = 0) -> Callable:
+    """Returns a function computing ``fn``'s output as triplets (value, Jacobian, Laplacian).
+
+    Same arguments as the reference (folx/interpreter.py:301-352): ``sparsity_threshold`` is an
+    absolute row count, or a fraction of the input size when in ``(0, 1)``; 0 disables sparse
+    Jacobians.  ``disable_jit`` is accepted for compatibility (there is no tracing compiler here).
+    ``batch_dims=1`` maps over a leading walker axis (what ``jax.vmap`` does for the reference);
+    ``folx_b200.vmap`` sets it.
+    """
+
+    def make(nb: int):
+        def wrapped(*args, weights=1.0, **kwargs):
+            flat = [a for a in args]
+            tens = [a.x if isinstance(a, FwdLaplArray) else a for a in flat]
+            total = sum(math.prod(t.shape[nb:]) for t in tens)
+            thr = int(sparsity_threshold * total) if 0 < sparsity_threshold < 1 else int(sparsity_threshold)
+            if any(isinstance(a, FwdLaplArray) for a in flat):
+                # already triplets: propagate them as they are; plain tensors are constants
+                # (reference: init_forward_laplacian_state returns its input, lines 273-274)
+                state = flat
+            else:
+                state = init_forward_laplacian_state(tens, thr > 0, weights, nb)
+            out = fn(*[LaplTensor(s, nb, thr) if isinstance(s, FwdLaplArray) else s for s in state],
+                     **kwargs)
+            return _tree_map(lambda o: o.arr if isinstance(o, LaplTensor) else o, out)
+
+        return wrapped
+
+    wrapped = make(batch_dims)
+    wrapped._folx_batched = make(batch_dims + 1)  # type: ignore[attr-defined]
+    return wrapped
+
+
+def vmap(fn: Callable, in_axes=0) -> Callable:
+    """Maps a forward-Laplacian function over a leading walker axis.
+
+    For functions made by ``forward_laplacian`` / the Laplacian operators this switches on the
+    built-in walker axis (all walkers go through each kernel together, the index maps are shared);
+    anything else is handed to ``torch.vmap``.
+    """
+    if in_axes != 0:
+        raise NotImplementedError('only in_axes=0 is supported')
+    batched = getattr(fn, '_folx_batched', None)
+    return batched if batched is not None else torch.vmap(fn)

@@ -56,7 +56,7 @@ _SIGNATURES = {
                                c_int64, c_void_p]),
     'fl_gather_rows': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                  c_int64, c_int32, POINTER(c_int64), POINTER(c_int64),
-                                 POINTER(c_int64), c_void_p]),
+                                 POINTER(c_int64), c_int64, c_int64, c_void_p]),
     'fl_index_union': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     'fl_index_intersection': (c_int32, [c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p,
                                         c_int64, c_void_p, c_void_p]),

@@ -1,0 +1,89 @@
+"""Laplacian operators (reference: folx/operators.py:19-79): same classes, same return values."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable
+
+import torch
+
+from .interpreter import forward_laplacian
+
+
+@dataclass(frozen=True)
+class ForwardLaplacianOperator:
+    """``ForwardLaplacianOperator(thr)(f)(x) -> (laplacian, jacobian.dense_array)``
+    (reference: folx/operators.py:27-38).  ``folx_b200.vmap`` of the result maps over walkers."""
+
+    sparsity_threshold: float | int
+
+    def __call__(self, f: Callable):
+        fwd = forward_laplacian(f, self.sparsity_threshold)
+
+        def make(run, batched):
+            def lap(x):
+                result = run(x)
+                jac = result.jacobian.dense_array
+                # mapped over walkers the Jacobian comes out walker-major, as under jax.vmap
+                return result.laplacian, (jac.movedim(0, 1) if batched else jac)
+
+            return lap
+
+        lap = make(fwd, False)
+        lap._folx_batched = make(fwd._folx_batched, True)  # type: ignore[attr-defined]
+        return lap
+
+
+class LoopLaplacianOperator:
+    """Laplacian by one Hessian-vector product per input coordinate (folx/operators.py:41-62).
+
+    Plain automatic differentiation (``torch.func``), no forward-Laplacian rules involved: this is
+    the cross-check the reference's README times against."""
+
+    @staticmethod
+    def __call__(f: Callable):
+        from torch.func import grad, jvp
+
+        def laplacian(x: torch.Tensor):
+            shape = x.shape
+            flat = x.reshape(-1)
+            n = flat.shape[0]
+
+            def f_(z):
+                return f(z.reshape(shape))
+
+            grad_f = grad(f_)
+            jacobian = grad_f(flat)
+            eye = torch.eye(n, dtype=x.dtype, device=x.device)
+            lap = x.new_zeros(())
+            for i in range(n):
+                lap = lap + jvp(grad_f, (flat,), (eye[i],))[1][i]
+            return lap, jacobian
+
+        laplacian._folx_batched = torch.vmap(laplacian)  # type: ignore[attr-defined]
+        return laplacian
+
+
+class ParallelLaplacianOperator:
+    """All Hessian-vector products at once (folx/operators.py:65-79)."""
+
+    @staticmethod
+    def __call__(f: Callable):
+        from torch.func import grad, jvp, vmap
+
+        def laplacian(x: torch.Tensor):
+            flat = x.reshape(-1)
+            n = flat.shape[0]
+            shape = x.shape
+
+            def f_(z):
+                return f(z.reshape(shape))
+
+            grad_f = grad(f_)
+            jacobian = grad_f(flat)
+            eye = torch.eye(n, dtype=x.dtype, device=x.device)
+            hvps = vmap(lambda v: jvp(grad_f, (flat,), (v,))[1])(eye)
+            return torch.diagonal(hvps).sum(), jacobian
+
+        laplacian._folx_batched = torch.vmap(laplacian)  # type: ignore[attr-defined]
+        return laplacian

@@ -1,0 +1,290 @@
+"""Rule registry and rule factories: the plugin API of the forward Laplacian.
+
+Same surface as the reference (folx/wrapped_functions.py:355-618, folx/wrapper.py:73-176):
+``register_function`` / ``deregister_function`` / ``is_registered`` / ``get_laplacian`` over a
+dictionary keyed by primitive name, and ``wrap_forward_laplacian(fn, in_axes, flags, name,
+index_static_args, custom_jac_hessian_jac)`` to build a rule from a plain function.  A rule is
+called as ``rule(args, kwargs, sparsity_threshold)`` with triplets and/or constants in ``args``
+(reference: ForwardLaplacian protocol, folx/api.py:444-450).
+
+Keys are the names of the reference's registry entries (the JAX primitive names and the jitted
+function names it registers: ``'tanh'``, ``'dot_general'``, ``'reduce_sum'``, ``'silu'``,
+``'slogdet'``, ``'_multi_head_self_attention'`` ...).
+"""
+
+from __future__ import annotations
+
+import functools
+import logging
+from typing import Any, Callable
+
+import torch
+
+from . import kernels, rules
+from .api import (
+    CustomTraceJacHessianJac,
+    ForwardLaplacian,
+    FunctionFlags,
+    FwdJacobian,
+    FwdLaplArgs,
+    FwdLaplArray,
+)
+
+_LAPLACE_FN_REGISTRY: dict[Any, ForwardLaplacian] = {}
+
+
+def register_function(primitive_or_name, laplacian: ForwardLaplacian) -> None:
+    """Registers a rule under a primitive / function name (folx/wrapped_functions.py:564-568)."""
+    _LAPLACE_FN_REGISTRY[primitive_or_name] = laplacian
+
+
+def deregister_function(primitive_or_name) -> None:
+    """Removes a rule (folx/wrapped_functions.py:571-575)."""
+    del _LAPLACE_FN_REGISTRY[primitive_or_name]
+
+
+def is_registered(primitive_or_name) -> bool:
+    return primitive_or_name in _LAPLACE_FN_REGISTRY
+
+
+def get_laplacian(primitive_or_name, wrap_if_missing: bool = False):
+    """Rule for a key; optionally wraps an unregistered callable with the generic rule
+    (folx/wrapped_functions.py:597-618)."""
+    if is_registered(primitive_or_name):
+        return _LAPLACE_FN_REGISTRY[primitive_or_name]
+    if wrap_if_missing:
+        if callable(primitive_or_name):
+            logging.warning(f'{primitive_or_name} not in registry. The following call might be slow '
+                            'as the generic (dense, autodiff) rule is used.')
+            return wrap_forward_laplacian(primitive_or_name)
+        raise TypeError(f"Can't wrap {primitive_or_name} based on function names.")
+    return None
+
+
+# ------------------------------------------------------------------------------------------
+# rule factories
+# ------------------------------------------------------------------------------------------
+_KERNEL_UNARY = {
+    torch.tanh: 'tanh', torch.nn.functional.tanh: 'tanh', torch.nn.functional.silu: 'silu',
+    torch.exp: 'exp', torch.log: 'log', torch.sqrt: 'sqrt', torch.rsqrt: 'rsqrt',
+    torch.square: 'square', torch.sigmoid: 'sigmoid', torch.nn.functional.sigmoid: 'sigmoid',
+    torch.nn.functional.softplus: 'softplus', torch.sin: 'sin', torch.cos: 'cos',
+    torch.neg: 'neg', torch.abs: 'abs', torch.reciprocal: 'reciprocal',
+}
+_KERNEL_BINARY = {torch.add: 'add', torch.sub: 'sub', torch.mul: 'mul', torch.div: 'div',
+                  torch.true_divide: 'div', torch.multiply: 'mul', torch.subtract: 'sub'}
+
+
+def _generic_dense_rule(fn, args, kwargs, flags, custom_jac_hessian_jac, in_axes):
+    """Rule of an arbitrary torch function: dense Jacobians, derivatives by ``torch.func``.
+
+    ``J_y[k] = jvp(f, x, J[k])``, ``lap_y = jvp(f, x, lap) + sum_k D^2 f[J[k], J[k]]`` (the trace
+    ``tr(J^T H J)`` written as second directional derivatives; reference: folx/wrapper.py:120-125
+    with the general Hessian path of folx/hessian.py:115-147).  Runs on the device through torch's
+    own kernels: this is the slow path for functions nobody registered a rule for.
+    """
+    from torch.func import jvp, vmap
+
+    pos = [i for i, a in enumerate(args) if isinstance(a, FwdLaplArray)]
+    trip = [rules.densify(args[i]) for i in pos]
+    rows = max(t.jacobian.data.shape[0] for t in trip)
+    trip = [rules._with_rows(t, rows) for t in trip]
+
+    def f(*xs):
+        full = list(args)
+        for i, x in zip(pos, xs):
+            full[i] = x
+        return fn(*full, **kwargs)
+
+    xs = tuple(t.x for t in trip)
+    y, lap_lin = jvp(f, xs, tuple(t.laplacian for t in trip))
+
+    def push(*tangents):
+        return jvp(f, xs, tangents)[1]
+
+    jac = vmap(push)(*(t.jacobian.data for t in trip))
+    if FunctionFlags.LINEAR in flags or (FunctionFlags.LINEAR_IN_ONE in flags and len(trip) == 1):
+        hess = 0.0
+    elif custom_jac_hessian_jac is not None:
+        extra = tuple(a for a in args if not isinstance(a, FwdLaplArray))
+
+        def merge(xs_, extra_):
+            xi, ei = iter(xs_), iter(extra_)
+            return tuple(next(xi) if isinstance(a, FwdLaplArray) else next(ei) for a in args)
+
+        hess = custom_jac_hessian_jac(FwdLaplArgs(tuple(trip)), extra, merge, None)
+    else:
+        def second(*tangents):
+            def first(*zs):
+                return jvp(f, zs, tangents)[1]
+
+            return jvp(first, xs, tangents)[1]
+
+        hess = vmap(second)(*(t.jacobian.data for t in trip)).sum(0)
+    lap = lap_lin + hess
+    return FwdLaplArray(y, FwdJacobian(jac.contiguous()), lap)
+
+
+def wrap_forward_laplacian(fn: Callable, in_axes=None, flags: FunctionFlags = FunctionFlags.GENERAL,
+                           name: str | None = None, index_static_args=None,
+                           custom_jac_hessian_jac: CustomTraceJacHessianJac | None = None) -> ForwardLaplacian:
+    """Adds forward-Laplacian propagation to ``fn`` (reference: folx/wrapper.py:73-138).
+
+    ``in_axes=()`` declares ``fn`` elementwise, ``None`` says all axes matter; ``flags`` describe its
+    structure (``LINEAR`` skips the Hessian term).  Functions this library has a kernel for
+    (the scalar functions of ``fl_elementwise`` and the four arithmetic operators) take the kernel
+    path, including sparse Jacobians; anything else goes through the dense autodiff rule.
+    """
+    if isinstance(in_axes, int):
+        in_axes = (in_axes,)
+
+    def new_fn(args, kwargs, sparsity_threshold: int):
+        if not any(isinstance(a, FwdLaplArray) for a in args):
+            return fn(*args, **kwargs)
+        if custom_jac_hessian_jac is None and not kwargs:
+            if fn in _KERNEL_UNARY and len(args) == 1:
+                return rules.elementwise(_KERNEL_UNARY[fn], args[0], 0.0, sparsity_threshold)
+            if fn in _KERNEL_BINARY and len(args) == 2:
+                return rules.binary(_KERNEL_BINARY[fn], args[0], args[1], sparsity_threshold)
+        return _generic_dense_rule(fn, args, kwargs, flags, custom_jac_hessian_jac, in_axes)
+
+    new_fn.__name__ = name or getattr(fn, '__name__', 'wrapped')
+    return new_fn
+
+
+def warp_without_fwd_laplacian(fn) -> ForwardLaplacian:
+    """Rule that drops the derivatives and applies ``fn`` to the values (folx/wrapper.py:141-154)."""
+
+    def wrapped(args, kwargs, sparsity_threshold: int):
+        strip = lambda a: a.x if isinstance(a, FwdLaplArray) else a
+        return fn(*[strip(a) for a in args], **{k: strip(v) for k, v in kwargs.items()})
+
+    return wrapped
+
+
+def wrap_elementwise(fn) -> ForwardLaplacian:
+    """Rule that applies ``fn`` to x, the Jacobian data and the Laplacian alike (folx/wrapper.py:157-176)."""
+
+    def wrapped(args, kwargs, sparsity_threshold: int):
+        assert len(args) == 1
+        x = args[0]
+        if isinstance(x, FwdLaplArray):
+            return FwdLaplArray(fn(x.x), FwdJacobian(fn(x.jacobian.data), x.jacobian.x0_idx), fn(x.laplacian))
+        return fn(x)
+
+    return wrapped
+
+
+# ------------------------------------------------------------------------------------------
+# built-in rules
+# ------------------------------------------------------------------------------------------
+def _unary(op):
+    def rule(args, kwargs, sparsity_threshold):
+        return rules.elementwise(op, args[0], kwargs.get('param', 0.0), sparsity_threshold)
+
+    rule.__name__ = op
+    return rule
+
+
+def _binary(op):
+    def rule(args, kwargs, sparsity_threshold):
+        return rules.binary(op, args[0], args[1], sparsity_threshold)
+
+    rule.__name__ = op
+    return rule
+
+
+def _integer_pow(args, kwargs, sparsity_threshold):
+    return rules.elementwise('integer_pow', args[0], kwargs['y'], sparsity_threshold)
+
+
+def _dot_general(args, kwargs, sparsity_threshold):
+    """``lhs @ rhs`` with exactly one triplet operand (folx/wrapped_functions.py:174-203)."""
+    lhs, rhs = args
+    bias = kwargs.get('bias')
+    if isinstance(lhs, FwdLaplArray) and isinstance(rhs, FwdLaplArray):
+        raise NotImplementedError(
+            'dot_general of two triplets is not supported; multi-head self attention has its own '
+            "fused rule ('_multi_head_self_attention')")
+    if isinstance(rhs, FwdLaplArray):
+        # W @ h == (h^T @ W^T)^T on the last two axes
+        nd = rhs.x.ndim
+        perm = list(range(nd))
+        perm[-1], perm[-2] = perm[-2], perm[-1]
+        out = rules.dot_general(rules.permute(rhs, perm), lhs.transpose(-1, -2).contiguous(), None,
+                                sparsity_threshold)
+        return rules.permute(out, perm)
+    return rules.dot_general(lhs, rhs, bias, sparsity_threshold)
+
+
+def _reduce_sum(args, kwargs, sparsity_threshold):
+    return rules.reduce_sum(args[0], kwargs['axes'], kwargs.get('keepdim', False), sparsity_threshold)
+
+
+def _reshape(args, kwargs, sparsity_threshold):
+    return rules.reshape(args[0], kwargs['new_sizes'], kwargs.get('batch_dims', 0))
+
+
+def _transpose(args, kwargs, sparsity_threshold):
+    return rules.permute(args[0], kwargs['permutation'])
+
+
+def _broadcast_in_dim(args, kwargs, sparsity_threshold):
+    return rules.broadcast_to(args[0], kwargs['shape'])
+
+
+def _slice(args, kwargs, sparsity_threshold):
+    return rules.getitem(args[0], kwargs['index'], kwargs.get('batch_dims', 0))
+
+
+def _concatenate(args, kwargs, sparsity_threshold):
+    return rules.concatenate(list(args), kwargs['dimension'], kwargs.get('batch_dims', 0))
+
+
+def _squeeze(args, kwargs, sparsity_threshold):
+    return rules.squeeze(args[0], kwargs['dimensions'])
+
+
+def _expand_dims(args, kwargs, sparsity_threshold):
+    return rules.expand_dims(args[0], kwargs['dimensions'])
+
+
+def _slogdet(args, kwargs, sparsity_threshold):
+    return rules.slogdet(args[0], sparsity_threshold)
+
+
+def _layer_norm(args, kwargs, sparsity_threshold):
+    x, gamma, beta = (list(args) + [None, None])[:3]
+    return rules.layer_norm(x, gamma, beta, kwargs.get('eps', 1e-6), sparsity_threshold)
+
+
+def _mhsa(args, kwargs, sparsity_threshold):
+    q, k, v, mask, input_mask = (list(args) + [None, None])[:5]
+    return rules.mhsa(q, k, v, mask, input_mask, sparsity_threshold)
+
+
+for _op in ('tanh', 'exp', 'log', 'sqrt', 'rsqrt', 'square', 'sigmoid', 'softplus', 'silu', 'sin',
+            'cos', 'neg', 'abs', 'reciprocal'):
+    register_function(_op, _unary(_op))
+register_function('logistic', _unary('sigmoid'))
+register_function('integer_pow', _integer_pow)
+for _op in ('add', 'sub', 'mul', 'div'):
+    register_function(_op, _binary(_op))
+register_function('add_any', _binary('add'))
+register_function('dot_general', _dot_general)
+register_function('reduce_sum', _reduce_sum)
+register_function('reshape', _reshape)
+register_function('transpose', _transpose)
+register_function('broadcast_in_dim', _broadcast_in_dim)
+register_function('slice', _slice)
+register_function('concatenate', _concatenate)
+register_function('squeeze', _squeeze)
+register_function('expand_dims', _expand_dims)
+register_function('slogdet', _slogdet)
+register_function('layer_norm', _layer_norm)
+register_function('_multi_head_self_attention', _mhsa)
+register_function('stop_gradient', warp_without_fwd_laplacian(lambda x: x))
+for _name, _fn in (('eq', torch.eq), ('lt', torch.lt), ('le', torch.le), ('gt', torch.gt),
+                   ('ge', torch.ge), ('ne', torch.ne), ('sign', torch.sign), ('floor', torch.floor),
+                   ('ceil', torch.ceil), ('round', torch.round), ('is_finite', torch.isfinite)):
+    register_function(_name, warp_without_fwd_laplacian(_fn))

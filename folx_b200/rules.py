@@ -1,0 +1,524 @@
+"""Forward-Laplacian rules on device triplets: mask bookkeeping on the host, arithmetic in kernels.
+
+Each public function here is one entry of the rule registry (``registry.py``) and mirrors one
+reference rule: same inputs, same output triplet, the same index map, and the same decisions
+about when a sparse Jacobian is kept, merged or densified.  The arithmetic itself is always a
+call into the C ABI (``kernels.py`` / ``sparse.py``).
+
+Shapes are *physical*: when the function is mapped over walkers the arrays carry one leading
+batch axis along which every index map has size 1 (``batch_dims`` says how many).
+"""
+
+from __future__ import annotations
+
+import logging
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from . import kernels, masks, sparse
+from .api import JAC_DIM, FunctionFlags, FwdJacobian, FwdLaplArray
+
+Arr = FwdLaplArray
+
+
+def is_triplet(x) -> bool:
+    return isinstance(x, FwdLaplArray)
+
+
+# ------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------
+def _mask_nd(a: Arr) -> np.ndarray | None:
+    """Index map with exactly ``x.ndim + 1`` axes (missing leading position axes become size 1)."""
+    m = a.jacobian.x0_idx
+    if m is None:
+        return None
+    want = a.x.ndim + 1
+    if m.ndim < want:
+        m = m.reshape(m.shape[0], *([1] * (want - m.ndim)), *m.shape[1:])
+    return m
+
+
+def _with_rows(a: Arr, rows: int) -> Arr:
+    """Dense triplet zero-padded to ``rows`` Jacobian rows (folx/utils.py:432-450)."""
+    K = a.jacobian.data.shape[0]
+    if K == rows:
+        return a
+    out = kernels.alloc_triplet(rows, a.x.shape, a.x.device, None)
+    out.x.copy_(a.x)
+    out.jacobian.data[:K].copy_(a.jacobian.data)
+    out.jacobian.data[K:].zero_()
+    out.laplacian.copy_(a.laplacian)
+    return out
+
+
+def densify(a: Arr) -> Arr:
+    """Triplet with a dense Jacobian of ``max_n + 1`` rows (reference: FwdLaplArray.dense)."""
+    if not a.jacobian.weak:
+        return a
+    return FwdLaplArray(a.x, FwdJacobian(a.jacobian.dense_array), a.laplacian)
+
+
+def broadcast_triplet(a: Arr, shape: Sequence[int]) -> Arr:
+    """Triplet expanded to ``shape`` (views; the kernels' front makes them contiguous)."""
+    shape = tuple(shape)
+    if tuple(a.x.shape) == shape:
+        return a
+    K = a.jacobian.data.shape[0]
+    nd = len(shape)
+    x = a.x.reshape((1,) * (nd - a.x.ndim) + tuple(a.x.shape)).expand(shape)
+    l = a.laplacian.reshape((1,) * (nd - a.x.ndim) + tuple(a.x.shape)).expand(shape)
+    j = a.jacobian.data.reshape(K, *((1,) * (nd - a.x.ndim)), *a.x.shape).expand(K, *shape)
+    m = _mask_nd(a)
+    if m is not None:
+        m = m.reshape(m.shape[0], *((1,) * (nd + 1 - m.ndim)), *m.shape[1:])
+    return FwdLaplArray(x, FwdJacobian(j, m), l)
+
+
+def _merged_duplicates(a: Arr, threshold: int) -> Arr:
+    """Rows that name the same input at a position summed: the per-position union frame.
+
+    Used only for Hessian terms (reference: find_out_idx + _materialize_args_for_idx,
+    folx/hessian.py:472-501); the propagated Jacobian keeps its own rows.
+    """
+    m, _ = masks.compact_repeated_dims_except(_mask_nd(a), JAC_DIM)
+    idx = np.moveaxis(masks.per_position_sorted_unique(np.moveaxis(m, 0, -1)), -1, 0)
+    data = a.jacobian.materialize_for_idx(masks.get_index_mask(m, idx), idx.shape[0])
+    return FwdLaplArray(a.x, FwdJacobian(data, idx), a.laplacian)
+
+
+# ------------------------------------------------------------------------------------------
+# elementwise (reference: wrap_forward_laplacian(f, in_axes=()), folx/wrapped_functions.py:384-431)
+# ------------------------------------------------------------------------------------------
+_TORCH_UNARY = {
+    'tanh': torch.tanh, 'silu': torch.nn.functional.silu, 'exp': torch.exp, 'log': torch.log,
+    'sqrt': torch.sqrt, 'rsqrt': torch.rsqrt, 'square': torch.square, 'sigmoid': torch.sigmoid,
+    'softplus': torch.nn.functional.softplus, 'sin': torch.sin, 'cos': torch.cos, 'neg': torch.neg,
+    'abs': torch.abs, 'reciprocal': torch.reciprocal,
+}
+_LINEAR_UNARY = {'neg', 'abs', 'scale', 'shift'}
+
+
+def elementwise(op: str, a, param: float = 0.0, sparsity_threshold: int = 0):
+    if not is_triplet(a):
+        if op == 'integer_pow':
+            return a ** int(param)
+        if op == 'scale':
+            return a * param
+        if op == 'shift':
+            return a + param
+        return _TORCH_UNARY[op](a)
+    out = kernels.elementwise(op, a, param)
+    if op not in _LINEAR_UNARY and a.jacobian.weak and masks.has_duplicate_x0_idx(_mask_nd(a)):
+        # the sum-of-squares identity needs one row per input and position (folx/hessian.py:460-470):
+        # take the Laplacian from the merged frame, keep the Jacobian rows as they are
+        merged = kernels.elementwise(op, _merged_duplicates(a, sparsity_threshold), param)
+        out = FwdLaplArray(out.x, out.jacobian, merged.laplacian)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# binary ops (reference: add/sub LINEAR, mul MULTIPLICATION, div with div_jac_hessian_jac;
+# folx/wrapped_functions.py:364-383, jvp dispatch folx/jvp.py:804-819)
+# ------------------------------------------------------------------------------------------
+def _const_binary(op: str, a: Arr, c, reverse: bool, threshold: int):
+    """triplet (op) constant, or constant (op) triplet when ``reverse``."""
+    if not torch.is_tensor(c) or c.numel() == 1:
+        s = float(c)
+        if op == 'add':
+            return elementwise('shift', a, s)
+        if op == 'sub':
+            return elementwise('shift', elementwise('neg', a), s) if reverse else elementwise('shift', a, -s)
+        if op == 'mul':
+            return elementwise('scale', a, s)
+        if reverse:
+            return elementwise('scale', elementwise('reciprocal', a, 0.0, threshold), s)
+        return elementwise('scale', a, 1.0 / s)
+    c = c.to(a.x.dtype)
+    shape = tuple(torch.broadcast_shapes(a.x.shape, c.shape))
+    a = broadcast_triplet(a, shape)
+    nonlinear_in_a = op == 'div' and reverse
+    if nonlinear_in_a and a.jacobian.weak and masks.has_duplicate_x0_idx(_mask_nd(a)):
+        lin = kernels.binary(op, c.expand(shape).contiguous(), a)
+        mer = kernels.binary(op, c.expand(shape).contiguous(), _merged_duplicates(a, threshold))
+        return FwdLaplArray(lin.x, lin.jacobian, mer.laplacian)
+    if reverse:
+        return kernels.binary(op, c.expand(shape).contiguous(), a)
+    trailing = tuple(c.shape) == shape[len(shape) - c.ndim:] if c.ndim else True
+    return kernels.binary(op, a, c.contiguous() if trailing else c.expand(shape).contiguous())
+
+
+def _align_rows(a: Arr, row_of: np.ndarray, n_rows: int, shape) -> Arr:
+    """Moves stored row r to output row ``row_of[r]`` (rows with the same target are summed)."""
+    K = a.jacobian.data.shape[0]
+    take = masks.gather_table(row_of.reshape(1, K), n_rows)  # (1, n_rows, n_slots)
+    take = np.transpose(take, (1, 2, 0))
+    data = sparse.gather_rows(a.jacobian.data, take.reshape(n_rows, take.shape[1]), tuple(shape), ())
+    return FwdLaplArray(a.x, FwdJacobian(data, None), a.laplacian)
+
+
+def binary(op: str, a, b, sparsity_threshold: int = 0):
+    ta, tb = is_triplet(a), is_triplet(b)
+    if not ta and not tb:
+        return {'add': torch.add, 'sub': torch.sub, 'mul': torch.mul, 'div': torch.div}[op](a, b)
+    if ta != tb:
+        return _const_binary(op, a if ta else b, b if ta else a, reverse=tb, threshold=sparsity_threshold)
+    shape = tuple(torch.broadcast_shapes(a.x.shape, b.x.shape))
+    if not (a.jacobian.weak and b.jacobian.weak):
+        # any dense operand makes the result dense (folx/api.py:233-236)
+        a, b = densify(a), densify(b)
+        rows = max(a.jacobian.data.shape[0], b.jacobian.data.shape[0])
+        a, b = _with_rows(a, rows), _with_rows(b, rows)
+        b_trailing = tuple(a.x.shape) == shape and tuple(b.x.shape) == shape[len(shape) - b.x.ndim:]
+        if not b_trailing:
+            b = broadcast_triplet(b, shape)
+        return kernels.binary(op, broadcast_triplet(a, shape), b)
+    # both sparse: rows with identical index maps are merged, the others are kept side by side
+    a, b = broadcast_triplet(a, shape), broadcast_triplet(b, shape)
+    ma, mb = masks.broadcast_except([_mask_nd(a), _mask_nd(b)], JAC_DIM)
+    result_mask, inv = masks.union_rows([ma, mb])
+    Ka = ma.shape[0]
+    n_rows = result_mask.shape[0]
+    in_place = (Ka == n_rows == mb.shape[0] and np.array_equal(inv[:Ka], np.arange(Ka))
+                and np.array_equal(inv[Ka:], np.arange(Ka)))
+    # equal, already ordered index maps: rows correspond one to one and nothing has to move
+    aa = a if in_place else _align_rows(a, inv[:Ka], n_rows, shape)
+    bb = b if in_place else _align_rows(b, inv[Ka:], n_rows, shape)
+    out = kernels.binary(op, aa, bb, x0_idx=result_mask)
+    if op in ('mul', 'div') and masks.has_duplicate_x0_idx(result_mask):
+        # two rows of the union may name the same input at a position (e.g. the i == j pairs of
+        # r_i - r_j); the Hessian term then needs the per-position frame (folx/hessian.py:472-501)
+        am, bm = _merged_pair(a, b)
+        fix = kernels.binary(op, am, bm)
+        out = FwdLaplArray(out.x, out.jacobian, fix.laplacian)
+    return out
+
+
+def _merged_pair(a: Arr, b: Arr):
+    ma, mb = masks.broadcast_except([_mask_nd(a), _mask_nd(b)], JAC_DIM)
+    both = np.concatenate([ma, mb], axis=0)
+    both_c, _ = masks.compact_repeated_dims_except(both, JAC_DIM)
+    idx = np.moveaxis(masks.per_position_sorted_unique(np.moveaxis(both_c, 0, -1)), -1, 0)
+    M = idx.shape[0]
+    am = FwdLaplArray(a.x, FwdJacobian(a.jacobian.materialize_for_idx(masks.get_index_mask(ma, idx), M)), a.laplacian)
+    bm = FwdLaplArray(b.x, FwdJacobian(b.jacobian.materialize_for_idx(masks.get_index_mask(mb, idx), M)), b.laplacian)
+    return am, bm
+
+
+# ------------------------------------------------------------------------------------------
+# dot_general with one constant operand (reference: folx/wrapped_functions.py:71-171)
+# ------------------------------------------------------------------------------------------
+def dot_general(a, W, bias=None, sparsity_threshold: int = 0):
+    """``y = a @ W (+ bias)`` contracting the last axis of the triplet with the first of ``W``."""
+    if not is_triplet(a):
+        y = a @ W
+        return y if bias is None else y + bias
+    x0 = _mask_nd(a)
+    if x0 is None:
+        return kernels.dot_general(a, W, bias, None)
+    last = a.x.ndim - 1
+    K = a.jacobian.data.shape[0]
+    if masks.mask_varies_along(x0, [last + 1]):
+        # rows are first aligned to the per-position union over the contracted axis
+        out_mask, (targets,) = masks.reduction_frame([x0], (last,))
+        M = out_mask.shape[0]
+        if M > sparsity_threshold:
+            logging.info(f'dot_general: union of {M} rows exceeds the sparsity threshold '
+                         f'({sparsity_threshold}); switching to dense.')
+            return kernels.dot_general(densify(a), W, bias, None)
+        data = a.jacobian.materialize_for_idx(targets, M)
+        a = FwdLaplArray(a.x, FwdJacobian(data, None), a.laplacian)
+        proj = out_mask.reshape(M, *out_mask.shape[1:], 1)
+    else:
+        proj = np.take(x0, [0], axis=last + 1)
+    return kernels.dot_general(a, W, bias, proj)
+
+
+# ------------------------------------------------------------------------------------------
+# reduce_sum (reference: SUMMATION rule, folx/wrapped_functions.py:387-391; sparse path
+# sparse_sum_jvp, folx/jvp.py:89-176; dense path is linear, folx/jvp.py:676-684)
+# ------------------------------------------------------------------------------------------
+def _adjacent_axes_last_stride(x: torch.Tensor, axes: tuple[int, ...]):
+    """If ``axes`` form one strided run in contiguous ``x``: (count, stride) of the merged axis."""
+    axes = tuple(sorted(axes))
+    if any(b != a + 1 for a, b in zip(axes, axes[1:])):
+        return None
+    n = int(np.prod([x.shape[a] for a in axes], dtype=np.int64))
+    return n, x.stride(axes[-1])
+
+
+def reduce_sum(a, axes, keepdim: bool = False, sparsity_threshold: int = 0):
+    if not is_triplet(a):
+        return a.sum(dim=axes, keepdim=keepdim)
+    nd = a.x.ndim
+    axes = tuple(sorted({ax % nd for ax in (axes if isinstance(axes, (tuple, list)) else (axes,))}))
+    if not axes:
+        return a
+    a = kernels.as_contiguous(a)
+    if _adjacent_axes_last_stride(a.x, axes) is None:
+        # bring the reduced axes together (a copy; only sparse / small tensors get here in practice)
+        keep = [d for d in range(nd) if d not in axes]
+        perm = keep + list(axes)
+        a = kernels.as_contiguous(permute(a, perm))
+        axes = tuple(range(len(keep), nd))
+        out = reduce_sum(a, axes, False, sparsity_threshold)
+        if keepdim:
+            raise NotImplementedError('keepdim with non-adjacent reduced axes')
+        return out
+    K = a.jacobian.data.shape[0]
+    kept = [d for d in range(nd) if d not in axes]
+    kept_shape = tuple(a.x.shape[d] for d in kept)
+    nr, rstride = _adjacent_axes_last_stride(a.x, axes)
+    x0 = _mask_nd(a)
+
+    def reduce_rows(data, table, table_shape, n_out):
+        # data: (rows, *shape) contiguous -> (n_out, *kept_shape)
+        rows = data.shape[0]
+        view = data.reshape(rows, *a.x.shape)
+        # an input row as the kernel sees it: the kept axes only (the reduced run is addressed
+        # through n_reduced / reduced_stride)
+        idx = tuple(0 if d in axes else slice(None) for d in range(nd))
+        row_view = view[(slice(None), *idx)]
+        return sparse.gather_rows(row_view, table, kept_shape, table_shape, n_reduced=nr,
+                                  reduced_stride=rstride)
+
+    # x and the Laplacian are plain sums
+    one = np.arange(nr, dtype=np.int64).reshape(1, nr)
+    y = reduce_rows(a.x.reshape(1, *a.x.shape), one, (), 1)[0]
+    lap = reduce_rows(a.laplacian.reshape(1, *a.x.shape), one, (), 1)[0]
+
+    if x0 is None:
+        table = (np.arange(K, dtype=np.int64)[:, None] * nr + np.arange(nr)[None, :])
+        jac = reduce_rows(a.jacobian.data, table, (), K)
+        out_mask = None
+    else:
+        # along reduced axes the true extent matters (every element is a separate source); the
+        # kept axes may stay compact (size 1 where the map is constant)
+        full = np.broadcast_to(x0, (K, *[a.x.shape[d] if d in axes else x0.shape[1 + d] for d in range(nd)]))
+        idx_out, targets = masks.sum_outdeps(full, axes)  # (M, *kept_c), (K, *shape_c)
+        M = idx_out.shape[0]
+        dense_out = M > sparsity_threshold
+        if dense_out:
+            logging.info(f'reduce_sum: output ({M}) reaches the sparsity threshold '
+                         f'({sparsity_threshold}); switching to dense.')
+            n_out = int(full.max()) + 1
+            targets = np.where(full >= 0, full, -1).astype(np.int64)
+            out_mask = None
+        else:
+            n_out = M
+            out_mask = idx_out
+        # sources per kept position: (k, reduced element); table positions are the kept axes
+        # along which the index map varies
+        kept_c = tuple(targets.shape[1 + d] for d in kept)
+        t = np.transpose(targets, [1 + d for d in kept] + [0] + [1 + d for d in axes])
+        t = t.reshape(int(np.prod(kept_c, dtype=np.int64)), K * nr)
+        take = masks.gather_table(t, n_out)  # (p, n_out, n_slots), entries k * nr + r
+        take = np.transpose(take, (1, 2, 0)).reshape(n_out, take.shape[2], *kept_c)
+        jac = reduce_rows(a.jacobian.data, take, kept_c, n_out)
+    out = FwdLaplArray(y, FwdJacobian(jac, out_mask), lap)
+    if keepdim:
+        for d in axes:
+            out = expand_dims(out, d)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# indexing ops: the same operation is applied to x, every Jacobian row, the Laplacian and the
+# index map (reference: INDEXING rules, folx/wrapped_functions.py:457-508; sparse_index_jvp,
+# folx/jvp.py:330-413)
+# ------------------------------------------------------------------------------------------
+def _index_op(a: Arr, fx, fj, fm) -> Arr:
+    m = _mask_nd(a)
+    if m is not None:
+        K = m.shape[0]
+        # expand the map over the per-sample axes the op may mix; batch-like axes where the map is
+        # constant AND x is large stay size 1
+        m = fm(m)
+    return FwdLaplArray(fx(a.x), FwdJacobian(fj(a.jacobian.data), m), fx(a.laplacian))
+
+
+def _full_mask_keep_batch(a: Arr, batch_dims: int) -> np.ndarray | None:
+    """Index map expanded to the full per-sample shape, size 1 along the leading batch axes."""
+    m = _mask_nd(a)
+    if m is None:
+        return None
+    shape = [1 if d < batch_dims else s for d, s in enumerate(a.x.shape)]
+    return np.broadcast_to(m, (m.shape[0], *shape))
+
+
+def reshape(a, shape, batch_dims: int = 0):
+    if not is_triplet(a):
+        return a.reshape(shape)
+    shape = tuple(shape)
+    K = a.jacobian.data.shape[0]
+    x = a.x.reshape(shape)
+    m = _full_mask_keep_batch(a, batch_dims)
+    if m is not None:
+        mshape = tuple(1 if d < batch_dims else s for d, s in enumerate(x.shape))
+        m = m.reshape(K, *mshape)
+    return FwdLaplArray(x, FwdJacobian(a.jacobian.data.reshape(K, *x.shape), m), a.laplacian.reshape(x.shape))
+
+
+def permute(a, perm):
+    if not is_triplet(a):
+        return a.permute(*perm)
+    perm = tuple(p % a.x.ndim for p in perm)
+    jperm = (0, *[p + 1 for p in perm])
+    m = _mask_nd(a)
+    return FwdLaplArray(a.x.permute(perm), FwdJacobian(a.jacobian.data.permute(jperm),
+                        None if m is None else np.transpose(m, jperm)), a.laplacian.permute(perm))
+
+
+def expand_dims(a, axis: int):
+    if not is_triplet(a):
+        return a.unsqueeze(axis)
+    axis = axis % (a.x.ndim + 1)
+    m = _mask_nd(a)
+    return FwdLaplArray(a.x.unsqueeze(axis), FwdJacobian(a.jacobian.data.unsqueeze(axis + 1),
+                        None if m is None else np.expand_dims(m, axis + 1)), a.laplacian.unsqueeze(axis))
+
+
+def squeeze(a, axis: int):
+    if not is_triplet(a):
+        return a.squeeze(axis)
+    axis = axis % a.x.ndim
+    assert a.x.shape[axis] == 1
+    m = _mask_nd(a)
+    return FwdLaplArray(a.x.squeeze(axis), FwdJacobian(a.jacobian.data.squeeze(axis + 1),
+                        None if m is None else np.squeeze(m, axis + 1)), a.laplacian.squeeze(axis))
+
+
+def broadcast_to(a, shape):
+    if not is_triplet(a):
+        return a.expand(shape)
+    return broadcast_triplet(a, tuple(shape))
+
+
+def getitem(a, index, batch_dims: int = 0):
+    """Basic (static) indexing: ints, slices, ``None`` and ``Ellipsis``."""
+    if not is_triplet(a):
+        return a[index]
+    if not isinstance(index, tuple):
+        index = (index,)
+    for it in index:
+        if not (isinstance(it, (int, slice)) or it is None or it is Ellipsis):
+            raise NotImplementedError('only static basic indexing is supported on triplets')
+    m = _full_mask_keep_batch(a, batch_dims)
+    jidx = (slice(None), *index)
+    if m is not None:
+        # an index that selects inside a batch axis does not change the (batch-constant) map
+        midx = []
+        d = 0
+        for it in index:
+            if it is Ellipsis:
+                midx.append(it)
+                d = a.x.ndim  # everything after an ellipsis counts from the right: never batch
+                continue
+            if it is None:
+                midx.append(it)
+                continue
+            if d < batch_dims:
+                midx.append(0 if isinstance(it, int) else slice(None))
+            else:
+                midx.append(it)
+            d += 1
+        m = m[(slice(None), *midx)]
+    return FwdLaplArray(a.x[index], FwdJacobian(a.jacobian.data[jidx], m), a.laplacian[index])
+
+
+def concatenate(arrs: Sequence, axis: int, batch_dims: int = 0):
+    """``cat`` of triplets and constants (reference: concatenate as INDEXING with
+    index_static_args=(), folx/wrapped_functions.py:474-479; mixed sparse rows are padded with
+    ``-1`` / zeros, folx/jvp.py:382-401; any dense operand densifies all, folx/jvp.py:728-730)."""
+    if not any(is_triplet(t) for t in arrs):
+        return torch.cat(list(arrs), dim=axis)
+    first = next(t for t in arrs if is_triplet(t))
+    nd = first.x.ndim
+    axis = axis % nd
+    trip = [t for t in arrs if is_triplet(t)]
+    all_sparse = all(t.jacobian.weak for t in trip)
+    if not all_sparse:
+        trip_d = [densify(t) for t in trip]
+        rows = max(t.jacobian.data.shape[0] for t in trip_d)
+    else:
+        rows = max(t.jacobian.data.shape[0] for t in trip)
+    dev, dt = first.x.device, first.x.dtype
+    total = sum((t.x.shape[axis] if is_triplet(t) else t.shape[axis]) for t in arrs)
+    out_shape = list(first.x.shape)
+    out_shape[axis] = total
+    out = kernels.alloc_triplet(rows, out_shape, dev, None)
+    mparts = []
+    off = 0
+    it = iter(trip_d if not all_sparse else trip)
+    for t in arrs:
+        n = t.x.shape[axis] if is_triplet(t) else t.shape[axis]
+        sl = [slice(None)] * nd
+        sl[axis] = slice(off, off + n)
+        sl = tuple(sl)
+        jsl = (slice(None), *sl)
+        if is_triplet(t):
+            t = next(it)
+            k = t.jacobian.data.shape[0]
+            out.x[sl].copy_(t.x)
+            out.laplacian[sl].copy_(t.laplacian)
+            out.jacobian.data[(slice(0, k), *sl)].copy_(t.jacobian.data)
+            if k < rows:
+                out.jacobian.data[(slice(k, rows), *sl)].zero_()
+            if all_sparse:
+                m = _full_mask_keep_batch(t, batch_dims)
+                pad = np.full((rows - k, *m.shape[1:]), -1, dtype=m.dtype)
+                mparts.append(np.concatenate([m, pad], axis=0))
+        else:
+            out.x[sl].copy_(t.to(dt).expand(out.x[sl].shape))
+            out.laplacian[sl].zero_()
+            out.jacobian.data[jsl].zero_()
+            if all_sparse:
+                shp = [1 if d < batch_dims else s for d, s in enumerate(out.x[sl].shape)]
+                mparts.append(np.full((rows, *shp), -1, dtype=np.int64))
+        off += n
+    mask = np.concatenate(mparts, axis=axis + 1) if all_sparse else None
+    return FwdLaplArray(out.x, FwdJacobian(out.jacobian.data, mask), out.laplacian)
+
+
+# ------------------------------------------------------------------------------------------
+# composite rules with fused kernels
+# ------------------------------------------------------------------------------------------
+def layer_norm(a, gamma=None, beta=None, eps: float = 1e-6, sparsity_threshold: int = 0):
+    """LayerNorm over the last axis (fused form of the rule chain, see ``fl_layernorm``)."""
+    if not is_triplet(a):
+        return torch.nn.functional.layer_norm(a, a.shape[-1:], gamma, beta, eps)
+    m = _mask_nd(a)
+    if m is not None and (masks.mask_varies_along(m, [a.x.ndim]) or masks.has_duplicate_x0_idx(m)):
+        # the mean over features would merge different index sets: same outcome as the
+        # reference's reduce_sum going dense
+        a = densify(a)
+    return kernels.layernorm(a, gamma, beta, eps)
+
+
+def slogdet(a, sparsity_threshold: int = 0):
+    """``(sign, log|det|)`` over the last two axes (reference: folx/slogdet.py:347-358)."""
+    if not is_triplet(a):
+        s, l = torch.linalg.slogdet(a)
+        return s, l
+    return kernels.slogdet(a)
+
+
+def mhsa(q, k, v, mask=None, input_mask=None, sparsity_threshold: int = 0):
+    """Fused attention rule (reference: mhsa_forward_laplacian)."""
+    if not any(is_triplet(t) for t in (q, k, v)):
+        s = torch.einsum('bihd,bjhd->bhij', q, k)
+        if mask is not None:
+            sq = mask[:, :, None] & mask[:, None, :]
+            s = torch.where(sq[:, None], s, torch.full_like(s, -1e20))
+        return torch.einsum('bhij,bjhd->bihd', torch.softmax(s, -1), v)
+    R = max(t.jacobian.max_n + 1 if t.jacobian.weak else t.jacobian.data.shape[0]
+            for t in (q, k, v) if is_triplet(t))
+    trip = []
+    for t in (q, k, v):
+        if not is_triplet(t):
+            t = FwdLaplArray(t, FwdJacobian(torch.zeros((R, *t.shape), dtype=t.dtype, device=t.device)),
+                             torch.zeros_like(t))
+        trip.append(t)
+    return kernels.mhsa(*trip, mask=mask, input_mask=input_mask)

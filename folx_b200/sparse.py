@@ -37,12 +37,15 @@ def _i64(vals):
 
 
 def gather_rows(data: torch.Tensor, take: np.ndarray, out_shape: tuple[int, ...],
-                table_shape: tuple[int, ...]) -> torch.Tensor:
+                table_shape: tuple[int, ...], n_reduced: int = 1, reduced_stride: int = 0,
+                out: torch.Tensor | None = None) -> torch.Tensor:
     """``out[o, pos] = sum_s data[take[o, s, tpos(pos)], pos]``.
 
     ``data``: ``(k_in, *in_shape)`` broadcastable to ``out_shape``; ``take``: ``(k_out, n_slots,
     *table_shape)`` with ``table_shape`` broadcastable to ``out_shape`` (size-1 axes: constant).
-    Returns ``(k_out, *out_shape)``.
+    With ``n_reduced > 1`` an entry is ``row * n_reduced + r`` and addresses element ``r`` of a
+    reduced axis of ``data`` whose stride is ``reduced_stride`` (that axis is not part of
+    ``out_shape`` / ``in_shape``).  Returns ``(k_out, *out_shape)``.
     """
     _require_cuda(data)
     nd = len(out_shape)
@@ -50,15 +53,15 @@ def gather_rows(data: torch.Tensor, take: np.ndarray, out_shape: tuple[int, ...]
     k_out, n_slots = take.shape[0], take.shape[1]
     in_shape = (1,) * (nd - (data.ndim - 1)) + tuple(data.shape[1:])
     tshape = (1,) * (nd - len(table_shape)) + tuple(table_shape)
-    if k_in > 0:
-        row = data[0].reshape(in_shape) if data[0].is_contiguous() else None
-        if row is None or (k_in > 1 and data.stride(0) < row.numel()):
-            data = data.contiguous()
-            row = data[0].reshape(in_shape)
-        in_strides = [0 if in_shape[d] == 1 else row.stride(d) for d in range(nd)]
-        in_row_stride = data.stride(0) if k_in > 1 else max(row.numel(), 1)
-    else:
-        in_strides, in_row_stride = [0] * nd, 1
+    # the kernel addresses the input through explicit strides, so views (slices, expanded or
+    # permuted tensors) are read in place
+    lead = nd - (data.ndim - 1)
+    in_strides = [0] * lead + [0 if data.shape[1 + d] == 1 else data.stride(1 + d)
+                               for d in range(data.ndim - 1)]
+    in_row_stride = data.stride(0) if k_in > 1 else 1
+    if any(st < 0 for st in in_strides):
+        data = data.contiguous()
+        return gather_rows(data, take, out_shape, table_shape, n_reduced, reduced_stride, out)
     # row-major strides of the table's position box; constant axes get stride 0
     tstrides, acc = [0] * nd, 1
     for d in range(nd - 1, -1, -1):
@@ -68,12 +71,13 @@ def gather_rows(data: torch.Tensor, take: np.ndarray, out_shape: tuple[int, ...]
     # merge axes beyond the kernel's limit is not needed for the shapes used here
     if nd > 6:
         raise ValueError('gather_rows: more than 6 position axes')
-    out = torch.empty((k_out, *out_shape), dtype=torch.float32, device=data.device)
+    if out is None:
+        out = torch.empty((k_out, *out_shape), dtype=torch.float32, device=data.device)
     N = int(np.prod(out_shape, dtype=np.int64))
     table = _device_table(take.reshape(k_out, n_slots, -1), data.device)
     lib.call('fl_gather_rows', _ptr(data), k_in, in_row_stride, _ptr(table), k_out, n_slots,
-             _ptr(out), max(N, 1), nd, _i64(out_shape), _i64(in_strides), _i64(tstrides),
-             _stream(data.device))
+             _ptr(out), out.stride(0) if k_out > 1 else max(N, 1), nd, _i64(out_shape),
+             _i64(in_strides), _i64(tstrides), n_reduced, reduced_stride, _stream(data.device))
     return out
 
 

@@ -1,0 +1,245 @@
+"""Wavefunction networks the forward Laplacian is benchmarked on.
+
+The reference ships no models; its README and the benchmark configurations describe them in
+words (an MLP on (100, 4) inputs; a FermiNet-style and a PsiFormer-style log|psi|).  The
+definitions below are written once, against the tensor API, and run unchanged on plain tensors
+(fp64 on the CPU for the brute-force oracle) and on ``LaplTensor``s (the kernels): parity tests
+evaluate the SAME function on both sides.
+
+Every function maps ONE walker's electron coordinates ``r: (N, 3)`` to a scalar.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn.functional as F
+
+from .attention import multi_head_self_attention
+
+
+def _normal(gen, *shape, fan_in=None, scale=None):
+    w = torch.randn(*shape, generator=gen)
+    if fan_in is not None:
+        w = w / math.sqrt(fan_in)
+    if scale is not None:
+        w = w * scale
+    return w
+
+
+def tree_to(params, device=None, dtype=None):
+    if isinstance(params, dict):
+        return {k: tree_to(v, device, dtype) for k, v in params.items()}
+    if isinstance(params, (list, tuple)):
+        return type(params)(tree_to(v, device, dtype) for v in params)
+    if torch.is_tensor(params):
+        return params.to(device=device, dtype=dtype if params.is_floating_point() else None)
+    return params
+
+
+# ------------------------------------------------------------------------------------------
+# README MLP (reference: README.md:43-70): 10 x (Dense(100) + SiLU), Dense(1), summed
+# ------------------------------------------------------------------------------------------
+def mlp_params(seed: int = 0, in_dim: int = 4, width: int = 100, depth: int = 10):
+    gen = torch.Generator().manual_seed(seed)
+    dims = [in_dim] + [width] * depth + [1]
+    # lecun-normal kernels, zero biases (flax defaults)
+    return [( _normal(gen, a, b, fan_in=a), torch.zeros(b)) for a, b in zip(dims[:-1], dims[1:])]
+
+
+def mlp(params, x):
+    """``x: (nodes, in_dim)`` -> scalar."""
+    h = x
+    for W, b in params[:-1]:
+        h = F.silu(F.linear(h, W.t(), b))
+    W, b = params[-1]
+    return F.linear(h, W.t(), b).sum()
+
+
+# ------------------------------------------------------------------------------------------
+# shared input features
+# ------------------------------------------------------------------------------------------
+def electron_nucleus(r, nuclei):
+    """``r_en: (N, M, 3)`` and ``|r_en|: (N, M)``."""
+    r_en = r.unsqueeze(1) - nuclei
+    return r_en, (r_en * r_en).sum(-1).sqrt()
+
+
+def electron_electron(r, eye):
+    """``r_ee: (N, N, 3)`` and ``|r_ee|: (N, N)`` with a differentiable zero on the diagonal
+    (the norm is taken of ``r_ee^2 + 1`` there and multiplied by 0)."""
+    r_ee = r.unsqueeze(1) - r.unsqueeze(0)
+    d = ((r_ee * r_ee).sum(-1) + eye).sqrt() * (1.0 - eye)
+    return r_ee, d
+
+
+def envelopes(d_en, sigma, pi):
+    """``sum_m pi[m, k] exp(-sigma[m, k] d_en[i, m])`` -> ``(N, K)``."""
+    return ((d_en.unsqueeze(-1) * (-sigma)).exp() * pi).sum(1)
+
+
+def log_abs_sum_of_determinants(orb_up, orb_dn):
+    """``log |sum_k det(up_k) det(dn_k)|`` from ``(n_det, n, n)`` orbital matrices."""
+    s_u, l_u = torch.linalg.slogdet(orb_up)
+    s_d, l_d = torch.linalg.slogdet(orb_dn)
+    logdet = l_u + l_d
+    sign = s_u * s_d
+    m = logdet.detach().amax(-1, keepdim=True)
+    return ((logdet - m).exp() * sign).sum(-1).abs().log() + m.squeeze(-1)
+
+
+# ------------------------------------------------------------------------------------------
+# FermiNet-style wavefunction
+# ------------------------------------------------------------------------------------------
+@dataclass
+class FermiNetConfig:
+    n_elec: int = 16
+    n_up: int = 8
+    n_nuc: int = 4
+    layers: int = 4
+    width1: int = 256
+    width2: int = 32
+    n_det: int = 16
+    seed: int = 0
+
+
+def ferminet_params(cfg: FermiNetConfig):
+    gen = torch.Generator().manual_seed(cfg.seed)
+    M, n_dn = cfg.n_nuc, cfg.n_elec - cfg.n_up
+    p = {'nuclei': (torch.rand(M, 3, generator=gen) * 4.0 - 2.0), 'layers': []}
+    d1, d2 = 4 * M, 4
+    for l in range(cfg.layers):
+        fan = 3 * d1 + 2 * d2
+        layer = {
+            'W_h': _normal(gen, d1, cfg.width1, fan_in=fan), 'W_up': _normal(gen, d1, cfg.width1, fan_in=fan),
+            'W_dn': _normal(gen, d1, cfg.width1, fan_in=fan), 'W_2u': _normal(gen, d2, cfg.width1, fan_in=fan),
+            'W_2d': _normal(gen, d2, cfg.width1, fan_in=fan), 'b': _normal(gen, cfg.width1, scale=0.1),
+        }
+        if l < cfg.layers - 1:
+            layer['V'] = _normal(gen, d2, cfg.width2, fan_in=d2)
+            layer['c'] = _normal(gen, cfg.width2, scale=0.1)
+        p['layers'].append(layer)
+        d1, d2 = cfg.width1, cfg.width2
+    n_orb = cfg.n_det * max(cfg.n_up, n_dn)
+    p['W_orb_up'] = _normal(gen, cfg.width1, cfg.n_det * cfg.n_up, fan_in=cfg.width1)
+    p['W_orb_dn'] = _normal(gen, cfg.width1, cfg.n_det * n_dn, fan_in=cfg.width1)
+    p['sigma_up'] = torch.rand(M, cfg.n_det * cfg.n_up, generator=gen) * 0.5 + 0.5
+    p['pi_up'] = torch.rand(M, cfg.n_det * cfg.n_up, generator=gen) * 0.5 + 0.5
+    p['sigma_dn'] = torch.rand(M, cfg.n_det * n_dn, generator=gen) * 0.5 + 0.5
+    p['pi_dn'] = torch.rand(M, cfg.n_det * n_dn, generator=gen) * 0.5 + 0.5
+    p['eye'] = torch.eye(cfg.n_elec)
+    del n_orb
+    return p
+
+
+def ferminet(cfg: FermiNetConfig, p, r):
+    """``log|psi|(r)`` for ``r: (n_elec, 3)``.
+
+    One- and two-electron streams with mean pooling per spin; the layer input
+    ``[h_i, mean_up h, mean_dn h, mean_up g_i., mean_dn g_i.]`` is never concatenated: its weight
+    matrix is kept in blocks and the pooled terms (one row per walker) are added after their own
+    small products.
+    """
+    N, nu = cfg.n_elec, cfg.n_up
+    r_en, d_en = electron_nucleus(r, p['nuclei'])
+    r_ee, d_ee = electron_electron(r, p['eye'])
+    h = torch.cat([r_en.reshape(N, -1), d_en], -1)           # (N, 4 M)
+    g = torch.cat([r_ee, d_ee.unsqueeze(-1)], -1)            # (N, N, 4)
+    for l, layer in enumerate(p['layers']):
+        pooled = (h[:nu].mean(0) @ layer['W_up'] + h[nu:].mean(0) @ layer['W_dn'])  # (width,)
+        pair = g[:, :nu].mean(1) @ layer['W_2u'] + g[:, nu:].mean(1) @ layer['W_2d']  # (N, width)
+        new_h = (F.linear(h, layer['W_h'].t(), layer['b']) + pair + pooled).tanh()
+        h = new_h + h if new_h.shape == h.shape else new_h
+        if 'V' in layer:
+            new_g = F.linear(g, layer['V'].t(), layer['c']).tanh()
+            g = new_g + g if new_g.shape == g.shape else new_g
+    n_dn = N - nu
+    orb_up = (h[:nu] @ p['W_orb_up']) * envelopes(d_en[:nu], p['sigma_up'], p['pi_up'])   # (nu, n_det nu)
+    orb_dn = (h[nu:] @ p['W_orb_dn']) * envelopes(d_en[nu:], p['sigma_dn'], p['pi_dn'])
+    orb_up = orb_up.reshape(nu, cfg.n_det, nu).permute(1, 0, 2)
+    orb_dn = orb_dn.reshape(n_dn, cfg.n_det, n_dn).permute(1, 0, 2)
+    return log_abs_sum_of_determinants(orb_up, orb_dn)
+
+
+# ------------------------------------------------------------------------------------------
+# PsiFormer-style wavefunction
+# ------------------------------------------------------------------------------------------
+@dataclass
+class PsiFormerConfig:
+    n_elec: int = 32
+    n_up: int = 16
+    n_nuc: int = 8
+    layers: int = 4
+    dim: int = 256
+    heads: int = 4
+    n_det: int = 16
+    seed: int = 0
+
+
+def psiformer_params(cfg: PsiFormerConfig):
+    gen = torch.Generator().manual_seed(cfg.seed)
+    M, D = cfg.n_nuc, cfg.dim
+    n_dn = cfg.n_elec - cfg.n_up
+    p = {'nuclei': torch.rand(M, 3, generator=gen) * 4.0 - 2.0,
+         'W_in': _normal(gen, 4 * M, D, fan_in=4 * M), 'b_in': _normal(gen, D, scale=0.1),
+         'spin': torch.cat([_normal(gen, 1, D, scale=0.1).expand(cfg.n_up, D),
+                            _normal(gen, 1, D, scale=0.1).expand(n_dn, D)]).contiguous(),
+         'layers': []}
+    for _ in range(cfg.layers):
+        p['layers'].append({
+            'Wq': _normal(gen, D, D, fan_in=D), 'Wk': _normal(gen, D, D, fan_in=D),
+            'Wv': _normal(gen, D, D, fan_in=D), 'Wo': _normal(gen, D, D, fan_in=D),
+            'W1': _normal(gen, D, D, fan_in=D), 'b1': _normal(gen, D, scale=0.1),
+            'W2': _normal(gen, D, D, fan_in=D), 'b2': _normal(gen, D, scale=0.1),
+            'g1': torch.ones(D), 'be1': torch.zeros(D), 'g2': torch.ones(D), 'be2': torch.zeros(D),
+        })
+    p['W_orb_up'] = _normal(gen, D, cfg.n_det * cfg.n_up, fan_in=D)
+    p['W_orb_dn'] = _normal(gen, D, cfg.n_det * n_dn, fan_in=D)
+    p['sigma_up'] = torch.rand(M, cfg.n_det * cfg.n_up, generator=gen) * 0.5 + 0.5
+    p['pi_up'] = torch.rand(M, cfg.n_det * cfg.n_up, generator=gen) * 0.5 + 0.5
+    p['sigma_dn'] = torch.rand(M, cfg.n_det * n_dn, generator=gen) * 0.5 + 0.5
+    p['pi_dn'] = torch.rand(M, cfg.n_det * n_dn, generator=gen) * 0.5 + 0.5
+    return p
+
+
+def psiformer(cfg: PsiFormerConfig, p, r):
+    """``log|psi|(r)`` for ``r: (n_elec, 3)``: embedding of electron-nucleus features, ``layers``
+    blocks of multi-head self attention + LayerNorm + tanh MLP + LayerNorm, determinants with
+    exponential envelopes."""
+    N, nu, H = cfg.n_elec, cfg.n_up, cfg.heads
+    dh = cfg.dim // H
+    r_en, d_en = electron_nucleus(r, p['nuclei'])
+    feats = torch.cat([r_en.reshape(N, -1), d_en], -1)
+    h = F.linear(feats, p['W_in'].t(), p['b_in']) + p['spin']
+    scale = 1.0 / math.sqrt(dh)
+    for layer in p['layers']:
+        q = ((h @ layer['Wq']) * scale).reshape(N, H, dh)
+        k = (h @ layer['Wk']).reshape(N, H, dh)
+        v = (h @ layer['Wv']).reshape(N, H, dh)
+        a = multi_head_self_attention(q, k, v).reshape(N, cfg.dim)
+        h = F.layer_norm(h + a @ layer['Wo'], (cfg.dim,), layer['g1'], layer['be1'], 1e-6)
+        m = F.linear(F.linear(h, layer['W1'].t(), layer['b1']).tanh(), layer['W2'].t(), layer['b2'])
+        h = F.layer_norm(h + m, (cfg.dim,), layer['g2'], layer['be2'], 1e-6)
+    n_dn = N - nu
+    orb_up = (h[:nu] @ p['W_orb_up']) * envelopes(d_en[:nu], p['sigma_up'], p['pi_up'])
+    orb_dn = (h[nu:] @ p['W_orb_dn']) * envelopes(d_en[nu:], p['sigma_dn'], p['pi_dn'])
+    orb_up = orb_up.reshape(nu, cfg.n_det, nu).permute(1, 0, 2)
+    orb_dn = orb_dn.reshape(n_dn, cfg.n_det, n_dn).permute(1, 0, 2)
+    return log_abs_sum_of_determinants(orb_up, orb_dn)
+
+
+def coulomb_potential(r: torch.Tensor, nuclei: torch.Tensor, charges: torch.Tensor | None = None):
+    """Potential energy of walkers ``r: (B, N, 3)`` in the field of ``nuclei`` (plain tensors)."""
+    B, N, _ = r.shape
+    if charges is None:
+        charges = torch.full((nuclei.shape[0],), N / nuclei.shape[0], dtype=r.dtype, device=r.device)
+    d_en = (r[:, :, None, :] - nuclei[None, None]).norm(dim=-1)
+    v = -(charges / d_en).sum((1, 2))
+    iu = torch.triu_indices(N, N, 1, device=r.device)
+    d_ee = (r[:, iu[0]] - r[:, iu[1]]).norm(dim=-1)
+    v = v + (1.0 / d_ee).sum(-1)
+    dn = (nuclei[:, None] - nuclei[None]).norm(dim=-1)
+    iu = torch.triu_indices(nuclei.shape[0], nuclei.shape[0], 1, device=r.device)
+    return v + (charges[iu[0]] * charges[iu[1]] / dn[iu[0], iu[1]]).sum()

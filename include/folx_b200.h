@@ -165,6 +165,10 @@ int32_t fl_layernorm(const float* x, const float* jac, const float* lap,
  *   jac_in : k_in rows, in_row_stride apart;  jac_out : k_out rows of prod(shape), out_row_stride apart
  *   take   : int32 [k_out][n_slots][table positions], DEVICE pointer
  *   shape / in_strides / table_strides : HOST pointers to `ndim` int64 values
+ * Reductions (sum over an axis, dense or sparse: reduce_sum, folx/wrapped_functions.py:387-391)
+ * use the same call: the reduced axis is not part of `shape`; a table entry then encodes
+ * row * n_reduced + r and reads in[row * in_row_stride + r * reduced_stride + ipos(pos)].
+ * With n_reduced == 1 an entry is simply a row number.
  * ------------------------------------------------------------------------------------------- */
 #define FL_GATHER_MAX_DIMS 6
 
@@ -172,7 +176,8 @@ int32_t fl_gather_rows(const float* jac_in, int64_t k_in, int64_t in_row_stride,
                        const int32_t* take, int64_t k_out, int64_t n_slots,
                        float* jac_out, int64_t out_row_stride,
                        int32_t ndim, const int64_t* shape, const int64_t* in_strides,
-                       const int64_t* table_strides, void* stream);
+                       const int64_t* table_strides, int64_t n_reduced, int64_t reduced_stride,
+                       void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Index-set algebra of find_out_idx on the device (folx/hessian.py:234-340), bit-exact.

@@ -1,0 +1,179 @@
+"""End-to-end parity of ``forward_laplacian`` on the GPU: whole functions through the rule
+registry and the kernels, against brute-force AD in fp64 (the identity the reference's own
+integration tests assert: test/test_operator.py:19-73, test/test_composite.py:13-83), plus the
+sparse index maps of the worked cases."""
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+import folx_b200 as folx
+from folx_b200 import wavefunctions as wf
+from oracle import brute
+
+pytestmark = pytest.mark.gpu
+
+
+def brute_force(f, x64):
+    y, J, lap = brute.jac_and_laplacian(f, x64)
+    return y, J, lap
+
+
+def check_against_brute(f_dev, f_cpu, x, thr, samples=(0,), rtol=1e-4, lap_rtol=2e-4):
+    lap_fn = folx.vmap(folx.ForwardLaplacianOperator(thr)(f_dev))
+    lap, jac = lap_fn(x)
+    assert lap.shape == (x.shape[0],) and jac.shape[0] == x.shape[0]
+    for s in samples:
+        y, J, L = brute_force(f_cpu, x[s].double().cpu())
+        n = J.numel()
+        got_j = jac[s].double().cpu().reshape(-1)
+        got_j = torch.cat([got_j, got_j.new_zeros(n - got_j.numel())])  # dense_array may be truncated
+        scale = float(J.abs().max())
+        torch.testing.assert_close(got_j, J.reshape(-1), rtol=rtol, atol=1e-5 * scale)
+        torch.testing.assert_close(lap[s].double().cpu(), L, rtol=lap_rtol, atol=2e-5 * max(float(L.abs()), scale))
+
+
+@pytest.mark.parametrize('thr', [0, 4])
+def test_readme_mlp(cuda_device, thr):
+    """BASELINE config 1: 10 x (Dense(100) + SiLU) + Dense(1), summed; x: (20, 100, 4)."""
+    params = wf.mlp_params(seed=0)
+    pd = wf.tree_to(params, cuda_device, torch.float32)
+    p64 = wf.tree_to(params, 'cpu', torch.float64)
+    x = torch.randn(20, 100, 4, generator=torch.Generator().manual_seed(0)).to(cuda_device)
+    check_against_brute(lambda z: wf.mlp(pd, z), lambda z: wf.mlp(p64, z), x, thr, samples=(0, 13))
+
+
+def test_readme_mlp_sparse_index_maps(cuda_device):
+    """Sparsity threshold 4: K = 1 -> first Dense aligns to K = 4 with x0_idx[c, i] = 4 i + c and
+    the map survives every Dense / SiLU until the final sum goes dense."""
+    params = wf.tree_to(wf.mlp_params(seed=0), cuda_device, torch.float32)
+    x = torch.randn(3, 100, 4, generator=torch.Generator().manual_seed(1)).to(cuda_device)
+
+    def first_layers(z):
+        W, b = params[0]
+        h1 = F.silu(F.linear(z, W.t(), b))
+        W, b = params[1]
+        return h1, F.silu(F.linear(h1, W.t(), b))
+
+    h1, h2 = folx.vmap(folx.forward_laplacian(first_layers, 4))(x)
+    for h in (h1, h2):
+        assert h.jacobian.weak and h.jacobian.data.shape == (4, 3, 100, 100)
+        m = np.broadcast_to(h.jacobian.x0_idx, (4, 1, 100, 100))
+        want = 4 * np.arange(100)[None, :] + np.arange(4)[:, None]
+        np.testing.assert_array_equal(m[:, 0, :, 0], want)
+        np.testing.assert_array_equal(m[:, 0, :, 57], want)
+    out = folx.vmap(folx.forward_laplacian(lambda z: wf.mlp(params, z), 4))(x)
+    assert not out.jacobian.weak and out.jacobian.data.shape == (400, 3)
+
+
+def test_pairwise_differences_index_maps(cuda_device):
+    """r_i - r_j with threshold 6: K = 2 with the same input twice on the diagonal; the squared
+    distance has 6 rows off the diagonal and 3 (+ padding) on it."""
+    N = 5
+    r = torch.randn(2, N, 3, generator=torch.Generator().manual_seed(2)).to(cuda_device)
+    eye = torch.eye(N, device=cuda_device)
+
+    def f(z):
+        r_ee = z.unsqueeze(1) - z.unsqueeze(0)
+        return r_ee, (r_ee * r_ee).sum(-1), wf.electron_electron(z, eye)[1]
+
+    r_ee, d2, d = folx.vmap(folx.forward_laplacian(f, 6))(r)
+    m = np.broadcast_to(r_ee.jacobian.x0_idx, (2, 1, N, N, 3))[:, 0]
+    i, j, c = np.meshgrid(np.arange(N), np.arange(N), np.arange(3), indexing='ij')
+    np.testing.assert_array_equal(m[0], 3 * i + c)
+    np.testing.assert_array_equal(m[1], 3 * j + c)
+    m2 = np.broadcast_to(d2.jacobian.x0_idx, (6, 1, N, N))[:, 0]
+    for a in range(N):
+        for b in range(N):
+            want = sorted({3 * a + k for k in range(3)} | {3 * b + k for k in range(3)})
+            assert [v for v in m2[:, a, b] if v >= 0] == want
+    # values: |r_i - r_j|, its gradient and Laplacian (2 / |r_ij| per electron pair, twice)
+    dist = (r[:, :, None] - r[:, None]).norm(dim=-1)
+    torch.testing.assert_close(d.x, dist, rtol=1e-5, atol=1e-6)
+    off = ~torch.eye(N, dtype=torch.bool, device=cuda_device)
+    torch.testing.assert_close(d.laplacian[:, off], 4.0 / dist[:, off], rtol=1e-4, atol=1e-5)
+    assert float(d.laplacian[:, ~off].abs().max()) == 0.0
+
+
+SMALL_FERMI = wf.FermiNetConfig(n_elec=4, n_up=2, n_nuc=2, layers=2, width1=32, width2=8, n_det=2, seed=3)
+SMALL_PSI = wf.PsiFormerConfig(n_elec=4, n_up=2, n_nuc=2, layers=2, dim=32, heads=2, n_det=2, seed=4)
+
+
+@pytest.mark.parametrize('thr', [0, 6])
+def test_ferminet_small(cuda_device, thr):
+    cfg = SMALL_FERMI
+    params = wf.ferminet_params(cfg)
+    pd, p64 = wf.tree_to(params, cuda_device, torch.float32), wf.tree_to(params, 'cpu', torch.float64)
+    r = torch.randn(3, cfg.n_elec, 3, generator=torch.Generator().manual_seed(5)).to(cuda_device)
+    check_against_brute(lambda z: wf.ferminet(cfg, pd, z), lambda z: wf.ferminet(cfg, p64, z), r, thr,
+                        samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+
+
+@pytest.mark.parametrize('thr', [0, 6])
+def test_psiformer_small(cuda_device, thr):
+    cfg = SMALL_PSI
+    params = wf.psiformer_params(cfg)
+    pd, p64 = wf.tree_to(params, cuda_device, torch.float32), wf.tree_to(params, 'cpu', torch.float64)
+    r = torch.randn(3, cfg.n_elec, 3, generator=torch.Generator().manual_seed(6)).to(cuda_device)
+    check_against_brute(lambda z: wf.psiformer(cfg, pd, z), lambda z: wf.psiformer(cfg, p64, z), r, thr,
+                        samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
+
+
+def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
+    """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
+    cfg = SMALL_FERMI
+    pd = wf.tree_to(wf.ferminet_params(cfg), cuda_device, torch.float32)
+    f = lambda z: wf.ferminet(cfg, pd, z)
+    r = torch.randn(4, cfg.n_elec, 3, generator=torch.Generator().manual_seed(7)).to(cuda_device)
+    lap0, jac0 = folx.vmap(folx.ForwardLaplacianOperator(0)(f))(r)
+    lap6, jac6 = folx.vmap(folx.ForwardLaplacianOperator(6)(f))(r)
+    torch.testing.assert_close(lap0, lap6, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(jac0, jac6, rtol=1e-3, atol=1e-4)
+    lap_l, jac_l = folx.LoopLaplacianOperator()(f)(r[0])
+    torch.testing.assert_close(jac0[0].reshape(-1), jac_l, rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(lap0[0], lap_l, rtol=2e-3, atol=2e-3)
+
+
+def test_single_walker_without_vmap(cuda_device):
+    params = wf.tree_to(wf.mlp_params(seed=1, depth=2, width=16), cuda_device, torch.float32)
+    x = torch.randn(6, 4, generator=torch.Generator().manual_seed(8)).to(cuda_device)
+    lap, jac = folx.ForwardLaplacianOperator(0)(lambda z: wf.mlp(params, z))(x)
+    p64 = wf.tree_to(wf.mlp_params(seed=1, depth=2, width=16), 'cpu', torch.float64)
+    y, J, L = brute_force(lambda z: wf.mlp(p64, z), x.double().cpu())
+    torch.testing.assert_close(jac.double().cpu().reshape(-1), J.reshape(-1), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(lap.double().cpu(), L, rtol=1e-4, atol=1e-6)
+
+
+def test_custom_rule_registration(cuda_device):
+    """register_function / wrap_forward_laplacian: a user rule replaces a built-in one, and an
+    unregistered function goes through the generic rule (reference: README.md:112-176)."""
+    x = torch.randn(2, 5, generator=torch.Generator().manual_seed(9)).to(cuda_device)
+    calls = []
+
+    def my_tanh(args, kwargs, sparsity_threshold):
+        calls.append(sparsity_threshold)
+        return folx.wrap_forward_laplacian(torch.tanh, in_axes=())(args, kwargs, sparsity_threshold)
+
+    builtin = folx.get_laplacian('tanh')
+    folx.register_function('tanh', my_tanh)
+    try:
+        out = folx.vmap(folx.forward_laplacian(lambda z: torch.tanh(z).sum(), 0))(x)
+    finally:
+        folx.register_function('tanh', builtin)
+    assert calls == [0]
+    want = (-2 * torch.tanh(x) * (1 - torch.tanh(x) ** 2)).sum(-1)
+    torch.testing.assert_close(out.laplacian, want, rtol=1e-4, atol=1e-5)
+
+    # generic rule for a function without a kernel
+    def cube_plus_sin(z):
+        return z * z * z + torch.sin(2 * z)
+
+    folx.register_function('cube_plus_sin', folx.wrap_forward_laplacian(cube_plus_sin, in_axes=()))
+    try:
+        out = folx.vmap(folx.forward_laplacian(lambda z: folx.apply_rule('cube_plus_sin', z).sum(), 0))(x)
+    finally:
+        folx.deregister_function('cube_plus_sin')
+    assert not folx.is_registered('cube_plus_sin')
+    want = (6 * x - 4 * torch.sin(2 * x)).sum(-1)
+    torch.testing.assert_close(out.laplacian, want, rtol=1e-4, atol=1e-4)

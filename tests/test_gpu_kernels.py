@@ -84,7 +84,7 @@ def test_binary_constant_and_broadcast(cuda_device, op):
     assert_close(to_host(got), rules.binary(op, rules.constant(cb, K), a))
     # triplet (op) broadcast triplet
     b = seeded_triplet(K, (8,), seed=8, positive=True)
-    bb = tuple(torch.broadcast_to(u, (*u.shape[:-1], *shape)) for u in b)
+    bb = (b[0].expand(shape), b[1][:, None, :].expand(K, *shape), b[2].expand(shape))
     got = kernels.binary(op, to_device(a, cuda_device), to_device(b, cuda_device))
     assert_close(to_host(got), rules.binary(op, a, bb))
 
