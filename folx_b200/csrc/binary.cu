@@ -8,8 +8,10 @@
 //        (reference: folx/wrapped_functions.py:378-383, folx/custom_hessian.py:35-59)
 //   add/sub: linear in both operands, no Hessian term (folx/wrapped_functions.py:364-369).
 //
-// Either operand may be a constant array (its lap pointer, and jac pointer, are NULL): then its Jacobian
-// and Laplacian are zero.  Operand b may be periodic along the position axis (broadcast).
+// Either operand may be a constant array (its lap pointer, and jac pointer, are NULL): then its
+// Jacobian and Laplacian are zero.  Operand b may be broadcast: seen as (outer, mid, inner)
+// positions, b holds (outer, 1, inner) -- this covers a bias over the last axis (outer = 1), a
+// per-walker row added to every electron (mid = electrons) and the plain case (mid = 1).
 // HBM-bound, one pass; algorithmic traffic 4 (K + 2) (N_a + N_b + N) bytes.
 #include "common.cuh"
 
@@ -36,45 +38,108 @@ __device__ __forceinline__ void coeffs(float a, float b, float& y, float& ca, fl
   }
 }
 
-template <int OP, bool A_TRIPLET, bool B_TRIPLET>
-__global__ void __launch_bounds__(256)
-binary_kernel(const float* __restrict__ a, const float* __restrict__ ja,
-              const float* __restrict__ la, int64_t jas, const float* __restrict__ b,
-              const float* __restrict__ jb, const float* __restrict__ lb, int64_t jbs,
-              float* __restrict__ y, float* __restrict__ jy, float* __restrict__ ly, int64_t jys,
-              int K, int64_t N, int64_t b_period) {
-  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= N) return;
-  int64_t ib = (b_period == N) ? i : (i % b_period);
-  float av = a[i], bv = b[ib];
-  float yv, ca, cb, hab, hbb;
-  coeffs<OP>(av, bv, yv, ca, cb, hab, hbb);
-  y[i] = yv;
-  float sab = 0.f, sbb = 0.f;
-#pragma unroll 4
-  for (int k = 0; k < K; ++k) {
-    float va = A_TRIPLET ? __ldcs(ja + (int64_t)k * jas + i) : 0.f;
-    float vb = B_TRIPLET ? __ldg(jb + (int64_t)k * jbs + ib) : 0.f;
-    if constexpr (OP == FL_BIN_MUL || OP == FL_BIN_DIV) {
-      sab = fmaf(va, vb, sab);
-      if constexpr (OP == FL_BIN_DIV) sbb = fmaf(vb, vb, sbb);
-    }
-    __stcs(jy + (int64_t)k * jys + i, fmaf(ca, va, cb * vb));
+// V = float (scalar) or float4.  All sizes and strides are in units of V.
+template <typename V> struct Lanes;
+template <> struct Lanes<float> {
+  static constexpr int n = 1;
+  __device__ static float get(const float& v, int) { return v; }
+  __device__ static void set(float& v, int, float x) { v = x; }
+};
+template <> struct Lanes<float4> {
+  static constexpr int n = 4;
+  __device__ static float get(const float4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+  __device__ static void set(float4& v, int i, float x) {
+    if (i == 0) v.x = x; else if (i == 1) v.y = x; else if (i == 2) v.z = x; else v.w = x;
   }
-  float lav = A_TRIPLET ? la[i] : 0.f;
-  float lbv = B_TRIPLET ? lb[ib] : 0.f;
-  ly[i] = fmaf(ca, lav, cb * lbv) + hab * sab + hbb * sbb;
+};
+
+template <int OP, bool A_TRIPLET, bool B_TRIPLET, typename V>
+__global__ void __launch_bounds__(256)
+binary_kernel(const V* __restrict__ a, const V* __restrict__ ja, const V* __restrict__ la,
+              int64_t jas, const V* __restrict__ b, const V* __restrict__ jb,
+              const V* __restrict__ lb, int64_t jbs, V* __restrict__ y, V* __restrict__ jy,
+              V* __restrict__ ly, int64_t jys, int K, int64_t N, int64_t inner, int64_t mid) {
+  using L = Lanes<V>;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const int64_t ib = (mid == 1) ? i : (i / (inner * mid)) * inner + i % inner;
+  const V av = a[i], bv = b[ib];
+  float ca[L::n], cb[L::n], hab[L::n], hbb[L::n], sab[L::n], sbb[L::n];
+  V yv;
+#pragma unroll
+  for (int l = 0; l < L::n; ++l) {
+    float yy;
+    coeffs<OP>(L::get(av, l), L::get(bv, l), yy, ca[l], cb[l], hab[l], hbb[l]);
+    L::set(yv, l, yy);
+    sab[l] = 0.f;
+    sbb[l] = 0.f;
+  }
+  y[i] = yv;
+  constexpr int U = 4;
+  int k = 0;
+  for (; k + U <= K; k += U) {
+    V va[U], vb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if constexpr (A_TRIPLET) va[u] = __ldcs(ja + (int64_t)(k + u) * jas + i);
+      if constexpr (B_TRIPLET) vb[u] = __ldg(jb + (int64_t)(k + u) * jbs + ib);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      V out;
+#pragma unroll
+      for (int l = 0; l < L::n; ++l) {
+        const float x = A_TRIPLET ? L::get(va[u], l) : 0.f;
+        const float z = B_TRIPLET ? L::get(vb[u], l) : 0.f;
+        if constexpr (OP == FL_BIN_MUL || OP == FL_BIN_DIV) {
+          sab[l] = fmaf(x, z, sab[l]);
+          if constexpr (OP == FL_BIN_DIV) sbb[l] = fmaf(z, z, sbb[l]);
+        }
+        L::set(out, l, fmaf(ca[l], x, cb[l] * z));
+      }
+      __stcs(jy + (int64_t)(k + u) * jys + i, out);
+    }
+  }
+  for (; k < K; ++k) {
+    V va, vb, out;
+    if constexpr (A_TRIPLET) va = __ldcs(ja + (int64_t)k * jas + i);
+    if constexpr (B_TRIPLET) vb = __ldg(jb + (int64_t)k * jbs + ib);
+#pragma unroll
+    for (int l = 0; l < L::n; ++l) {
+      const float x = A_TRIPLET ? L::get(va, l) : 0.f;
+      const float z = B_TRIPLET ? L::get(vb, l) : 0.f;
+      if constexpr (OP == FL_BIN_MUL || OP == FL_BIN_DIV) {
+        sab[l] = fmaf(x, z, sab[l]);
+        if constexpr (OP == FL_BIN_DIV) sbb[l] = fmaf(z, z, sbb[l]);
+      }
+      L::set(out, l, fmaf(ca[l], x, cb[l] * z));
+    }
+    __stcs(jy + (int64_t)k * jys + i, out);
+  }
+  V lav, lbv, lout;
+  if constexpr (A_TRIPLET) lav = la[i];
+  if constexpr (B_TRIPLET) lbv = lb[ib];
+#pragma unroll
+  for (int l = 0; l < L::n; ++l) {
+    const float x = A_TRIPLET ? L::get(lav, l) : 0.f;
+    const float z = B_TRIPLET ? L::get(lbv, l) : 0.f;
+    L::set(lout, l, fmaf(ca[l], x, cb[l] * z) + hab[l] * sab[l] + hbb[l] * sbb[l]);
+  }
+  ly[i] = lout;
 }
 
-template <int OP>
-int32_t dispatch(const float* a, const float* ja, const float* la, int64_t jas, const float* b,
-                 const float* jb, const float* lb, int64_t jbs, float* y, float* jy, float* ly,
-                 int64_t jys, int64_t K, int64_t N, int64_t b_period, cudaStream_t st) {
-  unsigned blocks = (unsigned)((N + 255) / 256);
+template <int OP, typename V>
+int32_t launch(const float* a, const float* ja, const float* la, int64_t jas, const float* b,
+               const float* jb, const float* lb, int64_t jbs, float* y, float* jy, float* ly,
+               int64_t jys, int64_t K, int64_t N, int64_t inner, int64_t mid, cudaStream_t st) {
+  constexpr int W = Lanes<V>::n;
+  const int64_t n = N / W;
+  unsigned blocks = (unsigned)((n + 255) / 256);
   bool at = la != nullptr, bt = lb != nullptr;
-#define FL_LAUNCH(AT, BT)                                                                     \
-  binary_kernel<OP, AT, BT><<<blocks, 256, 0, st>>>(a, ja, la, jas, b, jb, lb, jbs, y, jy, ly, \
-                                                    jys, (int)K, N, b_period)
+#define FL_LAUNCH(AT, BT)                                                                        \
+  binary_kernel<OP, AT, BT, V><<<blocks, 256, 0, st>>>(                                          \
+      (const V*)a, (const V*)ja, (const V*)la, jas / W, (const V*)b, (const V*)jb, (const V*)lb, \
+      jbs / W, (V*)y, (V*)jy, (V*)ly, jys / W, (int)K, n, inner / W, mid)
   if (at && bt) FL_LAUNCH(true, true);
   else if (at) FL_LAUNCH(true, false);
   else if (bt) FL_LAUNCH(false, true);
@@ -84,6 +149,18 @@ int32_t dispatch(const float* a, const float* ja, const float* la, int64_t jas, 
   return FL_OK;
 }
 
+template <int OP>
+int32_t dispatch(const float* a, const float* ja, const float* la, int64_t jas, const float* b,
+                 const float* jb, const float* lb, int64_t jbs, float* y, float* jy, float* ly,
+                 int64_t jys, int64_t K, int64_t N, int64_t inner, int64_t mid, cudaStream_t st) {
+  auto al = [](const void* p) { return p == nullptr || aligned16(p); };
+  bool vec = N % 4 == 0 && inner % 4 == 0 && jas % 4 == 0 && jbs % 4 == 0 && jys % 4 == 0 &&
+             al(a) && al(ja) && al(la) && al(b) && al(jb) && al(lb) && al(y) && al(jy) && al(ly);
+  if (vec)
+    return launch<OP, float4>(a, ja, la, jas, b, jb, lb, jbs, y, jy, ly, jys, K, N, inner, mid, st);
+  return launch<OP, float>(a, ja, la, jas, b, jb, lb, jbs, y, jy, ly, jys, K, N, inner, mid, st);
+}
+
 }  // namespace
 }  // namespace fl
 
@@ -91,14 +168,15 @@ extern "C" int32_t fl_binary(int32_t op, const float* a, const float* jac_a, con
                              int64_t jac_a_stride, const float* b, const float* jac_b,
                              const float* lap_b, int64_t jac_b_stride, float* y, float* jac_y,
                              float* lap_y, int64_t jac_y_stride, int64_t K, int64_t N,
-                             int64_t b_period, void* stream) {
+                             int64_t b_inner, int64_t b_mid, void* stream) {
   using namespace fl;
   FL_REQUIRE(op >= FL_BIN_ADD && op <= FL_BIN_DIV, FL_EUNSUPPORTED, "fl_binary: unknown op %d", op);
   FL_REQUIRE(K >= 0 && N >= 0 && K < (1ll << 31) && (N + 255) / 256 < (1ll << 31), FL_EBADSHAPE,
              "fl_binary: bad sizes K=%lld N=%lld", (long long)K, (long long)N);
   if (N == 0) return FL_OK;
-  FL_REQUIRE(b_period > 0 && b_period <= N && N % b_period == 0, FL_EBADSHAPE,
-             "fl_binary: b_period %lld does not divide N %lld", (long long)b_period, (long long)N);
+  FL_REQUIRE(b_inner > 0 && b_mid > 0 && N % (b_inner * b_mid) == 0, FL_EBADSHAPE,
+             "fl_binary: broadcast (inner %lld, mid %lld) does not tile N %lld", (long long)b_inner,
+             (long long)b_mid, (long long)N);
   FL_REQUIRE(a && b && y && lap_y && (K == 0 || jac_y), FL_EBADSHAPE, "fl_binary: null pointer");
   // an operand is a triplet iff its lap pointer is given; its jac may be NULL only when K == 0
   FL_REQUIRE((lap_a != nullptr || jac_a == nullptr) && (lap_b != nullptr || jac_b == nullptr) &&
@@ -109,15 +187,15 @@ extern "C" int32_t fl_binary(int32_t op, const float* a, const float* jac_a, con
   switch (op) {
     case FL_BIN_ADD:
       return dispatch<FL_BIN_ADD>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,
-                                  jac_y, lap_y, jac_y_stride, K, N, b_period, st);
+                                  jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
     case FL_BIN_SUB:
       return dispatch<FL_BIN_SUB>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,
-                                  jac_y, lap_y, jac_y_stride, K, N, b_period, st);
+                                  jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
     case FL_BIN_MUL:
       return dispatch<FL_BIN_MUL>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,
-                                  jac_y, lap_y, jac_y_stride, K, N, b_period, st);
+                                  jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
     default:
       return dispatch<FL_BIN_DIV>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,
-                                  jac_y, lap_y, jac_y_stride, K, N, b_period, st);
+                                  jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
   }
 }

@@ -12,11 +12,12 @@
 // shared memory by converter warps.
 //
 // Kernel structure (one persistent CTA per SM, 320 threads):
-//   warp 4      TMA producer: A tile (128 x 32 fp32) + W_hi^T, W_lo^T tiles (n_tile x 32) per stage,
-//               128-byte swizzle, completion on an mbarrier
-//   warps 6-9   converters: A -> (A_hi in place, A_lo) in shared memory
+//   warp 4      TMA producer: A tile (128 x 16 fp32) + W_hi^T, W_lo^T tiles (n_tile x 16) per stage
+//               (4 stages), 64-byte swizzle, completion on an mbarrier
+//   warps 6-9   converters: A_lo = tf32(A - trunc_tf32(A)) into a second shared-memory tile
 //   warp 5      MMA issuer: 3 tcgen05.mma (kind::tf32, M = 128, N = n_tile, K = 8) per K slice
-//               into one of two TMEM accumulators (2 x 256 columns)
+//               into one of two TMEM accumulators (2 x 256 columns); the two products with the
+//               raw A tile go out as soon as the copy lands, the A_lo product after the converters
 //   warps 0-3   epilogue: tcgen05.ld -> registers -> (+bias) -> swizzled staging -> TMA store,
 //               overlapping the next tile's main loop through the second accumulator
 // Every mbarrier wait is bounded; when one runs out the CTA raises a shared abort flag, all
@@ -29,9 +30,14 @@ namespace fl {
 namespace {
 
 constexpr int BLOCK_M = 128;
-constexpr int BLOCK_K = 32;  // fp32 elements = one 128-byte swizzle row
+constexpr int BLOCK_K = 16;  // fp32 elements = one 64-byte swizzle row
 constexpr int UMMA_K = 8;    // K of one tcgen05.mma kind::tf32
-constexpr int STAGES = 2;
+constexpr int STAGES = 4;    // 4 x 48 KB: three stages in flight while one is consumed
+// The tensor core reads the upper 19 bits of an fp32 operand (sign, exponent, 10 mantissa bits)
+// and ignores the rest, i.e. it sees trunc_tf32(A).  The products with the raw A tile can then be
+// issued as soon as the copy lands; only the A_lo products wait for the converter warps.  With
+// this switch off the converters also round A in place and every product waits for them.
+constexpr bool kHwTruncates = true;
 constexpr int MAX_N = 256;
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
 constexpr int W_TILE_BYTES = MAX_N * BLOCK_K * 4;
@@ -152,15 +158,21 @@ __device__ __forceinline__ float tf32_rna(float v) {
   return __uint_as_float(r);
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are one 128-byte swizzle span:
-// 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1, SWIZZLE_128B.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+// What the tensor core sees of an fp32 operand: the low 13 mantissa bits dropped.
+__device__ __forceinline__ float tf32_trunc(float v) {
+  return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are one 64-byte swizzle span
+// (16 fp32): 8-row groups are 512 bytes apart (stride byte offset), descriptor version 1,
+// layout type SWIZZLE_64B (4).
+__device__ __forceinline__ uint64_t smem_desc_tile(uint32_t saddr) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
   d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)((8 * BLOCK_K * 4) >> 4) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)4 << 61;
   return d;
 }
 
@@ -263,21 +275,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MAX_N);
         for (int ks = 0; ks < num_k_steps; ++ks) {
-          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag) ||
+          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag)) { ok = false; break; }
+          if (!kHwTruncates &&
               !mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           uint8_t* sb = smem + stage * STAGE_BYTES;
-          const uint64_t d_ahi = smem_desc_sw128(smem_u32(sb));
-          const uint64_t d_alo = smem_desc_sw128(smem_u32(sb + A_TILE_BYTES));
-          const uint64_t d_whi = smem_desc_sw128(smem_u32(sb + 2 * A_TILE_BYTES));
-          const uint64_t d_wlo = smem_desc_sw128(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES));
+          const uint64_t d_ahi = smem_desc_tile(smem_u32(sb));
+          const uint64_t d_alo = smem_desc_tile(smem_u32(sb + A_TILE_BYTES));
+          const uint64_t d_whi = smem_desc_tile(smem_u32(sb + 2 * A_TILE_BYTES));
+          const uint64_t d_wlo = smem_desc_tile(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES));
+          // products that need only what the copy delivered: A_hi W_hi and A_hi W_lo
 #pragma unroll
           for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-            // advance inside the 128-byte swizzle row: 8 fp32 = 32 bytes = 2 descriptor units
+            // advance inside the swizzle row: 8 fp32 = 32 bytes = 2 descriptor units
             const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
-            umma_tf32(tmem_d, d_alo + off, d_whi + off, idesc, (ks | kk) != 0);
+            umma_tf32(tmem_d, d_ahi + off, d_whi + off, idesc, (ks | kk) != 0);
             umma_tf32(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
-            umma_tf32(tmem_d, d_ahi + off, d_whi + off, idesc, 1);
+          }
+          // the tail of A comes from the converter warps
+          if (kHwTruncates &&
+              !mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+            const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
+            umma_tf32(tmem_d, d_alo + off, d_whi + off, idesc, 1);
           }
           umma_commit(smem_u32(&ctrl->empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -303,10 +325,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int i = ct + 128 * j;
           float4 v = a4[i];
           float4 h, l;
-          h.x = tf32_rna(v.x); h.y = tf32_rna(v.y); h.z = tf32_rna(v.z); h.w = tf32_rna(v.w);
+          if (kHwTruncates) {
+            h.x = tf32_trunc(v.x); h.y = tf32_trunc(v.y); h.z = tf32_trunc(v.z); h.w = tf32_trunc(v.w);
+          } else {
+            h.x = tf32_rna(v.x); h.y = tf32_rna(v.y); h.z = tf32_rna(v.z); h.w = tf32_rna(v.w);
+            a4[i] = h;
+          }
           l.x = tf32_rna(v.x - h.x); l.y = tf32_rna(v.y - h.y);
           l.z = tf32_rna(v.z - h.z); l.w = tf32_rna(v.w - h.w);
-          a4[i] = h;
           lo4[i] = l;
         }
         fence_proxy_async();
@@ -408,17 +434,19 @@ EncodeTiledFn get_encode() {
   return fn;
 }
 
-// 2-D fp32 row-major tensor map with 128-byte swizzle; the box is 32 columns wide.
+// 2-D fp32 row-major tensor map; the box is box_cols (16 or 32) columns wide and swizzled over
+// its own row width (64 or 128 bytes).
 int32_t make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, int64_t row_stride,
-                 int box_rows, const char* what) {
+                 int box_rows, int box_cols, const char* what) {
   EncodeTiledFn enc = get_encode();
   FL_REQUIRE(enc != nullptr, FL_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t gstride[1] = {(cuuint64_t)row_stride * 4};
-  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride,
-                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   box_cols == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   FL_REQUIRE(r == CUDA_SUCCESS, FL_ECUDA, "cuTensorMapEncodeTiled(%s) failed with %d", what, (int)r);
   return FL_OK;
@@ -477,10 +505,10 @@ int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* wo
   const float* wlo = whi + wrows * g.k_pad;
   CUtensorMap tmA, tmWhi, tmWlo, tmY;
   int32_t rc;
-  if ((rc = make_map(&tmA, A, M, Kc, Kc, BLOCK_M, "A")) != FL_OK) return rc;
-  if ((rc = make_map(&tmWhi, whi, wrows, g.k_pad, g.k_pad, (int)g.n_tile, "W_hi")) != FL_OK) return rc;
-  if ((rc = make_map(&tmWlo, wlo, wrows, g.k_pad, g.k_pad, (int)g.n_tile, "W_lo")) != FL_OK) return rc;
-  if ((rc = make_map(&tmY, Y, M, N, N, 32, "Y")) != FL_OK) return rc;
+  if ((rc = make_map(&tmA, A, M, Kc, Kc, BLOCK_M, BLOCK_K, "A")) != FL_OK) return rc;
+  if ((rc = make_map(&tmWhi, whi, wrows, g.k_pad, g.k_pad, (int)g.n_tile, BLOCK_K, "W_hi")) != FL_OK) return rc;
+  if ((rc = make_map(&tmWlo, wlo, wrows, g.k_pad, g.k_pad, (int)g.n_tile, BLOCK_K, "W_lo")) != FL_OK) return rc;
+  if ((rc = make_map(&tmY, Y, M, N, N, 32, 32, "Y")) != FL_OK) return rc;
   const int num_m_tiles = (int)((M + BLOCK_M - 1) / BLOCK_M);
   const int64_t tiles = (int64_t)num_m_tiles * g.n_chunks;
   int grid = (int)(tiles < sm_count() ? tiles : sm_count());

@@ -1,0 +1,73 @@
+"""Walker-batch driver around the forward Laplacian: chunking, local energy, multi-GPU mean.
+
+The reference leaves batching to the caller (``jax.vmap`` / ``batched_vmap``, folx/vmap.py:11-83,
+motivated by Jacobian memory, README.md:189-200).  Here one call evaluates a batch of walkers in
+chunks that bound the Jacobian footprint, turns (laplacian, gradient) into local energies on the
+device and -- when the walkers are sharded over several GPUs, one process each -- combines the
+per-GPU sums with a single all-reduce of three doubles.
+"""
+
+from __future__ import annotations
+
+from typing import Callable
+
+import torch
+
+from . import kernels
+from .interpreter import vmap
+from .operators import ForwardLaplacianOperator
+
+
+def walker_laplacians(f: Callable, r: torch.Tensor, sparsity_threshold: int | float = 0,
+                      chunk: int | None = None):
+    """``(laplacian (B,), gradient (B, n))`` of a scalar function of one walker, for ``B`` walkers."""
+    lap_fn = vmap(ForwardLaplacianOperator(sparsity_threshold)(f))
+    B = r.shape[0]
+    chunk = B if chunk is None else max(1, min(chunk, B))
+    laps, jacs = [], []
+    for s in range(0, B, chunk):
+        lap, jac = lap_fn(r[s : s + chunk])
+        laps.append(lap)
+        jacs.append(jac)
+    return (laps[0], jacs[0]) if len(laps) == 1 else (torch.cat(laps), torch.cat(jacs))
+
+
+def local_energy_sums(f: Callable, r: torch.Tensor, potential: Callable | None = None,
+                      sparsity_threshold: int | float = 0, chunk: int | None = None):
+    """Local energies of the walkers on this GPU and ``[sum E, sum E^2, count]`` (fp64, device)."""
+    lap_fn = vmap(ForwardLaplacianOperator(sparsity_threshold)(f))
+    B = r.shape[0]
+    chunk = B if chunk is None else max(1, min(chunk, B))
+    total = torch.zeros(3, dtype=torch.float64, device=r.device)
+    energies = []
+    for s in range(0, B, chunk):
+        rc = r[s : s + chunk]
+        lap, jac = lap_fn(rc)
+        pot = potential(rc) if potential is not None else None
+        e, sums = kernels.local_energy(lap, jac.reshape(jac.shape[0], -1).t(), pot)
+        energies.append(e)
+        total += sums
+    return (energies[0] if len(energies) == 1 else torch.cat(energies)), total
+
+
+def reduce_energy(sums: torch.Tensor, group=None):
+    """Mean and variance of the local energy over ALL ranks from per-rank ``[sum E, sum E^2, n]``.
+
+    The only exchange of the data-parallel path: one all-reduce of three doubles (NCCL over
+    NVLink for GPU tensors, any ``torch.distributed`` backend otherwise).  Without an initialised
+    process group the local sums are used as they are.
+    """
+    s = sums.clone()
+    if torch.distributed.is_available() and torch.distributed.is_initialized():
+        torch.distributed.all_reduce(s, op=torch.distributed.ReduceOp.SUM, group=group)
+    n = s[2]
+    mean = s[0] / n
+    var = s[1] / n - mean * mean
+    return mean, var, n
+
+
+def shard_bounds(total: int, world: int, rank: int) -> tuple[int, int]:
+    """Contiguous block of walkers owned by ``rank`` (sizes differ by at most one)."""
+    base, rem = divmod(total, world)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)

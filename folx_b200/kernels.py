@@ -85,14 +85,47 @@ def elementwise(op: str, a: FwdLaplArray, param: float = 0.0) -> FwdLaplArray:
     return out
 
 
+def _broadcast_run(shape_a, shape_b):
+    """(inner, mid) if ``b`` equals ``a`` except for ONE run of broadcast axes, else None."""
+    nd = len(shape_a)
+    sb = (1,) * (nd - len(shape_b)) + tuple(shape_b)
+    bc = [d for d in range(nd) if sb[d] == 1 and shape_a[d] != 1]
+    if any(sb[d] != shape_a[d] for d in range(nd) if d not in bc):
+        return None
+    if not bc:
+        return int(np.prod(shape_a, dtype=np.int64)) or 1, 1
+    if bc != list(range(bc[0], bc[-1] + 1)):
+        return None
+    inner = int(np.prod(shape_a[bc[-1] + 1:], dtype=np.int64))
+    mid = int(np.prod([shape_a[d] for d in bc], dtype=np.int64))
+    return inner, mid
+
+
 def binary(op: str, a, b, x0_idx: np.ndarray | None = None) -> FwdLaplArray:
     """y = a (op) b for triplets with aligned Jacobian rows; either side may be a plain tensor.
 
-    ``b`` may be smaller than ``a`` when its shape equals the trailing part of ``a``'s shape
-    (broadcast over the leading positions).
+    ``a`` has the output shape; ``b`` may be smaller along one run of axes (a bias over the last
+    axis, a per-walker row shared by all electrons ...): that broadcast happens inside the
+    kernel.  Other broadcasts are expanded first.
     """
     a_t, b_t = isinstance(a, FwdLaplArray), isinstance(b, FwdLaplArray)
     assert a_t or b_t
+    shape = tuple((a.x if a_t else a).shape)
+    bshape = tuple((b.x if b_t else b).shape)
+    run = _broadcast_run(shape, bshape)
+    if run is None:
+        if b_t:
+            K = b.jacobian.data.shape[0]
+            nd = len(shape)
+            pad = (1,) * (nd - len(bshape))
+            b = FwdLaplArray(b.x.reshape(pad + bshape).expand(shape),
+                             FwdJacobian(b.jacobian.data.reshape(K, *pad, *bshape).expand(K, *shape),
+                                         b.jacobian.x0_idx),
+                             b.laplacian.reshape(pad + bshape).expand(shape))
+        else:
+            b = b.expand(shape)
+        run = (int(np.prod(shape, dtype=np.int64)) or 1, 1)
+    inner, mid = run
     if a_t:
         a = as_contiguous(a)
     if b_t:
@@ -100,9 +133,7 @@ def binary(op: str, a, b, x0_idx: np.ndarray | None = None) -> FwdLaplArray:
     ax = a.x if a_t else a.contiguous()
     bx = b.x if b_t else b.contiguous()
     _require_cuda(ax, bx)
-    N, Nb = ax.numel(), bx.numel()
-    if Nb > N or N % max(Nb, 1) != 0:
-        raise ValueError(f'binary: operand b ({tuple(bx.shape)}) does not tile a ({tuple(ax.shape)})')
+    N = ax.numel()
     K = a.jacobian.data.shape[0] if a_t else b.jacobian.data.shape[0]
     if a_t and b_t and b.jacobian.data.shape[0] != K:
         raise ValueError('binary: operands have different numbers of Jacobian rows')
@@ -116,7 +147,7 @@ def binary(op: str, a, b, x0_idx: np.ndarray | None = None) -> FwdLaplArray:
         _ptr(ax), _ptr(ja), _ptr(a.laplacian if a_t else None), _jac_stride(ja) if a_t else 0,
         _ptr(bx), _ptr(jb), _ptr(b.laplacian if b_t else None), _jac_stride(jb) if b_t else 0,
         _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), _jac_stride(out.jacobian.data),
-        K, N, Nb, _stream(ax.device),
+        K, N, inner, mid, _stream(ax.device),
     )
     return out
 
@@ -275,3 +306,25 @@ def mhsa(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, mask: torch.Tensor |
         _jac_stride(out.jacobian.data), _stream(qx.device),
     )
     return out
+
+
+def local_energy(lap: torch.Tensor, jac: torch.Tensor, pot: torch.Tensor | None = None):
+    """``E_L = -1/2 (lap + |grad|^2) + V`` per walker and ``[sum E, sum E^2, B]`` in fp64.
+
+    ``lap``: ``(B,)``, ``jac``: ``(K, B)`` (Jacobian axis first), ``pot``: ``(B,)`` or None.
+    Returns ``(energy (B,) fp32, sums (3,) fp64)`` on the device.
+    """
+    _require_cuda(lap, jac, pot)
+    B = lap.numel()
+    K = jac.shape[0]
+    if jac.numel() and (jac.stride(-1) != 1 or (K > 1 and jac.stride(0) < B)):
+        jac = jac.contiguous()
+    lap = lap.contiguous()
+    pot = pot.contiguous() if pot is not None else None
+    energy = torch.empty(B, dtype=torch.float32, device=lap.device)
+    sums = torch.empty(3, dtype=torch.float64, device=lap.device)
+    nbytes = lib.load().fl_local_energy_workspace_bytes(B)
+    ws = torch.empty(nbytes // 8 + 1, dtype=torch.float64, device=lap.device)
+    lib.call('fl_local_energy', _ptr(lap), _ptr(jac), _jac_stride(jac) if K > 1 else max(B, 1),
+             _ptr(pot), B, K, _ptr(energy), _ptr(ws), ws.numel() * 8, _ptr(sums), _stream(lap.device))
+    return energy, sums

@@ -44,7 +44,7 @@ _SIGNATURES = {
                                  c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     'fl_binary': (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                             c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
-                            c_int64, c_int64, c_void_p]),
+                            c_int64, c_int64, c_int64, c_void_p]),
     'fl_dot_general_workspace_bytes': (c_int64, [c_int64, c_int64]),
     'fl_dot_general_prepare': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     'fl_dot_general': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
@@ -63,6 +63,9 @@ _SIGNATURES = {
     'fl_slogdet': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                              c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     'fl_mhsa': (c_int32, [c_void_p] * 14 + [c_int64] * 9 + [c_void_p]),
+    'fl_local_energy_workspace_bytes': (c_int64, [c_int64]),
+    'fl_local_energy': (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
+                                  c_void_p, c_int64, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -146,8 +146,7 @@ def _const_binary(op: str, a: Arr, c, reverse: bool, threshold: int):
         return FwdLaplArray(lin.x, lin.jacobian, mer.laplacian)
     if reverse:
         return kernels.binary(op, c.expand(shape).contiguous(), a)
-    trailing = tuple(c.shape) == shape[len(shape) - c.ndim:] if c.ndim else True
-    return kernels.binary(op, a, c.contiguous() if trailing else c.expand(shape).contiguous())
+    return kernels.binary(op, a, c)  # a one-run broadcast of c happens inside the kernel
 
 
 def _align_rows(a: Arr, row_of: np.ndarray, n_rows: int, shape) -> Arr:
@@ -171,9 +170,8 @@ def binary(op: str, a, b, sparsity_threshold: int = 0):
         a, b = densify(a), densify(b)
         rows = max(a.jacobian.data.shape[0], b.jacobian.data.shape[0])
         a, b = _with_rows(a, rows), _with_rows(b, rows)
-        b_trailing = tuple(a.x.shape) == shape and tuple(b.x.shape) == shape[len(shape) - b.x.ndim:]
-        if not b_trailing:
-            b = broadcast_triplet(b, shape)
+        if op in ('add', 'mul') and tuple(a.x.shape) != shape and tuple(b.x.shape) == shape:
+            a, b = b, a  # commutative: keep the full-size operand first, broadcast the other in-kernel
         return kernels.binary(op, broadcast_triplet(a, shape), b)
     # both sparse: rows with identical index maps are merged, the others are kept side by side
     a, b = broadcast_triplet(a, shape), broadcast_triplet(b, shape)

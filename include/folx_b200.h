@@ -82,9 +82,10 @@ int32_t fl_elementwise(int32_t op, float param,
  * terms of folx/hessian.py:177-188 (mul: 2 sum_k Ja_k Jb_k) and folx/custom_hessian.py:35-59
  * (div: -2/b^2 sum_k Ja_k Jb_k + 2a/b^3 sum_k Jb_k^2).
  * Either operand may be a constant array: pass NULL for its jac and lap (zero derivatives).
- * Broadcasting: operand b may be broadcast along the position axis with period `b_period`
- * (position i of b is i % b_period; b_period == N means no broadcast); its buffers then hold
- * b_period positions.
+ * Broadcasting: the N positions are seen as (outer, b_mid, b_inner) and operand b holds
+ * (outer, 1, b_inner): position i of b is (i / (b_inner * b_mid)) * b_inner + i % b_inner.
+ * b_mid == 1 means no broadcast; outer == 1 is a bias over the trailing b_inner positions;
+ * b_mid == electrons is a per-walker row shared by all electrons.
  * ------------------------------------------------------------------------------------------- */
 enum { FL_BIN_ADD = 0, FL_BIN_SUB = 1, FL_BIN_MUL = 2, FL_BIN_DIV = 3 };
 
@@ -92,7 +93,7 @@ int32_t fl_binary(int32_t op,
                   const float* a, const float* jac_a, const float* lap_a, int64_t jac_a_stride,
                   const float* b, const float* jac_b, const float* lap_b, int64_t jac_b_stride,
                   float* y, float* jac_y, float* lap_y, int64_t jac_y_stride,
-                  int64_t K, int64_t N, int64_t b_period, void* stream);
+                  int64_t K, int64_t N, int64_t b_inner, int64_t b_mid, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * dot_general with one constant operand: y = x W (+ b).  Replaces _dot_general_one_constant
@@ -235,6 +236,23 @@ int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_lap,
                 int64_t B, int64_t n, int64_t H, int64_t d, int64_t R,
                 int64_t q_jac_stride, int64_t k_jac_stride, int64_t v_jac_stride,
                 int64_t o_jac_stride, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Local energy per walker and its statistics.  No counterpart in the reference (it returns
+ * (laplacian, jacobian), folx/operators.py:34-36, and leaves the energy to the caller); this is
+ * the step a sharded run reduces across GPUs.
+ *     E_L[w] = -1/2 (lap[w] + sum_k jac[k][w]^2) + pot[w]
+ *     sums   = [ sum_w E_L, sum_w E_L^2, B ]  (fp64, device)
+ *   lap, pot (or NULL), energy : [B];  jac : [K][B] (row stride jac_stride)
+ *   workspace : fl_local_energy_workspace_bytes(B) bytes of device scratch (per-block partial
+ *               sums; the second launch adds them in a fixed order, so the result is
+ *               bit-reproducible)
+ * ------------------------------------------------------------------------------------------- */
+int64_t fl_local_energy_workspace_bytes(int64_t B);
+
+int32_t fl_local_energy(const float* lap, const float* jac, int64_t jac_stride, const float* pot,
+                        int64_t B, int64_t K, float* energy,
+                        void* workspace, int64_t workspace_bytes, double* sums, void* stream);
 
 #ifdef __cplusplus
 }

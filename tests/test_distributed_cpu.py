@@ -1,0 +1,66 @@
+"""The multi-rank path on the CPU: walker sharding and the energy all-reduce with gloo ranks."""
+
+import os
+import socket
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from folx_b200 import harness
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(('127.0.0.1', 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, out):
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(0)
+        energies = torch.randn(101, generator=g, dtype=torch.float64)  # the same on every rank
+        a, b = harness.shard_bounds(energies.numel(), world, rank)
+        mine = energies[a:b]
+        sums = torch.stack([mine.sum(), (mine * mine).sum(), torch.tensor(float(b - a), dtype=torch.float64)])
+        mean, var, n = harness.reduce_energy(sums)
+        out[rank] = (float(mean), float(var), float(n), a, b)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_energy_allreduce_two_gloo_ranks():
+    world = 2
+    port = _free_port()
+    with mp.Manager() as m:
+        out = m.dict()
+        mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
+        res = dict(out)
+    energies = torch.randn(101, generator=torch.Generator().manual_seed(0), dtype=torch.float64)
+    for rank in range(world):
+        mean, var, n, a, b = res[rank]
+        assert n == 101.0
+        assert abs(mean - float(energies.mean())) < 1e-12
+        assert abs(var - float(energies.var(unbiased=False))) < 1e-12
+    assert res[0][3] == 0 and res[0][4] == res[1][3] and res[1][4] == 101
+
+
+def test_shard_bounds_cover_everything_once():
+    for total in (0, 1, 7, 16384):
+        for world in (1, 2, 3, 8):
+            spans = [harness.shard_bounds(total, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == total
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def test_reduce_energy_without_process_group():
+    sums = torch.tensor([6.0, 14.0, 3.0], dtype=torch.float64)
+    mean, var, n = harness.reduce_energy(sums)
+    assert float(mean) == 2.0 and abs(float(var) - (14.0 / 3 - 4.0)) < 1e-12 and float(n) == 3.0
