@@ -146,7 +146,7 @@ def run_ours(args, rank, world, device):
     from folx_b200 import kernels, lib
 
     lib.load()
-    host = make_host_inputs(seed=rank)
+    host = make_host_inputs(seed=rank, n_samples=B)
     pinned = {k: tuple(t.pin_memory() for t in host[k]) for k in ('dense', 'sparse')}
     W = host['W'].to(device)
     bias = host['bias'].to(device)
@@ -304,6 +304,20 @@ def cpu_baseline(sample: int, repeats: int = 3):
 def run_reference(args, rank, world):
     if rank != 0:
         return None
+    if args.workload != 'operators':
+        base = cpu_model_baseline(args.workload, walkers=max(1, min(args.steps, 4)))
+        return {
+            'impl': 'reference', 'metric': METRIC, 'value': base['value'], 'unit': UNIT, 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': 1e3 / base['value'],
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32',
+            'data': 'synthetic',
+            'config': {'workload': MODEL_WORKLOADS[args.workload][3] + '; each step is one walker',
+                       'note': 'brute-force automatic differentiation of the same function on the host '
+                               '(the reference needs JAX, which is not installed here)'},
+            'cpu_baseline': base,
+            'e2e': {'value': base['value'], 'unit': UNIT, 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+            'gpu_launches': 0,
+        }
     times = []
     sample = 256
     from oracle import rules
@@ -333,13 +347,146 @@ def run_reference(args, rank, world):
     }
 
 
+# ------------------------------------------------------------------------------------------
+# workloads: whole wavefunctions (BASELINE.json configs[0], [2], [3], [4])
+# ------------------------------------------------------------------------------------------
+MODEL_WORKLOADS = {
+    # name: (walkers per GPU, chunk, sparsity threshold, description)
+    'mlp': (20, 20, 4, 'README MLP (configs[0]): 10 x (Dense(100)+SiLU) + Dense(1), x (20,100,4), threshold 4'),
+    'ferminet': (4096, 2048, 6, 'FermiNet-style (configs[2]): 16 electrons, 4 nuclei, 4 layers 256/32, 16 dets'),
+    'psiformer': (4096, 512, 6, 'PsiFormer-style (configs[3]): 32 electrons, 8 nuclei, 4 layers, 4 heads x 64, 16 dets'),
+    'psiformer64': (2048, 128, 6, 'scaled PsiFormer (configs[4]): 64 electrons, 16 nuclei, 16 dets of 32x32; '
+                                   '16384 walkers over 8 GPUs = 2048 per GPU'),
+}
+
+
+def build_model(name: str, device, dtype=torch.float32):
+    from folx_b200 import wavefunctions as wf
+
+    if name == 'mlp':
+        p = wf.tree_to(wf.mlp_params(seed=0), device, dtype)
+        return (lambda z: wf.mlp(p, z)), (100, 4), None
+    if name == 'ferminet':
+        cfg = wf.FermiNetConfig()
+        p = wf.tree_to(wf.ferminet_params(cfg), device, dtype)
+        return (lambda z: wf.ferminet(cfg, p, z)), (cfg.n_elec, 3), (lambda r: wf.coulomb_potential(r, p['nuclei']))
+    cfg = wf.PsiFormerConfig() if name == 'psiformer' else wf.PsiFormerConfig(n_elec=64, n_up=32, n_nuc=16)
+    p = wf.tree_to(wf.psiformer_params(cfg), device, dtype)
+    return (lambda z: wf.psiformer(cfg, p, z)), (cfg.n_elec, 3), (lambda r: wf.coulomb_potential(r, p['nuclei']))
+
+
+def time_model(name: str, device, rank: int, world: int, steps: int, warmup: int, walkers: int | None = None):
+    """Walker-Laplacians/s of a whole wavefunction: device-resident and end to end."""
+    from folx_b200 import harness, kernels
+
+    n_walkers, chunk, thr, desc = MODEL_WORKLOADS[name]
+    if walkers is not None:
+        n_walkers, chunk = walkers, min(chunk, walkers)
+    f, shape, pot = build_model(name, device)
+    host_r = torch.randn(n_walkers, *shape, generator=torch.Generator().manual_seed(rank)).pin_memory()
+    r = host_r.to(device)
+
+    def step(rr):
+        e, sums = harness.local_energy_sums(f, rr, pot, sparsity_threshold=thr, chunk=chunk)
+        mean, var, n = harness.reduce_energy(sums)  # the one exchange: all-reduce of 3 doubles
+        return e, mean
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(warmup, 3)):
+        step(r)
+    kernels.check_gemm_status(device)
+    barrier()
+    from folx_b200 import lib as _lib
+
+    launches0 = _lib.launches()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step(r)
+    e1.record()
+    barrier()
+    launches = _lib.launches() - launches0
+    ms = e0.elapsed_time(e1) / steps
+    # end to end: coordinates come from pinned host memory, energies go back to the host
+    host_e = torch.empty(n_walkers).pin_memory()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    g0.record()
+    for _ in range(max(2, min(steps, 3))):
+        e, mean = step(host_r.to(device, non_blocking=True))
+        host_e.copy_(e, non_blocking=True)
+        mean_host = float(mean)  # device -> host read of the step's result
+    g1.record()
+    barrier()
+    e2e_ms = g0.elapsed_time(g1) / max(2, min(steps, 3))
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    kernels.check_gemm_status(device)
+    return {'workload': desc, 'walkers_per_gpu': n_walkers, 'chunk': chunk, 'sparsity_threshold': thr,
+            'ms_per_step': ms, 'value': world * n_walkers / (ms / 1e3),
+            'e2e_ms_per_step': e2e_ms, 'e2e_value': world * n_walkers / (e2e_ms / 1e3),
+            'h2d_bytes_per_step': host_r.numel() * 4, 'd2h_bytes_per_step': n_walkers * 4 + 8,
+            'mean_energy': mean_host, 'gpu_launches': launches}
+
+
+def cpu_model_baseline(name: str, walkers: int = 2):
+    """Brute-force Laplacian of the same wavefunction on the host (torch.func, fp32)."""
+    from oracle import brute
+
+    f, shape, _ = build_model(name, 'cpu')
+    r = torch.randn(walkers, *shape, generator=torch.Generator().manual_seed(0))
+    brute.jac_and_laplacian(f, r[0])
+    t0 = time.perf_counter()
+    for w in range(walkers):
+        brute.jac_and_laplacian(f, r[w])
+    t = time.perf_counter() - t0
+    return {'value': walkers / t, 'unit': UNIT, 'cores': torch.get_num_threads(), 'kind': 'port',
+            'sample': f'{walkers} walkers, Jacobian + Hessian trace by automatic differentiation '
+                      f'(torch.func, fp32) of the same function; host has {os.cpu_count()} logical cores',
+            'seconds': t}
+
+
+def run_model(args, rank, world, device):
+    name = args.workload
+    with ClockSampler(device.index or 0) as clocks:
+        m = time_model(name, device, rank, world, args.steps, args.warmup, args.walkers)
+    return {
+        'metric': METRIC, 'value': m['value'], 'unit': UNIT, 'n_gpus': world, 'steps': args.steps,
+        'warmup': max(args.warmup, 3), 'ms_per_step': m['ms_per_step'], 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': {'workload': m['workload'], 'walkers_per_gpu': m['walkers_per_gpu'], 'chunk': m['chunk'],
+                   'sparsity_threshold': m['sparsity_threshold'],
+                   'l2': 'Jacobian tensors are GB-sized (>> 126 MB L2) and streamed by every kernel',
+                   'exchange': 'one all-reduce of [sum E, sum E^2, n] (3 x f64) per step'},
+        'clocks': clocks.summary(),
+        'e2e': {'value': m['e2e_value'], 'unit': UNIT, 'h2d_bytes_per_step': m['h2d_bytes_per_step'],
+                'd2h_bytes_per_step': m['d2h_bytes_per_step'], 'ms_per_step': m['e2e_ms_per_step']},
+        'gpu_launches': m['gpu_launches'], 'mean_energy': m['mean_energy'],
+        'roofline': None,
+    }
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--workload', default='operators', choices=['operators', *MODEL_WORKLOADS])
+    ap.add_argument('--walkers', type=int, default=None, help='walkers per GPU (model workloads)')
+    ap.add_argument('--no-models', action='store_true', help='skip the short model timings of the default run')
+    ap.add_argument('--samples', type=int, default=None,
+                    help='samples per GPU of the operator workload (default 4096; smaller values are for profiling)')
     args = ap.parse_args()
+    if args.samples is not None:
+        global B
+        B = args.samples
 
     rank = int(os.environ.get('RANK', 0))
     world = int(os.environ.get('WORLD_SIZE', 1))
@@ -358,9 +505,25 @@ def main():
     if world > 1:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         torch.distributed.init_process_group('nccl', device_id=device)
-    res = run_ours(args, rank, world, device)
+    if args.workload == 'operators':
+        res = run_ours(args, rank, world, device)
+        if not args.no_models:
+            # short timings of the whole wavefunctions, reported beside the headline workload
+            models = {}
+            for name, walkers in (('ferminet', 2048), ('psiformer', 512)):
+                try:
+                    torch.cuda.empty_cache()
+                    models[name] = time_model(name, device, rank, world, steps=3, warmup=3, walkers=walkers)
+                except Exception as e:  # a model failing must not lose the headline line
+                    models[name] = {'error': f'{type(e).__name__}: {e}'}
+            res['models'] = models
+        if rank == 0:
+            res['cpu_baseline'] = cpu_baseline(sample=128) if world == 1 else None
+    else:
+        res = run_model(args, rank, world, device)
+        if rank == 0:
+            res['cpu_baseline'] = cpu_model_baseline(args.workload) if world == 1 else None
     if rank == 0:
-        res['cpu_baseline'] = cpu_baseline(sample=128) if world == 1 else None
         print(json.dumps(res), flush=True)
     if world > 1:
         torch.distributed.barrier()

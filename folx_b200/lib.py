@@ -109,6 +109,18 @@ def check(fn_name: str, code: int) -> None:
         raise FolxB200Error(fn_name, code, msg.decode() if msg else '')
 
 
+LAUNCH_COUNTS: dict[str, int] = {}
+
+
 def call(fn_name: str, *args) -> None:
-    """Calls a status-returning entry point and raises FolxB200Error on failure."""
+    """Calls a status-returning entry point and raises FolxB200Error on failure.
+
+    Every call is tallied in ``LAUNCH_COUNTS`` (entry point -> number of calls) so that callers
+    can report how many kernels of this library they launched."""
+    LAUNCH_COUNTS[fn_name] = LAUNCH_COUNTS.get(fn_name, 0) + 1
     check(fn_name, getattr(load(), fn_name)(*args))
+
+
+def launches() -> int:
+    """Total number of C-ABI kernel calls made so far in this process."""
+    return sum(LAUNCH_COUNTS.values())
