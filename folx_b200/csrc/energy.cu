@@ -105,3 +105,74 @@ extern "C" int32_t fl_local_energy(const float* lap, const float* jac, int64_t j
   return energy_launch(lap, jac, jac_stride, pot, B, K, energy, (double*)workspace, sums,
                        (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some callers cannot hand over scratch memory and must not trigger an allocation themselves:
+// an XLA/JAX custom call whose buffers were all planned by the compiler before the step runs, a
+// Monte-Carlo driver whose framework has already claimed the whole device for its own pool (a
+// cudaMalloc from a plug-in then fails or fragments that pool), code running between the steps of
+// a latency-critical loop where an allocation would stall the stream.  For them the per-block
+// partial sums live in a fixed array inside the library image instead of a workspace argument.
+//
+// The array exists once per GPU that loads the library (FL_LOCAL_ENERGY_STATIC_MAX_WALKERS / 256
+// blocks x 2 doubles = 64 KiB, held until the process exits).  Host code cannot use the array's
+// name as a device address -- it has to ask the runtime for it -- so the first call on each
+// device looks the address up (cudaGetSymbolAddress, with that device current) and remembers it.
+// All calls on a device share the array and it keeps whatever the previous call left there; that
+// is harmless here because every entry the finishing launch reads was written by the same
+// call's first launch, so nothing needs clearing -- but two calls that are in flight at the same
+// time on one GPU (different streams) would overwrite each other's partial sums.
+// ---------------------------------------------------------------------------------------------
+namespace fl {
+namespace {
+
+constexpr int64_t kStaticMaxBlocks = FL_LOCAL_ENERGY_STATIC_MAX_WALKERS / kThreads;
+static __device__ __align__(256) double g_static_partials[2 * kStaticMaxBlocks];
+
+constexpr int kMaxDevices = 64;
+static double* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the static scratch on the current device (looked up once per device).
+int32_t static_scratch(double** out) {
+  int dev = -1;
+  FL_CUDA(cudaGetDevice(&dev));
+  FL_REQUIRE(dev >= 0 && dev < kMaxDevices, FL_EUNSUPPORTED,
+             "fl_local_energy_static: device ordinal %d out of range", dev);
+  if (g_static_ptr[dev] == nullptr) {
+    double* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&p, g_static_partials);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(static energy scratch)");
+    FL_REQUIRE(p != nullptr, FL_ECUDA, "fl_local_energy_static: no address for the static scratch");
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return FL_OK;
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_local_energy_static(const float* lap, const float* jac, int64_t jac_stride,
+                                          const float* pot, int64_t B, int64_t K, float* energy,
+                                          double* sums, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(B >= 0 && K >= 0 && K < (1ll << 31), FL_EBADSHAPE, "fl_local_energy_static: bad sizes");
+  FL_REQUIRE(B <= FL_LOCAL_ENERGY_STATIC_MAX_WALKERS, FL_EBADSHAPE,
+             "fl_local_energy_static: %lld walkers exceed the built-in scratch (max %lld); use "
+             "fl_local_energy with a caller-provided workspace",
+             (long long)B, (long long)FL_LOCAL_ENERGY_STATIC_MAX_WALKERS);
+  FL_REQUIRE(sums != nullptr, FL_EBADSHAPE, "fl_local_energy_static: sums is NULL");
+  if (B == 0) {
+    FL_CUDA(cudaMemsetAsync(sums, 0, 3 * sizeof(double), (cudaStream_t)stream));
+    return FL_OK;
+  }
+  FL_REQUIRE(lap && energy && (K == 0 || jac), FL_EBADSHAPE, "fl_local_energy_static: null pointer");
+  FL_REQUIRE(K <= 1 || jac_stride >= B, FL_EBADSHAPE,
+             "fl_local_energy_static: Jacobian row stride < B");
+  double* scratch = nullptr;
+  int32_t rc = static_scratch(&scratch);
+  if (rc != FL_OK) return rc;
+  return energy_launch(lap, jac, jac_stride, pot, B, K, energy, scratch, sums, (cudaStream_t)stream);
+}

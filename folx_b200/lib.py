@@ -66,6 +66,8 @@ _SIGNATURES = {
     'fl_local_energy_workspace_bytes': (c_int64, [c_int64]),
     'fl_local_energy': (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,
                                   c_void_p, c_int64, c_void_p, c_void_p]),
+    'fl_local_energy_static': (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64,
+                                         c_void_p, c_void_p, c_void_p]),
 }
 
 _lib = None

@@ -254,6 +254,25 @@ int32_t fl_local_energy(const float* lap, const float* jac, int64_t jac_stride, 
                         int64_t B, int64_t K, float* energy,
                         void* workspace, int64_t workspace_bytes, double* sums, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * fl_local_energy without a workspace argument and without any allocation.  It has no
+ * counterpart in the reference.  It is meant for callers that can neither pass scratch memory
+ * nor allocate: custom calls inside a compiler-planned step (all buffers fixed beforehand),
+ * hosts whose framework owns the whole device memory pool, latency-critical loops.  Same inputs,
+ * outputs and results as fl_local_energy; the per-block partial sums go to a fixed 64 KiB array
+ * that is part of the library image on every GPU that loads it.
+ *   - B <= FL_LOCAL_ENERGY_STATIC_MAX_WALKERS, otherwise FL_EBADSHAPE (use fl_local_energy).
+ *   - The first call on each device looks up the array's device address (that device must be
+ *     current); make that first call outside any stream capture.
+ *   - All calls on one GPU share the array; calls that overlap in time on the same GPU (for
+ *     example on two streams) race on it.  Calls on one stream are ordered and safe.
+ * ------------------------------------------------------------------------------------------- */
+#define FL_LOCAL_ENERGY_STATIC_MAX_WALKERS 1048576
+
+int32_t fl_local_energy_static(const float* lap, const float* jac, int64_t jac_stride,
+                               const float* pot, int64_t B, int64_t K, float* energy,
+                               double* sums, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
