@@ -142,6 +142,26 @@ def algorithmic(name: str):
     return 8 * rows * F, 0
 
 
+def measure_tf32_peak(device, n: int = 8192):
+    """cuBLAS TF32 GEMM throughput on this GPU (a library call used ONLY to measure a ceiling)."""
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device=device)
+        b = torch.randn(n, n, device=device)
+        best = float('inf')
+        for _ in range(6):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b)
+            e1.record()
+            torch.cuda.synchronize(device)
+            best = min(best, e0.elapsed_time(e1))
+        return round(2 * n**3 / best / 1e9, 1)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
 def run_ours(args, rank, world, device):
     from folx_b200 import kernels, lib
 
@@ -247,13 +267,17 @@ def run_ours(args, rank, world, device):
     ms = kern[dominant]['ms']
     if dominant.startswith('dot_general'):
         achieved = flops / ms / 1e9
+        # DRAM traffic of this kernel from the committed ncu capture (profiles/gemm_tc_kernel_*):
+        # 364.0 MB read + written for 200 704 rows; it grows in proportion to the rows of a launch
+        rows = ((D if dominant.endswith('dense') else KS) + 2) * B
         roofline = {'kernel': dominant, 'bound': 'tensor', 'achieved': round(achieved, 1),
                     'peak': round(tf32_peak, 1), 'unit': 'TFLOP/s', 'frac': round(achieved / tf32_peak, 3),
-                    'traffic': None,
+                    'traffic': round(364.0e6 * rows / 200704),
                     'note': 'achieved = fp32-equivalent (algorithmic) flops; the 3xTF32 split executes 3x '
                             'that on the tensor pipe, so the ceiling is peak/3; peak = measured bf16 / 2 '
-                            f'({peaks["source"]})',
+                            f'({peaks["source"]}); traffic scaled from the ncu capture at 2048 samples',
                     'frac_of_3xtf32_ceiling': round(3 * achieved / tf32_peak, 3),
+                    'tf32_cublas_tflops_this_run': measure_tf32_peak(device),
                     'hbm_frac': kern[dominant]['frac_hbm']}
     else:
         achieved = nbytes / ms / 1e6
@@ -452,6 +476,50 @@ def cpu_model_baseline(name: str, walkers: int = 2):
             'seconds': t}
 
 
+def run_kernel_case(args, device):
+    """Single-kernel cases at BASELINE shapes, for profiling (`--workload attention|slogdet`)."""
+    from folx_b200 import kernels
+
+    g = torch.Generator(device=device).manual_seed(0)
+    walkers = args.walkers or 128
+
+    def rand(K, shape, scale=1.0):
+        a = kernels.alloc_triplet(K, shape, device)
+        a.x.normal_(generator=g).mul_(scale)
+        a.jacobian.data.normal_(generator=g).mul_(scale)
+        a.laplacian.normal_(generator=g).mul_(scale)
+        return a
+
+    if args.workload == 'attention':  # PsiFormer layer: n = 32, H = 4, d = 64, R = 96
+        q, k, v = (rand(96, (walkers, 32, 4, 64), 0.3) for _ in range(3))
+        fn = lambda: kernels.mhsa(q, k, v)
+        nbytes = 4 * 4 * walkers * 4 * 98 * 32 * 64
+        desc = f'attention-Laplacian kernel, {walkers} walkers x 4 heads, n=32, d=64, R=96'
+    else:  # PsiFormer determinants: 32 matrices of 16 x 16 per walker, K = 96
+        a = rand(96, (walkers, 32, 16, 16))
+        a.x.div_(4.0).add_(1.5 * torch.eye(16, device=device))
+        fn = lambda: kernels.slogdet(a)
+        nbytes = 4 * walkers * 32 * 98 * 256
+        desc = f'slogdet kernel, {walkers} walkers x 32 matrices of 16x16, K=96'
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1) / args.steps
+    peaks = load_peaks()
+    return {'metric': METRIC, 'value': walkers / (ms / 1e3), 'unit': UNIT, 'n_gpus': 1, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic', 'config': {'workload': desc},
+            'gpu_launches': args.steps,
+            'roofline': {'bound': 'hbm', 'achieved': round(nbytes / ms / 1e6, 1), 'peak': peaks['hbm_gbs'],
+                         'unit': 'GB/s', 'frac': round(nbytes / ms / 1e6 / peaks['hbm_gbs'], 3), 'traffic': None}}
+
+
 def run_model(args, rank, world, device):
     name = args.workload
     with ClockSampler(device.index or 0) as clocks:
@@ -478,7 +546,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='operators', choices=['operators', *MODEL_WORKLOADS])
+    ap.add_argument('--workload', default='operators', choices=['operators', 'attention', 'slogdet', *MODEL_WORKLOADS])
     ap.add_argument('--walkers', type=int, default=None, help='walkers per GPU (model workloads)')
     ap.add_argument('--no-models', action='store_true', help='skip the short model timings of the default run')
     ap.add_argument('--samples', type=int, default=None,
@@ -519,6 +587,8 @@ def main():
             res['models'] = models
         if rank == 0:
             res['cpu_baseline'] = cpu_baseline(sample=128) if world == 1 else None
+    elif args.workload in ('attention', 'slogdet'):
+        res = run_kernel_case(args, device)
     else:
         res = run_model(args, rank, world, device)
         if rank == 0:

@@ -84,15 +84,18 @@ template <int NP, bool VEC>
 __global__ void __launch_bounds__(kThreads)
 mhsa_kernel(Args a) {
   constexpr int T = NP / 16;  // per-thread tile edge in the score phase
-  constexpr int PP = NP + 1;  // pitch of the n x n matrices
+  constexpr int PP = NP + 4;  // pitch of the n x n matrices (rows stay 16-byte aligned)
   extern __shared__ __align__(16) float smem[];
   float* Q = smem;                 // [NP][DP]
   float* Kx = Q + NP * DP;
   float* V = Kx + NP * DP;
   float* buf = V + NP * DP;        // 2 x {QR, KR, VR}
   float* Pm = buf + 6 * NP * DP;   // [NP][PP]
-  float* PR = Pm + NP * PP;
-  float* TV = PR + NP * PP;
+  // p_r and the weights of v in the Hessian term for the row in flight; double buffered when
+  // shared memory allows (n <= 32), which saves one block-wide barrier per row
+  constexpr int NBUF = NP <= 32 ? 2 : 1;
+  float* PRb = Pm + NP * PP;          // NBUF x [NP][PP]
+  float* TVb = PRb + NBUF * NP * PP;  // NBUF x [NP][PP]
   __shared__ uint8_t rowmask_s[64];
 
   const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
@@ -197,18 +200,18 @@ mhsa_kernel(Args a) {
   // ---------------- stream the Laplacian row (it == 0) and the R Jacobian rows -------------------
   for (int it = 0; it <= a.R; ++it) {
     const int cur = it & 1;
+    if constexpr (VEC) cp_async_wait<0>();  // the tiles of this iteration (issued one iteration ago)
+    __syncthreads();  // tiles visible to all; every warp has left the previous iteration
     if (it < a.R) {
-      // prefetch Jacobian row r = it into the other buffer
+      // prefetch Jacobian row r = it into the other buffer (last read in the previous iteration)
       float* nb = buf + (cur ^ 1) * 3 * NP * DP;
       load_tile<NP, VEC>(nb + 0 * NP * DP, a.qj + (int64_t)it * a.qjs, a, b, h, rowmask_s, true);
       load_tile<NP, VEC>(nb + 1 * NP * DP, a.kj + (int64_t)it * a.kjs, a, b, h, rowmask_s, true);
       load_tile<NP, VEC>(nb + 2 * NP * DP, a.vj + (int64_t)it * a.vjs, a, b, h, rowmask_s, true);
       if constexpr (VEC) cp_async_commit();
     }
-    if constexpr (VEC) {
-      if (it < a.R) cp_async_wait<1>(); else cp_async_wait<0>();
-    }
-    __syncthreads();
+    float* PR = PRb + (NBUF == 2 ? cur : 0) * NP * PP;
+    float* TV = TVb + (NBUF == 2 ? cur : 0) * NP * PP;
     const float* QR = buf + cur * 3 * NP * DP;
     const float* KR = QR + NP * DP;
     const float* VR = KR + NP * DP;
@@ -239,7 +242,7 @@ mhsa_kernel(Args a) {
           for (int y = 0; y < T; ++y) {
             s1[x][y] += dot4(qrv[x], kv[y]);
             s2[x][y] += dot4(qv[x], krv[y]);
-            if (hess) s3[x][y] += dot4(qrv[x], krv[y]);
+            s3[x][y] += dot4(qrv[x], krv[y]);
           }
       }
 #pragma unroll
@@ -259,15 +262,13 @@ mhsa_kernel(Args a) {
           r2 = fmaf(pr[y], sr[y], r2);
           r3 = fmaf(p[x][y], 2.0f * s3[x][y], r3);
         }
-        if (hess) {
-          r2 = half_warp_sum(r2);  // rowsum(p_r s_r)
-          r3 = half_warp_sum(r3);  // rowsum(2 p q_r k_r^T)
-        }
+        r2 = half_warp_sum(r2);  // rowsum(p_r s_r)
+        r3 = half_warp_sum(r3);  // rowsum(2 p q_r k_r^T)
 #pragma unroll
         for (int y = 0; y < T; ++y) {
           const int j = tx + 16 * y;
           PR[i * PP + j] = pr[y];
-          if (hess) TV[i * PP + j] = pr[y] * (sr[y] - r1) + p[x][y] * (2.0f * s3[x][y] - r2 - r3);
+          TV[i * PP + j] = pr[y] * (sr[y] - r1) + p[x][y] * (2.0f * s3[x][y] - r2 - r3);
         }
       }
     }
@@ -281,23 +282,34 @@ mhsa_kernel(Args a) {
         oj[x] = make_float4(0.f, 0.f, 0.f, 0.f);
         ct[x] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      for (int j = 0; j < n; ++j) {
-        const float4 vv = *reinterpret_cast<const float4*>(V + j * DP + 4 * tx);
-        const float4 vr = *reinterpret_cast<const float4*>(VR + j * DP + 4 * tx);
+      // padded key columns carry p = p_r = tv = 0 and zero rows of v, so the loop runs to NP
+      for (int j = 0; j < NP; j += 4) {
+        float4 vv[4], vr[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          vv[u] = *reinterpret_cast<const float4*>(V + (j + u) * DP + 4 * tx);
+          vr[u] = *reinterpret_cast<const float4*>(VR + (j + u) * DP + 4 * tx);
+        }
 #pragma unroll
         for (int x = 0; x < T; ++x) {
           const int i = ty + 16 * x;
-          const float prv = PR[i * PP + j], pv = Pm[i * PP + j];
-          oj[x].x = fmaf(prv, vv.x, fmaf(pv, vr.x, oj[x].x));
-          oj[x].y = fmaf(prv, vv.y, fmaf(pv, vr.y, oj[x].y));
-          oj[x].z = fmaf(prv, vv.z, fmaf(pv, vr.z, oj[x].z));
-          oj[x].w = fmaf(prv, vv.w, fmaf(pv, vr.w, oj[x].w));
-          if (hess) {
-            const float tv = TV[i * PP + j], p2 = 2.0f * prv;
-            ct[x].x = fmaf(tv, vv.x, fmaf(p2, vr.x, ct[x].x));
-            ct[x].y = fmaf(tv, vv.y, fmaf(p2, vr.y, ct[x].y));
-            ct[x].z = fmaf(tv, vv.z, fmaf(p2, vr.z, ct[x].z));
-            ct[x].w = fmaf(tv, vv.w, fmaf(p2, vr.w, ct[x].w));
+          const float4 pr4 = *reinterpret_cast<const float4*>(PR + i * PP + j);
+          const float4 p4 = *reinterpret_cast<const float4*>(Pm + i * PP + j);
+          const float4 tv4 = *reinterpret_cast<const float4*>(TV + i * PP + j);
+          const float prs[4] = {pr4.x, pr4.y, pr4.z, pr4.w};
+          const float ps[4] = {p4.x, p4.y, p4.z, p4.w};
+          const float tvs[4] = {tv4.x, tv4.y, tv4.z, tv4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const float prv = prs[u], pv = ps[u], tv = tvs[u], p2 = 2.0f * prs[u];
+            oj[x].x = fmaf(prv, vv[u].x, fmaf(pv, vr[u].x, oj[x].x));
+            oj[x].y = fmaf(prv, vv[u].y, fmaf(pv, vr[u].y, oj[x].y));
+            oj[x].z = fmaf(prv, vv[u].z, fmaf(pv, vr[u].z, oj[x].z));
+            oj[x].w = fmaf(prv, vv[u].w, fmaf(pv, vr[u].w, oj[x].w));
+            ct[x].x = fmaf(tv, vv[u].x, fmaf(p2, vr[u].x, ct[x].x));
+            ct[x].y = fmaf(tv, vv[u].y, fmaf(p2, vr[u].y, ct[x].y));
+            ct[x].z = fmaf(tv, vv[u].z, fmaf(p2, vr[u].z, ct[x].z));
+            ct[x].w = fmaf(tv, vv[u].w, fmaf(p2, vr[u].w, ct[x].w));
           }
         }
       }
@@ -326,7 +338,7 @@ mhsa_kernel(Args a) {
         }
       }
     }
-    __syncthreads();
+    if constexpr (NBUF == 1) __syncthreads();  // single p_r / tv buffers: all reads done before the next row
   }
 
 #pragma unroll
@@ -344,7 +356,7 @@ mhsa_kernel(Args a) {
 
 template <int NP>
 int32_t launch(const Args& a, bool vec, cudaStream_t st) {
-  constexpr size_t smem = (size_t)(9 * NP * DP + 3 * NP * (NP + 1)) * sizeof(float);
+  constexpr size_t smem = (size_t)(9 * NP * DP + (NP <= 32 ? 5 : 3) * NP * (NP + 4)) * sizeof(float);
   auto kv = mhsa_kernel<NP, true>;
   auto ks = mhsa_kernel<NP, false>;
   static bool attr = false;
