@@ -10,10 +10,13 @@
 //     o_r = p_r v + p v_r
 //     lap_o = [same formula with the Laplacian rows in place of the Jacobian rows]
 //           + sum_r m_r { [p_r c_r + p (2 q_r k_r^T - rowsum(p_r s_r) - rowsum(2 p q_r k_r^T))] v + 2 p_r v_r }
+// The bracket multiplying v is summed over r in registers (the q_r k_r^T part as one accumulated
+// n x n matrix) and applied to v once after the last row, which removes one of the seven
+// contractions per row.
 // Masking follows the reference (lines 389-407, 421-424): scores of masked pairs are -1e20,
 // Jacobian / Laplacian rows of masked electrons are read as zero, m_r = input_mask[r, walker]
 // gates the Hessian term of coordinate r only.
-// Per Jacobian row: three n x n x d and four n x d x n contractions on the CUDA cores (fp32).
+// Per Jacobian row: three n x n x d and three n x d x n contractions on the CUDA cores (fp32).
 #include "common.cuh"
 
 namespace fl {
@@ -91,11 +94,9 @@ mhsa_kernel(Args a) {
   float* V = Kx + NP * DP;
   float* buf = V + NP * DP;        // 2 x {QR, KR, VR}
   float* Pm = buf + 6 * NP * DP;   // [NP][PP]
-  // p_r and the weights of v in the Hessian term for the row in flight; double buffered when
-  // shared memory allows (n <= 32), which saves one block-wide barrier per row
-  constexpr int NBUF = NP <= 32 ? 2 : 1;
-  float* PRb = Pm + NP * PP;          // NBUF x [NP][PP]
-  float* TVb = PRb + NBUF * NP * PP;  // NBUF x [NP][PP]
+  // p_r of the row in flight; double buffered, which saves one block-wide barrier per row
+  constexpr int NBUF = 2;
+  float* PRb = Pm + NP * PP;  // NBUF x [NP][PP]
   __shared__ uint8_t rowmask_s[64];
 
   const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
@@ -196,6 +197,14 @@ mhsa_kernel(Args a) {
   float4 lap_acc[T];
 #pragma unroll
   for (int x = 0; x < T; ++x) lap_acc[x] = make_float4(0.f, 0.f, 0.f, 0.f);
+  // Terms of the Hessian part that multiply v are summed over the rows first and applied to v
+  // once at the end:  sum_r m_r [p_r c_r - p rowsum(p_r s_r)]  +  p (2 S3 - rowsum(2 p S3)),
+  // with S3 = sum_r m_r q_r k_r^T accumulated across the rows.
+  float tvsum[T][T], s3sum[T][T];
+#pragma unroll
+  for (int x = 0; x < T; ++x)
+#pragma unroll
+    for (int y = 0; y < T; ++y) { tvsum[x][y] = 0.f; s3sum[x][y] = 0.f; }
 
   // ---------------- stream the Laplacian row (it == 0) and the R Jacobian rows -------------------
   for (int it = 0; it <= a.R; ++it) {
@@ -210,12 +219,14 @@ mhsa_kernel(Args a) {
       load_tile<NP, VEC>(nb + 2 * NP * DP, a.vj + (int64_t)it * a.vjs, a, b, h, rowmask_s, true);
       if constexpr (VEC) cp_async_commit();
     }
-    float* PR = PRb + (NBUF == 2 ? cur : 0) * NP * PP;
-    float* TV = TVb + (NBUF == 2 ? cur : 0) * NP * PP;
+    float* PR = PRb + cur * NP * PP;
     const float* QR = buf + cur * 3 * NP * DP;
     const float* KR = QR + NP * DP;
     const float* VR = KR + NP * DP;
     const bool hess = it > 0;
+    // m_r gates the Hessian contribution of coordinate r (reference line 481)
+    const float m = !hess ? 0.f
+                          : (a.input_mask ? (a.input_mask[(int64_t)(it - 1) * a.B + b] ? 1.f : 0.f) : 1.f);
 
     // ---- score phase: q_r k^T, q k_r^T, q_r k_r^T ----
     {
@@ -255,26 +266,24 @@ mhsa_kernel(Args a) {
           r1 = fmaf(p[x][y], sr[y], r1);
         }
         r1 = half_warp_sum(r1);  // rowsum(p s_r)
-        float pr[T], r2 = 0.f, r3 = 0.f;
+        float pr[T], r2 = 0.f;
 #pragma unroll
         for (int y = 0; y < T; ++y) {
           pr[y] = p[x][y] * (sr[y] - r1);
           r2 = fmaf(pr[y], sr[y], r2);
-          r3 = fmaf(p[x][y], 2.0f * s3[x][y], r3);
         }
         r2 = half_warp_sum(r2);  // rowsum(p_r s_r)
-        r3 = half_warp_sum(r3);  // rowsum(2 p q_r k_r^T)
 #pragma unroll
         for (int y = 0; y < T; ++y) {
-          const int j = tx + 16 * y;
-          PR[i * PP + j] = pr[y];
-          TV[i * PP + j] = pr[y] * (sr[y] - r1) + p[x][y] * (2.0f * s3[x][y] - r2 - r3);
+          PR[i * PP + tx + 16 * y] = pr[y];
+          tvsum[x][y] = fmaf(m, pr[y] * (sr[y] - r1) - p[x][y] * r2, tvsum[x][y]);
+          s3sum[x][y] = fmaf(m, s3[x][y], s3sum[x][y]);
         }
       }
     }
     __syncthreads();
 
-    // ---- value phase: o_r = p_r v + p v_r ; hessian term = tv v + 2 p_r v_r ----
+    // ---- value phase: o_r = p_r v + p v_r ; per-row Hessian term 2 p_r v_r ----
     {
       float4 oj[T], ct[T];
 #pragma unroll
@@ -282,7 +291,7 @@ mhsa_kernel(Args a) {
         oj[x] = make_float4(0.f, 0.f, 0.f, 0.f);
         ct[x] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
-      // padded key columns carry p = p_r = tv = 0 and zero rows of v, so the loop runs to NP
+      // padded key columns carry p = p_r = 0 and zero rows of v, so the loop runs to NP
       for (int j = 0; j < NP; j += 4) {
         float4 vv[4], vr[4];
 #pragma unroll
@@ -295,21 +304,19 @@ mhsa_kernel(Args a) {
           const int i = ty + 16 * x;
           const float4 pr4 = *reinterpret_cast<const float4*>(PR + i * PP + j);
           const float4 p4 = *reinterpret_cast<const float4*>(Pm + i * PP + j);
-          const float4 tv4 = *reinterpret_cast<const float4*>(TV + i * PP + j);
           const float prs[4] = {pr4.x, pr4.y, pr4.z, pr4.w};
           const float ps[4] = {p4.x, p4.y, p4.z, p4.w};
-          const float tvs[4] = {tv4.x, tv4.y, tv4.z, tv4.w};
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            const float prv = prs[u], pv = ps[u], tv = tvs[u], p2 = 2.0f * prs[u];
+            const float prv = prs[u], pv = ps[u];
             oj[x].x = fmaf(prv, vv[u].x, fmaf(pv, vr[u].x, oj[x].x));
             oj[x].y = fmaf(prv, vv[u].y, fmaf(pv, vr[u].y, oj[x].y));
             oj[x].z = fmaf(prv, vv[u].z, fmaf(pv, vr[u].z, oj[x].z));
             oj[x].w = fmaf(prv, vv[u].w, fmaf(pv, vr[u].w, oj[x].w));
-            ct[x].x = fmaf(tv, vv[u].x, fmaf(p2, vr[u].x, ct[x].x));
-            ct[x].y = fmaf(tv, vv[u].y, fmaf(p2, vr[u].y, ct[x].y));
-            ct[x].z = fmaf(tv, vv[u].z, fmaf(p2, vr[u].z, ct[x].z));
-            ct[x].w = fmaf(tv, vv[u].w, fmaf(p2, vr[u].w, ct[x].w));
+            ct[x].x = fmaf(prv, vr[u].x, ct[x].x);
+            ct[x].y = fmaf(prv, vr[u].y, ct[x].y);
+            ct[x].z = fmaf(prv, vr[u].z, ct[x].z);
+            ct[x].w = fmaf(prv, vr[u].w, ct[x].w);
           }
         }
       }
@@ -318,11 +325,11 @@ mhsa_kernel(Args a) {
         for (int x = 0; x < T; ++x) lap_acc[x] = oj[x];
       } else {
         const int r = it - 1;
-        const float m = a.input_mask ? (a.input_mask[(int64_t)r * a.B + b] ? 1.f : 0.f) : 1.f;
+        const float m2 = 2.0f * m;
 #pragma unroll
         for (int x = 0; x < T; ++x) {
-          lap_acc[x].x = fmaf(m, ct[x].x, lap_acc[x].x); lap_acc[x].y = fmaf(m, ct[x].y, lap_acc[x].y);
-          lap_acc[x].z = fmaf(m, ct[x].z, lap_acc[x].z); lap_acc[x].w = fmaf(m, ct[x].w, lap_acc[x].w);
+          lap_acc[x].x = fmaf(m2, ct[x].x, lap_acc[x].x); lap_acc[x].y = fmaf(m2, ct[x].y, lap_acc[x].y);
+          lap_acc[x].z = fmaf(m2, ct[x].z, lap_acc[x].z); lap_acc[x].w = fmaf(m2, ct[x].w, lap_acc[x].w);
           const int i = ty + 16 * x;
           if (i < n) {
             float* dst = a.oj + (int64_t)r * a.ojs + (((int64_t)b * n + i) * a.H + h) * d + 4 * tx;
@@ -338,7 +345,41 @@ mhsa_kernel(Args a) {
         }
       }
     }
-    if constexpr (NBUF == 1) __syncthreads();  // single p_r / tv buffers: all reads done before the next row
+  }
+
+  // ---------------- the summed weights of v, applied once --------------------------------------
+  {
+    __syncthreads();  // every warp has finished reading the p_r buffers
+    float* TV = PRb;
+#pragma unroll
+    for (int x = 0; x < T; ++x) {
+      const int i = ty + 16 * x;
+      float r3 = 0.f;
+#pragma unroll
+      for (int y = 0; y < T; ++y) r3 = fmaf(p[x][y], 2.0f * s3sum[x][y], r3);
+      r3 = half_warp_sum(r3);  // rowsum(2 p S3)
+#pragma unroll
+      for (int y = 0; y < T; ++y)
+        TV[i * PP + tx + 16 * y] = tvsum[x][y] + p[x][y] * (2.0f * s3sum[x][y] - r3);
+    }
+    __syncthreads();
+    for (int j = 0; j < NP; j += 4) {
+      float4 vv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) vv[u] = *reinterpret_cast<const float4*>(V + (j + u) * DP + 4 * tx);
+#pragma unroll
+      for (int x = 0; x < T; ++x) {
+        const float4 t4 = *reinterpret_cast<const float4*>(TV + (ty + 16 * x) * PP + j);
+        const float ts[4] = {t4.x, t4.y, t4.z, t4.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          lap_acc[x].x = fmaf(ts[u], vv[u].x, lap_acc[x].x);
+          lap_acc[x].y = fmaf(ts[u], vv[u].y, lap_acc[x].y);
+          lap_acc[x].z = fmaf(ts[u], vv[u].z, lap_acc[x].z);
+          lap_acc[x].w = fmaf(ts[u], vv[u].w, lap_acc[x].w);
+        }
+      }
+    }
   }
 
 #pragma unroll
@@ -356,7 +397,7 @@ mhsa_kernel(Args a) {
 
 template <int NP>
 int32_t launch(const Args& a, bool vec, cudaStream_t st) {
-  constexpr size_t smem = (size_t)(9 * NP * DP + (NP <= 32 ? 5 : 3) * NP * (NP + 4)) * sizeof(float);
+  constexpr size_t smem = (size_t)(9 * NP * DP + 3 * NP * (NP + 4)) * sizeof(float);
   auto kv = mhsa_kernel<NP, true>;
   auto ks = mhsa_kernel<NP, false>;
   static bool attr = false;
