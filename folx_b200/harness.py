@@ -32,22 +32,47 @@ def walker_laplacians(f: Callable, r: torch.Tensor, sparsity_threshold: int | fl
     return (laps[0], jacs[0]) if len(laps) == 1 else (torch.cat(laps), torch.cat(jacs))
 
 
+class EnergyEvaluator:
+    """Local energies of walker batches for one wavefunction ``f`` (and potential).
+
+    ``graph=True`` replays each chunk from a CUDA graph after the first calls (``graph.py``): the
+    Python side of the forward Laplacian -- dispatch and index-map algebra -- then runs once per
+    chunk shape, which is what ``jax.jit`` gives the reference.
+    """
+
+    def __init__(self, f: Callable, potential: Callable | None = None,
+                 sparsity_threshold: int | float = 0, chunk: int | None = None, graph: bool = False):
+        self.chunk = chunk
+        lap_fn = vmap(ForwardLaplacianOperator(sparsity_threshold)(f))
+
+        def chunk_energy(rc):
+            lap, jac = lap_fn(rc)
+            pot = potential(rc) if potential is not None else None
+            return kernels.local_energy(lap, jac.reshape(jac.shape[0], -1).t(), pot)
+
+        if graph:
+            from .graph import cuda_graph
+
+            chunk_energy = cuda_graph(chunk_energy)
+        self._chunk_energy = chunk_energy
+        self._graph = graph
+
+    def __call__(self, r: torch.Tensor):
+        B = r.shape[0]
+        chunk = B if self.chunk is None else max(1, min(self.chunk, B))
+        total = torch.zeros(3, dtype=torch.float64, device=r.device)
+        energies = torch.empty(B, dtype=torch.float32, device=r.device)
+        for s in range(0, B, chunk):
+            e, sums = self._chunk_energy(r[s : s + chunk])
+            energies[s : s + chunk].copy_(e)  # graph outputs are reused by the next replay
+            total += sums
+        return energies, total
+
+
 def local_energy_sums(f: Callable, r: torch.Tensor, potential: Callable | None = None,
                       sparsity_threshold: int | float = 0, chunk: int | None = None):
     """Local energies of the walkers on this GPU and ``[sum E, sum E^2, count]`` (fp64, device)."""
-    lap_fn = vmap(ForwardLaplacianOperator(sparsity_threshold)(f))
-    B = r.shape[0]
-    chunk = B if chunk is None else max(1, min(chunk, B))
-    total = torch.zeros(3, dtype=torch.float64, device=r.device)
-    energies = []
-    for s in range(0, B, chunk):
-        rc = r[s : s + chunk]
-        lap, jac = lap_fn(rc)
-        pot = potential(rc) if potential is not None else None
-        e, sums = kernels.local_energy(lap, jac.reshape(jac.shape[0], -1).t(), pot)
-        energies.append(e)
-        total += sums
-    return (energies[0] if len(energies) == 1 else torch.cat(energies)), total
+    return EnergyEvaluator(f, potential, sparsity_threshold, chunk)(r)
 
 
 def reduce_energy(sums: torch.Tensor, group=None):
