@@ -23,7 +23,7 @@ from typing import Any, Callable, Sequence
 import numpy as np
 import torch
 
-from . import registry
+from . import kernels, registry
 from .api import FwdJacobian, FwdLaplArray
 
 
@@ -44,27 +44,41 @@ class BatchedConst(torch.Tensor):
 class LaplTensor:
     """A tensor seen by the traced function: value, Jacobian and Laplacian travel together."""
 
-    __slots__ = ('arr', 'nb', 'thr')
+    __slots__ = ('_arr', 'nb', 'thr', '_terms')
 
-    def __init__(self, arr: FwdLaplArray, nb: int, thr: int):
-        self.arr, self.nb, self.thr = arr, nb, thr
+    def __init__(self, arr: FwdLaplArray | None, nb: int, thr: int, terms=None):
+        # `terms` is a pending sum [(dense triplet or constant, +1 / -1), ...] that has not been
+        # written out yet: a chain of additions is evaluated in one pass, together with the
+        # elementwise function that consumes it if there is one (what XLA's fusion does for the
+        # reference's add / tanh rules)
+        self._arr, self.nb, self.thr, self._terms = arr, nb, thr, terms
+
+    @property
+    def arr(self) -> FwdLaplArray:
+        if self._arr is None:
+            self._arr = kernels.addn(self._terms, 'identity')
+            self._terms = None
+        return self._arr
+
+    def _x_like(self) -> torch.Tensor:
+        return self._arr.x if self._arr is not None else self._terms[0][0].x
 
     # ---- tensor-like attributes (per walker) ----
     @property
     def shape(self):
-        return torch.Size(self.arr.x.shape[self.nb:])
+        return torch.Size(self._x_like().shape[self.nb:])
 
     @property
     def ndim(self):
-        return self.arr.x.ndim - self.nb
+        return self._x_like().ndim - self.nb
 
     @property
     def dtype(self):
-        return self.arr.x.dtype
+        return self._x_like().dtype
 
     @property
     def device(self):
-        return self.arr.x.device
+        return self._x_like().device
 
     def dim(self):
         return self.ndim
@@ -107,7 +121,56 @@ class LaplTensor:
         return t
 
     # ---- arithmetic ----
+    def _dense_terms(self):
+        """This tensor as a list of sum terms, or None if its Jacobian is sparse."""
+        if self._arr is None:
+            return list(self._terms)
+        return None if self._arr.jacobian.weak else [(self._arr, 1.0)]
+
+    def _try_lazy_sum(self, op: str, other, reverse: bool):
+        """`a + b` / `a - b` of dense operands becomes a pending sum instead of a kernel launch."""
+        if op not in ('add', 'sub') or reverse or not registry.is_builtin(op):
+            return None
+        mine = self._dense_terms()
+        if mine is None:
+            return None
+        sign = 1.0 if op == 'add' else -1.0
+        phys = tuple(self._x_like().shape)
+        if isinstance(other, LaplTensor):
+            if other.ndim > self.ndim or other.nb != self.nb:
+                return None
+            theirs = other._rank_to(self.ndim)._dense_terms()
+            if theirs is None:
+                return None
+            oshape = tuple(theirs[0][0].x.shape)
+            theirs = [(t, sign * s) for t, s in theirs]
+        elif torch.is_tensor(other) and other.ndim >= 1 and other.is_floating_point():
+            c = other.as_subclass(torch.Tensor)
+            if isinstance(other, BatchedConst):
+                rank_o = c.ndim - self.nb
+                if rank_o > self.ndim:
+                    return None
+                c = c.reshape(*c.shape[: self.nb], *((1,) * (self.ndim - rank_o)), *c.shape[self.nb:])
+            elif c.ndim > self.ndim:
+                return None
+            oshape = tuple(c.shape)
+            theirs = [(c, sign)]
+        else:
+            return None
+        try:
+            if tuple(torch.broadcast_shapes(phys, oshape)) != phys:
+                return None
+        except RuntimeError:
+            return None
+        terms = mine + theirs
+        if len(terms) > 4:
+            return None
+        return LaplTensor(None, self.nb, self.thr, terms)
+
     def _binary(self, op: str, other, reverse: bool = False):
+        lazy = self._try_lazy_sum(op, other, reverse)
+        if lazy is not None:
+            return lazy
         a = self
         if isinstance(other, LaplTensor):
             rank = max(a.ndim, other.ndim)
@@ -161,6 +224,9 @@ class LaplTensor:
         return self._wrap(_call('dot_general', (W, self.arr), {}, self.thr))
 
     def _unary(self, key: str):
+        if self._arr is None and key in ('tanh', 'silu', 'exp') and registry.is_builtin(key):
+            # pending sum + elementwise function: one fused pass
+            return LaplTensor(kernels.addn(self._terms, key), self.nb, self.thr)
         return self._wrap(_call(key, (self.arr,), {}, self.thr))
 
     def tanh(self): return self._unary('tanh')

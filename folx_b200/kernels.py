@@ -328,3 +328,51 @@ def local_energy(lap: torch.Tensor, jac: torch.Tensor, pot: torch.Tensor | None 
     lib.call('fl_local_energy', _ptr(lap), _ptr(jac), _jac_stride(jac) if K > 1 else max(B, 1),
              _ptr(pot), B, K, _ptr(energy), _ptr(ws), ws.numel() * 8, _ptr(sums), _stream(lap.device))
     return energy, sums
+
+
+def addn(terms, op: str = 'identity') -> FwdLaplArray:
+    """``f(sum_t scale_t * a_t)`` in one pass; ``terms`` is a list of ``(operand, scale)``.
+
+    Operands are dense triplets or plain tensors (constants).  The first operand must have the
+    output shape; the others may be smaller along one run of axes (see ``binary``).  Triplets may
+    have different numbers of Jacobian rows: missing rows count as zero.
+    """
+    first = terms[0][0]
+    assert isinstance(first, FwdLaplArray)
+    shape = tuple(first.x.shape)
+    N = first.x.numel()
+    dev = first.x.device
+    K = max((t.jacobian.data.shape[0] for t, _ in terms if isinstance(t, FwdLaplArray)), default=0)
+    arr = (lib.FlAddnTerm * len(terms))()
+    keep = []
+    for q, (t, scale) in enumerate(terms):
+        is_t = isinstance(t, FwdLaplArray)
+        tshape = tuple((t.x if is_t else t).shape)
+        run = _broadcast_run(shape, tshape)
+        if run is None:
+            if is_t:
+                k = t.jacobian.data.shape[0]
+                pad = (1,) * (len(shape) - len(tshape))
+                t = FwdLaplArray(t.x.reshape(pad + tshape).expand(shape),
+                                 FwdJacobian(t.jacobian.data.reshape(k, *pad, *tshape).expand(k, *shape)),
+                                 t.laplacian.reshape(pad + tshape).expand(shape))
+            else:
+                t = t.expand(shape)
+            run = (N or 1, 1)
+        if is_t:
+            t = as_contiguous(t)
+            x, j, l = t.x, t.jacobian.data, t.laplacian
+            _require_cuda(x, j, l)
+            keep.append(t)
+            arr[q] = lib.FlAddnTerm(x.data_ptr(), j.data_ptr() if j.shape[0] else 0, l.data_ptr(),
+                                    _jac_stride(j), j.shape[0], run[0], run[1], float(scale))
+        else:
+            x = t.to(torch.float32).contiguous()
+            _require_cuda(x)
+            keep.append(x)
+            arr[q] = lib.FlAddnTerm(x.data_ptr(), 0, 0, 0, 0, run[0], run[1], float(scale))
+    out = alloc_triplet(K, shape, dev, None)
+    lib.call('fl_addn_elementwise', lib.ADDN_OPS[op], len(terms), arr, _ptr(out.x),
+             _ptr(out.jacobian.data), _ptr(out.laplacian), K, N, _jac_stride(out.jacobian.data),
+             _stream(dev))
+    return out

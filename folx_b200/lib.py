@@ -26,6 +26,14 @@ ELEMENTWISE_OPS = {
     'abs': 13, 'scale': 14, 'shift': 15, 'reciprocal': 16,
 }
 BINARY_OPS = {'add': 0, 'sub': 1, 'mul': 2, 'div': 3}
+ADDN_OPS = {'identity': 0, 'tanh': 1, 'silu': 2, 'exp': 3}
+
+
+class FlAddnTerm(ctypes.Structure):
+    """One operand of fl_addn_elementwise (mirrors the struct in include/folx_b200.h)."""
+
+    _fields_ = [('x', c_void_p), ('jac', c_void_p), ('lap', c_void_p), ('jac_stride', c_int64),
+                ('K', c_int64), ('inner', c_int64), ('mid', c_int64), ('scale', c_float)]
 
 
 class FolxB200Error(RuntimeError):
@@ -68,6 +76,8 @@ _SIGNATURES = {
                                   c_void_p, c_int64, c_void_p, c_void_p]),
     'fl_local_energy_static': (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                          c_void_p, c_void_p, c_void_p]),
+    'fl_addn_elementwise': (c_int32, [c_int32, c_int32, POINTER(FlAddnTerm), c_void_p, c_void_p,
+                                      c_void_p, c_int64, c_int64, c_int64, c_void_p]),
 }
 
 _lib = None

@@ -288,3 +288,13 @@ for _name, _fn in (('eq', torch.eq), ('lt', torch.lt), ('le', torch.le), ('gt', 
                    ('ge', torch.ge), ('ne', torch.ne), ('sign', torch.sign), ('floor', torch.floor),
                    ('ceil', torch.ceil), ('round', torch.round), ('is_finite', torch.isfinite)):
     register_function(_name, warp_without_fwd_laplacian(_fn))
+
+# The rules above, as shipped.  The front end fuses chains of additions with a following
+# elementwise function only while the entries involved are still these (a user-registered
+# replacement must see every call).
+_BUILTIN = dict(_LAPLACE_FN_REGISTRY)
+
+
+def is_builtin(key) -> bool:
+    """True while ``key`` still maps to the rule this library registered for it."""
+    return key in _BUILTIN and _LAPLACE_FN_REGISTRY.get(key) is _BUILTIN[key]

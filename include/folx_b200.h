@@ -96,6 +96,34 @@ int32_t fl_binary(int32_t op,
                   int64_t K, int64_t N, int64_t b_inner, int64_t b_mid, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Sum of up to FL_ADDN_MAX_TERMS triplets followed by an elementwise function, one pass:
+ *     s = sum_t scale_t a_t,   y = f(s)   with the elementwise rule applied to the summed triplet.
+ * Fuses a chain of `add`/`sub` rules (folx/wrapped_functions.py:364-369) and the elementwise
+ * rule that consumes it (folx/wrapped_functions.py:384-431), e.g. tanh(x W + b + pooled).
+ * A term may be a constant (jac = lap = NULL, K = 0), may have fewer Jacobian rows than the
+ * output (rows >= K are zero: a dense Jacobian truncated at its highest input,
+ * folx/api.py:182-196) and may be broadcast like operand b of fl_binary (inner, mid).
+ * `terms` is a HOST array; its pointers are device pointers.
+ * ------------------------------------------------------------------------------------------- */
+#define FL_ADDN_MAX_TERMS 4
+enum { FL_ADDN_IDENTITY = 0, FL_ADDN_TANH = 1, FL_ADDN_SILU = 2, FL_ADDN_EXP = 3 };
+
+typedef struct FlAddnTerm {
+  const float* x;
+  const float* jac;
+  const float* lap;
+  int64_t jac_stride;
+  int64_t K;
+  int64_t inner;
+  int64_t mid;
+  float scale;
+} FlAddnTerm;
+
+int32_t fl_addn_elementwise(int32_t op, int32_t n_terms, const FlAddnTerm* terms,
+                            float* y, float* jac_y, float* lap_y,
+                            int64_t K, int64_t N, int64_t jac_y_stride, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * dot_general with one constant operand: y = x W (+ b).  Replaces _dot_general_one_constant
  * (folx/wrapped_functions.py:71-171, three lax.dot_general calls at 167-169) and the bias
  * `add` rule that follows a Dense layer (folx/wrapped_functions.py:364-366).

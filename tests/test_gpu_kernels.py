@@ -199,3 +199,22 @@ def test_errors_are_reported_not_swallowed(cuda_device):
     with pytest.raises(RuntimeError):
         kernels.elementwise('tanh', to_device(seeded_triplet(2, (4,), seed=1), 'cpu', stacked=False))
     assert a.x.is_cuda
+
+
+@pytest.mark.parametrize('op', ['identity', 'tanh', 'silu', 'exp'])
+def test_addn_fused_sum_and_activation(cuda_device, op):
+    """sum of a full triplet, a triplet with fewer rows, a broadcast triplet and a constant."""
+    shape = (3, 6, 8)
+    a = seeded_triplet(7, shape, seed=21, scale=0.3)
+    b = seeded_triplet(4, shape, seed=22, scale=0.3)      # fewer Jacobian rows: zero beyond row 4
+    c = seeded_triplet(7, (3, 1, 8), seed=23, scale=0.3)  # broadcast along the middle axis
+    bias = seeded_triplet(0, (8,), seed=24)[0]
+    got = kernels.addn([(to_device(a, cuda_device), 1.0), (to_device(b, cuda_device), -1.0),
+                        (to_device(c, cuda_device), 1.0), (bias.float().to(cuda_device), 1.0)], op)
+    pad = lambda t: (t[0], torch.cat([t[1], torch.zeros(7 - t[1].shape[0], *t[1].shape[1:], dtype=t[1].dtype)]), t[2])
+    bb = pad(b)
+    cc = tuple(torch.broadcast_to(u, (*u.shape[:-3], *shape)) for u in c)
+    s = rules.binary('add', rules.binary('add', rules.binary('sub', a, bb), cc),
+                     rules.constant(torch.broadcast_to(bias, shape), 7))
+    want = s if op == 'identity' else rules.elementwise(op, s)
+    assert_close(to_host(got), want)
