@@ -25,13 +25,20 @@ __device__ __forceinline__ float hdot(float4 a, float4 b) {
 }
 
 // F == 128 * VPL: lane l holds float4 number l + 32 j of the row, j < VPL.
-template <int VPL>
+// TWO: the input is the sum a + c2 * b of two triplets (a residual connection feeding the
+// normalisation), added while loading: x2 / jac2 / lap2 with K2 <= K rows, row stride js2_4.
+__device__ __forceinline__ float4 axpy4(float4 a, float c, float4 b) {
+  return make_float4(fmaf(c, b.x, a.x), fmaf(c, b.y, a.y), fmaf(c, b.z, a.z), fmaf(c, b.w, a.w));
+}
+
+template <int VPL, bool TWO>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
                const float4* __restrict__ lap, const float4* __restrict__ gamma,
                const float4* __restrict__ beta, float eps, float4* __restrict__ y,
                float4* __restrict__ jy, float4* __restrict__ ly, int64_t P, int K, int64_t js4,
-               int64_t jys4) {
+               int64_t jys4, const float4* __restrict__ x2, const float4* __restrict__ jac2,
+               const float4* __restrict__ lap2, int K2, int64_t js2_4, float c2) {
   const int lane = threadIdx.x & 31;
   const int64_t p = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (p >= P) return;
@@ -44,6 +51,7 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     z[j] = ld_stream(x + row + lane + 32 * j);
+    if constexpr (TWO) z[j] = axpy4(z[j], c2, ld_stream(x2 + row + lane + 32 * j));
     s += hsum(z[j]);
     g[j] = gamma ? __ldg(gamma + lane + 32 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
   }
@@ -101,14 +109,23 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
 #pragma unroll
     for (int u = 0; u < kRowUnroll; ++u)
 #pragma unroll
-      for (int j = 0; j < VPL; ++j) v[u][j] = ld_stream(jac + (int64_t)(k + u) * js4 + row + lane + 32 * j);
+      for (int j = 0; j < VPL; ++j) {
+        v[u][j] = ld_stream(jac + (int64_t)(k + u) * js4 + row + lane + 32 * j);
+        if constexpr (TWO)
+          if (k + u < K2)
+            v[u][j] = axpy4(v[u][j], c2, ld_stream(jac2 + (int64_t)(k + u) * js2_4 + row + lane + 32 * j));
+      }
 #pragma unroll
     for (int u = 0; u < kRowUnroll; ++u) process(v[u], k + u);
   }
   for (; k < K; ++k) {
     float4 v[VPL];
 #pragma unroll
-    for (int j = 0; j < VPL; ++j) v[j] = ld_stream(jac + (int64_t)k * js4 + row + lane + 32 * j);
+    for (int j = 0; j < VPL; ++j) {
+      v[j] = ld_stream(jac + (int64_t)k * js4 + row + lane + 32 * j);
+      if constexpr (TWO)
+        if (k < K2) v[j] = axpy4(v[j], c2, ld_stream(jac2 + (int64_t)k * js2_4 + row + lane + 32 * j));
+    }
     process(v, k);
   }
 
@@ -117,6 +134,7 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     l[j] = ld_stream(lap + row + lane + 32 * j);
+    if constexpr (TWO) l[j] = axpy4(l[j], c2, ld_stream(lap2 + row + lane + 32 * j));
     t += hsum(l[j]);
   }
   const float lm = warp_sum(t) * invF;
@@ -221,17 +239,17 @@ extern "C" int32_t fl_layernorm(const float* x, const float* jac, const float* l
   cudaStream_t st = (cudaStream_t)stream;
   int64_t blocks = (P + kWarpsPerBlock - 1) / kWarpsPerBlock;
   FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_layernorm: P too large");
-  bool vec = (F % 128 == 0) && F <= 1024 && (jac_stride % 4 == 0) && (jac_y_stride % 4 == 0) &&
+  bool vec = (F % 128 == 0) && F <= 1024 && (K <= 1 || (jac_stride % 4 == 0 && jac_y_stride % 4 == 0)) &&
              aligned16(x) && aligned16(lap) && aligned16(y) && aligned16(lap_y) &&
              (K == 0 || (aligned16(jac) && aligned16(jac_y))) && (!gamma || aligned16(gamma)) &&
              (!beta || aligned16(beta));
   if (vec) {
 #define FL_LN(V)                                                                                  \
   case V:                                                                                         \
-    layernorm_rows<V><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, st>>>(                          \
+    layernorm_rows<V, false><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, st>>>(                   \
         (const float4*)x, (const float4*)jac, (const float4*)lap, (const float4*)gamma,           \
         (const float4*)beta, eps, (float4*)y, (float4*)jac_y, (float4*)lap_y, P, (int)K,          \
-        jac_stride / 4, jac_y_stride / 4);                                                        \
+        jac_stride / 4, jac_y_stride / 4, nullptr, nullptr, nullptr, 0, 0, 0.f);                  \
     break;
     switch ((int)(F / 128)) {
       FL_LN(1) FL_LN(2) FL_LN(3) FL_LN(4) FL_LN(5) FL_LN(6) FL_LN(7) FL_LN(8)
@@ -248,5 +266,48 @@ extern "C" int32_t fl_layernorm(const float* x, const float* jac, const float* l
         jac_y_stride);
   }
   FL_CHECK_LAUNCH("fl_layernorm launch");
+  return FL_OK;
+}
+
+extern "C" int32_t fl_add_layernorm(const float* x, const float* jac, const float* lap,
+                                    const float* x2, const float* jac2, const float* lap2,
+                                    int64_t K2, int64_t jac2_stride, float scale2,
+                                    const float* gamma, const float* beta, float eps, float* y,
+                                    float* jac_y, float* lap_y, int64_t P, int64_t F, int64_t K,
+                                    int64_t jac_stride, int64_t jac_y_stride, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(P >= 0 && F > 0 && K >= 0 && K2 >= 0 && K2 <= K && K < (1ll << 31), FL_EBADSHAPE,
+             "fl_add_layernorm: bad sizes P=%lld F=%lld K=%lld K2=%lld", (long long)P, (long long)F,
+             (long long)K, (long long)K2);
+  if (P == 0) return FL_OK;
+  FL_REQUIRE(x && lap && x2 && lap2 && y && lap_y && (K == 0 || (jac && jac_y)) && (K2 == 0 || jac2),
+             FL_EBADSHAPE, "fl_add_layernorm: null pointer");
+  FL_REQUIRE(K == 0 || (jac_stride >= P * F && jac_y_stride >= P * F), FL_EBADSHAPE,
+             "fl_add_layernorm: Jacobian row stride smaller than P*F");
+  FL_REQUIRE(K2 <= 1 || jac2_stride >= P * F, FL_EBADSHAPE,
+             "fl_add_layernorm: second Jacobian row stride smaller than P*F");
+  bool vec = (F % 128 == 0) && F <= 1024 && (K <= 1 || (jac_stride % 4 == 0 && jac_y_stride % 4 == 0)) &&
+             (K2 <= 1 || jac2_stride % 4 == 0) && aligned16(x) && aligned16(lap) && aligned16(x2) &&
+             aligned16(lap2) && aligned16(y) && aligned16(lap_y) &&
+             (K == 0 || (aligned16(jac) && aligned16(jac_y))) && (K2 == 0 || aligned16(jac2)) &&
+             (!gamma || aligned16(gamma)) && (!beta || aligned16(beta));
+  FL_REQUIRE(vec, FL_EUNSUPPORTED,
+             "fl_add_layernorm: needs F a multiple of 128 (<= 1024) and 16-byte aligned buffers");
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t blocks = (P + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_add_layernorm: P too large");
+#define FL_LN2(V)                                                                                 \
+  case V:                                                                                         \
+    layernorm_rows<V, true><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, st>>>(                    \
+        (const float4*)x, (const float4*)jac, (const float4*)lap, (const float4*)gamma,           \
+        (const float4*)beta, eps, (float4*)y, (float4*)jac_y, (float4*)lap_y, P, (int)K,          \
+        jac_stride / 4, jac_y_stride / 4, (const float4*)x2, (const float4*)jac2,                 \
+        (const float4*)lap2, (int)K2, jac2_stride / 4, scale2);                                   \
+    break;
+  switch ((int)(F / 128)) {
+    FL_LN2(1) FL_LN2(2) FL_LN2(3) FL_LN2(4) FL_LN2(5) FL_LN2(6) FL_LN2(7) FL_LN2(8)
+  }
+#undef FL_LN2
+  FL_CHECK_LAUNCH("fl_add_layernorm launch");
   return FL_OK;
 }

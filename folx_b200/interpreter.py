@@ -416,6 +416,14 @@ def _slogdet(x):
 def _layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
     if len(tuple(normalized_shape)) != 1:
         raise NotImplementedError('layer_norm on triplets normalises the last axis only')
+    terms = x._terms if x._arr is None else None
+    if (terms is not None and len(terms) == 2 and registry.is_builtin('layer_norm')
+            and all(isinstance(t, FwdLaplArray) and t.x.shape == terms[0][0].x.shape for t, _ in terms)
+            and terms[0][1] == 1.0 and x.shape[-1] % 128 == 0 and x.shape[-1] <= 1024
+            and (terms[1][0].jacobian.data.shape[0] <= terms[0][0].jacobian.data.shape[0] or terms[1][1] == 1.0)):
+        # a residual connection feeding the normalisation: one fused pass
+        (a, _), (b, sb) = terms
+        return LaplTensor(kernels.add_layernorm(a, b, sb, weight, bias, eps), x.nb, x.thr)
     return x._wrap(_call('layer_norm', (x.arr, weight, bias), {'eps': eps}, x.thr))
 
 

@@ -376,3 +376,28 @@ def addn(terms, op: str = 'identity') -> FwdLaplArray:
              _ptr(out.jacobian.data), _ptr(out.laplacian), K, N, _jac_stride(out.jacobian.data),
              _stream(dev))
     return out
+
+
+def add_layernorm(a: FwdLaplArray, b: FwdLaplArray, scale_b: float, gamma, beta, eps: float = 1e-6) -> FwdLaplArray:
+    """``LayerNorm(a + scale_b * b)`` over the last axis in one pass (a residual connection feeding
+    the normalisation).  Both operands dense, same shape; ``b`` may have fewer Jacobian rows."""
+    a, b = as_contiguous(a), as_contiguous(b)
+    if b.jacobian.data.shape[0] > a.jacobian.data.shape[0]:
+        if scale_b != 1.0:
+            raise ValueError('add_layernorm: the operand with more rows must come first')
+        a, b = b, a
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    x2, j2, l2 = b.x, b.jacobian.data, b.laplacian
+    _require_cuda(x, j, l, x2, j2, l2, gamma, beta)
+    assert x.shape == x2.shape
+    F = x.shape[-1]
+    P = x.numel() // F
+    K, K2 = j.shape[0], j2.shape[0]
+    out = alloc_triplet(K, x.shape, x.device, None)
+    lib.call('fl_add_layernorm', _ptr(x), _ptr(j), _ptr(l), _ptr(x2), _ptr(j2), _ptr(l2), K2,
+             _jac_stride(j2), float(scale_b),
+             _ptr(gamma.contiguous() if gamma is not None else None),
+             _ptr(beta.contiguous() if beta is not None else None), float(eps),
+             _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), P, F, K, _jac_stride(j),
+             _jac_stride(out.jacobian.data), _stream(x.device))
+    return out

@@ -178,6 +178,18 @@ int32_t fl_layernorm(const float* x, const float* jac, const float* lap,
                      int64_t P, int64_t F, int64_t K, int64_t jac_stride, int64_t jac_y_stride,
                      void* stream);
 
+/* LayerNorm(a + scale2 * b): fl_layernorm with a residual connection added while loading (the
+ * `add` rule, folx/wrapped_functions.py:364-366, fused into the normalisation).  b has K2 <= K
+ * Jacobian rows (rows >= K2 are zero).  Needs F % 128 == 0, F <= 1024 and 16-byte aligned
+ * buffers; otherwise FL_EUNSUPPORTED (add first, then fl_layernorm). */
+int32_t fl_add_layernorm(const float* x, const float* jac, const float* lap,
+                         const float* x2, const float* jac2, const float* lap2,
+                         int64_t K2, int64_t jac2_stride, float scale2,
+                         const float* gamma, const float* beta, float eps,
+                         float* y, float* jac_y, float* lap_y,
+                         int64_t P, int64_t F, int64_t K, int64_t jac_stride, int64_t jac_y_stride,
+                         void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Sparse Jacobians: moving rows into another row frame with a static table.
  *     out[o, pos] = sum_{s < n_slots} in[take[o, s, tpos(pos)], ipos(pos)]      (take < 0: nothing)

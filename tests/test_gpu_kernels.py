@@ -218,3 +218,17 @@ def test_addn_fused_sum_and_activation(cuda_device, op):
                      rules.constant(torch.broadcast_to(bias, shape), 7))
     want = s if op == 'identity' else rules.elementwise(op, s)
     assert_close(to_host(got), want)
+
+
+@pytest.mark.parametrize('K,K2,P,F,scale', [(6, 6, 9, 256, 1.0), (7, 3, 5, 128, -1.0), (0, 0, 4, 384, 1.0)])
+def test_add_layernorm_fused(cuda_device, K, K2, P, F, scale):
+    a = seeded_triplet(K, (P, F), seed=31)
+    b = seeded_triplet(K2, (P, F), seed=32)
+    g = torch.Generator().manual_seed(33)
+    gamma = torch.randn(F, generator=g, dtype=torch.float64).float().double()
+    beta = torch.randn(F, generator=g, dtype=torch.float64).float().double()
+    got = kernels.add_layernorm(to_device(a, cuda_device), to_device(b, cuda_device), scale,
+                                gamma.float().to(cuda_device), beta.float().to(cuda_device), 1e-6)
+    bp = (b[0], torch.cat([b[1], torch.zeros(K - K2, P, F, dtype=torch.float64)]), b[2])
+    s = rules.binary('add' if scale > 0 else 'sub', a, bp)
+    assert_close(to_host(got), rules.layernorm(s, gamma, beta, 1e-6))
