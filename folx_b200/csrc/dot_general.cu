@@ -60,12 +60,12 @@ extern "C" int32_t fl_dot_general(const float* x, const float* jac, const float*
     const Piece& p = merged[i];
     bool tc_ok = have_ws && gemm_tc_supported(p.a, p.rows, F_in, F_out, p.o) && F_in >= 16 &&
                  F_out >= 16;
-    bool use_tc = g_mode == 2 ? true : (g_mode == 1 ? false : tc_ok);
-    if (g_mode == 2)
+    bool use_tc = g_mode >= 2 ? true : (g_mode == 1 ? false : tc_ok);
+    if (g_mode >= 2)
       FL_REQUIRE(tc_ok, FL_EUNSUPPORTED,
                  "fl_dot_general: tensor-core kernel forced but shape/workspace unsuitable");
     int32_t rc = use_tc ? gemm_tc(p.a, p.rows, F_in, F_out, workspace, bias, p.bias_rows, p.o,
-                                  status, st)
+                                  status, g_mode == 3 ? 1 : (g_mode == 4 ? 2 : 0), st)
                         : gemm_ffma(p.a, p.rows, F_in, F_out, W, bias, p.bias_rows, p.o, st);
     if (rc != FL_OK) return rc;
   }

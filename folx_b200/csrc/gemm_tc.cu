@@ -22,6 +22,15 @@
 //               overlapping the next tile's main loop through the second accumulator
 // Every mbarrier wait is bounded; when one runs out the CTA raises a shared abort flag, all
 // roles drain, tensor memory is released and a status word is written for the host.
+//
+// Pair variant (gemm_tc_kernel<2>, the default when the problem has at least two row tiles): two
+// CTAs of a cluster share every tile of W.  The kernel is bound by shared-memory bandwidth (per
+// K slice one CTA moves 152 KB through its shared memory in the single-CTA form, more than half
+// of it W); with tcgen05.mma.cta_group::2 (M = 256) each CTA stages its own 128 rows of A but only
+// half of the W tile, and the tensor cores of both SMs read both halves.  Roles are the same in
+// both CTAs except that only the even CTA issues MMAs; converter and epilogue warps of the odd CTA
+// arrive on the even CTA's barriers through the cluster shared window, and the even CTA relays
+// "stage free" and "accumulator full" to the odd CTA with one remote arrive each.
 #include <cuda.h>
 
 #include "gemm.cuh"
@@ -32,7 +41,7 @@ namespace {
 constexpr int BLOCK_M = 128;
 constexpr int BLOCK_K = 16;  // fp32 elements = one 64-byte swizzle row
 constexpr int UMMA_K = 8;    // K of one tcgen05.mma kind::tf32
-constexpr int STAGES = 4;    // 4 x 48 KB: three stages in flight while one is consumed
+constexpr int MAX_STAGES = 6;
 // The tensor core reads the upper 19 bits of an fp32 operand (sign, exponent, 10 mantissa bits)
 // and ignores the rest, i.e. it sees trunc_tf32(A).  The products with the raw A tile can then be
 // issued as soon as the copy lands; only the A_lo products wait for the converter warps.  With
@@ -45,13 +54,19 @@ constexpr bool kHwTruncates = true;
 constexpr bool kDirectStore = false;
 constexpr int MAX_N = 256;
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
-constexpr int W_TILE_BYTES = MAX_N * BLOCK_K * 4;
-constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * W_TILE_BYTES;
 constexpr int EPI_WARPS = 4;
 constexpr int EPI_BUF_BYTES = 32 * 32 * 4;
 constexpr int EPI_BYTES = EPI_WARPS * 2 * EPI_BUF_BYTES;
 constexpr int CTRL_BYTES = 256;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
+// Per-variant geometry.  One CTA: 4 stages of 48 KB (A, A_lo, W_hi, W_lo).  Pair: every CTA holds
+// half of the W rows, 6 stages of 32 KB.
+template <int CTAS>
+struct Geom {
+  static constexpr int STAGES = CTAS == 2 ? 6 : 4;
+  static constexpr int W_TILE_BYTES = (MAX_N / CTAS) * BLOCK_K * 4;
+  static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * W_TILE_BYTES;
+  static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + CTRL_BYTES;
+};
 constexpr int NUM_THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr uint32_t SPIN_LIMIT = 1u << 20;  // probes of <= ~2 us each: a wait gives up after ~2 s
@@ -181,10 +196,71 @@ __device__ __forceinline__ uint64_t smem_desc_tile(uint32_t saddr) {
   return d;
 }
 
+// ---- cluster helpers (pair variant) ---------------------------------------------------------
+
+// Address of the same shared-memory offset in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+
+// Arrive on a barrier of a CTA of this cluster.  Plain form (release at CTA scope): what the
+// arrive orders is either tensor-memory reads or shared-memory writes that the arriving CTA's own
+// SM consumes (each SM's tensor core reads its own A tile), never generic-proxy data of another
+// CTA.  The .release.cluster form was measured to cost ~0.5 us per arrive on the converters'
+// critical path (0.38 ms against 0.22 ms on the 401 408 x 256 x 256 case).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// try_wait with cluster-scope acquire: the barrier may have been completed by the other CTA.
+__device__ __forceinline__ bool mbar_try_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(2000u)
+      : "memory");
+  return ok != 0;
+}
+
+template <int CTAS>
+__device__ __forceinline__ bool mbar_wait_t(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < SPIN_LIMIT; ++it) {
+    if (CTAS == 2 ? mbar_try_cluster(bar, parity) : mbar_try(bar, parity)) return true;
+    if (it > 16 && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
+                   : "memory");
+}
+
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
 struct Ctrl {
-  uint64_t full[STAGES];
-  uint64_t conv[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t conv[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tfull[2];
   uint64_t tempty[2];
   uint32_t tmem_base;
@@ -192,12 +268,20 @@ struct Ctrl {
 };
 static_assert(sizeof(Ctrl) <= CTRL_BYTES, "control block too large");
 
+// CTAS = 1: one CTA per tile of 128 rows.  CTAS = 2: launched as clusters of two CTAs; the pair
+// works on two consecutive row tiles and shares W (see the header comment).  num_m_tiles counts
+// groups of CTAS row tiles.
+template <int CTAS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmWhi,
                const __grid_constant__ CUtensorMap tmWlo, const __grid_constant__ CUtensorMap tmY,
                const float* __restrict__ bias, int64_t bias_rows, int num_m_tiles, int num_k_steps,
                int n_tile, int n_chunks, int n_total, float* __restrict__ Y, int64_t M_rows,
                int32_t* __restrict__ status) {
+  using G = Geom<CTAS>;
+  constexpr int STAGES = G::STAGES;
+  constexpr int STAGE_BYTES = G::STAGE_BYTES;
+  constexpr int W_TILE_BYTES = G::W_TILE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* epi = smem + STAGES * STAGE_BYTES;
@@ -207,33 +291,47 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_tiles = num_m_tiles * n_chunks;
+  // position inside the pair and work-item stride (clusters of CTAS consecutive blocks)
+  const uint32_t rank = CTAS == 2 ? (blockIdx.x & 1u) : 0u;
+  const int first_tile = (int)blockIdx.x / CTAS;
+  const int tile_step = (int)gridDim.x / CTAS;
+  const int w_rows = n_tile / CTAS;  // rows of W^T this CTA stages per tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(smem_u32(&ctrl->full[s]), 1);
-      mbar_init(smem_u32(&ctrl->conv[s]), 128);
+      mbar_init(smem_u32(&ctrl->conv[s]), CTAS == 2 ? 2 : 128);
       mbar_init(smem_u32(&ctrl->empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctrl->tfull[a]), 1);
-      mbar_init(smem_u32(&ctrl->tempty[a]), 128);
+      mbar_init(smem_u32(&ctrl->tempty[a]), CTAS == 2 ? 8 : 128);
     }
     ctrl->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                     smem_u32(&ctrl->tmem_base)),
-                 "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&ctrl->tmem_base)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                       smem_u32(&ctrl->tmem_base)),
+                   "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();  // both CTAs' barriers exist before any remote arrive
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
 
-  const uint32_t stage_bytes_tx = (uint32_t)(A_TILE_BYTES + 2 * n_tile * BLOCK_K * 4);
+  const uint32_t stage_bytes_tx = (uint32_t)(A_TILE_BYTES + 2 * w_rows * BLOCK_K * 4);
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -241,18 +339,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const int m_tile = t / n_chunks, n_chunk = t % n_chunks;
+      bool first_round = true;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+        const int m_tile = (t / n_chunks) * CTAS + (int)rank, n_chunk = t % n_chunks;
         for (int ks = 0; ks < num_k_steps; ++ks) {
-          if (!mbar_wait(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag)) { ok = false; break; }
+          if (!mbar_wait_t<CTAS>(smem_u32(&ctrl->empty[stage]), phase ^ 1, abort_flag)) { ok = false; break; }
+          // The MMA commit lands on the even CTA's barrier only: pass it on.  (Nothing to pass in
+          // the first trip round the ring, where the wait above returns on the fresh barrier.)
+          if (CTAS == 2 && rank == 0 && !first_round)
+            mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->empty[stage]), 1));
           uint8_t* sb = smem + stage * STAGE_BYTES;
           const uint32_t bar = smem_u32(&ctrl->full[stage]);
           mbar_expect_tx(bar, stage_bytes_tx);
           tma_load_2d(smem_u32(sb), &tmA, ks * BLOCK_K, m_tile * BLOCK_M, bar);
-          tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES), &tmWhi, ks * BLOCK_K, n_chunk * n_tile, bar);
-          tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES), &tmWlo, ks * BLOCK_K,
-                      n_chunk * n_tile, bar);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          const int w_row0 = n_chunk * n_tile + (int)rank * w_rows;
+          tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES), &tmWhi, ks * BLOCK_K, w_row0, bar);
+          tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES), &tmWlo, ks * BLOCK_K, w_row0,
+                      bar);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; first_round = false; }
         }
       }
       if (!ok) {
@@ -266,52 +370,69 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else if (warp == 5) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      // kind::tf32 instruction descriptor: D = fp32, A = B = TF32, both K-major, M = 128, N = n_tile.
+    // ---------------- MMA issuer (the even CTA of a pair issues for both) ----------------
+    if (lane == 0 && rank == 0) {
+      // kind::tf32 instruction descriptor: D = fp32, A = B = TF32, both K-major,
+      // M = 128 per CTA, N = n_tile.
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_tile >> 3) << 17) |
-                             ((uint32_t)(BLOCK_M >> 4) << 24);
+                             ((uint32_t)((BLOCK_M * CTAS) >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(smem_u32(&ctrl->tempty[acc]), acc_phase ^ 1, abort_flag)) break;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+        if (!mbar_wait_t<CTAS>(smem_u32(&ctrl->tempty[acc]), acc_phase ^ 1, abort_flag)) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * MAX_N);
         for (int ks = 0; ks < num_k_steps; ++ks) {
-          if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag)) { ok = false; break; }
-          if (!kHwTruncates &&
-              !mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
-          tc_fence_after();
           uint8_t* sb = smem + stage * STAGE_BYTES;
           const uint64_t d_ahi = smem_desc_tile(smem_u32(sb));
           const uint64_t d_alo = smem_desc_tile(smem_u32(sb + A_TILE_BYTES));
           const uint64_t d_whi = smem_desc_tile(smem_u32(sb + 2 * A_TILE_BYTES));
           const uint64_t d_wlo = smem_desc_tile(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES));
-          // products that need only what the copy delivered: A_hi W_hi and A_hi W_lo
+          if (CTAS == 2) {
+            // The converters of both CTAs arrive here after they have seen their own copies land,
+            // so this one wait covers A, A_lo and W of both halves.
+            if (!mbar_wait_t<2>(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
 #pragma unroll
-          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-            // advance inside the swizzle row: 8 fp32 = 32 bytes = 2 descriptor units
-            const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
-            umma_tf32(tmem_d, d_ahi + off, d_whi + off, idesc, (ks | kk) != 0);
-            umma_tf32(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
-          }
-          // the tail of A comes from the converter warps
-          if (kHwTruncates &&
-              !mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
-          tc_fence_after();
+            for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+              const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
+              umma_tf32_pair(tmem_d, d_ahi + off, d_whi + off, idesc, (ks | kk) != 0);
+              umma_tf32_pair(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
+              umma_tf32_pair(tmem_d, d_alo + off, d_whi + off, idesc, 1);
+            }
+            umma_commit_pair(smem_u32(&ctrl->empty[stage]));
+          } else {
+            if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag)) { ok = false; break; }
+            if (!kHwTruncates &&
+                !mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            // products that need only what the copy delivered: A_hi W_hi and A_hi W_lo
 #pragma unroll
-          for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
-            const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
-            umma_tf32(tmem_d, d_alo + off, d_whi + off, idesc, 1);
+            for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+              // advance inside the swizzle row: 8 fp32 = 32 bytes = 2 descriptor units
+              const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
+              umma_tf32(tmem_d, d_ahi + off, d_whi + off, idesc, (ks | kk) != 0);
+              umma_tf32(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
+            }
+            // the tail of A comes from the converter warps
+            if (kHwTruncates &&
+                !mbar_wait(smem_u32(&ctrl->conv[stage]), phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+              const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
+              umma_tf32(tmem_d, d_alo + off, d_whi + off, idesc, 1);
+            }
+            umma_commit(smem_u32(&ctrl->empty[stage]));
           }
-          umma_commit(smem_u32(&ctrl->empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(smem_u32(&ctrl->tfull[acc]));
+        if (CTAS == 2) umma_commit_pair(smem_u32(&ctrl->tfull[acc]));
+        else umma_commit(smem_u32(&ctrl->tfull[acc]));
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -321,7 +442,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
       for (int ks = 0; ks < num_k_steps; ++ks) {
         if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag)) { ok = false; break; }
         float4* a4 = (float4*)(smem + stage * STAGE_BYTES);
@@ -341,8 +462,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           l.z = tf32_rna(v.z - h.z); l.w = tf32_rna(v.w - h.w);
           lo4[i] = l;
         }
-        fence_proxy_async();
-        mbar_arrive(smem_u32(&ctrl->conv[stage]));
+        if (CTAS == 2) {
+          // one arrive per CTA: remote arrives are expensive, so the four warps meet first
+          fence_proxy_async();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (ct == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->conv[stage]), 0));
+        } else {
+          fence_proxy_async();
+          mbar_arrive(smem_u32(&ctrl->conv[stage]));
+        }
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
@@ -353,9 +481,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint8_t* my_buf = epi + warp * 2 * EPI_BUF_BYTES;
     int buf = 0;
     const int chunks = (n_tile + 31) / 32;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-      const int m_tile = t / n_chunks, n_chunk = t % n_chunks;
-      if (!mbar_wait(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag)) break;
+    for (int t = first_tile; t < num_tiles; t += tile_step) {
+      const int m_tile = (t / n_chunks) * CTAS + (int)rank, n_chunk = t % n_chunks;
+      if (!mbar_wait_t<CTAS>(smem_u32(&ctrl->tfull[acc]), acc_phase, abort_flag)) break;
+      // the commit lands on the even CTA's barrier only: pass it on to the odd CTA
+      if (CTAS == 2 && rank == 0 && threadIdx.x == 0)
+        mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->tfull[acc]), 1));
       tc_fence_after();
       const int64_t row = (int64_t)m_tile * BLOCK_M + warp * 32 + lane;
       const bool add_bias = bias != nullptr && row < bias_rows;
@@ -367,7 +498,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (c == chunks - 1) {
           // accumulator fully read: hand it back to the MMA warp
           tc_fence_before();
-          mbar_arrive(smem_u32(&ctrl->tempty[acc]));
+          if (CTAS == 2) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&ctrl->tempty[acc]), 0));
+          } else {
+            mbar_arrive(smem_u32(&ctrl->tempty[acc]));
+          }
         }
         if (col0 >= n_total) continue;
         if (add_bias) {
@@ -412,11 +548,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   tc_fence_before();
   __syncthreads();
+  // Neither CTA of a pair may leave (or release tensor memory) while the other can still reach
+  // its shared memory or barriers.
+  if (CTAS == 2) cluster_sync_all();
   if (warp == 0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"(TMEM_COLS)
-                 : "memory");
+    if (CTAS == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(TMEM_COLS)
+                   : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                   "r"(TMEM_COLS)
+                   : "memory");
   }
   if (threadIdx.x == 0 && ctrl->abort_flag && status) atomicExch(status, FL_ETIMEOUT);
 }
@@ -506,33 +650,98 @@ int32_t gemm_tc_prepare(const float* W, int64_t Kc, int64_t N, void* workspace, 
   return FL_OK;
 }
 
+namespace {
+
+// Number of 2-CTA clusters of the pair kernel that can be resident at once (0: cannot launch).
+int max_pair_clusters() {
+  static int cached[64];
+  static bool known[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!known[dev]) {
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * sm_count());
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Geom<2>::SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<2>, &cfg) != cudaSuccess) {
+      cudaGetLastError();
+      n = 0;
+    }
+    cached[dev] = n;
+    known[dev] = true;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
 int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* workspace,
-                const float* bias, int64_t bias_rows, float* Y, int32_t* status, cudaStream_t st) {
+                const float* bias, int64_t bias_rows, float* Y, int32_t* status, int ctas,
+                cudaStream_t st) {
   FL_REQUIRE(gemm_tc_supported(A, M, Kc, N, Y), FL_EUNSUPPORTED,
              "tensor-core GEMM needs F_in %% 4 == 0, F_out %% 4 == 0 and 16-byte aligned buffers");
   FL_REQUIRE(aligned16(workspace), FL_EBADSHAPE, "dot_general workspace must be 16-byte aligned");
   static bool attr_set = false;
   if (!attr_set) {
-    FL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 SMEM_BYTES));
+    FL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Geom<1>::SMEM_BYTES));
+    FL_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 Geom<2>::SMEM_BYTES));
     attr_set = true;
   }
   WSplitGeom g = wsplit_geom(Kc, N);
   const int64_t wrows = g.n_chunks * g.n_tile;
   const float* whi = (const float*)workspace;
   const float* wlo = whi + wrows * g.k_pad;
+  const int num_m_tiles = (int)((M + BLOCK_M - 1) / BLOCK_M);
+  // Pairs pay off once there are two row tiles to share a W tile between.
+  const int pair_clusters = (ctas == 1 || num_m_tiles < 2) ? 0 : max_pair_clusters();
+  const bool pair = pair_clusters > 0;
+  FL_REQUIRE(ctas != 2 || pair, FL_EUNSUPPORTED,
+             "pair tensor-core GEMM forced but unavailable (rows %lld, clusters %d)", (long long)M,
+             pair_clusters);
+  const int w_box_rows = (int)g.n_tile / (pair ? 2 : 1);
   CUtensorMap tmA, tmWhi, tmWlo, tmY;
   int32_t rc;
   if ((rc = make_map(&tmA, A, M, Kc, Kc, BLOCK_M, BLOCK_K, "A")) != FL_OK) return rc;
-  if ((rc = make_map(&tmWhi, whi, wrows, g.k_pad, g.k_pad, (int)g.n_tile, BLOCK_K, "W_hi")) != FL_OK) return rc;
-  if ((rc = make_map(&tmWlo, wlo, wrows, g.k_pad, g.k_pad, (int)g.n_tile, BLOCK_K, "W_lo")) != FL_OK) return rc;
+  if ((rc = make_map(&tmWhi, whi, wrows, g.k_pad, g.k_pad, w_box_rows, BLOCK_K, "W_hi")) != FL_OK) return rc;
+  if ((rc = make_map(&tmWlo, wlo, wrows, g.k_pad, g.k_pad, w_box_rows, BLOCK_K, "W_lo")) != FL_OK) return rc;
   if ((rc = make_map(&tmY, Y, M, N, N, 32, 32, "Y")) != FL_OK) return rc;
-  const int num_m_tiles = (int)((M + BLOCK_M - 1) / BLOCK_M);
-  const int64_t tiles = (int64_t)num_m_tiles * g.n_chunks;
-  int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-  gemm_tc_kernel<<<grid, NUM_THREADS, SMEM_BYTES, st>>>(
-      tmA, tmWhi, tmWlo, tmY, bias, bias_rows, num_m_tiles, (int)(g.k_pad / BLOCK_K),
-      (int)g.n_tile, (int)g.n_chunks, (int)N, Y, M, status);
+  const int num_k_steps = (int)(g.k_pad / BLOCK_K);
+  if (pair) {
+    const int groups = (num_m_tiles + 1) / 2;
+    const int64_t tiles = (int64_t)groups * g.n_chunks;
+    const int clusters = (int)(tiles < pair_clusters ? tiles : pair_clusters);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = Geom<2>::SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<2>, tmA, tmWhi, tmWlo, tmY, bias, bias_rows,
+                               groups, num_k_steps, (int)g.n_tile, (int)g.n_chunks, (int)N, Y, M,
+                               status));
+  } else {
+    const int64_t tiles = (int64_t)num_m_tiles * g.n_chunks;
+    int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    gemm_tc_kernel<1><<<grid, NUM_THREADS, Geom<1>::SMEM_BYTES, st>>>(
+        tmA, tmWhi, tmWlo, tmY, bias, bias_rows, num_m_tiles, num_k_steps, (int)g.n_tile,
+        (int)g.n_chunks, (int)N, Y, M, status);
+  }
   FL_CHECK_LAUNCH("gemm_tc launch");
   return FL_OK;
 }

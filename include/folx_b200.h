@@ -158,7 +158,9 @@ int32_t fl_dot_general(const float* x, const float* jac, const float* lap,
 
 /* Selects the GEMM implementation: 0 = automatic (tensor-core path when the shape allows),
  * 1 = force the CUDA-core fp32 kernel, 2 = force the tensor-core kernel (FL_EUNSUPPORTED if the
- * shape does not fit).  Process-wide; meant for tests and benchmarks. */
+ * shape does not fit), 3 = tensor-core kernel with one CTA per row tile, 4 = tensor-core kernel
+ * with CTA pairs sharing each tile of W (needs at least two row tiles).  Process-wide; meant for
+ * tests and benchmarks. */
 void fl_dot_general_set_mode(int32_t mode);
 
 /* ---------------------------------------------------------------------------------------------

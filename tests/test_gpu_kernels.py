@@ -114,6 +114,27 @@ def test_dot_general(cuda_device, mode, K, P, F_in, F_out, with_bias):
     assert_close(to_host(got), rules.dot_general(t, W, b))
 
 
+@pytest.mark.parametrize('mode', [3, 4])  # 3: one CTA per row tile, 4: CTA pairs sharing W
+@pytest.mark.parametrize('K,P,F_in,F_out', [
+    (2, 130, 32, 16),     # 5 row tiles: the last pair has one tile out of range
+    (3, 129, 256, 256), (7, 33, 64, 48), (5, 200, 100, 100), (2, 80, 36, 260), (1, 300, 256, 512),
+    (30, 1000, 64, 128),  # more tiles than the grid: persistent loop, both accumulators, ring wrap
+])
+def test_dot_general_tensor_core_variants(cuda_device, mode, K, P, F_in, F_out):
+    t = seeded_triplet(K, (P, F_in), seed=21)
+    g = torch.Generator().manual_seed(22)
+    W = (torch.randn(F_in, F_out, generator=g, dtype=torch.float64) / F_in**0.5).float().double()
+    b = (torch.randn(F_out, generator=g, dtype=torch.float64) * 0.1).float().double()
+    lib.load().fl_dot_general_set_mode(mode)
+    try:
+        got = kernels.dot_general(to_device(t, cuda_device), W.float().to(cuda_device),
+                                  b.float().to(cuda_device))
+        kernels.check_gemm_status(cuda_device)
+    finally:
+        lib.load().fl_dot_general_set_mode(0)
+    assert_close(to_host(got), rules.dot_general(t, W, b))
+
+
 def test_dot_general_unstacked_inputs(cuda_device):
     t = seeded_triplet(4, (70, 64), seed=11)
     W = torch.randn(64, 32, dtype=torch.float64).float().double()
