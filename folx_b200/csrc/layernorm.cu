@@ -31,7 +31,11 @@ __device__ __forceinline__ float4 axpy4(float4 a, float c, float4 b) {
   return make_float4(fmaf(c, b.x, a.x), fmaf(c, b.y, a.y), fmaf(c, b.z, a.z), fmaf(c, b.w, a.w));
 }
 
-template <int VPL, bool TWO>
+// SPLIT > 1: SPLIT consecutive warps of a block share one position and take K / SPLIT Jacobian
+// rows each (every one of them recomputes the statistics of x); their partial sums meet in shared
+// memory before the Laplacian row is written.  Used when there are too few positions to fill the
+// machine with one warp each.
+template <int VPL, bool TWO, int SPLIT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
                const float4* __restrict__ lap, const float4* __restrict__ gamma,
@@ -40,8 +44,14 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
                int64_t jys4, const float4* __restrict__ x2, const float4* __restrict__ jac2,
                const float4* __restrict__ lap2, int K2, int64_t js2_4, float c2) {
   const int lane = threadIdx.x & 31;
-  const int64_t p = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (p >= P) return;
+  const int wib = threadIdx.x >> 5;
+  const int part = wib % SPLIT;
+  const int64_t p_raw = (int64_t)blockIdx.x * (kWarpsPerBlock / SPLIT) + wib / SPLIT;
+  if (SPLIT == 1 && p_raw >= P) return;
+  // with SPLIT > 1 every warp reaches the block barrier: out-of-range warps redo the last position
+  // and write nothing
+  const bool live = p_raw < P;
+  const int64_t p = live ? p_raw : P - 1;
   constexpr int F4 = 32 * VPL;
   const float invF = 1.0f / (float)(F4 * 4);
   const int64_t row = p * F4;
@@ -66,10 +76,12 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
 #pragma unroll
   for (int j = 0; j < VPL; ++j) {
     z[j].x *= r; z[j].y *= r; z[j].z *= r; z[j].w *= r;
-    float4 bt = beta ? __ldg(beta + lane + 32 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-    st_stream(y + row + lane + 32 * j,
-              make_float4(fmaf(g[j].x, z[j].x, bt.x), fmaf(g[j].y, z[j].y, bt.y),
-                          fmaf(g[j].z, z[j].z, bt.z), fmaf(g[j].w, z[j].w, bt.w)));
+    if (part == 0 && live) {
+      float4 bt = beta ? __ldg(beta + lane + 32 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+      st_stream(y + row + lane + 32 * j,
+                make_float4(fmaf(g[j].x, z[j].x, bt.x), fmaf(g[j].y, z[j].y, bt.y),
+                            fmaf(g[j].z, z[j].z, bt.z), fmaf(g[j].w, z[j].w, bt.w)));
+    }
   }
 
   float4 s1[VPL];  // sum_k b_k u_k
@@ -98,13 +110,17 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
     for (int j = 0; j < VPL; ++j) {
       s1[j].x = fmaf(b, v[j].x, s1[j].x); s1[j].y = fmaf(b, v[j].y, s1[j].y);
       s1[j].z = fmaf(b, v[j].z, s1[j].z); s1[j].w = fmaf(b, v[j].w, s1[j].w);
-      st_stream(out + 32 * j, make_float4(g[j].x * (v[j].x - z[j].x * b), g[j].y * (v[j].y - z[j].y * b),
+      if (SPLIT == 1 || live)
+        st_stream(out + 32 * j, make_float4(g[j].x * (v[j].x - z[j].x * b), g[j].y * (v[j].y - z[j].y * b),
                                           g[j].z * (v[j].z - z[j].z * b), g[j].w * (v[j].w - z[j].w * b)));
     }
   };
 
-  int k = 0;
-  for (; k + kRowUnroll <= K; k += kRowUnroll) {
+  // rows [k, k_end) of this warp's share
+  const int per = (K + SPLIT - 1) / SPLIT;
+  int k = part * per;
+  const int k_end = min(K, k + per);
+  for (; k + kRowUnroll <= k_end; k += kRowUnroll) {
     float4 v[kRowUnroll][VPL];
 #pragma unroll
     for (int u = 0; u < kRowUnroll; ++u)
@@ -118,7 +134,7 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
 #pragma unroll
     for (int u = 0; u < kRowUnroll; ++u) process(v[u], k + u);
   }
-  for (; k < K; ++k) {
+  for (; k < k_end; ++k) {
     float4 v[VPL];
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
@@ -127,6 +143,27 @@ layernorm_rows(const float4* __restrict__ x, const float4* __restrict__ jac,
         if (k < K2) v[j] = axpy4(v[j], c2, ld_stream(jac2 + (int64_t)k * js2_4 + row + lane + 32 * j));
     }
     process(v, k);
+  }
+
+  if constexpr (SPLIT > 1) {
+    __shared__ float4 sh1[kWarpsPerBlock][VPL * 32];
+    __shared__ float sh2[kWarpsPerBlock];
+    if (part != 0) {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) sh1[wib][lane + 32 * j] = s1[j];
+      if (lane == 0) sh2[wib] = s2;
+    }
+    __syncthreads();
+    if (part != 0 || !live) return;
+#pragma unroll
+    for (int o = 1; o < SPLIT; ++o) {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j) {
+        const float4 a = sh1[wib + o][lane + 32 * j];
+        s1[j].x += a.x; s1[j].y += a.y; s1[j].z += a.z; s1[j].w += a.w;
+      }
+      s2 += sh2[wib + o];
+    }
   }
 
   float4 l[VPL];
@@ -221,6 +258,33 @@ layernorm_rows_generic(const float* __restrict__ x, const float* __restrict__ ja
   }
 }
 
+// Warps per position: 1 when the positions alone give every SM ~40 warps, else 2, and 4 only when
+// there are very few positions (measured on B200 at K = 96: P = 4096 x 256 features 0.160 -> 0.144
+// ms with 2; P = 512 x 1024 features 0.105 -> 0.076 ms with 4).
+int pick_split(int64_t P, int64_t K) {
+  const int64_t want = (int64_t)sm_count() * 40;
+  if (P >= want || K < 8) return 1;
+  if (4 * P >= want || K < 16) return 2;
+  return 4;
+}
+
+template <int VPL, bool TWO>
+void launch_rows(int split, int64_t P, cudaStream_t st, const float* x, const float* jac,
+                 const float* lap, const float* gamma, const float* beta, float eps, float* y,
+                 float* jac_y, float* lap_y, int K, int64_t js4, int64_t jys4, const float* x2,
+                 const float* jac2, const float* lap2, int K2, int64_t js2_4, float c2) {
+#define FL_LN_GO(S)                                                                               \
+  layernorm_rows<VPL, TWO, S>                                                                     \
+      <<<(unsigned)((P + kWarpsPerBlock / S - 1) / (kWarpsPerBlock / S)), kWarpsPerBlock * 32, 0, \
+         st>>>((const float4*)x, (const float4*)jac, (const float4*)lap, (const float4*)gamma,    \
+               (const float4*)beta, eps, (float4*)y, (float4*)jac_y, (float4*)lap_y, P, K, js4,   \
+               jys4, (const float4*)x2, (const float4*)jac2, (const float4*)lap2, K2, js2_4, c2)
+  if (split == 4) FL_LN_GO(4);
+  else if (split == 2) FL_LN_GO(2);
+  else FL_LN_GO(1);
+#undef FL_LN_GO
+}
+
 }  // namespace
 }  // namespace fl
 
@@ -244,12 +308,11 @@ extern "C" int32_t fl_layernorm(const float* x, const float* jac, const float* l
              (K == 0 || (aligned16(jac) && aligned16(jac_y))) && (!gamma || aligned16(gamma)) &&
              (!beta || aligned16(beta));
   if (vec) {
+    const int split = pick_split(P, K);
 #define FL_LN(V)                                                                                  \
   case V:                                                                                         \
-    layernorm_rows<V, false><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, st>>>(                   \
-        (const float4*)x, (const float4*)jac, (const float4*)lap, (const float4*)gamma,           \
-        (const float4*)beta, eps, (float4*)y, (float4*)jac_y, (float4*)lap_y, P, (int)K,          \
-        jac_stride / 4, jac_y_stride / 4, nullptr, nullptr, nullptr, 0, 0, 0.f);                  \
+    launch_rows<V, false>(split, P, st, x, jac, lap, gamma, beta, eps, y, jac_y, lap_y, (int)K,   \
+                          jac_stride / 4, jac_y_stride / 4, nullptr, nullptr, nullptr, 0, 0, 0.f); \
     break;
     switch ((int)(F / 128)) {
       FL_LN(1) FL_LN(2) FL_LN(3) FL_LN(4) FL_LN(5) FL_LN(6) FL_LN(7) FL_LN(8)
@@ -296,13 +359,12 @@ extern "C" int32_t fl_add_layernorm(const float* x, const float* jac, const floa
   cudaStream_t st = (cudaStream_t)stream;
   int64_t blocks = (P + kWarpsPerBlock - 1) / kWarpsPerBlock;
   FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_add_layernorm: P too large");
+  const int split = pick_split(P, K);
 #define FL_LN2(V)                                                                                 \
   case V:                                                                                         \
-    layernorm_rows<V, true><<<(unsigned)blocks, kWarpsPerBlock * 32, 0, st>>>(                    \
-        (const float4*)x, (const float4*)jac, (const float4*)lap, (const float4*)gamma,           \
-        (const float4*)beta, eps, (float4*)y, (float4*)jac_y, (float4*)lap_y, P, (int)K,          \
-        jac_stride / 4, jac_y_stride / 4, (const float4*)x2, (const float4*)jac2,                 \
-        (const float4*)lap2, (int)K2, jac2_stride / 4, scale2);                                   \
+    launch_rows<V, true>(split, P, st, x, jac, lap, gamma, beta, eps, y, jac_y, lap_y, (int)K,    \
+                         jac_stride / 4, jac_y_stride / 4, x2, jac2, lap2, (int)K2,               \
+                         jac2_stride / 4, scale2);                                                \
     break;
   switch ((int)(F / 128)) {
     FL_LN2(1) FL_LN2(2) FL_LN2(3) FL_LN2(4) FL_LN2(5) FL_LN2(6) FL_LN2(7) FL_LN2(8)

@@ -182,7 +182,9 @@ def test_dot_general_bench_shape_linearity(cuda_device):
 
 
 @pytest.mark.parametrize('K,P,F', [(0, 3, 128), (5, 9, 256), (3, 17, 1024), (4, 6, 100), (2, 5, 7),
-                                   (7, 33, 384)])
+                                   (7, 33, 384),
+                                   # few positions: 2 or 4 warps share a position's Jacobian rows
+                                   (9, 5, 128), (21, 11, 256), (18, 3, 1024), (16, 1, 384)])
 @pytest.mark.parametrize('affine', [False, True])
 def test_layernorm(cuda_device, K, P, F, affine):
     t = seeded_triplet(K, (P, F), seed=13)
@@ -241,7 +243,8 @@ def test_addn_fused_sum_and_activation(cuda_device, op):
     assert_close(to_host(got), want)
 
 
-@pytest.mark.parametrize('K,K2,P,F,scale', [(6, 6, 9, 256, 1.0), (7, 3, 5, 128, -1.0), (0, 0, 4, 384, 1.0)])
+@pytest.mark.parametrize('K,K2,P,F,scale', [(6, 6, 9, 256, 1.0), (7, 3, 5, 128, -1.0), (0, 0, 4, 384, 1.0),
+                                            (19, 6, 7, 256, 1.0), (10, 10, 3, 512, -1.0)])
 def test_add_layernorm_fused(cuda_device, K, K2, P, F, scale):
     a = seeded_triplet(K, (P, F), seed=31)
     b = seeded_triplet(K2, (P, F), seed=32)
