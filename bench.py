@@ -307,11 +307,11 @@ def run_ours(args, rank, world, device):
     if dominant.startswith('dot_general'):
         achieved = flops / ms / 1e9
         # DRAM traffic of this kernel from the committed ncu capture (profiles/gemm_tc_kernel_*):
-        # 364.0 MB read + written for 200 704 rows; it grows in proportion to the rows of a launch
+        # 362.0 MB read + written for 200 704 rows; it grows in proportion to the rows of a launch
         rows = ((D if dominant.endswith('dense') else KS) + 2) * B
         roofline = {'kernel': dominant, 'bound': 'tensor', 'achieved': round(achieved, 1),
                     'peak': round(tf32_peak, 1), 'unit': 'TFLOP/s', 'frac': round(achieved / tf32_peak, 3),
-                    'traffic': round(364.0e6 * rows / 200704),
+                    'traffic': round(362.0e6 * rows / 200704),
                     'note': 'achieved = fp32-equivalent (algorithmic) flops; the 3xTF32 split executes 3x '
                             'that on the tensor pipe, so the ceiling is peak/3; peak = measured bf16 / 2 '
                             f'({peaks["source"]}); traffic scaled from the ncu capture at 2048 samples',
