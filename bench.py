@@ -191,14 +191,15 @@ def run_ours(args, rank, world, device):
             torch.distributed.barrier()
         torch.cuda.synchronize(device)
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    kernels.check_gemm_status(device)
-
     # ---- device-resident timing ----
+    # The clock sampler (a thread that spawns nvidia-smi) starts before the warm-up so that the GPU
+    # does not sit idle between the warm-up and the timed steps while the host forks.
     timers: list = []
-    barrier()
     with ClockSampler(device.index or 0) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            step()
+        kernels.check_gemm_status(device)
+        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):

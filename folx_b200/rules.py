@@ -239,12 +239,34 @@ def dot_general(a, W, bias=None, sparsity_threshold: int = 0):
 # sparse_sum_jvp, folx/jvp.py:89-176; dense path is linear, folx/jvp.py:676-684)
 # ------------------------------------------------------------------------------------------
 def _adjacent_axes_last_stride(x: torch.Tensor, axes: tuple[int, ...]):
-    """If ``axes`` form one strided run in contiguous ``x``: (count, stride) of the merged axis."""
+    """If ``axes`` form one strided run in ``x`` (adjacent axes whose strides nest): (count,
+    stride) of the merged axis."""
     axes = tuple(sorted(axes))
     if any(b != a + 1 for a, b in zip(axes, axes[1:])):
         return None
+    if any(x.shape[a] > 1 and x.shape[b] > 1 and x.stride(a) != x.stride(b) * x.shape[b]
+           for a, b in zip(axes, axes[1:])):
+        return None
     n = int(np.prod([x.shape[a] for a in axes], dtype=np.int64))
     return n, x.stride(axes[-1])
+
+
+def _readable_in_place(a: Arr, axes: tuple[int, ...]) -> bool:
+    """Can the gather kernel read this triplet where it lies?  True for a view (a slice along
+    some axes, say) whose x, Jacobian rows and Laplacian share one set of non-negative strides
+    with a contiguous innermost axis, and whose reduced axes form one strided run."""
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    if j.shape[1:] != x.shape or l.shape != x.shape or x.ndim == 0:
+        return False
+    sx = [0 if n == 1 else s for n, s in zip(x.shape, x.stride())]
+    if any(s < 0 for s in sx) or (x.shape[-1] > 1 and sx[-1] != 1):
+        return False
+    for t, strides in ((l, l.stride()), (j, j.stride()[1:])):
+        if [0 if n == 1 else s for n, s in zip(x.shape, strides)] != sx:
+            return False
+    if j.shape[0] > 1 and j.stride(0) < 0:
+        return False
+    return _adjacent_axes_last_stride(x, axes) is not None
 
 
 def reduce_sum(a, axes, keepdim: bool = False, sparsity_threshold: int = 0):
@@ -254,7 +276,8 @@ def reduce_sum(a, axes, keepdim: bool = False, sparsity_threshold: int = 0):
     axes = tuple(sorted({ax % nd for ax in (axes if isinstance(axes, (tuple, list)) else (axes,))}))
     if not axes:
         return a
-    a = kernels.as_contiguous(a)
+    if not _readable_in_place(a, axes):
+        a = kernels.as_contiguous(a)
     if _adjacent_axes_last_stride(a.x, axes) is None:
         # bring the reduced axes together (a copy; only sparse / small tensors get here in practice)
         keep = [d for d in range(nd) if d not in axes]

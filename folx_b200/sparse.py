@@ -74,6 +74,8 @@ def gather_rows(data: torch.Tensor, take: np.ndarray, out_shape: tuple[int, ...]
     if out is None:
         out = torch.empty((k_out, *out_shape), dtype=torch.float32, device=data.device)
     N = int(np.prod(out_shape, dtype=np.int64))
+    if k_out == 0 or N == 0:
+        return out
     table = _device_table(take.reshape(k_out, n_slots, -1), data.device)
     lib.call('fl_gather_rows', _ptr(data), k_in, in_row_stride, _ptr(table), k_out, n_slots,
              _ptr(out), out.stride(0) if k_out > 1 else max(N, 1), nd, _i64(out_shape),

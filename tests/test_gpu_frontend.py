@@ -120,6 +120,45 @@ def test_psiformer_small(cuda_device, thr):
                         samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
 
 
+def check_benchmark_size(f_dev, f_cpu, x, thr):
+    """Full-size networks are deep enough for fp32 round-off to show (plain fp32 reverse-mode AD of
+    the same function is itself 3e-5 .. 4e-4 off the fp64 Jacobian in max norm), so the bound is
+    norm-wise and tied to that: the forward-Laplacian Jacobian must be within 8x the error of fp32
+    AD (or 5e-4; walkers close to a node of the determinant amplify round-off in both), the
+    Laplacian within 3e-3 relative."""
+    lap, jac = folx.vmap(folx.ForwardLaplacianOperator(thr)(f_dev))(x)
+    for s in range(x.shape[0]):
+        y, J, L = brute_force(f_cpu, x[s].double().cpu())
+        J = J.reshape(-1)
+        ad32 = torch.func.jacrev(f_dev)(x[s]).reshape(-1).double().cpu()
+        err_ad = float((ad32 - J).abs().max() / J.abs().max())
+        err = float((jac[s].double().cpu().reshape(-1) - J).abs().max() / J.abs().max())
+        assert err <= max(8 * err_ad, 5e-4), (err, err_ad)
+        assert abs(float(lap[s]) - float(L)) <= 3e-3 * max(abs(float(L)), float(J.abs().max())), (float(lap[s]), float(L))
+
+
+@pytest.mark.parametrize('thr', [0, 6])
+def test_ferminet_benchmark_size(cuda_device, thr):
+    """The FermiNet-style benchmark configuration itself (16 electrons, 4 layers of 256/32, 16
+    determinants) on two walkers against fp64 brute force."""
+    cfg = wf.FermiNetConfig()
+    params = wf.ferminet_params(cfg)
+    pd, p64 = wf.tree_to(params, cuda_device, torch.float32), wf.tree_to(params, 'cpu', torch.float64)
+    r = torch.randn(2, cfg.n_elec, 3, generator=torch.Generator().manual_seed(15)).to(cuda_device)
+    check_benchmark_size(lambda z: wf.ferminet(cfg, pd, z), lambda z: wf.ferminet(cfg, p64, z), r, thr)
+
+
+@pytest.mark.parametrize('thr', [0, 6])
+def test_psiformer_benchmark_size(cuda_device, thr):
+    """The PsiFormer-style benchmark configuration itself (32 electrons, 4 layers, 4 heads of 64,
+    16 determinants of 16 x 16) on two walkers against fp64 brute force."""
+    cfg = wf.PsiFormerConfig()
+    params = wf.psiformer_params(cfg)
+    pd, p64 = wf.tree_to(params, cuda_device, torch.float32), wf.tree_to(params, 'cpu', torch.float64)
+    r = torch.randn(2, cfg.n_elec, 3, generator=torch.Generator().manual_seed(15)).to(cuda_device)
+    check_benchmark_size(lambda z: wf.psiformer(cfg, pd, z), lambda z: wf.psiformer(cfg, p64, z), r, thr)
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

@@ -1,0 +1,52 @@
+"""GPU parity of host-side rules that address views in place (no staging copy): reduce_sum over
+contiguous triplets and over slices / permutations of one, against the oracle."""
+
+import pytest
+import torch
+
+from folx_b200 import rules as dev_rules
+from folx_b200.api import FwdJacobian, FwdLaplArray
+from oracle import rules
+
+from gpu_util import assert_close, seeded_triplet, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+def view_of(a: FwdLaplArray, index) -> FwdLaplArray:
+    return FwdLaplArray(a.x[index], FwdJacobian(a.jacobian.data[(slice(None), *index)], None),
+                        a.laplacian[index])
+
+
+def host_view(t, index):
+    x, J, lap = t
+    return x[index], J[(slice(None), *index)], lap[index]
+
+
+CASES = [
+    # (shape, index applied to the positions, reduced axes)
+    ((6, 10, 16), (slice(None), slice(0, 4), slice(None)), (1,)),     # a slice of the middle axis
+    ((6, 10, 16), (slice(None), slice(4, 10), slice(None)), (1,)),    # the other part of it
+    ((9, 8), (slice(2, 7), slice(None)), (0,)),                      # slice of the leading axis
+    ((5, 6, 7, 8), (slice(None), slice(1, 5), slice(None), slice(None)), (1, 2)),  # nested run broken by the slice
+    ((5, 6, 7, 8), (slice(None), slice(None), slice(2, 6), slice(None)), (1, 2)),
+    ((4, 12), (slice(None), slice(0, 12, 3)), (1,)),                 # strided innermost axis
+    ((7, 5, 16), (slice(None), slice(None), slice(None)), (0, 2)),    # non-adjacent reduced axes
+]
+
+
+@pytest.mark.parametrize('shape,index,axes', CASES)
+@pytest.mark.parametrize('K', [0, 5])
+def test_reduce_sum_reads_views_in_place(cuda_device, shape, index, axes, K):
+    t = seeded_triplet(K, shape, seed=41)
+    a = view_of(to_device(t, cuda_device), index)
+    got = dev_rules.reduce_sum(a, axes)
+    want = rules.reduce_sum(host_view(t, index), axes)
+    assert_close(to_host(got), want)
+
+
+def test_reduce_sum_keepdim_and_full(cuda_device):
+    t = seeded_triplet(3, (4, 6, 8), seed=42)
+    a = to_device(t, cuda_device)
+    assert_close(to_host(dev_rules.reduce_sum(a, (1,), keepdim=True)), rules.reduce_sum(t, (1,), True))
+    assert_close(to_host(dev_rules.reduce_sum(a, (0, 1, 2))), rules.reduce_sum(t, (0, 1, 2)))
