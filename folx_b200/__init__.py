@@ -11,7 +11,7 @@ from .api import (  # noqa: F401
     FwdLaplArgs,
     FwdLaplArray,
 )
-from .attention import multi_head_self_attention  # noqa: F401
+from .attention import multi_head_self_attention, multi_head_self_edge_attention  # noqa: F401
 from .interpreter import LaplTensor, apply_rule, forward_laplacian, vmap  # noqa: F401
 from .operators import (  # noqa: F401
     ForwardLaplacianOperator,
@@ -33,7 +33,7 @@ __all__ = [
     'ParallelLaplacianOperator', 'wrap_forward_laplacian', 'warp_without_fwd_laplacian',
     'wrap_elementwise', 'register_function', 'deregister_function', 'is_registered', 'get_laplacian',
     'FwdLaplArray', 'FwdJacobian', 'FwdLaplArgs', 'FunctionFlags', 'JAC_DIM',
-    'multi_head_self_attention', 'apply_rule', 'LaplTensor',
+    'multi_head_self_attention', 'multi_head_self_edge_attention', 'apply_rule', 'LaplTensor',
 ]
 
 __version__ = '0.1.0'

@@ -59,6 +59,10 @@ struct Args {
   float *o, *oj, *ol;
   int B, n, H, d, R;
   int64_t qjs, kjs, vjs, ojs;
+  // edge bias added to the scores (EDGE kernels only): e (B, n, H, n), its Jacobian rows and
+  // Laplacian; ejs = Jacobian row stride
+  const float *e, *ej, *el;
+  int64_t ejs;
 };
 
 // Loads one (n x d) tile of a (B, n, H, d) tensor into smem rows [NP][DP]; rows >= n, columns >= d
@@ -83,7 +87,11 @@ __device__ __forceinline__ void load_tile(float* dst, const float* src, const Ar
   }
 }
 
-template <int NP, bool VEC>
+// EDGE: scores are q k^T + e with an edge triplet e (multi-head self EDGE attention, reference
+// mhsea_forward_laplacian_kernel, folx/experimental/pallas/attention/forward_laplacian.py:733-854):
+// s_r gains e_r and the direct Laplacian part gains lap(e); the q_r k_r^T term does not change.
+// The n x n rows of e are read straight from global memory into the score-phase registers.
+template <int NP, bool VEC, bool EDGE>
 __global__ void __launch_bounds__(kThreads)
 mhsa_kernel(Args a) {
   constexpr int T = NP / 16;  // per-thread tile edge in the score phase
@@ -135,6 +143,15 @@ mhsa_kernel(Args a) {
       for (int x = 0; x < T; ++x)
 #pragma unroll
         for (int y = 0; y < T; ++y) s[x][y] += dot4(qv[x], kv[y]);
+    }
+    if constexpr (EDGE) {
+#pragma unroll
+      for (int x = 0; x < T; ++x)
+#pragma unroll
+        for (int y = 0; y < T; ++y) {
+          const int i = ty + 16 * x, j = tx + 16 * y;
+          if (i < n && j < n) s[x][y] += __ldg(a.e + (((int64_t)b * n + i) * a.H + h) * n + j);
+        }
     }
 #pragma unroll
     for (int x = 0; x < T; ++x) {
@@ -230,6 +247,21 @@ mhsa_kernel(Args a) {
 
     // ---- score phase: q_r k^T, q k_r^T, q_r k_r^T ----
     {
+      // e_r of this row (issued first so that the loads overlap the contractions); pairs with a
+      // masked electron contribute nothing (reference line 806: "* square_mask")
+      float er[EDGE ? T : 1][EDGE ? T : 1];
+      if constexpr (EDGE) {
+        const float* src = hess ? a.ej + (int64_t)(it - 1) * a.ejs : a.el;
+#pragma unroll
+        for (int x = 0; x < T; ++x)
+#pragma unroll
+          for (int y = 0; y < T; ++y) {
+            const int i = ty + 16 * x, j = tx + 16 * y;
+            er[x][y] = (i < n && j < n && rowmask_s[i] && rowmask_s[j])
+                           ? __ldcs(src + (((int64_t)b * n + i) * a.H + h) * n + j)
+                           : 0.f;
+          }
+      }
       float s1[T][T], s2[T][T], s3[T][T];
 #pragma unroll
       for (int x = 0; x < T; ++x)
@@ -263,6 +295,7 @@ mhsa_kernel(Args a) {
 #pragma unroll
         for (int y = 0; y < T; ++y) {
           sr[y] = s1[x][y] + s2[x][y];
+          if constexpr (EDGE) sr[y] += er[x][y];
           r1 = fmaf(p[x][y], sr[y], r1);
         }
         r1 = half_warp_sum(r1);  // rowsum(p s_r)
@@ -395,11 +428,11 @@ mhsa_kernel(Args a) {
   }
 }
 
-template <int NP>
+template <int NP, bool EDGE>
 int32_t launch(const Args& a, bool vec, cudaStream_t st) {
   constexpr size_t smem = (size_t)(9 * NP * DP + 3 * NP * (NP + 4)) * sizeof(float);
-  auto kv = mhsa_kernel<NP, true>;
-  auto ks = mhsa_kernel<NP, false>;
+  auto kv = mhsa_kernel<NP, true, EDGE>;
+  auto ks = mhsa_kernel<NP, false, EDGE>;
   static bool attr = false;
   if (!attr) {
     FL_CUDA(cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -417,6 +450,38 @@ int32_t launch(const Args& a, bool vec, cudaStream_t st) {
 }  // namespace
 }  // namespace fl
 
+// Shared argument checks and dispatch of fl_mhsa / fl_mhsea.
+namespace fl {
+namespace {
+int32_t run_attention(const char* who, Args a, int64_t B, int64_t n, int64_t H, int64_t d,
+                      int64_t R, bool edge, cudaStream_t st) {
+  FL_REQUIRE(B >= 0 && n >= 1 && H >= 1 && d >= 1 && R >= 0, FL_EBADSHAPE,
+             "%s: bad sizes B=%lld n=%lld H=%lld d=%lld R=%lld", who, (long long)B, (long long)n,
+             (long long)H, (long long)d, (long long)R);
+  FL_REQUIRE(n <= 64 && d <= DMAX, FL_EUNSUPPORTED,
+             "%s: sequence length %lld (max 64) or head dim %lld (max %d) not supported", who,
+             (long long)n, (long long)d, DMAX);
+  if (B == 0) return FL_OK;
+  FL_REQUIRE(a.q && a.k && a.v && a.ql && a.kl && a.vl && a.o && a.ol &&
+                 (R == 0 || (a.qj && a.kj && a.vj && a.oj)),
+             FL_EBADSHAPE, "%s: null pointer", who);
+  FL_REQUIRE(!edge || (a.e && a.el && (R == 0 || a.ej)), FL_EBADSHAPE, "%s: null edge pointer", who);
+  auto al = [](const void* p) { return p == nullptr || aligned16(p); };
+  bool vec = d % 4 == 0 && al(a.q) && al(a.k) && al(a.v) && al(a.qj) && al(a.kj) && al(a.vj) &&
+             al(a.ql) && al(a.kl) && al(a.vl) && al(a.oj) && a.qjs % 4 == 0 && a.kjs % 4 == 0 &&
+             a.vjs % 4 == 0 && a.ojs % 4 == 0;
+  if (edge) {
+    if (n <= 16) return launch<16, true>(a, vec, st);
+    if (n <= 32) return launch<32, true>(a, vec, st);
+    return launch<64, true>(a, vec, st);
+  }
+  if (n <= 16) return launch<16, false>(a, vec, st);
+  if (n <= 32) return launch<32, false>(a, vec, st);
+  return launch<64, false>(a, vec, st);
+}
+}  // namespace
+}  // namespace fl
+
 extern "C" int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_lap, const float* k,
                            const float* k_jac, const float* k_lap, const float* v,
                            const float* v_jac, const float* v_lap, const uint8_t* mask,
@@ -425,25 +490,23 @@ extern "C" int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_la
                            int64_t q_jac_stride, int64_t k_jac_stride, int64_t v_jac_stride,
                            int64_t o_jac_stride, void* stream) {
   using namespace fl;
-  FL_REQUIRE(B >= 0 && n >= 1 && H >= 1 && d >= 1 && R >= 0, FL_EBADSHAPE,
-             "fl_mhsa: bad sizes B=%lld n=%lld H=%lld d=%lld R=%lld", (long long)B, (long long)n,
-             (long long)H, (long long)d, (long long)R);
-  FL_REQUIRE(n <= 64 && d <= DMAX, FL_EUNSUPPORTED,
-             "fl_mhsa: sequence length %lld (max 64) or head dim %lld (max %d) not supported",
-             (long long)n, (long long)d, DMAX);
-  if (B == 0) return FL_OK;
-  FL_REQUIRE(q && k && v && q_lap && k_lap && v_lap && o && o_lap &&
-                 (R == 0 || (q_jac && k_jac && v_jac && o_jac)),
-             FL_EBADSHAPE, "fl_mhsa: null pointer");
   Args a{q, q_jac, q_lap, k, k_jac, k_lap, v, v_jac, v_lap, mask, input_mask, o, o_jac, o_lap,
          (int)B, (int)n, (int)H, (int)d, (int)R, q_jac_stride, k_jac_stride, v_jac_stride,
-         o_jac_stride};
-  auto al = [](const void* p) { return p == nullptr || aligned16(p); };
-  bool vec = d % 4 == 0 && al(q) && al(k) && al(v) && al(q_jac) && al(k_jac) && al(v_jac) &&
-             al(q_lap) && al(k_lap) && al(v_lap) && al(o_jac) && q_jac_stride % 4 == 0 &&
-             k_jac_stride % 4 == 0 && v_jac_stride % 4 == 0 && o_jac_stride % 4 == 0;
-  cudaStream_t st = (cudaStream_t)stream;
-  if (n <= 16) return launch<16>(a, vec, st);
-  if (n <= 32) return launch<32>(a, vec, st);
-  return launch<64>(a, vec, st);
+         o_jac_stride, nullptr, nullptr, nullptr, 0};
+  return run_attention("fl_mhsa", a, B, n, H, d, R, false, (cudaStream_t)stream);
+}
+
+extern "C" int32_t fl_mhsea(const float* q, const float* q_jac, const float* q_lap, const float* k,
+                            const float* k_jac, const float* k_lap, const float* e,
+                            const float* e_jac, const float* e_lap, const float* v,
+                            const float* v_jac, const float* v_lap, const uint8_t* mask,
+                            const uint8_t* input_mask, float* o, float* o_jac, float* o_lap,
+                            int64_t B, int64_t n, int64_t H, int64_t d, int64_t R,
+                            int64_t q_jac_stride, int64_t k_jac_stride, int64_t e_jac_stride,
+                            int64_t v_jac_stride, int64_t o_jac_stride, void* stream) {
+  using namespace fl;
+  Args a{q, q_jac, q_lap, k, k_jac, k_lap, v, v_jac, v_lap, mask, input_mask, o, o_jac, o_lap,
+         (int)B, (int)n, (int)H, (int)d, (int)R, q_jac_stride, k_jac_stride, v_jac_stride,
+         o_jac_stride, e, e_jac, e_lap, e_jac_stride};
+  return run_attention("fl_mhsea", a, B, n, H, d, R, true, (cudaStream_t)stream);
 }

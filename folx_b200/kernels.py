@@ -270,15 +270,16 @@ def slogdet(a: FwdLaplArray):
 
 
 def mhsa(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, mask: torch.Tensor | None = None,
-         input_mask: torch.Tensor | None = None) -> FwdLaplArray:
-    """Softmax self attention ``o = softmax(q k^T) v`` on triplets of shape ``(B, n, H, d)``.
+         input_mask: torch.Tensor | None = None, e: FwdLaplArray | None = None) -> FwdLaplArray:
+    """Softmax self attention ``o = softmax(q k^T [+ e]) v`` on triplets of shape ``(B, n, H, d)``.
 
-    Reference: mhsa_forward_laplacian (folx/experimental/pallas/attention/forward_laplacian.py:
-    27-179).  Sparse Jacobians are densified first, as the reference does (lines 164-178);
-    ``mask`` is ``(B, n)`` bool, ``input_mask`` is ``(R, B)`` bool.
+    Reference: mhsa_forward_laplacian / mhsea_forward_laplacian
+    (folx/experimental/pallas/attention/forward_laplacian.py:27-179, 495-620).  Sparse Jacobians
+    are densified first, as the reference does (lines 164-178); ``mask`` is ``(B, n)`` bool,
+    ``input_mask`` is ``(R, B)`` bool, the optional edge bias ``e`` has shape ``(B, n, H, n)``.
     """
     trip = []
-    for t in (q, k, v):
+    for t in (q, k, v) + ((e,) if e is not None else ()):
         if t.jacobian.weak:
             t = t.dense
         trip.append(as_contiguous(t))
@@ -291,7 +292,7 @@ def mhsa(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, mask: torch.Tensor |
         if R > 1 and j.stride(0) < t.x.numel():
             j = j.contiguous()
         fixed.append((t.x, j, t.laplacian))
-    (qx, qj, ql), (kx, kj, kl), (vx, vj, vl) = fixed
+    (qx, qj, ql), (kx, kj, kl), (vx, vj, vl) = fixed[:3]
     _require_cuda(qx, qj, ql, kx, kj, kl, vx, vj, vl)
     B, n, H, d = qx.shape
     out = alloc_triplet(R, (B, n, H, d), qx.device, None)
@@ -299,13 +300,32 @@ def mhsa(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, mask: torch.Tensor |
     im8 = input_mask.to(torch.uint8).contiguous() if input_mask is not None else None
     if im8 is not None and tuple(im8.shape) != (R, B):
         raise ValueError(f'mhsa: input_mask must have shape {(R, B)}, got {tuple(im8.shape)}')
+    if e is None:
+        lib.call(
+            'fl_mhsa', _ptr(qx), _ptr(qj), _ptr(ql), _ptr(kx), _ptr(kj), _ptr(kl), _ptr(vx), _ptr(vj),
+            _ptr(vl), _ptr(m8), _ptr(im8), _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian),
+            B, n, H, d, R, _jac_stride(qj), _jac_stride(kj), _jac_stride(vj),
+            _jac_stride(out.jacobian.data), _stream(qx.device),
+        )
+        return out
+    ex, ej, el = fixed[3]
+    _require_cuda(ex, ej, el)
+    if tuple(ex.shape) != (B, n, H, n):
+        raise ValueError(f'mhsea: the edge bias must have shape {(B, n, H, n)}, got {tuple(ex.shape)}')
     lib.call(
-        'fl_mhsa', _ptr(qx), _ptr(qj), _ptr(ql), _ptr(kx), _ptr(kj), _ptr(kl), _ptr(vx), _ptr(vj),
-        _ptr(vl), _ptr(m8), _ptr(im8), _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian),
-        B, n, H, d, R, _jac_stride(qj), _jac_stride(kj), _jac_stride(vj),
-        _jac_stride(out.jacobian.data), _stream(qx.device),
+        'fl_mhsea', _ptr(qx), _ptr(qj), _ptr(ql), _ptr(kx), _ptr(kj), _ptr(kl), _ptr(ex), _ptr(ej),
+        _ptr(el), _ptr(vx), _ptr(vj), _ptr(vl), _ptr(m8), _ptr(im8), _ptr(out.x),
+        _ptr(out.jacobian.data), _ptr(out.laplacian), B, n, H, d, R, _jac_stride(qj), _jac_stride(kj),
+        _jac_stride(ej), _jac_stride(vj), _jac_stride(out.jacobian.data), _stream(qx.device),
     )
     return out
+
+
+def mhsea(q: FwdLaplArray, k: FwdLaplArray, e: FwdLaplArray, v: FwdLaplArray,
+          mask: torch.Tensor | None = None, input_mask: torch.Tensor | None = None) -> FwdLaplArray:
+    """Self attention with an edge bias added to the scores (argument order of the reference's
+    ``_multi_head_self_edge_attention``)."""
+    return mhsa(q, k, v, mask, input_mask, e)
 
 
 def local_energy(lap: torch.Tensor, jac: torch.Tensor, pot: torch.Tensor | None = None):

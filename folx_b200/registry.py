@@ -263,6 +263,11 @@ def _mhsa(args, kwargs, sparsity_threshold):
     return rules.mhsa(q, k, v, mask, input_mask, sparsity_threshold)
 
 
+def _mhsea(args, kwargs, sparsity_threshold):
+    q, k, e, v, mask, input_mask = (list(args) + [None, None])[:6]
+    return rules.mhsea(q, k, e, v, mask, input_mask, sparsity_threshold)
+
+
 for _op in ('tanh', 'exp', 'log', 'sqrt', 'rsqrt', 'square', 'sigmoid', 'softplus', 'silu', 'sin',
             'cos', 'neg', 'abs', 'reciprocal'):
     register_function(_op, _unary(_op))
@@ -283,6 +288,7 @@ register_function('expand_dims', _expand_dims)
 register_function('slogdet', _slogdet)
 register_function('layer_norm', _layer_norm)
 register_function('_multi_head_self_attention', _mhsa)
+register_function('_multi_head_self_edge_attention', _mhsea)
 register_function('stop_gradient', warp_without_fwd_laplacian(lambda x: x))
 for _name, _fn in (('eq', torch.eq), ('lt', torch.lt), ('le', torch.le), ('gt', torch.gt),
                    ('ge', torch.ge), ('ne', torch.ne), ('sign', torch.sign), ('floor', torch.floor),

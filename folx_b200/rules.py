@@ -526,20 +526,29 @@ def slogdet(a, sparsity_threshold: int = 0):
     return kernels.slogdet(a)
 
 
-def mhsa(q, k, v, mask=None, input_mask=None, sparsity_threshold: int = 0):
-    """Fused attention rule (reference: mhsa_forward_laplacian)."""
-    if not any(is_triplet(t) for t in (q, k, v)):
+def mhsa(q, k, v, mask=None, input_mask=None, sparsity_threshold: int = 0, e=None):
+    """Fused attention rule (reference: mhsa_forward_laplacian; with an edge bias ``e`` of shape
+    ``(B, n, H, n)`` added to the scores: mhsea_forward_laplacian)."""
+    if not any(is_triplet(t) for t in (q, k, v, e)):
         s = torch.einsum('bihd,bjhd->bhij', q, k)
+        if e is not None:
+            s = s + e.permute(0, 2, 1, 3)
         if mask is not None:
             sq = mask[:, :, None] & mask[:, None, :]
             s = torch.where(sq[:, None], s, torch.full_like(s, -1e20))
         return torch.einsum('bhij,bjhd->bihd', torch.softmax(s, -1), v)
     R = max(t.jacobian.max_n + 1 if t.jacobian.weak else t.jacobian.data.shape[0]
-            for t in (q, k, v) if is_triplet(t))
+            for t in (q, k, v, e) if is_triplet(t))
     trip = []
-    for t in (q, k, v):
-        if not is_triplet(t):
+    for t in (q, k, v, e):
+        if t is not None and not is_triplet(t):
             t = FwdLaplArray(t, FwdJacobian(torch.zeros((R, *t.shape), dtype=t.dtype, device=t.device)),
                              torch.zeros_like(t))
         trip.append(t)
-    return kernels.mhsa(*trip, mask=mask, input_mask=input_mask)
+    return kernels.mhsa(*trip[:3], mask=mask, input_mask=input_mask, e=trip[3])
+
+
+def mhsea(q, k, e, v, mask=None, input_mask=None, sparsity_threshold: int = 0):
+    """Self attention with an edge bias (reference: mhsea_forward_laplacian,
+    folx/experimental/pallas/attention/forward_laplacian.py:495-620); argument order as there."""
+    return mhsa(q, k, v, mask, input_mask, sparsity_threshold, e)

@@ -280,6 +280,26 @@ int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_lap,
                 int64_t o_jac_stride, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Multi-head self EDGE attention on triplets: scores q k^T + e with an edge-bias triplet e.
+ * Replaces mhsea_forward_laplacian and its Pallas kernel
+ * (folx/experimental/pallas/attention/forward_laplacian.py:495-620, 733-854), registered in the
+ * reference under '_multi_head_self_edge_attention'
+ * (folx/experimental/pallas/attention/__init__.py:50-79).  Same kernel, masks and limits as
+ * fl_mhsa; additionally
+ *   e, e_lap : [B][n][H][n] (query electron, head, key electron);  e_jac : [R][B][n][H][n]
+ * e_jac and e_lap enter the score derivatives only for pairs of valid electrons.
+ * ------------------------------------------------------------------------------------------- */
+int32_t fl_mhsea(const float* q, const float* q_jac, const float* q_lap,
+                 const float* k, const float* k_jac, const float* k_lap,
+                 const float* e, const float* e_jac, const float* e_lap,
+                 const float* v, const float* v_jac, const float* v_lap,
+                 const uint8_t* mask, const uint8_t* input_mask,
+                 float* o, float* o_jac, float* o_lap,
+                 int64_t B, int64_t n, int64_t H, int64_t d, int64_t R,
+                 int64_t q_jac_stride, int64_t k_jac_stride, int64_t e_jac_stride,
+                 int64_t v_jac_stride, int64_t o_jac_stride, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Local energy per walker and its statistics.  No counterpart in the reference (it returns
  * (laplacian, jacobian), folx/operators.py:34-36, and leaves the energy to the caller); this is
  * the step a sharded run reduces across GPUs.

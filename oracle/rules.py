@@ -173,7 +173,8 @@ def slogdet(t: Triplet):
 # (folx/experimental/pallas/attention/utils.py:210-220).
 # q, k, v: (B, n, H, d); *_J: (R, B, n, H, d); mask: (B, n) bool; input_mask: (R, B) bool.
 # --------------------------------------------------------------------------------------------
-def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: torch.Tensor) -> Triplet:
+def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: torch.Tensor,
+         e: Triplet | None = None) -> Triplet:
     qx, qJ, ql = q
     kx, kJ, kl = k
     vx, vJ, vl = v
@@ -186,6 +187,14 @@ def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: tor
     sq = (mask[:, :, None] & mask[:, None, :])  # (B, n, n)
     # scores (B, H, n, n)
     s = torch.einsum('bihd,bjhd->bhij', qx, kx)
+    if e is not None:
+        # edge bias (B, n, H, n) -> (B, H, n, n); its derivatives count only between valid
+        # electrons (reference: "* square_mask", forward_laplacian.py:661-666, 806)
+        ex, eJ, el = e
+        sqf = sq[:, None].to(dt)
+        s = s + ex.permute(0, 2, 1, 3)
+        eJ = eJ.permute(0, 1, 3, 2, 4) * sqf
+        el = el.permute(0, 2, 1, 3) * sqf
     s = torch.where(sq[:, None], s, torch.full_like(s, -big))
     p = torch.softmax(s, dim=-1)
     o = torch.einsum('bhij,bjhd->bihd', p, vx)
@@ -201,6 +210,8 @@ def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: tor
 
     # Laplacian, linear part: s_D = q k_D^T + q_D k^T
     sD = torch.einsum('bihd,bjhd->bhij', qx, kl) + torch.einsum('bihd,bjhd->bhij', ql, kx)
+    if e is not None:
+        sD = sD + el
     psD = p * sD
     o_lap = pv(psD, vx) - bihd(rs(psD)) * o + pv(p, vl)
 
@@ -210,6 +221,8 @@ def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: tor
         qr_k = torch.einsum('bihd,bjhd->bhij', qJ[r], kx)
         q_kr = torch.einsum('bihd,bjhd->bhij', qx, kJ[r])
         sr = qr_k + q_kr
+        if e is not None:
+            sr = sr + eJ[r]
         psr = p * sr
         cr_sum = rs(psr)
         pr = psr - p * cr_sum  # d p / d x_r
@@ -223,6 +236,14 @@ def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: tor
         w = input_mask[r].to(dt)[:, None, None, None]
         o_lap = o_lap + w * contrib
     return o, o_J, o_lap
+
+
+def mhsea(q: Triplet, k: Triplet, e: Triplet, v: Triplet, mask: torch.Tensor,
+          input_mask: torch.Tensor) -> Triplet:
+    """Multi-head self edge attention (reference: mhsea_forward_laplacian_kernel,
+    folx/experimental/pallas/attention/forward_laplacian.py:733-854): ``mhsa`` with
+    ``e`` (B, n, H, n) added to the scores; argument order as in the reference."""
+    return mhsa(q, k, v, mask, input_mask, e)
 
 
 # --------------------------------------------------------------------------------------------

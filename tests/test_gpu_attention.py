@@ -91,3 +91,38 @@ def test_mhsa_psiformer_shape_properties(cuda_device):
     out2 = kernels.mhsa(q, k2, v)
     torch.testing.assert_close(out2.x, out.x, rtol=1e-4, atol=1e-5)
     torch.testing.assert_close(out2.jacobian.data, out.jacobian.data, rtol=1e-3, atol=1e-4)
+
+
+def edge_inputs(B, n, H, R, mask, input_mask, seed):
+    e = seeded_triplet(R, (B, n, H, n), seed=seed, scale=0.5)
+    # edges between padded electrons / along padded coordinates carry no derivatives
+    sq = (mask[:, :, None] & mask[:, None, :])[:, :, None, :]
+    return (e[0], e[1] * sq[None] * input_mask[:, :, None, None, None], e[2] * sq)
+
+
+@pytest.mark.parametrize('B,n,H,d,R,max_sequence', [
+    (1, 1, 1, 1, 3, 1), (1, 16, 4, 32, 48, 16), (1, 16, 4, 32, 48, 4),
+    (2, 5, 2, 8, 7, 5), (3, 32, 4, 64, 12, 32), (2, 32, 2, 64, 9, 20), (2, 64, 2, 64, 6, 64),
+    (1, 40, 1, 48, 5, 33), (2, 7, 3, 6, 4, 7),
+])
+def test_mhsea_matches_oracle(cuda_device, B, n, H, d, R, max_sequence):
+    """Edge attention (reference shapes: test/experimental/pallas/test_attention.py:389-470)."""
+    q, k, v, mask, input_mask = make_inputs(B, n, H, d, R, max_sequence, seed=B + n + d)
+    e = edge_inputs(B, n, H, R, mask, input_mask, seed=2 * n + d)
+    dev = lambda t: to_device(t, cuda_device)
+    got = kernels.mhsea(dev(q), dev(k), dev(e), dev(v), mask.to(cuda_device), input_mask.to(cuda_device))
+    want = rules.mhsea(q, k, e, v, mask, input_mask)
+    g, w = blank_out(to_host(got), mask), blank_out(want, mask)
+    assert_close(g[:2], w[:2], rtol=1e-4, atol_scale=2e-5)
+    assert_close(g[2:], w[2:], rtol=1e-3, atol_scale=5e-5)
+
+
+def test_mhsea_with_zero_edges_equals_mhsa(cuda_device):
+    B, n, H, d, R = 2, 16, 2, 32, 10
+    q, k, v, mask, input_mask = make_inputs(B, n, H, d, R, n, seed=77)
+    dev = lambda t: to_device(t, cuda_device)
+    zero = tuple(torch.zeros_like(t) for t in seeded_triplet(R, (B, n, H, n), seed=0))
+    a = kernels.mhsea(dev(q), dev(k), dev(zero), dev(v))
+    b = kernels.mhsa(dev(q), dev(k), dev(v))
+    for x, y in zip(to_host(a), to_host(b)):
+        assert torch.equal(x, y)

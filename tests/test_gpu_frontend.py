@@ -159,6 +159,31 @@ def test_psiformer_benchmark_size(cuda_device, thr):
     check_benchmark_size(lambda z: wf.psiformer(cfg, pd, z), lambda z: wf.psiformer(cfg, p64, z), r, thr)
 
 
+def test_edge_attention_through_the_front_end(cuda_device):
+    """A function whose attention scores carry a distance-dependent edge bias (LapNet-style):
+    ``multi_head_self_edge_attention`` dispatches to the fused rule and matches brute force."""
+    n, H, d = 5, 2, 4
+    g = torch.Generator().manual_seed(21)
+    Wq, Wk, Wv = (torch.randn(3, H * d, generator=g) * 0.5 for _ in range(3))
+    we = torch.randn(H, generator=g)
+
+    def f(P, r):
+        Wq, Wk, Wv, we = P
+        q = (r @ Wq).reshape(n, H, d)
+        k = (r @ Wk).reshape(n, H, d)
+        v = (r @ Wv).reshape(n, H, d)
+        diff = r[:, None, :] - r[None, :, :]
+        dist2 = (diff * diff).sum(-1)                       # (n, n)
+        e = -dist2[:, None, :] * we[None, :, None]          # (n, H, n)
+        o = folx.multi_head_self_edge_attention(q, k, e, v)
+        return (o * o).sum()
+
+    pd = tuple(t.to(cuda_device) for t in (Wq, Wk, Wv, we))
+    p64 = tuple(t.double() for t in (Wq, Wk, Wv, we))
+    r = torch.randn(3, n, 3, generator=g).to(cuda_device)
+    check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), r, 0, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

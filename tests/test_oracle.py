@@ -135,6 +135,38 @@ def test_mhsa_matches_brute_force(masked):
     assert_triplet_close(keep(out), keep(ref), rtol=1e-8, atol=1e-9)
 
 
+def _edge_attention(q, k, e, v, mask):
+    s = torch.einsum('bihd,bjhd->bhij', q, k) + e.permute(0, 2, 1, 3)
+    sq = mask[:, :, None] & mask[:, None, :]
+    s = torch.where(sq[:, None], s, torch.full_like(s, -1e40))
+    return torch.einsum('bhij,bjhd->bihd', torch.softmax(s, -1), v)
+
+
+@pytest.mark.parametrize('masked', [False, True])
+def test_mhsea_matches_brute_force(masked):
+    """Edge attention: the brute-force derivative of softmax(q k^T + e) v (the identity the
+    reference asserts in test/experimental/pallas/test_attention.py:389-470)."""
+    B, n, H, d, R = 2, 4, 2, 3, 5
+    q = rand_triplet(R, (B, n, H, d), seed=14)
+    k = rand_triplet(R, (B, n, H, d), seed=15)
+    v = rand_triplet(R, (B, n, H, d), seed=16)
+    e = rand_triplet(R, (B, n, H, n), seed=17)
+    mask = torch.ones(B, n, dtype=torch.bool)
+    if masked:
+        mask[0, 3] = False
+        mask[1, 2:] = False
+        zero = lambda t: (t[0], t[1] * mask[None, :, :, None, None], t[2] * mask[:, :, None, None])
+        q, k, v = zero(q), zero(k), zero(v)
+        sq = (mask[:, :, None] & mask[:, None, :])[:, :, None, :].to(DT)  # (B, n, 1, n)
+        e = (e[0], e[1] * sq[None], e[2] * sq)
+    input_mask = torch.ones(R, B, dtype=torch.bool)
+    out = rules.mhsea(q, k, e, v, mask, input_mask)
+    ref = brute.propagate(lambda a, b, c, dd: _edge_attention(a, b, c, dd, mask), [q, k, e, v])
+    keep = lambda t: (t[0] * mask[:, :, None, None], t[1] * mask[None, :, :, None, None],
+                      t[2] * mask[:, :, None, None])
+    assert_triplet_close(keep(out), keep(ref), rtol=1e-8, atol=1e-9)
+
+
 def test_mhsa_input_mask_drops_hessian_terms_of_masked_coordinates():
     B, n, H, d, R = 1, 3, 1, 2, 4
     q = rand_triplet(R, (B, n, H, d), seed=7)
