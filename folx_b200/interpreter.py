@@ -215,7 +215,22 @@ class LaplTensor:
 
     def __matmul__(self, W):
         if isinstance(W, LaplTensor):
-            return self._wrap(_call('dot_general', (self.arr, W.arr), {}, self.thr))
+            # two non-constant operands: vectors become matrices, ranks are aligned behind the
+            # walker axes (torch.matmul semantics), then the pair rule runs
+            a, b = self, W
+            va, vb = a.ndim == 1, b.ndim == 1
+            if va:
+                a = a.unsqueeze(0)
+            if vb:
+                b = b.unsqueeze(-1)
+            rank = max(a.ndim, b.ndim)
+            a, b = a._rank_to(rank), b._rank_to(rank)
+            out = self._wrap(_call('dot_general', (a.arr, b.arr), {}, self.thr))
+            if vb:
+                out = out.squeeze(-1)
+            if va:
+                out = out.squeeze(-1 if vb else -2)
+            return out
         if W.ndim == 1:
             return (self @ W[:, None]).squeeze(-1)
         return self._wrap(_call('dot_general', (self.arr, W), {}, self.thr))

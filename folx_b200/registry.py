@@ -199,13 +199,13 @@ def _integer_pow(args, kwargs, sparsity_threshold):
 
 
 def _dot_general(args, kwargs, sparsity_threshold):
-    """``lhs @ rhs`` with exactly one triplet operand (folx/wrapped_functions.py:174-203)."""
+    """``lhs @ rhs``: one triplet operand and a constant (folx/wrapped_functions.py:174-203) or
+    two triplets (folx/wrapped_functions.py:205-309)."""
     lhs, rhs = args
     bias = kwargs.get('bias')
     if isinstance(lhs, FwdLaplArray) and isinstance(rhs, FwdLaplArray):
-        raise NotImplementedError(
-            'dot_general of two triplets is not supported; multi-head self attention has its own '
-            "fused rule ('_multi_head_self_attention')")
+        # both operands carry derivatives (folx/wrapped_functions.py:205-309)
+        return rules.dot_general_pair(lhs, rhs, sparsity_threshold)
     if isinstance(rhs, FwdLaplArray):
         # W @ h == (h^T @ W^T)^T on the last two axes
         nd = rhs.x.ndim

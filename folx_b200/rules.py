@@ -234,6 +234,23 @@ def dot_general(a, W, bias=None, sparsity_threshold: int = 0):
     return kernels.dot_general(a, W, bias, proj)
 
 
+def dot_general_pair(a: Arr, b: Arr, sparsity_threshold: int = 0) -> Arr:
+    """Matrix product of two triplets, ``a: (..., m, c)`` times ``b: (..., c, n)``.
+
+    The reference sends a product of two non-constant operands through a multiplication followed
+    by a sum over the contracted axis (folx/wrapped_functions.py:253-286): the Hessian term is
+    ``2 sum_k sum_c Ja[k, c] Jb[k, c]`` (folx/hessian.py:177-188).  The same decomposition is used
+    here, so sparse operands stay sparse by the rules of ``mul`` (row union) and ``reduce_sum``
+    (union over the contracted axis).  Both operands have the same rank (>= 2); leading axes
+    broadcast.
+    """
+    nd = a.x.ndim
+    if nd < 2 or b.x.ndim != nd or a.x.shape[-1] != b.x.shape[-2]:
+        raise ValueError(f'dot_general_pair: cannot multiply {tuple(a.x.shape)} by {tuple(b.x.shape)}')
+    prod = binary('mul', expand_dims(a, nd), expand_dims(b, nd - 2), sparsity_threshold)  # (..., m, c, n)
+    return reduce_sum(prod, (nd - 1,), False, sparsity_threshold)
+
+
 # ------------------------------------------------------------------------------------------
 # reduce_sum (reference: SUMMATION rule, folx/wrapped_functions.py:387-391; sparse path
 # sparse_sum_jvp, folx/jvp.py:89-176; dense path is linear, folx/jvp.py:676-684)

@@ -114,6 +114,21 @@ def dot_general(t: Triplet, W: torch.Tensor, bias: torch.Tensor | None = None) -
     return y, J @ W, lap @ W
 
 
+def dot_general_pair(a: Triplet, b: Triplet) -> Triplet:
+    """Matrix product of two triplets over the last axis of ``a`` and the second to last of ``b``.
+
+    Reference: the two-operand path of dot_general (folx/wrapped_functions.py:205-309) with the
+    Hessian term of a product, ``2 sum_k Ja_k Jb_k`` contracted like the product itself
+    (dot_product_jac_hessian_jac, folx/hessian.py:177-188).
+    """
+    ax, aJ, al = a
+    bx, bJ, bl = b
+    y = ax @ bx
+    J = aJ @ bx + ax @ bJ
+    lap = al @ bx + ax @ bl + 2 * (aJ @ bJ).sum(0)
+    return y, J, lap
+
+
 # --------------------------------------------------------------------------------------------
 # reductions (linear): folx/wrapped_functions.py:387-391, dense path folx/jvp.py:676-684
 # --------------------------------------------------------------------------------------------

@@ -184,6 +184,29 @@ def test_edge_attention_through_the_front_end(cuda_device):
     check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), r, 0, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
 
 
+@pytest.mark.parametrize('thr', [0, 6])
+def test_product_of_two_non_constant_matrices(cuda_device, thr):
+    """``(r W1) (r W2)^T`` and a matrix-vector product of two traced values: the two-triplet
+    dot_general (mul + sum over the contracted axis), dense and with sparse Jacobians."""
+    n = 4
+    g = torch.Generator().manual_seed(23)
+    W1, W2 = torch.randn(3, 5, generator=g) * 0.5, torch.randn(3, 5, generator=g) * 0.5
+    w = torch.randn(5, generator=g)
+
+    def f(P, r):
+        W1, W2, w = P
+        a = torch.tanh(r @ W1)             # (n, 5), row i depends on electron i only
+        b = r @ W2                          # (n, 5)
+        s = a @ b.transpose(0, 1)           # (n, n): two non-constant operands
+        u = a @ (b * w).sum(0)              # matrix times vector
+        return torch.tanh(s).sum() + (u * u).sum()
+
+    pd = tuple(t.to(cuda_device) for t in (W1, W2, w))
+    p64 = tuple(t.double() for t in (W1, W2, w))
+    r = torch.randn(3, n, 3, generator=g).to(cuda_device)
+    check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), r, thr, samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

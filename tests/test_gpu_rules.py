@@ -50,3 +50,11 @@ def test_reduce_sum_keepdim_and_full(cuda_device):
     a = to_device(t, cuda_device)
     assert_close(to_host(dev_rules.reduce_sum(a, (1,), keepdim=True)), rules.reduce_sum(t, (1,), True))
     assert_close(to_host(dev_rules.reduce_sum(a, (0, 1, 2))), rules.reduce_sum(t, (0, 1, 2)))
+
+
+@pytest.mark.parametrize('K', [0, 6])
+@pytest.mark.parametrize('sa,sb', [((3, 5), (5, 4)), ((2, 3, 5), (2, 5, 4)), ((2, 1, 7), (2, 7, 1)), ((4, 6, 8), (1, 8, 3))])
+def test_dot_general_of_two_triplets(cuda_device, K, sa, sb):
+    a, b = seeded_triplet(K, sa, seed=51), seeded_triplet(K, sb, seed=52)
+    got = dev_rules.dot_general_pair(to_device(a, cuda_device), to_device(b, cuda_device))
+    assert_close(to_host(got), rules.dot_general_pair(a, b))

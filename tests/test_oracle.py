@@ -182,6 +182,12 @@ def test_mhsa_input_mask_drops_hessian_terms_of_masked_coordinates():
     torch.testing.assert_close(a[2], b[2], rtol=1e-10, atol=1e-12)
 
 
+def test_dot_general_pair_matches_brute_force():
+    a = rand_triplet(4, (2, 3, 5), seed=21)
+    b = rand_triplet(4, (2, 5, 4), seed=22)
+    assert_triplet_close(rules.dot_general_pair(a, b), brute.propagate(lambda x, y: x @ y, [a, b]), rtol=1e-9)
+
+
 def test_reduce_sum_and_init():
     t = rand_triplet(3, (4, 5))
     assert_triplet_close(rules.reduce_sum(t, -1), brute.propagate(lambda x: x.sum(-1), [t]))
