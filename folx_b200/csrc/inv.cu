@@ -1,0 +1,200 @@
+// Batched matrix inverse forward-Laplacian rule for small square matrices (n <= 32).
+//
+// With C = A^-1 and M_k = C dA_k (reference: inv_wrapper, folx/linear_solve.py:114-145, which
+// forms M for all k with an einsum and contracts it twice more):
+//   J_k(C)  = -M_k C
+//   lap(C)  = (2 sum_k M_k M_k - C lapA) C
+// A group of N lanes owns one matrix (N = n padded to 8, 16 or 32; 32 / N matrices per warp):
+// lane i holds row i of every product.  C comes from Gauss-Jordan elimination with partial
+// pivoting in shared memory; the K Jacobian matrices then stream through shared memory once,
+// M_k is never written to global memory and sum_k M_k M_k accumulates in shared memory.
+// Work per matrix: 4 (2 K + 3) n^2 bytes of HBM traffic against 6 K n^3 flops on the CUDA cores.
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kBlock = 128;
+
+template <int N>
+__device__ __forceinline__ unsigned group_mask() {
+  if constexpr (N == 32) return 0xffffffffu;
+  const unsigned lane = threadIdx.x & 31u;
+  return ((1u << N) - 1u) << (lane / N * N);
+}
+
+template <int N>
+__global__ void __launch_bounds__(kBlock)
+inv_kernel(const float* __restrict__ A, const float* __restrict__ J, const float* __restrict__ lapA,
+           int64_t n_mat, int K, int64_t js, int n, float* __restrict__ C_out,
+           float* __restrict__ J_out, int64_t jos, float* __restrict__ lap_out) {
+  constexpr int P = N + 1;             // pitch: lane-per-row accesses hit distinct banks
+  constexpr int MPB = kBlock / N;      // matrices per block
+  constexpr int kPerMat = 4 * N * P;   // Cm, D (also [A | I] scratch and output staging), M, Acc
+  extern __shared__ float smem[];
+  const int g = threadIdx.x / N;       // matrix slot in the block
+  const int i = threadIdx.x % N;       // this lane's row
+  const unsigned mask = group_mask<N>();
+  float* Cm = smem + (size_t)g * kPerMat;
+  float* D = Cm + N * P;
+  float* M = D + N * P;
+  float* Acc = M + N * P;
+  const int64_t m = (int64_t)blockIdx.x * MPB + g;
+  const bool live = m < n_mat;
+  const int64_t mm = live ? m : 0;
+  const int nn = n * n;
+
+  // group-wide copy of an n x n matrix from global into a padded N x P tile
+  auto load = [&](const float* src, float* dst, float diag_fill) {
+#pragma unroll 4
+    for (int q = 0; q < N; ++q) {
+      const int e = i + N * q, r = e / N, c = e % N;
+      dst[r * P + c] = (r < n && c < n) ? __ldcs(src + r * n + c) : (r == c ? diag_fill : 0.f);
+    }
+  };
+  auto store = [&](float* dst, const float* src) {
+    if (!live) return;
+#pragma unroll 4
+    for (int q = 0; q < N; ++q) {
+      const int e = i + N * q, r = e / N, c = e % N;
+      if (r < n && c < n) __stcs(dst + r * n + c, src[r * P + c]);
+    }
+  };
+
+  // ---------------- C = A^-1: Gauss-Jordan with partial pivoting on [A | I] = [D | Cm] -----------
+  load(A + mm * nn, D, 1.f);
+#pragma unroll 4
+  for (int c = 0; c < N; ++c) Cm[i * P + c] = (i == c) ? 1.f : 0.f;
+  __syncwarp(mask);
+  for (int c = 0; c < N; ++c) {
+    // pivot row: the first row r >= c with the largest |D[r][c]|
+    float best = i >= c ? fabsf(D[i * P + c]) : -1.f;
+    int piv = i;
+#pragma unroll
+    for (int o = N / 2; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(mask, best, o, N);
+      const int op = __shfl_xor_sync(mask, piv, o, N);
+      if (ob > best || (ob == best && op < piv)) { best = ob; piv = op; }
+    }
+    if (piv != c) {  // lanes swap the two rows, one column pair each
+      float a = D[c * P + i], b = D[piv * P + i];
+      D[c * P + i] = b; D[piv * P + i] = a;
+      a = Cm[c * P + i]; b = Cm[piv * P + i];
+      Cm[c * P + i] = b; Cm[piv * P + i] = a;
+    }
+    __syncwarp(mask);
+    const float ipv = 1.0f / D[c * P + c];
+    __syncwarp(mask);
+    D[c * P + i] *= ipv;
+    Cm[c * P + i] *= ipv;
+    __syncwarp(mask);
+    if (i != c) {
+      const float f = D[i * P + c];
+#pragma unroll 4
+      for (int col = 0; col < N; ++col) {
+        D[i * P + col] = fmaf(-f, D[c * P + col], D[i * P + col]);
+        Cm[i * P + col] = fmaf(-f, Cm[c * P + col], Cm[i * P + col]);
+      }
+      D[i * P + c] = 0.f;
+    }
+    __syncwarp(mask);
+  }
+  store(C_out + mm * nn, Cm);
+
+  // ---------------- Acc = -C lapA -----------------------------------------------------------------
+  __syncwarp(mask);
+  load(lapA + mm * nn, D, 0.f);
+  __syncwarp(mask);
+#pragma unroll 2
+  for (int j = 0; j < N; ++j) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int l = 0; l < N; ++l) s = fmaf(Cm[i * P + l], D[l * P + j], s);
+    Acc[i * P + j] = -s;
+  }
+
+  // ---------------- stream the K Jacobian matrices ------------------------------------------------
+  for (int k = 0; k < K; ++k) {
+    __syncwarp(mask);
+    load(J + (int64_t)k * js + mm * nn, D, 0.f);
+    __syncwarp(mask);
+    // M = C dA_k (row i)
+#pragma unroll 2
+    for (int j = 0; j < N; ++j) {
+      float s = 0.f;
+#pragma unroll 8
+      for (int l = 0; l < N; ++l) s = fmaf(Cm[i * P + l], D[l * P + j], s);
+      M[i * P + j] = s;
+    }
+    __syncwarp(mask);
+    // J_k(C) = -M C into the staging tile (D is free again); Acc += 2 M M
+#pragma unroll 2
+    for (int j = 0; j < N; ++j) {
+      float s = 0.f, t = 0.f;
+#pragma unroll 8
+      for (int l = 0; l < N; ++l) {
+        const float mil = M[i * P + l];
+        s = fmaf(mil, Cm[l * P + j], s);
+        t = fmaf(mil, M[l * P + j], t);
+      }
+      D[i * P + j] = -s;
+      Acc[i * P + j] = fmaf(2.f, t, Acc[i * P + j]);
+    }
+    __syncwarp(mask);
+    store(J_out + (int64_t)k * jos + mm * nn, D);
+  }
+
+  // ---------------- lap(C) = Acc C ----------------------------------------------------------------
+  __syncwarp(mask);
+#pragma unroll 2
+  for (int j = 0; j < N; ++j) {
+    float s = 0.f;
+#pragma unroll 8
+    for (int l = 0; l < N; ++l) s = fmaf(Acc[i * P + l], Cm[l * P + j], s);
+    D[i * P + j] = s;
+  }
+  __syncwarp(mask);
+  store(lap_out + mm * nn, D);
+}
+
+template <int N>
+int32_t launch(const float* A, const float* J, const float* lapA, int64_t n_mat, int64_t K,
+               int64_t js, int n, float* C, float* J_out, int64_t jos, float* lap_out,
+               cudaStream_t st) {
+  constexpr int MPB = kBlock / N;
+  constexpr size_t smem = (size_t)MPB * 4 * N * (N + 1) * sizeof(float);
+  static bool attr = false;
+  if (!attr && smem > 48 * 1024) {
+    FL_CUDA(cudaFuncSetAttribute(inv_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    attr = true;
+  }
+  const int64_t blocks = (n_mat + MPB - 1) / MPB;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_inv: too many matrices");
+  inv_kernel<N><<<(unsigned)blocks, kBlock, smem, st>>>(A, J, lapA, n_mat, (int)K, js, n, C, J_out,
+                                                      jos, lap_out);
+  FL_CHECK_LAUNCH("fl_inv launch");
+  return FL_OK;
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_inv(const float* A, const float* jac, const float* lap, int64_t n_mat,
+                          int64_t n, int64_t K, int64_t jac_stride, float* inv, float* jac_out,
+                          int64_t jac_out_stride, float* lap_out, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(n_mat >= 0 && n >= 1 && K >= 0 && K < (1ll << 31), FL_EBADSHAPE,
+             "fl_inv: bad sizes n_mat=%lld n=%lld K=%lld", (long long)n_mat, (long long)n,
+             (long long)K);
+  FL_REQUIRE(n <= 32, FL_EUNSUPPORTED, "fl_inv: n=%lld > 32 is not supported", (long long)n);
+  if (n_mat == 0) return FL_OK;
+  FL_REQUIRE(A && lap && inv && lap_out && (K == 0 || (jac && jac_out)), FL_EBADSHAPE,
+             "fl_inv: null pointer");
+  FL_REQUIRE(K <= 1 || (jac_stride >= n_mat * n * n && jac_out_stride >= n_mat * n * n),
+             FL_EBADSHAPE, "fl_inv: Jacobian row stride smaller than n_mat*n*n");
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n <= 8) return launch<8>(A, jac, lap, n_mat, K, jac_stride, (int)n, inv, jac_out, jac_out_stride, lap_out, st);
+  if (n <= 16) return launch<16>(A, jac, lap, n_mat, K, jac_stride, (int)n, inv, jac_out, jac_out_stride, lap_out, st);
+  return launch<32>(A, jac, lap, n_mat, K, jac_stride, (int)n, inv, jac_out, jac_out_stride, lap_out, st);
+}

@@ -428,6 +428,36 @@ def _slogdet(x):
     return x._wrap(sign), x._wrap(out)
 
 
+def _det(x):
+    return x._wrap(_call('det', (x.arr,), {}, x.thr))
+
+
+def _inv(x):
+    return x._wrap(_call('inv', (x.arr,), {}, x.thr))
+
+
+def _solve(A, b):
+    """``torch.linalg.solve(A, b)``: a vector right-hand side (one axis fewer than ``A``) becomes a
+    one-column matrix; ranks are aligned behind the walker axes before the rule runs."""
+    t0 = A if isinstance(A, LaplTensor) else b
+    nd = lambda t: t.ndim - (t0.nb if isinstance(t, BatchedConst) else 0)  # per-walker rank
+    vector = nd(b) == nd(A) - 1
+    if vector:
+        b = b.unsqueeze(-1)
+    rank = max(nd(A), nd(b))
+
+    def prep(t):
+        if isinstance(t, LaplTensor):
+            return t._rank_to(rank).arr
+        if isinstance(t, BatchedConst):
+            c = t.as_subclass(torch.Tensor)
+            return c.reshape(*c.shape[: t0.nb], *((1,) * (rank - (c.ndim - t0.nb))), *c.shape[t0.nb:])
+        return t.reshape((1,) * (t0.nb + rank - t.ndim) + tuple(t.shape))
+
+    out = t0._wrap(_call('solve', (prep(A), prep(b)), {}, t0.thr))
+    return out.squeeze(-1) if vector else out
+
+
 def _layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
     if len(tuple(normalized_shape)) != 1:
         raise NotImplementedError('layer_norm on triplets normalises the last axis only')
@@ -487,6 +517,8 @@ _TORCH_TABLE: dict[Any, Callable] = {
     torch.flatten: _method('flatten'), torch.broadcast_to: _method('broadcast_to'),
     torch.cat: _cat, torch.concatenate: _cat, torch.concat: _cat, torch.stack: _stack,
     torch.linalg.slogdet: _slogdet, torch.slogdet: _slogdet,
+    torch.linalg.det: _det, torch.det: _det, torch.linalg.inv: _inv, torch.inverse: _inv,
+    torch.linalg.solve: _solve,
     torch.nn.functional.layer_norm: _layer_norm, torch.logsumexp: _logsumexp,
     torch.softmax: _softmax_unsupported, torch.nn.functional.softmax: _softmax_unsupported,
     torch.detach: _method('detach'),

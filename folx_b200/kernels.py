@@ -269,6 +269,28 @@ def slogdet(a: FwdLaplArray):
     return sign, out
 
 
+def inv(a: FwdLaplArray) -> FwdLaplArray:
+    """Inverse of the matrices in the last two axes (folx/linear_solve.py:114-145).  The Jacobian
+    is densified first: an inverse depends on every coordinate its matrix depends on."""
+    if a.jacobian.weak:
+        a = a.dense
+    a = as_contiguous(a)
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    _require_cuda(x, j, l)
+    n = x.shape[-1]
+    if x.ndim < 2 or x.shape[-2] != n:
+        raise ValueError(f'inv: matrices must be square, got {tuple(x.shape[-2:])}')
+    n_mat = x.numel() // (n * n) if n else 0
+    K = j.shape[0]
+    if K > 1 and j.stride(0) < x.numel():
+        j = j.contiguous()
+    out = alloc_triplet(K, tuple(x.shape), x.device, None)
+    lib.call('fl_inv', _ptr(x), _ptr(j), _ptr(l), n_mat, n, K, _jac_stride(j), _ptr(out.x),
+             _ptr(out.jacobian.data), _jac_stride(out.jacobian.data), _ptr(out.laplacian),
+             _stream(x.device))
+    return out
+
+
 def mhsa(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, mask: torch.Tensor | None = None,
          input_mask: torch.Tensor | None = None, e: FwdLaplArray | None = None) -> FwdLaplArray:
     """Softmax self attention ``o = softmax(q k^T [+ e]) v`` on triplets of shape ``(B, n, H, d)``.

@@ -263,6 +263,18 @@ def _mhsa(args, kwargs, sparsity_threshold):
     return rules.mhsa(q, k, v, mask, input_mask, sparsity_threshold)
 
 
+def _det(args, kwargs, sparsity_threshold):
+    return rules.det(args[0], sparsity_threshold)
+
+
+def _inv(args, kwargs, sparsity_threshold):
+    return rules.inv(args[0], sparsity_threshold)
+
+
+def _solve(args, kwargs, sparsity_threshold):
+    return rules.solve(args[0], args[1], sparsity_threshold)
+
+
 def _mhsea(args, kwargs, sparsity_threshold):
     q, k, e, v, mask, input_mask = (list(args) + [None, None])[:6]
     return rules.mhsea(q, k, e, v, mask, input_mask, sparsity_threshold)
@@ -286,6 +298,9 @@ register_function('concatenate', _concatenate)
 register_function('squeeze', _squeeze)
 register_function('expand_dims', _expand_dims)
 register_function('slogdet', _slogdet)
+register_function('det', _det)
+register_function('inv', _inv)
+register_function('solve', _solve)
 register_function('layer_norm', _layer_norm)
 register_function('_multi_head_self_attention', _mhsa)
 register_function('_multi_head_self_edge_attention', _mhsea)

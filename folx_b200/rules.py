@@ -543,6 +543,53 @@ def slogdet(a, sparsity_threshold: int = 0):
     return kernels.slogdet(a)
 
 
+def det(a, sparsity_threshold: int = 0):
+    """``det A = sign exp(log|det A|)`` through the log-determinant rule, as the reference does
+    (det_wrapper, folx/slogdet.py:361-395)."""
+    if not is_triplet(a):
+        return torch.linalg.det(a)
+    sign, logdet = kernels.slogdet(a)
+    return binary('mul', elementwise('exp', logdet), sign, sparsity_threshold)
+
+
+def inv(a, sparsity_threshold: int = 0):
+    """Matrix inverse over the last two axes (reference: inv_wrapper, folx/linear_solve.py:114-145)."""
+    if not is_triplet(a):
+        return torch.linalg.inv(a)
+    return kernels.inv(a)
+
+
+def _zero_triplet_like(c: torch.Tensor, rows: int, shape) -> Arr:
+    c = c.to(torch.float32).expand(shape).contiguous()
+    return FwdLaplArray(c, FwdJacobian(torch.zeros((rows, *shape), dtype=c.dtype, device=c.device)),
+                        torch.zeros_like(c))
+
+
+def solve(A, b, sparsity_threshold: int = 0):
+    """``A^-1 b`` with ``b: (..., n, m)`` (reference: solve_wrapper, folx/linear_solve.py:54-111).
+
+    Evaluated as the product of the inverse triplet with ``b``, which has the same derivatives:
+    ``d(Cb) = dC b + C db`` with ``dC = -C dA C`` is the reference's ``A d_c y = d_c b - d_c A y``.
+    A constant operand takes part with zero derivatives."""
+    if not is_triplet(A) and not is_triplet(b):
+        return torch.linalg.solve(A, b)
+    t = A if is_triplet(A) else b
+    rows = t.jacobian.max_n + 1 if t.jacobian.weak else t.jacobian.data.shape[0]
+    if not is_triplet(A):
+        lead = tuple(torch.broadcast_shapes(A.shape[:-2], b.x.shape[:-2]))
+        A = _zero_triplet_like(A, rows, (*lead, *A.shape[-2:]))
+    if not is_triplet(b):
+        lead = tuple(torch.broadcast_shapes(A.x.shape[:-2], b.shape[:-2]))
+        b = _zero_triplet_like(b, rows, (*lead, *b.shape[-2:]))
+    C = kernels.inv(A)
+    nd = max(C.x.ndim, b.x.ndim)
+    while C.x.ndim < nd:
+        C = expand_dims(C, 0)
+    while b.x.ndim < nd:
+        b = expand_dims(b, 0)
+    return dot_general_pair(C, b, sparsity_threshold)
+
+
 def mhsa(q, k, v, mask=None, input_mask=None, sparsity_threshold: int = 0, e=None):
     """Fused attention rule (reference: mhsa_forward_laplacian; with an edge bias ``e`` of shape
     ``(B, n, H, n)`` added to the scores: mhsea_forward_laplacian)."""

@@ -258,6 +258,17 @@ int32_t fl_slogdet(const float* A, const float* jac, const float* lap,
                    float* lap_out, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Matrix inverse of a triplet of small square matrices.  Replaces inv_wrapper
+ * (folx/linear_solve.py:114-145).  With C = A^-1 and M_k = C dA_k:
+ *     J_k(C) = -M_k C,     lap(C) = (2 sum_k M_k M_k - C lapA) C
+ *   A, lap, inv, lap_out : [n_mat][n][n];  jac, jac_out : [K][n_mat][n][n] (row strides given)
+ * n <= 32.  A singular matrix yields non-finite values, as a plain inverse would.
+ * ------------------------------------------------------------------------------------------- */
+int32_t fl_inv(const float* A, const float* jac, const float* lap,
+               int64_t n_mat, int64_t n, int64_t K, int64_t jac_stride,
+               float* inv, float* jac_out, int64_t jac_out_stride, float* lap_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Multi-head self attention on triplets, fused.  Replaces mhsa_forward_laplacian and its Pallas
  * kernel (folx/experimental/pallas/attention/forward_laplacian.py:27-179, 349-487), registered
  * in the reference under the jitted name '_multi_head_self_attention'

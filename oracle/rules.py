@@ -188,6 +188,36 @@ def slogdet(t: Triplet):
 # (folx/experimental/pallas/attention/utils.py:210-220).
 # q, k, v: (B, n, H, d); *_J: (R, B, n, H, d); mask: (B, n) bool; input_mask: (R, B) bool.
 # --------------------------------------------------------------------------------------------
+def det(t: Triplet) -> Triplet:
+    """``det A`` from the log-determinant rule (reference: det_wrapper, folx/slogdet.py:361-395):
+    ``J = det J_log``, ``lap = det (lap_log + sum_k J_log_k^2)``."""
+    sign, (ld, J, lap) = slogdet(t)
+    d = sign * torch.exp(ld)
+    return d, d * J, d * (lap + (J * J).sum(0))
+
+
+def inv(t: Triplet) -> Triplet:
+    """``C = A^-1`` (reference: inv_wrapper, folx/linear_solve.py:114-145): with ``M_k = C dA_k``,
+    ``J_k = -M_k C`` and ``lap = (2 sum_k M_k M_k - C lapA) C``."""
+    A, J, lap = t
+    C = torch.linalg.inv(A)
+    M = C @ J
+    inner = 2 * (M @ M).sum(0) - C @ lap
+    return C, -(M @ C), inner @ C
+
+
+def solve(A: Triplet, b: Triplet) -> Triplet:
+    """``y = A^-1 b`` for a matrix right-hand side ``(..., n, m)`` (reference: solve_wrapper,
+    folx/linear_solve.py:54-111): ``A J_k = db_k - dA_k y``,
+    ``A lap = lap_b - lapA y - 2 sum_k dA_k J_k``."""
+    Ax, AJ, Al = A
+    bx, bJ, bl = b
+    y = torch.linalg.solve(Ax, bx)
+    J = torch.linalg.solve(Ax, bJ - AJ @ y)
+    lap = torch.linalg.solve(Ax, bl - Al @ y - 2 * (AJ @ J).sum(0))
+    return y, J, lap
+
+
 def mhsa(q: Triplet, k: Triplet, v: Triplet, mask: torch.Tensor, input_mask: torch.Tensor,
          e: Triplet | None = None) -> Triplet:
     qx, qJ, ql = q

@@ -1,0 +1,83 @@
+"""GPU parity of the linear-algebra rules beside slogdet -- inverse, determinant, linear solve
+(folx/linear_solve.py:54-145, folx/slogdet.py:361-395 restated in the oracle) -- and of the same
+operations reached through the front end."""
+
+import pytest
+import torch
+
+import folx_b200 as folx
+from folx_b200 import kernels
+from folx_b200 import rules as dev_rules
+from oracle import brute, rules
+
+from gpu_util import assert_close, seeded_triplet, to_device, to_host
+
+pytestmark = pytest.mark.gpu
+
+
+def well_conditioned(K, batch, n, seed):
+    x, J, lap = seeded_triplet(K, (*batch, n, n), seed=seed)
+    x = (x / n**0.5 + 1.5 * torch.eye(n, dtype=torch.float64)).float().double()
+    return x, J, lap
+
+
+@pytest.mark.parametrize('n', [1, 2, 3, 5, 8, 9, 12, 16, 17, 24, 32])
+@pytest.mark.parametrize('K,batch', [(0, (3,)), (5, (7,)), (19, (2, 3))])
+def test_inv_matches_oracle(cuda_device, n, K, batch):
+    t = well_conditioned(K, batch, n, seed=n + K)
+    got = kernels.inv(to_device(t, cuda_device))
+    assert_close(to_host(got), rules.inv(t), rtol=2e-4, atol_scale=2e-5)
+
+
+def test_inv_with_row_exchanges(cuda_device):
+    g = torch.Generator().manual_seed(6)
+    n, K = 8, 5
+    x = torch.randn(64, n, n, generator=g, dtype=torch.float64)
+    x[:, 0, 0] = 1e-3  # forces row exchanges
+    x = x.float().double()
+    J = torch.randn(K, 64, n, n, generator=g, dtype=torch.float64).float().double()
+    lap = torch.randn(64, n, n, generator=g, dtype=torch.float64).float().double()
+    keep = torch.linalg.cond(x) < 30
+    t = (x[keep], J[:, keep], lap[keep])
+    got = kernels.inv(to_device(t, cuda_device))
+    assert_close(to_host(got), rules.inv(t), rtol=2e-3, atol_scale=2e-4)
+
+
+@pytest.mark.parametrize('n,K', [(3, 4), (8, 9), (16, 5)])
+def test_det_and_solve_rules(cuda_device, n, K):
+    A = well_conditioned(K, (4,), n, seed=n)
+    b = seeded_triplet(K, (4, n, 3), seed=n + 1)
+    got = dev_rules.det(to_device(A, cuda_device))
+    assert_close(to_host(got), rules.det(A), rtol=3e-4, atol_scale=3e-5)
+    got = dev_rules.solve(to_device(A, cuda_device), to_device(b, cuda_device))
+    assert_close(to_host(got), rules.solve(A, b), rtol=3e-4, atol_scale=3e-5)
+    # a constant operand on either side
+    zero = lambda t: (t[0], torch.zeros_like(t[1]), torch.zeros_like(t[2]))
+    got = dev_rules.solve(A[0].float().to(cuda_device), to_device(b, cuda_device))
+    assert_close(to_host(got), rules.solve(zero(A), b), rtol=3e-4, atol_scale=3e-5)
+    got = dev_rules.solve(to_device(A, cuda_device), b[0].float().to(cuda_device))
+    assert_close(to_host(got), rules.solve(A, zero(b)), rtol=3e-4, atol_scale=3e-5)
+
+
+def test_linalg_through_the_front_end(cuda_device):
+    """det, inv and solve of matrices built from the coordinates, against brute-force AD."""
+    n = 3
+    g = torch.Generator().manual_seed(9)
+    W = torch.randn(3, n, generator=g) * 0.4
+    w = torch.randn(n, generator=g)
+
+    def f(P, r):
+        W, w = P
+        A = r @ W + 2.0 * torch.eye(n, dtype=r.dtype, device=r.device)   # (n, n)
+        y = torch.linalg.solve(A, torch.tanh(r @ W) @ w)                  # (n,)
+        return torch.linalg.det(A) + (torch.linalg.inv(A) * A.transpose(0, 1)).sum() + (y * y).sum()
+
+    pd = tuple(t.to(cuda_device) for t in (W, w))
+    p64 = tuple(t.double() for t in (W, w))
+    r = torch.randn(3, n, 3, generator=g).to(cuda_device)
+    lap, jac = folx.vmap(folx.ForwardLaplacianOperator(0)(lambda z: f(pd, z)))(r)
+    for s in range(3):
+        y, J, L = brute.jac_and_laplacian(lambda z: f(p64, z), r[s].double().cpu())
+        scale = float(J.abs().max())
+        torch.testing.assert_close(jac[s].double().cpu().reshape(-1), J.reshape(-1), rtol=5e-4, atol=5e-5 * scale)
+        torch.testing.assert_close(lap[s].double().cpu(), L, rtol=2e-3, atol=1e-4 * max(float(L.abs()), scale))

@@ -105,6 +105,22 @@ def test_slogdet_matches_brute_force(n):
     torch.testing.assert_close(sign, torch.linalg.slogdet(t[0])[0])
 
 
+def _well_conditioned(K, shape, seed):
+    x, J, lap = rand_triplet(K, shape, seed=seed)
+    n = shape[-1]
+    return x + 3.0 * torch.eye(n, dtype=DT), J, lap
+
+
+def test_det_inv_solve_match_brute_force():
+    """The linear-algebra rules against brute-force AD (the identity the reference asserts in
+    test/test_layers.py for slogdet/det/inv/solve)."""
+    A = _well_conditioned(4, (2, 4, 4), seed=31)
+    b = rand_triplet(4, (2, 4, 3), seed=32)
+    assert_triplet_close(rules.det(A), brute.propagate(torch.linalg.det, [A]), rtol=1e-8)
+    assert_triplet_close(rules.inv(A), brute.propagate(torch.linalg.inv, [A]), rtol=1e-8)
+    assert_triplet_close(rules.solve(A, b), brute.propagate(torch.linalg.solve, [A, b]), rtol=1e-8)
+
+
 def _attention(q, k, v, mask):
     s = torch.einsum('bihd,bjhd->bhij', q, k)
     sq = mask[:, :, None] & mask[:, None, :]
