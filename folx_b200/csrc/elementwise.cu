@@ -198,8 +198,143 @@ int32_t launch(float param, const float* x, const float* jac, const float* lap, 
   return FL_OK;
 }
 
+// ---- a chain of elementwise functions in one pass ---------------------------------------------
+// y = f_n(... f_1(x)): the intermediate Jacobians are multiples of J, J^(i) = (f_i .. f_1)' J, so
+// the whole chain needs sum_k J_k^2 once: with d1 = (f_n .. f_1)'(x) and d2 = (f_n .. f_1)''(x)
+// composed per element (d2 <- f'' d1^2 + f' d2, d1 <- f' d1), J_y = d1 J and
+// lap_y = d1 lap + d2 sum_k J_k^2.  The reference applies the rules one after the other
+// (each one the formula at the top of this file) and leaves the fusion to XLA.
+constexpr int kMaxChain = 4;
+struct Chain {
+  int n;
+  int op[kMaxChain];
+  float param[kMaxChain];
+};
+
+__device__ __forceinline__ D eval_dyn(int op, float x, float param) {
+  switch (op) {
+#define FL_EV(OP) case OP: return eval<OP>(x, param);
+    FL_EV(FL_OP_TANH) FL_EV(FL_OP_SILU) FL_EV(FL_OP_EXP) FL_EV(FL_OP_LOG) FL_EV(FL_OP_SQRT)
+    FL_EV(FL_OP_RSQRT) FL_EV(FL_OP_SQUARE) FL_EV(FL_OP_SIGMOID) FL_EV(FL_OP_SOFTPLUS)
+    FL_EV(FL_OP_INTEGER_POW) FL_EV(FL_OP_SIN) FL_EV(FL_OP_COS) FL_EV(FL_OP_NEG) FL_EV(FL_OP_ABS)
+    FL_EV(FL_OP_SCALE) FL_EV(FL_OP_SHIFT) FL_EV(FL_OP_RECIPROCAL)
+#undef FL_EV
+  }
+  return D{x, 1.f, 0.f};
+}
+
+__device__ __forceinline__ D eval_chain(const Chain& c, float x) {
+  D t{x, 1.f, 0.f};
+  for (int s = 0; s < c.n; ++s) {
+    const D r = eval_dyn(c.op[s], t.y, c.param[s]);
+    t.d2 = fmaf(r.d2, t.d1 * t.d1, r.d1 * t.d2);
+    t.d1 = r.d1 * t.d1;
+    t.y = r.y;
+  }
+  return t;
+}
+
+__global__ void __launch_bounds__(256)
+chain_vec4(Chain ch, const float4* __restrict__ x, const float4* __restrict__ jac,
+           const float4* __restrict__ lap, float4* __restrict__ y, float4* __restrict__ jac_y,
+           float4* __restrict__ lap_y, int K, int64_t n4, int64_t js4, int64_t jys4) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 xv = ld_stream(x + i);
+  float4 lv = ld_stream(lap + i);
+  const D a = eval_chain(ch, xv.x), b = eval_chain(ch, xv.y), c = eval_chain(ch, xv.z),
+          d = eval_chain(ch, xv.w);
+  st_stream(y + i, make_float4(a.y, b.y, c.y, d.y));
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const float4* jp = jac + i;
+  float4* jo = jac_y + i;
+  int k = 0;
+  for (; k + kUnroll <= K; k += kUnroll) {
+    float4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) v[u] = ld_stream(jp + (int64_t)(k + u) * js4);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      acc.x = fmaf(v[u].x, v[u].x, acc.x);
+      acc.y = fmaf(v[u].y, v[u].y, acc.y);
+      acc.z = fmaf(v[u].z, v[u].z, acc.z);
+      acc.w = fmaf(v[u].w, v[u].w, acc.w);
+      st_stream(jo + (int64_t)(k + u) * jys4,
+                make_float4(a.d1 * v[u].x, b.d1 * v[u].y, c.d1 * v[u].z, d.d1 * v[u].w));
+    }
+  }
+  for (; k < K; ++k) {
+    float4 v = ld_stream(jp + (int64_t)k * js4);
+    acc.x = fmaf(v.x, v.x, acc.x);
+    acc.y = fmaf(v.y, v.y, acc.y);
+    acc.z = fmaf(v.z, v.z, acc.z);
+    acc.w = fmaf(v.w, v.w, acc.w);
+    st_stream(jo + (int64_t)k * jys4, make_float4(a.d1 * v.x, b.d1 * v.y, c.d1 * v.z, d.d1 * v.w));
+  }
+  st_stream(lap_y + i, make_float4(fmaf(a.d2, acc.x, a.d1 * lv.x), fmaf(b.d2, acc.y, b.d1 * lv.y),
+                                   fmaf(c.d2, acc.z, c.d1 * lv.z), fmaf(d.d2, acc.w, d.d1 * lv.w)));
+}
+
+__global__ void __launch_bounds__(256)
+chain_scalar(Chain ch, const float* __restrict__ x, const float* __restrict__ jac,
+             const float* __restrict__ lap, float* __restrict__ y, float* __restrict__ jac_y,
+             float* __restrict__ lap_y, int K, int64_t n, int64_t js, int64_t jys) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const D a = eval_chain(ch, x[i]);
+  y[i] = a.y;
+  float acc = 0.f;
+  for (int k = 0; k < K; ++k) {
+    float v = jac[(int64_t)k * js + i];
+    acc = fmaf(v, v, acc);
+    jac_y[(int64_t)k * jys + i] = a.d1 * v;
+  }
+  lap_y[i] = fmaf(a.d2, acc, a.d1 * lap[i]);
+}
+
 }  // namespace
 }  // namespace fl
+
+extern "C" int32_t fl_elementwise_chain(int32_t n_ops, const int32_t* ops, const float* params,
+                                        const float* x, const float* jac, const float* lap,
+                                        float* y, float* jac_y, float* lap_y, int64_t K,
+                                        int64_t N, int64_t jac_stride, int64_t jac_y_stride,
+                                        void* stream) {
+  using namespace fl;
+  FL_REQUIRE(n_ops >= 1 && n_ops <= kMaxChain && ops, FL_EBADSHAPE,
+             "fl_elementwise_chain: between 1 and %d functions, got %d", kMaxChain, n_ops);
+  Chain ch;
+  ch.n = n_ops;
+  for (int s = 0; s < kMaxChain; ++s) {
+    ch.op[s] = s < n_ops ? ops[s] : 0;
+    ch.param[s] = (s < n_ops && params) ? params[s] : 0.f;
+    FL_REQUIRE(ch.op[s] >= 0 && ch.op[s] < FL_OP_COUNT_, FL_EUNSUPPORTED,
+               "fl_elementwise_chain: unknown op %d", ch.op[s]);
+  }
+  FL_REQUIRE(K >= 0 && N >= 0 && K < (1ll << 31), FL_EBADSHAPE,
+             "fl_elementwise_chain: bad sizes K=%lld N=%lld", (long long)K, (long long)N);
+  FL_REQUIRE(K == 0 || (jac_stride >= N && jac_y_stride >= N), FL_EBADSHAPE,
+             "fl_elementwise_chain: Jacobian row stride smaller than N");
+  FL_REQUIRE((N + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_elementwise_chain: N too large");
+  if (N == 0) return FL_OK;
+  FL_REQUIRE(x && lap && y && lap_y && (K == 0 || (jac && jac_y)), FL_EBADSHAPE,
+             "fl_elementwise_chain: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t js = jac_stride, jys = jac_y_stride;
+  bool vec = (N % 4 == 0) && (js % 4 == 0) && (jys % 4 == 0) && aligned16(x) && aligned16(lap) &&
+             aligned16(y) && aligned16(lap_y) && (K == 0 || (aligned16(jac) && aligned16(jac_y)));
+  if (vec) {
+    const int64_t n4 = N / 4;
+    chain_vec4<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(
+        ch, (const float4*)x, (const float4*)jac, (const float4*)lap, (float4*)y, (float4*)jac_y,
+        (float4*)lap_y, (int)K, n4, js / 4, jys / 4);
+  } else {
+    chain_scalar<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(ch, x, jac, lap, y, jac_y, lap_y,
+                                                             (int)K, N, js, jys);
+  }
+  FL_CHECK_LAUNCH("fl_elementwise_chain launch");
+  return FL_OK;
+}
 
 extern "C" int32_t fl_elementwise(int32_t op, float param, const float* x, const float* jac,
                                   const float* lap, float* y, float* jac_y, float* lap_y,

@@ -23,7 +23,7 @@ from typing import Any, Callable, Sequence
 import numpy as np
 import torch
 
-from . import kernels, registry
+from . import kernels, registry, rules
 from .api import FwdJacobian, FwdLaplArray
 
 
@@ -41,27 +41,45 @@ class BatchedConst(torch.Tensor):
     lines the axes up.  Index its axes from the right (negative ``dim``)."""
 
 
+_CHAINABLE = frozenset({'tanh', 'silu', 'exp', 'log', 'sqrt', 'rsqrt', 'square', 'sigmoid', 'softplus',
+                        'sin', 'cos', 'neg', 'abs', 'reciprocal'})
+
+
 class LaplTensor:
     """A tensor seen by the traced function: value, Jacobian and Laplacian travel together."""
 
-    __slots__ = ('_arr', 'nb', 'thr', '_terms')
+    __slots__ = ('_arr', 'nb', 'thr', '_terms', '_chain')
 
-    def __init__(self, arr: FwdLaplArray | None, nb: int, thr: int, terms=None):
+    def __init__(self, arr: FwdLaplArray | None, nb: int, thr: int, terms=None, chain=None):
         # `terms` is a pending sum [(dense triplet or constant, +1 / -1), ...] that has not been
         # written out yet: a chain of additions is evaluated in one pass, together with the
         # elementwise function that consumes it if there is one (what XLA's fusion does for the
         # reference's add / tanh rules)
-        self._arr, self.nb, self.thr, self._terms = arr, nb, thr, terms
+        # `chain` is a pending chain of elementwise functions (source triplet, [(name, param), ...]):
+        # consecutive scalar functions are evaluated by one pass over the triplet when the value is
+        # first needed
+        self._arr, self.nb, self.thr, self._terms, self._chain = arr, nb, thr, terms, chain
 
     @property
     def arr(self) -> FwdLaplArray:
         if self._arr is None:
-            self._arr = kernels.addn(self._terms, 'identity')
-            self._terms = None
+            if self._terms is not None:
+                self._arr = kernels.addn(self._terms, 'identity')
+                self._terms = None
+            else:
+                src, ops = self._chain
+                if len(ops) == 1:  # a single function goes through its registered rule as usual
+                    kw = {'y': int(ops[0][1])} if ops[0][0] == 'integer_pow' else {}
+                    self._arr = _call(ops[0][0], (src,), kw, self.thr)
+                else:
+                    self._arr = rules.elementwise_chain(ops, src, self.thr)
+                self._chain = None
         return self._arr
 
     def _x_like(self) -> torch.Tensor:
-        return self._arr.x if self._arr is not None else self._terms[0][0].x
+        if self._arr is not None:
+            return self._arr.x
+        return self._terms[0][0].x if self._terms is not None else self._chain[0].x
 
     # ---- tensor-like attributes (per walker) ----
     @property
@@ -123,9 +141,10 @@ class LaplTensor:
     # ---- arithmetic ----
     def _dense_terms(self):
         """This tensor as a list of sum terms, or None if its Jacobian is sparse."""
-        if self._arr is None:
+        if self._terms is not None:
             return list(self._terms)
-        return None if self._arr.jacobian.weak else [(self._arr, 1.0)]
+        arr = self.arr
+        return None if arr.jacobian.weak else [(arr, 1.0)]
 
     def _try_lazy_sum(self, op: str, other, reverse: bool):
         """`a + b` / `a - b` of dense operands becomes a pending sum instead of a kernel launch."""
@@ -239,9 +258,15 @@ class LaplTensor:
         return self._wrap(_call('dot_general', (W, self.arr), {}, self.thr))
 
     def _unary(self, key: str):
-        if self._arr is None and key in ('tanh', 'silu', 'exp') and registry.is_builtin(key):
+        if self._terms is not None and key in ('tanh', 'silu', 'exp') and registry.is_builtin(key):
             # pending sum + elementwise function: one fused pass
             return LaplTensor(kernels.addn(self._terms, key), self.nb, self.thr)
+        if key in _CHAINABLE and registry.is_builtin(key):
+            # scalar functions stay pending so that a run of them becomes one pass
+            if self._arr is None and self._chain is not None and len(self._chain[1]) < 4:
+                src, ops = self._chain
+                return LaplTensor(None, self.nb, self.thr, chain=(src, ops + [(key, 0.0)]))
+            return LaplTensor(None, self.nb, self.thr, chain=(self.arr, [(key, 0.0)]))
         return self._wrap(_call(key, (self.arr,), {}, self.thr))
 
     def tanh(self): return self._unary('tanh')
@@ -461,7 +486,7 @@ def _solve(A, b):
 def _layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
     if len(tuple(normalized_shape)) != 1:
         raise NotImplementedError('layer_norm on triplets normalises the last axis only')
-    terms = x._terms if x._arr is None else None
+    terms = x._terms if x._arr is None and x._terms is not None else None
     if (terms is not None and len(terms) == 2 and registry.is_builtin('layer_norm')
             and all(isinstance(t, FwdLaplArray) and t.x.shape == terms[0][0].x.shape for t, _ in terms)
             and terms[0][1] == 1.0 and x.shape[-1] % 128 == 0 and x.shape[-1] <= 1024

@@ -85,6 +85,29 @@ def elementwise(op: str, a: FwdLaplArray, param: float = 0.0) -> FwdLaplArray:
     return out
 
 
+def elementwise_chain(ops, a: FwdLaplArray) -> FwdLaplArray:
+    """``f_n(... f_1(x))`` for ``ops = [(name, param), ...]`` (1 to 4 functions) in one pass."""
+    import ctypes
+
+    ops = [(o, 0.0) if isinstance(o, str) else (o[0], float(o[1])) for o in ops]
+    if len(ops) == 1:
+        return elementwise(ops[0][0], a, ops[0][1])
+    a = as_contiguous(a)
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    _require_cuda(x, j, l)
+    K, N = j.shape[0], x.numel()
+    out = alloc_triplet(K, x.shape, x.device, a.jacobian.x0_idx)
+    codes = (ctypes.c_int32 * len(ops))(*[lib.ELEMENTWISE_OPS[o] for o, _ in ops])
+    params = (ctypes.c_float * len(ops))(*[p for _, p in ops])
+    lib.call(
+        'fl_elementwise_chain', len(ops), ctypes.cast(codes, ctypes.c_void_p),
+        ctypes.cast(params, ctypes.c_void_p), _ptr(x), _ptr(j), _ptr(l), _ptr(out.x),
+        _ptr(out.jacobian.data), _ptr(out.laplacian), K, N, _jac_stride(j),
+        _jac_stride(out.jacobian.data), _stream(x.device),
+    )
+    return out
+
+
 def _broadcast_run(shape_a, shape_b):
     """(inner, mid) if ``b`` equals ``a`` except for ONE run of broadcast axes, else None."""
     nd = len(shape_a)

@@ -50,6 +50,9 @@ _SIGNATURES = {
     'fl_last_error': (c_char_p, []),
     'fl_elementwise': (c_int32, [c_int32, c_float, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    'fl_elementwise_chain': (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                       c_int64, c_void_p]),
     'fl_binary': (c_int32, [c_int32, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                             c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                             c_int64, c_int64, c_int64, c_void_p]),

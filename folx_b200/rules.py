@@ -119,6 +119,23 @@ def elementwise(op: str, a, param: float = 0.0, sparsity_threshold: int = 0):
     return out
 
 
+def elementwise_chain(ops, a, sparsity_threshold: int = 0):
+    """``f_n(... f_1(a))`` for ``ops = [(name, param), ...]``: the result of applying
+    ``elementwise`` once per function, computed in one pass over the triplet."""
+    ops = [(o, 0.0) if isinstance(o, str) else (o[0], float(o[1])) for o in ops]
+    if not is_triplet(a) or len(ops) == 1:
+        for o, p in ops:
+            a = elementwise(o, a, p, sparsity_threshold)
+        return a
+    out = kernels.elementwise_chain(ops, a)
+    if (any(o not in _LINEAR_UNARY for o, _ in ops) and a.jacobian.weak
+            and masks.has_duplicate_x0_idx(_mask_nd(a))):
+        # same frame rule as a single function: Laplacian from the merged rows
+        merged = kernels.elementwise_chain(ops, _merged_duplicates(a, sparsity_threshold))
+        out = FwdLaplArray(out.x, out.jacobian, merged.laplacian)
+    return out
+
+
 # ------------------------------------------------------------------------------------------
 # binary ops (reference: add/sub LINEAR, mul MULTIPLICATION, div with div_jac_hessian_jac;
 # folx/wrapped_functions.py:364-383, jvp dispatch folx/jvp.py:804-819)

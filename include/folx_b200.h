@@ -75,6 +75,18 @@ int32_t fl_elementwise(int32_t op, float param,
                        int64_t K, int64_t N, int64_t jac_stride, int64_t jac_y_stride,
                        void* stream);
 
+/* A chain y = f_n(... f_1(x)) of 1 to 4 of the functions above in one pass over the triplet
+ * (`ops` and `params` are HOST arrays of n_ops entries, ops[0] applied first; params may be
+ * NULL).  The reference applies one rule per function (folx/wrapped_functions.py:384-431) and
+ * leaves the fusion of consecutive elementwise stages to XLA; the intermediate Jacobians are
+ * multiples of J, so the chain needs sum_k J_k^2 only once and the result equals applying the
+ * rules one after the other.  Other arguments as fl_elementwise. */
+int32_t fl_elementwise_chain(int32_t n_ops, const int32_t* ops, const float* params,
+                             const float* x, const float* jac, const float* lap,
+                             float* y, float* jac_y, float* lap_y,
+                             int64_t K, int64_t N, int64_t jac_stride, int64_t jac_y_stride,
+                             void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Binary elementwise rules on two triplets with aligned Jacobian rows (same K, same index map).
  * Replaces wrap_forward_laplacian(mul | div | add | sub, in_axes=()) with both operands

@@ -207,6 +207,28 @@ def test_product_of_two_non_constant_matrices(cuda_device, thr):
     check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), r, thr, samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
 
 
+@pytest.mark.parametrize('thr', [0, 4])
+def test_runs_of_scalar_functions_are_fused(cuda_device, thr):
+    """A run of scalar functions is evaluated by one kernel launch (fl_elementwise_chain) and
+    matches brute force; a value used twice is still correct."""
+    from folx_b200 import lib
+    g = torch.Generator().manual_seed(31)
+    W = torch.randn(4, 6, generator=g) * 0.7
+
+    def f(Wm, x):
+        h = x @ Wm                                   # (5, 6)
+        a = F.silu(torch.tanh(h))                    # two functions, one pass
+        b = torch.exp(-torch.square(torch.sin(h)))  # four functions, one pass
+        t = torch.tanh(h)
+        return (a * b).sum() + (t * torch.sigmoid(t)).sum()   # t is consumed twice
+
+    x = torch.randn(3, 5, 4, generator=g).to(cuda_device)
+    Wd, W64 = W.to(cuda_device), W.double()
+    before = dict(lib.LAUNCH_COUNTS)
+    check_against_brute(lambda z: f(Wd, z), lambda z: f(W64, z), x, thr, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+    assert lib.LAUNCH_COUNTS.get('fl_elementwise_chain', 0) - before.get('fl_elementwise_chain', 0) >= 2
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

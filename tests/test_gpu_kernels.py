@@ -32,6 +32,22 @@ def test_elementwise_param(cuda_device, op, param):
     assert_close(to_host(got), rules.elementwise(op, t, param))
 
 
+@pytest.mark.parametrize('ops', [
+    ['tanh', 'silu'], ['tanh', 'exp', 'square'], ['square', 'sqrt', 'log', 'sin'],
+    [('scale', 0.5), 'tanh'], ['sigmoid', ('integer_pow', 3)], ['neg', 'abs'],
+])
+@pytest.mark.parametrize('K,shape', [(0, (5,)), (3, (7, 3)), (17, (3, 5, 16))])
+def test_elementwise_chain_equals_successive_rules(cuda_device, ops, K, shape):
+    """One pass over the triplet for f_n(... f_1(x)) against the rules applied one by one."""
+    t = seeded_triplet(K, shape, seed=5, positive=True)
+    want = t
+    for o in ops:
+        name, param = (o, 0.0) if isinstance(o, str) else o
+        want = rules.elementwise(name, want, param)
+    got = kernels.elementwise_chain(ops, to_device(t, cuda_device))
+    assert_close(to_host(got), want)
+
+
 def test_elementwise_unstacked_and_empty(cuda_device):
     t = seeded_triplet(3, (6, 5), seed=3)
     got = kernels.elementwise('tanh', to_device(t, cuda_device, stacked=False))
