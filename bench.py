@@ -92,9 +92,10 @@ class ClockSampler:
 # workload: operator microbench (BASELINE.json configs[1])
 # ------------------------------------------------------------------------------------------
 B, D, F, KS = 4096, 96, 256, 3  # samples, dense Jacobian rows, features, sparse rows per position
-# tanh followed by silu as ONE launch (fl_elementwise_chain), as the front end evaluates a run of
-# scalar functions; FOLX_B200_NO_CHAIN=1 times them as two launches
-FUSE_SCALAR_RUN = not os.environ.get('FOLX_B200_NO_CHAIN')
+# The microbench times SINGLE primitives, so tanh and silu are two launches.  FOLX_B200_CHAIN=1
+# evaluates them as one launch (fl_elementwise_chain), which is what the front end does with a run
+# of scalar functions inside a traced function; that variant is for comparison only.
+FUSE_SCALAR_RUN = bool(os.environ.get('FOLX_B200_CHAIN'))
 
 
 def make_host_inputs(seed: int, n_samples: int = B):
