@@ -230,7 +230,11 @@ def run_ours(args, rank, world, device):
     # downloaded (three streams; PCIe is full duplex).  Host data is laid out slice by slice in
     # pinned memory; every byte of every input and output crosses the bus inside the timed region.
     e2e_steps = max(2, min(args.steps, 5))
-    n_slices = 8 if B % 8 == 0 and B >= 64 else 1
+    # 4 slices measured best (9.9 ms; 8: 10.3, 16: 10.9, 32: 12.5; both directions of the bus busy
+    # at once take 9.3 ms for these bytes)
+    n_slices = int(os.environ.get('FOLX_B200_E2E_SLICES', 4))
+    if n_slices < 1 or B % n_slices != 0 or B < 64:
+        n_slices = 1
     sl = B // n_slices
 
     def slices_of(t3):
