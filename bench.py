@@ -556,6 +556,24 @@ def run_kernel_case(args, device):
         fn = lambda: kernels.mhsa(q, k, v)
         nbytes = 4 * 4 * walkers * 4 * 98 * 32 * 64
         desc = f'attention-Laplacian kernel, {walkers} walkers x 4 heads, n=32, d=64, R=96'
+    elif args.workload == 'gather':
+        # the sparse Jacobian of the operator microbench (3 rows per position, row r of sample s
+        # belongs to electron s mod 32) scattered into its dense frame of 96 rows, and the sum of
+        # the dense result over the feature axis (both run on the table-driven gather kernel)
+        import numpy as np
+        from folx_b200 import rules as dev_rules
+        from folx_b200.api import FwdJacobian, FwdLaplArray
+        n = args.walkers or 2048
+        idx = (3 * (np.arange(n) % 32)[None, :, None] + np.arange(3)[:, None, None]).astype(np.int32)
+        a = rand(3, (n, F))
+        a = FwdLaplArray(a.x, FwdJacobian(a.jacobian.data, idx), a.laplacian)
+        walkers = n
+
+        def fn():
+            d = a.jacobian.dense_array          # (96, n, F): 3 rows read, 96 written
+            return dev_rules.reduce_sum(FwdLaplArray(a.x, FwdJacobian(d, None), a.laplacian), (1,))
+        nbytes = 4 * n * F * (3 + 96) + 4 * n * F * 98 + 4 * n * 98
+        desc = f'gather kernel: densify (3 -> 96 rows) + feature sum of the dense triplet, {n} samples x 256'
     else:  # PsiFormer determinants: 32 matrices of 16 x 16 per walker, K = 96
         a = rand(96, (walkers, 32, 16, 16))
         a.x.div_(4.0).add_(1.5 * torch.eye(16, device=device))
@@ -611,7 +629,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='operators', choices=['operators', 'attention', 'slogdet', *MODEL_WORKLOADS])
+    ap.add_argument('--workload', default='operators', choices=['operators', 'attention', 'slogdet', 'gather', *MODEL_WORKLOADS])
     ap.add_argument('--walkers', type=int, default=None, help='walkers per GPU (model workloads)')
     ap.add_argument('--no-models', action='store_true', help='skip the short model timings of the default run')
     ap.add_argument('--samples', type=int, default=None,
@@ -652,7 +670,7 @@ def main():
             res['models'] = models
         if rank == 0:
             res['cpu_baseline'] = cpu_baseline(sample=1024) if world == 1 else None
-    elif args.workload in ('attention', 'slogdet'):
+    elif args.workload in ('attention', 'slogdet', 'gather'):
         res = run_kernel_case(args, device)
     else:
         res = run_model(args, rank, world, device)

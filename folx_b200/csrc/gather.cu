@@ -25,6 +25,39 @@ struct GatherGeom {
   int64_t table_stride[kMaxDims];  // stride of each axis in the table (0: table constant along it)
 };
 
+// Offsets of output position `pos` inside an input row and inside the table.  Positions below
+// 2^31 (all practical sizes) take 32-bit divisions, which are several times cheaper than the
+// 64-bit ones.
+__device__ __forceinline__ void decode_position(int64_t pos, const GatherGeom& g, int64_t& in_off,
+                                                int64_t& t_off) {
+  in_off = 0;
+  t_off = 0;
+  if ((pos >> 31) == 0) {
+    unsigned rem = (unsigned)pos;
+#pragma unroll
+    for (int d = kMaxDims - 1; d >= 0; --d) {
+      if (d < g.ndim) {
+        const unsigned n = (unsigned)g.shape[d];
+        const unsigned q = rem / n, i = rem - q * n;
+        rem = q;
+        in_off += (int64_t)i * g.in_stride[d];
+        t_off += (int64_t)i * g.table_stride[d];
+      }
+    }
+  } else {
+    int64_t rem = pos;
+#pragma unroll
+    for (int d = kMaxDims - 1; d >= 0; --d) {
+      if (d < g.ndim) {
+        int64_t i = rem % g.shape[d];
+        rem /= g.shape[d];
+        in_off += i * g.in_stride[d];
+        t_off += i * g.table_stride[d];
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const float* __restrict__ in, int64_t in_row_stride,
                    const int32_t* __restrict__ take, int64_t table_positions, int k_out,
@@ -32,17 +65,10 @@ gather_rows_kernel(const float* __restrict__ in, int64_t in_row_stride,
                    int nr, int64_t red_stride, GatherGeom g) {
   int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (pos >= N) return;
-  int64_t rem = pos, in_off = 0, t_off = 0;
-#pragma unroll
-  for (int d = kMaxDims - 1; d >= 0; --d) {
-    if (d < g.ndim) {
-      int64_t i = rem % g.shape[d];
-      rem /= g.shape[d];
-      in_off += i * g.in_stride[d];
-      t_off += i * g.table_stride[d];
-    }
-  }
-  for (int o = 0; o < k_out; ++o) {
+  int64_t in_off, t_off;
+  decode_position(pos, g, in_off, t_off);
+  // output rows are spread over blockIdx.y: with few positions that is where the parallelism is
+  for (int o = blockIdx.y; o < k_out; o += gridDim.y) {
     float acc = 0.f;
     for (int s = 0; s < n_slots; ++s) {
       int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
@@ -52,6 +78,35 @@ gather_rows_kernel(const float* __restrict__ in, int64_t in_row_stride,
       }
     }
     __stcs(out + (int64_t)o * out_row_stride + pos, acc);
+  }
+}
+
+// Many slots per output element (a reduction over a long axis, typically the contiguous innermost
+// one): one warp per (output row, position), lanes stride over the slots -- consecutive slots of
+// a reduced contiguous axis are consecutive addresses, so the loads coalesce -- and a shuffle tree
+// adds the partial sums (a fixed order: the result does not depend on scheduling).
+__global__ void __launch_bounds__(256)
+gather_reduce_warp(const float* __restrict__ in, int64_t in_row_stride,
+                   const int32_t* __restrict__ take, int64_t table_positions, int k_out,
+                   int n_slots, float* __restrict__ out, int64_t out_row_stride, int64_t N,
+                   int nr, int64_t red_stride, GatherGeom g) {
+  const int lane = threadIdx.x & 31;
+  const int64_t pos = (int64_t)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  if (pos >= N) return;
+  int64_t in_off, t_off;
+  decode_position(pos, g, in_off, t_off);
+  for (int o = blockIdx.y; o < k_out; o += gridDim.y) {
+    float acc = 0.f;
+    for (int s = lane; s < n_slots; s += 32) {
+      int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
+      if (r >= 0) {
+        const int row = r / nr, red = r - row * nr;
+        acc += __ldcs(in + (int64_t)row * in_row_stride + (int64_t)red * red_stride + in_off);
+      }
+    }
+#pragma unroll
+    for (int w = 16; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+    if (lane == 0) __stcs(out + (int64_t)o * out_row_stride + pos, acc);
   }
 }
 
@@ -65,17 +120,9 @@ gather_rows_vec4(const float4* __restrict__ in, int64_t in_row_stride4,
   int64_t pos = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (pos >= N4) return;
   // g.shape[last] and g.in_stride are already expressed in float4 units by the host
-  int64_t rem = pos, in_off = 0, t_off = 0;
-#pragma unroll
-  for (int d = kMaxDims - 1; d >= 0; --d) {
-    if (d < g.ndim) {
-      int64_t i = rem % g.shape[d];
-      rem /= g.shape[d];
-      in_off += i * g.in_stride[d];
-      t_off += i * g.table_stride[d];
-    }
-  }
-  for (int o = 0; o < k_out; ++o) {
+  int64_t in_off, t_off;
+  decode_position(pos, g, in_off, t_off);
+  for (int o = blockIdx.y; o < k_out; o += gridDim.y) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < n_slots; ++s) {
       int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
@@ -135,12 +182,24 @@ extern "C" int32_t fl_gather_rows(const float* jac_in, int64_t k_in, int64_t in_
     for (int d = 0; d < last; ++d) g4.in_stride[d] /= 4;
     int64_t N4 = N / 4;
     FL_REQUIRE((N4 + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_gather_rows: too many positions");
-    gather_rows_vec4<<<(unsigned)((N4 + 255) / 256), 256, 0, st>>>(
+    // rows go to blockIdx.y only while the position blocks alone do not fill the machine
+    const int64_t xb = (N4 + 255) / 256;
+    const unsigned gy = (unsigned)(xb >= 8 * sm_count() ? 1 : (k_out < 65535 ? k_out : 65535));
+    gather_rows_vec4<<<dim3((unsigned)xb, gy), 256, 0, st>>>(
         (const float4*)jac_in, in_row_stride / 4, take, T, (int)k_out, (int)n_slots,
         (float4*)jac_out, out_row_stride / 4, N4, (int)n_reduced, reduced_stride / 4, g4);
+  } else if (n_slots >= 16) {
+    const int64_t xb = (N + 7) / 8;  // 8 warps per block, one warp per position
+    FL_REQUIRE(xb < (1ll << 31), FL_EBADSHAPE, "fl_gather_rows: too many positions");
+    const unsigned gy = (unsigned)(xb >= 8 * sm_count() ? 1 : (k_out < 65535 ? k_out : 65535));
+    gather_reduce_warp<<<dim3((unsigned)xb, gy), 256, 0, st>>>(
+        jac_in, in_row_stride, take, T, (int)k_out, (int)n_slots, jac_out, out_row_stride, N,
+        (int)n_reduced, reduced_stride, g);
   } else {
     FL_REQUIRE((N + 255) / 256 < (1ll << 31), FL_EBADSHAPE, "fl_gather_rows: too many positions");
-    gather_rows_kernel<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(
+    const int64_t xb = (N + 255) / 256;
+    const unsigned gy = (unsigned)(xb >= 8 * sm_count() ? 1 : (k_out < 65535 ? k_out : 65535));
+    gather_rows_kernel<<<dim3((unsigned)xb, gy), 256, 0, st>>>(
         jac_in, in_row_stride, take, T, (int)k_out, (int)n_slots, jac_out, out_row_stride, N,
         (int)n_reduced, reduced_stride, g);
   }

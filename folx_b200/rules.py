@@ -480,6 +480,9 @@ def getitem(a, index, batch_dims: int = 0):
                 midx.append(it)
             d += 1
         m = m[(slice(None), *midx)]
+        # back to the compact form: axes along which the selected map is constant get size 1
+        # again, so that later gathers keep one table entry per distinct position
+        m, _ = masks.compact_repeated_dims_except(np.ascontiguousarray(m), JAC_DIM)
     return FwdLaplArray(a.x[index], FwdJacobian(a.jacobian.data[jidx], m), a.laplacian[index])
 
 
