@@ -329,7 +329,10 @@ def run_ours(args, rank, world, device):
                             'that on the tensor pipe, so the ceiling is peak/3; peak = measured bf16 / 2 '
                             f'({peaks["source"]}); traffic scaled from the ncu capture at 2048 samples',
                     'frac_of_3xtf32_ceiling': round(3 * achieved / tf32_peak, 3),
-                    'tf32_cublas_tflops_this_run': measure_tf32_peak(device),
+                    # a library TF32 GEMM timed beside it, only on request (it is not part of any
+                    # path; 709-750 TFLOP/s were measured on this pool)
+                    'tf32_cublas_tflops_this_run': (measure_tf32_peak(device)
+                                                    if os.environ.get('FOLX_B200_MEASURE_TF32') else None),
                     'hbm_frac': kern[dominant]['frac_hbm']}
     else:
         achieved = nbytes / ms / 1e6

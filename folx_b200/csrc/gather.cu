@@ -97,12 +97,24 @@ gather_reduce_warp(const float* __restrict__ in, int64_t in_row_stride,
   decode_position(pos, g, in_off, t_off);
   for (int o = blockIdx.y; o < k_out; o += gridDim.y) {
     float acc = 0.f;
-    for (int s = lane; s < n_slots; s += 32) {
-      int r = __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off);
-      if (r >= 0) {
-        const int row = r / nr, red = r - row * nr;
-        acc += __ldcs(in + (int64_t)row * in_row_stride + (int64_t)red * red_stride + in_off);
+    // four table entries, then four data loads, in flight per lane
+    for (int s0 = lane; s0 < n_slots; s0 += 128) {
+      int r[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int s = s0 + 32 * u;
+        r[u] = s < n_slots ? __ldg(take + ((int64_t)o * n_slots + s) * table_positions + t_off) : -1;
       }
+      float v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[u] = 0.f;
+        if (r[u] >= 0) {
+          const int row = r[u] / nr, red = r[u] - row * nr;
+          v[u] = __ldcs(in + (int64_t)row * in_row_stride + (int64_t)red * red_stride + in_off);
+        }
+      }
+      acc += (v[0] + v[1]) + (v[2] + v[3]);
     }
 #pragma unroll
     for (int w = 16; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
