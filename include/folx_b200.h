@@ -322,6 +322,12 @@ int32_t fl_mhsea(const float* q, const float* q_jac, const float* q_lap,
                  int64_t q_jac_stride, int64_t k_jac_stride, int64_t e_jac_stride,
                  int64_t v_jac_stride, int64_t o_jac_stride, void* stream);
 
+/* Selects the attention kernel of fl_mhsa / fl_mhsea: 0 = automatic (the tensor-core kernel,
+ * split-fp32 on mma.sync, for 16 < n <= 32 and 16-byte aligned buffers; the CUDA-core kernel
+ * otherwise), 1 = force the CUDA-core kernel, 2 = force the tensor-core kernel (FL_EUNSUPPORTED if
+ * the shape does not fit).  Process-wide; meant for tests and benchmarks. */
+void fl_mhsa_set_mode(int32_t mode);
+
 /* ---------------------------------------------------------------------------------------------
  * Local energy per walker and its statistics.  No counterpart in the reference (it returns
  * (laplacian, jacobian), folx/operators.py:34-36, and leaves the energy to the caller); this is

@@ -8,12 +8,20 @@ Rows of masked electrons are blanked before comparing, as the reference's test d
 import pytest
 import torch
 
-from folx_b200 import kernels
+from folx_b200 import kernels, lib
 from oracle import rules
 
 from gpu_util import assert_close, seeded_triplet, to_device, to_host
 
 pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(params=[0, 1], ids=['auto', 'cuda-core'])
+def attention_mode(request):
+    """0: the kernel the library picks (tensor cores for 16 < n <= 32), 1: the CUDA-core kernel."""
+    lib.load().fl_mhsa_set_mode(request.param)
+    yield request.param
+    lib.load().fl_mhsa_set_mode(0)
 
 
 def make_inputs(B, n, H, d, R, max_sequence, seed, scale=0.5):
@@ -39,9 +47,9 @@ def blank_out(t, mask):
 @pytest.mark.parametrize('B,n,H,d,R,max_sequence', [
     (1, 1, 1, 1, 3, 1), (1, 16, 4, 32, 48, 16), (1, 16, 4, 32, 48, 4),
     (2, 5, 2, 8, 7, 5), (3, 32, 4, 64, 12, 32), (2, 32, 2, 64, 9, 20), (2, 64, 2, 64, 6, 64),
-    (1, 40, 1, 48, 5, 33), (2, 7, 3, 6, 4, 7),
+    (1, 40, 1, 48, 5, 33), (2, 7, 3, 6, 4, 7), (2, 24, 2, 32, 5, 17), (1, 17, 3, 16, 6, 17), (4, 32, 4, 64, 96, 32),
 ])
-def test_mhsa_matches_oracle(cuda_device, B, n, H, d, R, max_sequence):
+def test_mhsa_matches_oracle(cuda_device, attention_mode, B, n, H, d, R, max_sequence):
     q, k, v, mask, input_mask = make_inputs(B, n, H, d, R, max_sequence, seed=B + n + d)
     got = kernels.mhsa(to_device(q, cuda_device), to_device(k, cuda_device), to_device(v, cuda_device),
                        mask.to(cuda_device), input_mask.to(cuda_device))
@@ -105,7 +113,7 @@ def edge_inputs(B, n, H, R, mask, input_mask, seed):
     (2, 5, 2, 8, 7, 5), (3, 32, 4, 64, 12, 32), (2, 32, 2, 64, 9, 20), (2, 64, 2, 64, 6, 64),
     (1, 40, 1, 48, 5, 33), (2, 7, 3, 6, 4, 7),
 ])
-def test_mhsea_matches_oracle(cuda_device, B, n, H, d, R, max_sequence):
+def test_mhsea_matches_oracle(cuda_device, attention_mode, B, n, H, d, R, max_sequence):
     """Edge attention (reference shapes: test/experimental/pallas/test_attention.py:389-470)."""
     q, k, v, mask, input_mask = make_inputs(B, n, H, d, R, max_sequence, seed=B + n + d)
     e = edge_inputs(B, n, H, R, mask, input_mask, seed=2 * n + d)
