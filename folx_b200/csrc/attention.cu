@@ -17,27 +17,19 @@
 // Jacobian / Laplacian rows of masked electrons are read as zero, m_r = input_mask[r, walker]
 // gates the Hessian term of coordinate r only.
 // Per Jacobian row: three n x n x d and three n x d x n contractions on the CUDA cores (fp32).
-#include "common.cuh"
+//
+// This file holds the CUDA-core kernel (any n <= 64, any alignment) and the entry points; for
+// 16 < n <= 64 with 16-byte friendly buffers the entry points pick the tensor-core kernel of
+// attention_mma.cu.
+#include "attention.cuh"
 
 namespace fl {
 namespace {
 
 int g_attention_mode = 0;     // 0: pick, 1: CUDA-core kernel, 2: tensor-core kernel (fl_mhsa_set_mode)
 
-constexpr int DP = 68;        // smem pitch of an (n x 64) tile, floats
-constexpr int DMAX = 64;      // largest head dimension
 constexpr int kThreads = 256;
-
-__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
-  uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-  int sz = valid ? 16 : 0;  // size 0: the 16 destination bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
+using Args = AttentionArgs;
 
 __device__ __forceinline__ float dot4(float4 a, float4 b) {
   return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w)));
@@ -54,18 +46,6 @@ __device__ __forceinline__ float half_warp_max(float v) {
   for (int o = 8; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
-
-struct Args {
-  const float *q, *qj, *ql, *k, *kj, *kl, *v, *vj, *vl;
-  const uint8_t *mask, *input_mask;
-  float *o, *oj, *ol;
-  int B, n, H, d, R;
-  int64_t qjs, kjs, vjs, ojs;
-  // edge bias added to the scores (EDGE kernels only): e (B, n, H, n), its Jacobian rows and
-  // Laplacian; ejs = Jacobian row stride
-  const float *e, *ej, *el;
-  int64_t ejs;
-};
 
 // Loads one (n x d) tile of a (B, n, H, d) tensor into smem rows [NP][DP]; rows >= n, columns >= d
 // and rows whose electron is masked (when zero_masked) are zero.  VEC: 16-byte cp.async.
@@ -430,377 +410,6 @@ mhsa_kernel(Args a) {
   }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Tensor-core variant for 16 < n <= 32: the same walk as mhsa_kernel, with the six contractions of
-// every Jacobian row on mma.sync (m16n8k8, TF32 operands, fp32 accumulation) in split-fp32
-// arithmetic: v = hi + lo with hi = v truncated to TF32, lo = v - hi, and every product taken as
-// lo*hi + hi*lo + hi*hi, so the result keeps fp32 accuracy.  The per-(walker, head) operands are
-// 32 x 64 and 32 x 32 tiles that change with every Jacobian row; they are too small to feed
-// tcgen05 from shared memory at its rate (a 128-row operand tile would be three quarters padding),
-// so the warp-level instruction is the one that fits: fragments are read straight from the
-// row-major tiles (pitches 68 / 36 / 72 floats keep those reads free of bank conflicts) and split
-// in registers.
-// Warp w owns the 16 x 8 tile (rows 16 (w & 1), columns 8 (w >> 1)) of every n x n matrix and the
-// 16 x 16 tile (rows 16 (w & 1), columns 16 (w >> 1)) of every n x d matrix; row sums over the
-// keys cross warps through a small shared-memory buffer (three block barriers per row).
-// ---------------------------------------------------------------------------------------------
-constexpr int VP = 72;  // pitch of the v tiles: 72 = 8 (mod 32) makes the B-fragment reads conflict-free
-
-struct FragA { uint32_t hi[4], lo[4]; };
-struct FragB { uint32_t hi[2], lo[2]; };
-
-__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
-  hi = __float_as_uint(v) & 0xffffe000u;  // a valid TF32 number: the tensor core uses it as is
-  lo = __float_as_uint(v - __uint_as_float(hi));
-}
-
-__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
-      "{%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-
-__device__ __forceinline__ void mma3(float (&c)[4], const FragA& a, const FragB& b) {
-  mma_tf32(c, a.lo, b.hi);
-  mma_tf32(c, a.hi, b.lo);
-  mma_tf32(c, a.hi, b.hi);
-}
-
-// A fragment (16 x 8) of the row-major tile X (pitch P): rows m0 .., columns k0 ..
-template <int P>
-__device__ __forceinline__ void load_a(FragA& f, const float* X, int m0, int k0, int g, int t) {
-  const float* p = X + (m0 + g) * P + k0 + t;
-  split_tf32(p[0], f.hi[0], f.lo[0]);
-  split_tf32(p[8 * P], f.hi[1], f.lo[1]);
-  split_tf32(p[4], f.hi[2], f.lo[2]);
-  split_tf32(p[8 * P + 4], f.hi[3], f.lo[3]);
-}
-// B fragment (8 x 8) of the operand B[k][n] = X[n][k]: X row-major with pitch P
-template <int P>
-__device__ __forceinline__ void load_bt(FragB& f, const float* X, int n0, int k0, int g, int t) {
-  const float* p = X + (n0 + g) * P + k0 + t;
-  split_tf32(p[0], f.hi[0], f.lo[0]);
-  split_tf32(p[4], f.hi[1], f.lo[1]);
-}
-// B fragment (8 x 8) of the operand B[k][n] = X[k][n]
-template <int P>
-__device__ __forceinline__ void load_b(FragB& f, const float* X, int k0, int n0, int g, int t) {
-  const float* p = X + (k0 + t) * P + n0 + g;
-  split_tf32(p[0], f.hi[0], f.lo[0]);
-  split_tf32(p[4 * P], f.hi[1], f.lo[1]);
-}
-
-template <int PITCH>
-__device__ __forceinline__ void load_tile32(float* dst, const float* src, const Args& a, int b, int h,
-                                            const uint8_t* rowmask, bool zero_masked) {
-  const int64_t row_stride = (int64_t)a.H * a.d;
-  const float* base = src + ((int64_t)b * a.n * a.H + h) * a.d;
-  for (int e = threadIdx.x; e < 32 * (DMAX / 4); e += kThreads) {
-    const int i = e / (DMAX / 4), c = (e % (DMAX / 4)) * 4;
-    const bool ok = i < a.n && c < a.d && !(zero_masked && !rowmask[i]);
-    cp_async16(dst + i * PITCH + c, ok ? base + i * row_stride + c : src, ok);
-  }
-}
-
-__device__ __forceinline__ float quad_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  return v;
-}
-__device__ __forceinline__ float quad_max(float v) {
-  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
-  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
-  return v;
-}
-
-constexpr int kMma32SmemFloats = 2 * 32 * DP + 32 * VP + 2 * (2 * 32 * DP + 32 * VP) + 2 * 32 * 36 + 2 * 4 * 32;
-
-template <bool EDGE>
-__global__ void __launch_bounds__(kThreads, 2)
-mhsa_mma32_kernel(Args a) {
-  constexpr int NP = 32, PP = NP + 4;
-  constexpr int kBuf = 2 * NP * DP + NP * VP;
-  extern __shared__ __align__(16) float smem[];
-  float* Q = smem;             // [32][DP]
-  float* Kx = Q + NP * DP;     // [32][DP]
-  float* V = Kx + NP * DP;     // [32][VP]
-  float* buf = V + NP * VP;    // 2 x {QR [32][DP], KR [32][DP], VR [32][VP]}
-  float* Pm = buf + 2 * kBuf;  // [32][PP]  softmax matrix
-  float* PR = Pm + NP * PP;    // [32][PP]  p_r of the row in flight
-  float* red1 = PR + NP * PP;  // [4][32]   partial row sums, first round
-  float* red2 = red1 + 4 * NP; // [4][32]   second round
-  __shared__ uint8_t rowmask_s[32];
-
-  const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, t = lane & 3;
-  const int mt = warp & 1, nt = warp >> 1;
-  const int n = a.n, d = a.d;
-  // score layout: this thread's elements are (R0, C0), (R0, C0 + 1), (R1, C0), (R1, C0 + 1)
-  const int R0 = 16 * mt + g, R1 = R0 + 8, C0 = 8 * nt + 2 * t;
-  // value layout: rows R0 / R1, columns CV0 + {0, 1} and CV0 + 8 + {0, 1}
-  const int CV0 = 16 * nt + 2 * t;
-
-  if (threadIdx.x < NP)
-    rowmask_s[threadIdx.x] = threadIdx.x < n ? (a.mask ? a.mask[(int64_t)b * n + threadIdx.x] : 1) : 0;
-  __syncthreads();
-
-  load_tile32<DP>(Q, a.q, a, b, h, rowmask_s, false);
-  load_tile32<DP>(Kx, a.k, a, b, h, rowmask_s, false);
-  load_tile32<VP>(V, a.v, a, b, h, rowmask_s, false);
-  load_tile32<DP>(buf, a.ql, a, b, h, rowmask_s, true);
-  load_tile32<DP>(buf + NP * DP, a.kl, a, b, h, rowmask_s, true);
-  load_tile32<VP>(buf + 2 * NP * DP, a.vl, a, b, h, rowmask_s, true);
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();
-
-  auto sum_over_warps = [&](const float* red, int row) {
-    return (red[row] + red[NP + row]) + (red[2 * NP + row] + red[3 * NP + row]);
-  };
-  auto edge_at = [&](const float* src, int i, int j) {
-    return src[(((int64_t)b * n + i) * a.H + h) * n + j];
-  };
-  const bool v00 = R0 < n && C0 < n, v01 = R0 < n && C0 + 1 < n, v10 = R1 < n && C0 < n,
-             v11 = R1 < n && C0 + 1 < n;
-  const bool u00 = v00 && rowmask_s[R0] && rowmask_s[C0], u01 = v01 && rowmask_s[R0] && rowmask_s[C0 + 1],
-             u10 = v10 && rowmask_s[R1] && rowmask_s[C0], u11 = v11 && rowmask_s[R1] && rowmask_s[C0 + 1];
-
-  // ---------------- softmax matrix p ----------------
-  float p[4];
-  {
-    float s[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int k0 = 0; k0 < DMAX; k0 += 8) {
-      FragA fa;
-      FragB fb;
-      load_a<DP>(fa, Q, 16 * mt, k0, g, t);
-      load_bt<DP>(fb, Kx, 8 * nt, k0, g, t);
-      mma3(s, fa, fb);
-    }
-    if constexpr (EDGE) {
-      if (v00) s[0] += edge_at(a.e, R0, C0);
-      if (v01) s[1] += edge_at(a.e, R0, C0 + 1);
-      if (v10) s[2] += edge_at(a.e, R1, C0);
-      if (v11) s[3] += edge_at(a.e, R1, C0 + 1);
-    }
-    // masked pairs (reference: scores of pairs with a padded electron are -1e20)
-    if (v00 && !u00) s[0] = -1e20f;
-    if (v01 && !u01) s[1] = -1e20f;
-    if (v10 && !u10) s[2] = -1e20f;
-    if (v11 && !u11) s[3] = -1e20f;
-    const float lo = -3.0e38f;
-    float m0 = quad_max(fmaxf(C0 < n ? s[0] : lo, C0 + 1 < n ? s[1] : lo));
-    float m1 = quad_max(fmaxf(C0 < n ? s[2] : lo, C0 + 1 < n ? s[3] : lo));
-    if (t == 0) { red1[nt * NP + R0] = m0; red1[nt * NP + R1] = m1; }
-    __syncthreads();
-    m0 = fmaxf(fmaxf(red1[R0], red1[NP + R0]), fmaxf(red1[2 * NP + R0], red1[3 * NP + R0]));
-    m1 = fmaxf(fmaxf(red1[R1], red1[NP + R1]), fmaxf(red1[2 * NP + R1], red1[3 * NP + R1]));
-    p[0] = C0 < n ? expf(s[0] - m0) : 0.f;
-    p[1] = C0 + 1 < n ? expf(s[1] - m0) : 0.f;
-    p[2] = C0 < n ? expf(s[2] - m1) : 0.f;
-    p[3] = C0 + 1 < n ? expf(s[3] - m1) : 0.f;
-    const float z0 = quad_sum(p[0] + p[1]), z1 = quad_sum(p[2] + p[3]);
-    if (t == 0) { red2[nt * NP + R0] = z0; red2[nt * NP + R1] = z1; }
-    __syncthreads();
-    const float i0 = 1.0f / sum_over_warps(red2, R0), i1 = 1.0f / sum_over_warps(red2, R1);
-    p[0] *= i0; p[1] *= i0; p[2] *= i1; p[3] *= i1;
-    *reinterpret_cast<float2*>(Pm + R0 * PP + C0) = make_float2(p[0], p[1]);
-    *reinterpret_cast<float2*>(Pm + R1 * PP + C0) = make_float2(p[2], p[3]);
-  }
-  __syncthreads();
-
-  // stores of a 16 x 16 value-layout tile pair (rows R0 / R1, columns CV0 + 8 u + {0, 1})
-  auto store_rows = [&](float* dst_base, const float (&acc)[2][4]) {
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int c = CV0 + 8 * u;
-      if (c < d) {
-        if (R0 < n)
-          __stcs(reinterpret_cast<float2*>(dst_base + (((int64_t)b * n + R0) * a.H + h) * d + c),
-                 make_float2(acc[u][0], acc[u][1]));
-        if (R1 < n)
-          __stcs(reinterpret_cast<float2*>(dst_base + (((int64_t)b * n + R1) * a.H + h) * d + c),
-                 make_float2(acc[u][2], acc[u][3]));
-      }
-    }
-  };
-
-  // o = p v
-  {
-    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-    for (int k0 = 0; k0 < NP; k0 += 8) {
-      FragA fa;
-      load_a<PP>(fa, Pm, 16 * mt, k0, g, t);
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        FragB fb;
-        load_b<VP>(fb, V, k0, 16 * nt + 8 * u, g, t);
-        mma3(acc[u], fa, fb);
-      }
-    }
-    store_rows(a.o, acc);
-  }
-
-  float lap_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-  float tvsum[4] = {0.f, 0.f, 0.f, 0.f}, s3sum[4] = {0.f, 0.f, 0.f, 0.f};
-
-  // ---------------- stream the Laplacian row (it == 0) and the R Jacobian rows -------------------
-  for (int it = 0; it <= a.R; ++it) {
-    const int cur = it & 1;
-    cp_async_wait<0>();
-    __syncthreads();  // tiles visible; every warp has left the previous iteration
-    if (it < a.R) {
-      float* nb = buf + (cur ^ 1) * kBuf;
-      load_tile32<DP>(nb, a.qj + (int64_t)it * a.qjs, a, b, h, rowmask_s, true);
-      load_tile32<DP>(nb + NP * DP, a.kj + (int64_t)it * a.kjs, a, b, h, rowmask_s, true);
-      load_tile32<VP>(nb + 2 * NP * DP, a.vj + (int64_t)it * a.vjs, a, b, h, rowmask_s, true);
-      cp_async_commit();
-    }
-    const float* QR = buf + cur * kBuf;
-    const float* KR = QR + NP * DP;
-    const float* VR = KR + NP * DP;
-    const bool hess = it > 0;
-    const float m = !hess ? 0.f
-                          : (a.input_mask ? (a.input_mask[(int64_t)(it - 1) * a.B + b] ? 1.f : 0.f) : 1.f);
-
-    float er[4] = {0.f, 0.f, 0.f, 0.f};
-    if constexpr (EDGE) {
-      const float* src = hess ? a.ej + (int64_t)(it - 1) * a.ejs : a.el;
-      if (u00) er[0] = __ldcs(&src[(((int64_t)b * n + R0) * a.H + h) * n + C0]);
-      if (u01) er[1] = __ldcs(&src[(((int64_t)b * n + R0) * a.H + h) * n + C0 + 1]);
-      if (u10) er[2] = __ldcs(&src[(((int64_t)b * n + R1) * a.H + h) * n + C0]);
-      if (u11) er[3] = __ldcs(&src[(((int64_t)b * n + R1) * a.H + h) * n + C0 + 1]);
-    }
-
-    // ---- score phase: q_r k^T, q k_r^T, q_r k_r^T ----
-    float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f}, s3[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int k0 = 0; k0 < DMAX; k0 += 8) {
-      FragA aq, aqr;
-      FragB bk, bkr;
-      load_a<DP>(aq, Q, 16 * mt, k0, g, t);
-      load_a<DP>(aqr, QR, 16 * mt, k0, g, t);
-      load_bt<DP>(bk, Kx, 8 * nt, k0, g, t);
-      load_bt<DP>(bkr, KR, 8 * nt, k0, g, t);
-      mma3(s1, aqr, bk);
-      mma3(s2, aq, bkr);
-      mma3(s3, aqr, bkr);
-    }
-    float sr[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) sr[e] = s1[e] + s2[e] + er[e];
-    {
-      const float q0 = quad_sum(fmaf(p[0], sr[0], p[1] * sr[1]));
-      const float q1 = quad_sum(fmaf(p[2], sr[2], p[3] * sr[3]));
-      if (t == 0) { red1[nt * NP + R0] = q0; red1[nt * NP + R1] = q1; }
-    }
-    __syncthreads();
-    const float r1a = sum_over_warps(red1, R0), r1b = sum_over_warps(red1, R1);  // rowsum(p s_r)
-    float c[4], pr[4];
-    c[0] = sr[0] - r1a; c[1] = sr[1] - r1a; c[2] = sr[2] - r1b; c[3] = sr[3] - r1b;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) pr[e] = p[e] * c[e];
-    *reinterpret_cast<float2*>(PR + R0 * PP + C0) = make_float2(pr[0], pr[1]);
-    *reinterpret_cast<float2*>(PR + R1 * PP + C0) = make_float2(pr[2], pr[3]);
-    {
-      const float q0 = quad_sum(fmaf(pr[0], sr[0], pr[1] * sr[1]));
-      const float q1 = quad_sum(fmaf(pr[2], sr[2], pr[3] * sr[3]));
-      if (t == 0) { red2[nt * NP + R0] = q0; red2[nt * NP + R1] = q1; }
-    }
-    __syncthreads();
-    {
-      const float r2a = sum_over_warps(red2, R0), r2b = sum_over_warps(red2, R1);  // rowsum(p_r s_r)
-      tvsum[0] = fmaf(m, pr[0] * c[0] - p[0] * r2a, tvsum[0]);
-      tvsum[1] = fmaf(m, pr[1] * c[1] - p[1] * r2a, tvsum[1]);
-      tvsum[2] = fmaf(m, pr[2] * c[2] - p[2] * r2b, tvsum[2]);
-      tvsum[3] = fmaf(m, pr[3] * c[3] - p[3] * r2b, tvsum[3]);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) s3sum[e] = fmaf(m, s3[e], s3sum[e]);
-    }
-
-    // ---- value phase: o_r = p_r v + p v_r ; per-row Hessian term 2 p_r v_r ----
-    float oj[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-    float ct[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-    for (int k0 = 0; k0 < NP; k0 += 8) {
-      FragA apr, ap;
-      load_a<PP>(apr, PR, 16 * mt, k0, g, t);
-      load_a<PP>(ap, Pm, 16 * mt, k0, g, t);
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        FragB bv, bvr;
-        load_b<VP>(bv, V, k0, 16 * nt + 8 * u, g, t);
-        load_b<VP>(bvr, VR, k0, 16 * nt + 8 * u, g, t);
-        mma3(oj[u], apr, bv);
-        mma3(oj[u], ap, bvr);
-        mma3(ct[u], apr, bvr);
-      }
-    }
-    if (!hess) {
-#pragma unroll
-      for (int u = 0; u < 2; ++u)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) lap_acc[u][e] = oj[u][e];
-    } else {
-      const float m2 = 2.0f * m;
-#pragma unroll
-      for (int u = 0; u < 2; ++u)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) lap_acc[u][e] = fmaf(m2, ct[u][e], lap_acc[u][e]);
-      store_rows(a.oj + (int64_t)(it - 1) * a.ojs, oj);
-    }
-  }
-
-  // ---------------- the summed weights of v, applied once --------------------------------------
-  __syncthreads();  // every warp has finished reading PR and the partial sums
-  {
-    const float q0 = quad_sum(2.0f * fmaf(p[0], s3sum[0], p[1] * s3sum[1]));
-    const float q1 = quad_sum(2.0f * fmaf(p[2], s3sum[2], p[3] * s3sum[3]));
-    if (t == 0) { red1[nt * NP + R0] = q0; red1[nt * NP + R1] = q1; }
-  }
-  __syncthreads();
-  {
-    const float r3a = sum_over_warps(red1, R0), r3b = sum_over_warps(red1, R1);  // rowsum(2 p S3)
-    *reinterpret_cast<float2*>(PR + R0 * PP + C0) =
-        make_float2(tvsum[0] + p[0] * (2.0f * s3sum[0] - r3a), tvsum[1] + p[1] * (2.0f * s3sum[1] - r3a));
-    *reinterpret_cast<float2*>(PR + R1 * PP + C0) =
-        make_float2(tvsum[2] + p[2] * (2.0f * s3sum[2] - r3b), tvsum[3] + p[3] * (2.0f * s3sum[3] - r3b));
-  }
-  __syncthreads();
-#pragma unroll
-  for (int k0 = 0; k0 < NP; k0 += 8) {
-    FragA atv;
-    load_a<PP>(atv, PR, 16 * mt, k0, g, t);
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      FragB bv;
-      load_b<VP>(bv, V, k0, 16 * nt + 8 * u, g, t);
-      mma3(lap_acc[u], atv, bv);
-    }
-  }
-  store_rows(a.ol, lap_acc);
-}
-
-template <bool EDGE>
-int32_t launch_mma32(const Args& a, cudaStream_t st) {
-  constexpr size_t smem = (size_t)kMma32SmemFloats * sizeof(float);
-  static bool attr = false;
-  if (!attr) {
-    FL_CUDA(cudaFuncSetAttribute(mhsa_mma32_kernel<EDGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem));
-    attr = true;
-  }
-  const int64_t blocks = (int64_t)a.B * a.H;
-  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_mhsa: too many (walker, head) pairs");
-  mhsa_mma32_kernel<EDGE><<<(unsigned)blocks, kThreads, smem, st>>>(a);
-  FL_CHECK_LAUNCH("fl_mhsa launch");
-  return FL_OK;
-}
-
 template <int NP, bool EDGE>
 int32_t launch(const Args& a, bool vec, cudaStream_t st) {
   constexpr size_t smem = (size_t)(9 * NP * DP + 3 * NP * (NP + 4)) * sizeof(float);
@@ -843,11 +452,11 @@ int32_t run_attention(const char* who, Args a, int64_t B, int64_t n, int64_t H, 
   bool vec = d % 4 == 0 && al(a.q) && al(a.k) && al(a.v) && al(a.qj) && al(a.kj) && al(a.vj) &&
              al(a.ql) && al(a.kl) && al(a.vl) && al(a.oj) && a.qjs % 4 == 0 && a.kjs % 4 == 0 &&
              a.vjs % 4 == 0 && a.ojs % 4 == 0;
-  // tensor-core kernel: 16 < n <= 32, 16-byte friendly buffers
-  const bool tc_ok = vec && n > 16 && n <= 32 && al(a.o) && al(a.ol);
+  // tensor-core kernel: 16 < n <= 64, 16-byte friendly buffers
+  const bool tc_ok = vec && attention_mma_supported(n, d) && al(a.o) && al(a.ol);
   FL_REQUIRE(g_attention_mode != 2 || tc_ok, FL_EUNSUPPORTED,
              "%s: tensor-core kernel forced but n=%lld / alignment do not fit", who, (long long)n);
-  if (tc_ok && g_attention_mode != 1) return edge ? launch_mma32<true>(a, st) : launch_mma32<false>(a, st);
+  if (tc_ok && g_attention_mode != 1) return launch_attention_mma(a, edge, st);
   if (edge) {
     if (n <= 16) return launch<16, true>(a, vec, st);
     if (n <= 32) return launch<32, true>(a, vec, st);

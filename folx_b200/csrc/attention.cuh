@@ -1,0 +1,40 @@
+// Shared between the two attention-Laplacian kernels (CUDA-core: attention.cu, tensor-core:
+// attention_mma.cu): argument block, tile geometry and the cp.async helpers.
+#pragma once
+
+#include "common.cuh"
+
+namespace fl {
+
+constexpr int DP = 68;    // shared-memory pitch of an (n x 64) tile, floats
+constexpr int DMAX = 64;  // largest head dimension
+
+struct AttentionArgs {
+  const float *q, *qj, *ql, *k, *kj, *kl, *v, *vj, *vl;
+  const uint8_t *mask, *input_mask;
+  float *o, *oj, *ol;
+  int B, n, H, d, R;
+  int64_t qjs, kjs, vjs, ojs;
+  // edge bias added to the scores (EDGE kernels only): e (B, n, H, n), its Jacobian rows and
+  // Laplacian; ejs = Jacobian row stride
+  const float *e, *ej, *el;
+  int64_t ejs;
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  int sz = valid ? 16 : 0;  // size 0: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Tensor-core kernel (attention_mma.cu): 16 < n <= 64, head dimension <= 64 and a multiple of 4,
+// all buffers 16-byte aligned (the caller checks the alignment).
+bool attention_mma_supported(int64_t n, int64_t d);
+int32_t launch_attention_mma(const AttentionArgs& a, bool edge, cudaStream_t st);
+
+}  // namespace fl

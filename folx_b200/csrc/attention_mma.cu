@@ -1,0 +1,487 @@
+// Tensor-core variant of the fused attention-Laplacian rule for 16 < n <= 64.
+//
+// The same walk as mhsa_kernel (attention.cu; reference: mhsa_forward_laplacian_kernel /
+// mhsea_forward_laplacian_kernel, folx/experimental/pallas/attention/forward_laplacian.py:349-487,
+// 733-854), with the six contractions of every Jacobian row on mma.sync (m16n8k8, TF32 operands,
+// fp32 accumulation) in split-fp32 arithmetic: v = hi + lo with hi = v truncated to TF32 and
+// lo = v - hi, every product taken as lo*hi + hi*lo + hi*hi, so the result keeps fp32 accuracy.
+// The per-(walker, head) operands are n x 64 and n x n tiles that change with every Jacobian row;
+// they are too small to feed tcgen05 from shared memory at its rate (a 128-row operand tile would
+// be mostly padding), so the warp-level instruction is the one that fits: fragments are read
+// straight from the row-major tiles (pitches 68 / n + 4 / 72 floats keep those reads free of bank
+// conflicts) and split in registers.
+// One CTA per (walker, head) with n / 4 warps.  Warp w owns the rows 16 (w mod n/16) .. + 15 and
+// one column group out of four: n / 32 tiles of 16 x 8 of every n x n matrix and a 16 x 16 tile of
+// every n x d matrix.  Row sums over the keys cross warps through a small shared-memory buffer
+// (three block barriers per Jacobian row).
+#include "attention.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int VP = 72;  // pitch of the v tiles: 72 = 8 (mod 32) makes the B-fragment reads conflict-free
+
+struct FragA { uint32_t hi[4], lo[4]; };
+struct FragB { uint32_t hi[2], lo[2]; };
+
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  hi = __float_as_uint(v) & 0xffffe000u;  // a valid TF32 number: the tensor core uses it as is
+  lo = __float_as_uint(v - __uint_as_float(hi));
+}
+
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__device__ __forceinline__ void mma3(float (&c)[4], const FragA& a, const FragB& b) {
+  mma_tf32(c, a.lo, b.hi);
+  mma_tf32(c, a.hi, b.lo);
+  mma_tf32(c, a.hi, b.hi);
+}
+
+// A fragment (16 x 8) of the row-major tile X (pitch P): rows m0 .., columns k0 ..
+template <int P>
+__device__ __forceinline__ void load_a(FragA& f, const float* X, int m0, int k0, int g, int t) {
+  const float* p = X + (m0 + g) * P + k0 + t;
+  split_tf32(p[0], f.hi[0], f.lo[0]);
+  split_tf32(p[8 * P], f.hi[1], f.lo[1]);
+  split_tf32(p[4], f.hi[2], f.lo[2]);
+  split_tf32(p[8 * P + 4], f.hi[3], f.lo[3]);
+}
+// B fragment (8 x 8) of the operand B[k][n] = X[n][k]: X row-major with pitch P
+template <int P>
+__device__ __forceinline__ void load_bt(FragB& f, const float* X, int n0, int k0, int g, int t) {
+  const float* p = X + (n0 + g) * P + k0 + t;
+  split_tf32(p[0], f.hi[0], f.lo[0]);
+  split_tf32(p[4], f.hi[1], f.lo[1]);
+}
+// B fragment (8 x 8) of the operand B[k][n] = X[k][n]
+template <int P>
+__device__ __forceinline__ void load_b(FragB& f, const float* X, int k0, int n0, int g, int t) {
+  const float* p = X + (k0 + t) * P + n0 + g;
+  split_tf32(p[0], f.hi[0], f.lo[0]);
+  split_tf32(p[4 * P], f.hi[1], f.lo[1]);
+}
+
+__device__ __forceinline__ float quad_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  return v;
+}
+__device__ __forceinline__ float quad_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+  return v;
+}
+
+template <int NP>
+struct Geo {
+  static constexpr int NW = NP / 4;        // warps per CTA: 8 (n <= 32) or 16 (n <= 64)
+  static constexpr int THREADS = 32 * NW;
+  static constexpr int MT = NP / 16;       // row tiles of 16
+  static constexpr int NG = NW / MT;       // warp groups along the columns (4)
+  static constexpr int TS = NP / 8 / NG;   // 16 x 8 score tiles per warp (1 or 2)
+  static constexpr int PP = NP + 4;        // pitch of the n x n matrices: = 4 (mod 32)
+  static constexpr int kBuf = 2 * NP * DP + NP * VP;  // {q, k, v}-shaped tile set
+  static constexpr int kSmemFloats = 3 * kBuf + 2 * NP * PP + 2 * NG * NP;
+};
+
+template <int NP, int PITCH>
+__device__ __forceinline__ void load_tile(float* dst, const float* src, const AttentionArgs& a, int b,
+                                          int h, const uint8_t* rowmask, bool zero_masked) {
+  const int64_t row_stride = (int64_t)a.H * a.d;
+  const float* base = src + ((int64_t)b * a.n * a.H + h) * a.d;
+  for (int e = threadIdx.x; e < NP * (DMAX / 4); e += Geo<NP>::THREADS) {
+    const int i = e / (DMAX / 4), c = (e % (DMAX / 4)) * 4;
+    const bool ok = i < a.n && c < a.d && !(zero_masked && !rowmask[i]);
+    cp_async16(dst + i * PITCH + c, ok ? base + i * row_stride + c : src, ok);
+  }
+}
+
+template <int NP, bool EDGE>
+__global__ void __launch_bounds__(Geo<NP>::THREADS, NP == 32 ? 2 : 1)
+mhsa_mma_kernel(AttentionArgs a) {
+  using G = Geo<NP>;
+  constexpr int PP = G::PP, TS = G::TS, NG = G::NG, kBuf = G::kBuf;
+  extern __shared__ __align__(16) float smem[];
+  float* Q = smem;              // [NP][DP]
+  float* Kx = Q + NP * DP;      // [NP][DP]
+  float* V = Kx + NP * DP;      // [NP][VP]
+  float* buf = V + NP * VP;     // 2 x {QR [NP][DP], KR [NP][DP], VR [NP][VP]}
+  float* Pm = buf + 2 * kBuf;   // [NP][PP]  softmax matrix
+  float* PR = Pm + NP * PP;     // [NP][PP]  p_r of the row in flight
+  float* red1 = PR + NP * PP;   // [NG][NP]  partial row sums, first round
+  float* red2 = red1 + NG * NP; // [NG][NP]  second round
+  __shared__ uint8_t rowmask_s[64];
+
+  const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int mt = warp % G::MT, ng = warp / G::MT;
+  const int n = a.n, d = a.d;
+  // score layout: tile s of this warp covers columns 8 (ng TS + s) ..; this thread's elements are
+  // (R0, C), (R0, C + 1), (R1, C), (R1, C + 1) with C = CS + 8 s
+  const int R0 = 16 * mt + g, R1 = R0 + 8, CS = 8 * ng * TS + 2 * t;
+  // value layout: rows R0 / R1, columns CV0 + 8 u + {0, 1}, u = 0, 1
+  const int CV0 = 16 * ng + 2 * t;
+
+  if (threadIdx.x < NP)
+    rowmask_s[threadIdx.x] = threadIdx.x < n ? (a.mask ? a.mask[(int64_t)b * n + threadIdx.x] : 1) : 0;
+  __syncthreads();
+
+  load_tile<NP, DP>(Q, a.q, a, b, h, rowmask_s, false);
+  load_tile<NP, DP>(Kx, a.k, a, b, h, rowmask_s, false);
+  load_tile<NP, VP>(V, a.v, a, b, h, rowmask_s, false);
+  // first streamed row: the Laplacians (treated like a Jacobian row without a Hessian term)
+  load_tile<NP, DP>(buf, a.ql, a, b, h, rowmask_s, true);
+  load_tile<NP, DP>(buf + NP * DP, a.kl, a, b, h, rowmask_s, true);
+  load_tile<NP, VP>(buf + 2 * NP * DP, a.vl, a, b, h, rowmask_s, true);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();
+
+  auto sum_groups = [&](const float* red, int row) {
+    return (red[row] + red[NP + row]) + (red[2 * NP + row] + red[3 * NP + row]);
+  };
+  auto max_groups = [&](const float* red, int row) {
+    return fmaxf(fmaxf(red[row], red[NP + row]), fmaxf(red[2 * NP + row], red[3 * NP + row]));
+  };
+  // element e of tile s: row / column, inside the matrix, and between two valid electrons
+  auto row_of = [&](int e) { return e < 2 ? R0 : R1; };
+  auto col_of = [&](int s, int e) { return CS + 8 * s + (e & 1); };
+  auto inside = [&](int s, int e) { return row_of(e) < n && col_of(s, e) < n; };
+  auto unmasked = [&](int s, int e) {
+    return inside(s, e) && rowmask_s[row_of(e)] && rowmask_s[col_of(s, e)];
+  };
+  auto edge_index = [&](int s, int e) {
+    return (((int64_t)b * n + row_of(e)) * a.H + h) * n + col_of(s, e);
+  };
+
+  // ---------------- softmax matrix p ----------------
+  float p[TS][4];
+  {
+    float sc[TS][4];
+#pragma unroll
+    for (int s = 0; s < TS; ++s) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sc[s][e] = 0.f;
+#pragma unroll
+      for (int k0 = 0; k0 < DMAX; k0 += 8) {
+        FragA fa;
+        FragB fb;
+        load_a<DP>(fa, Q, 16 * mt, k0, g, t);
+        load_bt<DP>(fb, Kx, 8 * (ng * TS + s), k0, g, t);
+        mma3(sc[s], fa, fb);
+      }
+    }
+    float m0 = -3.0e38f, m1 = -3.0e38f;
+#pragma unroll
+    for (int s = 0; s < TS; ++s)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if constexpr (EDGE)
+          if (inside(s, e)) sc[s][e] += __ldg(a.e + edge_index(s, e));
+        // masked pairs (reference: scores of pairs with a padded electron are -1e20)
+        if (inside(s, e) && !unmasked(s, e)) sc[s][e] = -1e20f;
+        if (col_of(s, e) < n) {
+          if (e < 2) m0 = fmaxf(m0, sc[s][e]);
+          else m1 = fmaxf(m1, sc[s][e]);
+        }
+      }
+    m0 = quad_max(m0);
+    m1 = quad_max(m1);
+    if (t == 0) { red1[ng * NP + R0] = m0; red1[ng * NP + R1] = m1; }
+    __syncthreads();
+    m0 = max_groups(red1, R0);
+    m1 = max_groups(red1, R1);
+    float z0 = 0.f, z1 = 0.f;
+#pragma unroll
+    for (int s = 0; s < TS; ++s)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        p[s][e] = col_of(s, e) < n ? expf(sc[s][e] - (e < 2 ? m0 : m1)) : 0.f;
+        if (e < 2) z0 += p[s][e];
+        else z1 += p[s][e];
+      }
+    z0 = quad_sum(z0);
+    z1 = quad_sum(z1);
+    if (t == 0) { red2[ng * NP + R0] = z0; red2[ng * NP + R1] = z1; }
+    __syncthreads();
+    const float i0 = 1.0f / sum_groups(red2, R0), i1 = 1.0f / sum_groups(red2, R1);
+#pragma unroll
+    for (int s = 0; s < TS; ++s) {
+      p[s][0] *= i0; p[s][1] *= i0; p[s][2] *= i1; p[s][3] *= i1;
+      *reinterpret_cast<float2*>(Pm + R0 * PP + CS + 8 * s) = make_float2(p[s][0], p[s][1]);
+      *reinterpret_cast<float2*>(Pm + R1 * PP + CS + 8 * s) = make_float2(p[s][2], p[s][3]);
+    }
+  }
+  __syncthreads();
+
+  // stores of a value-layout tile pair (rows R0 / R1, columns CV0 + 8 u + {0, 1})
+  auto store_rows = [&](float* dst_base, const float (&acc)[2][4]) {
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int c = CV0 + 8 * u;
+      if (c < d) {
+        if (R0 < n)
+          __stcs(reinterpret_cast<float2*>(dst_base + (((int64_t)b * n + R0) * a.H + h) * d + c),
+                 make_float2(acc[u][0], acc[u][1]));
+        if (R1 < n)
+          __stcs(reinterpret_cast<float2*>(dst_base + (((int64_t)b * n + R1) * a.H + h) * d + c),
+                 make_float2(acc[u][2], acc[u][3]));
+      }
+    }
+  };
+
+  // o = p v
+  {
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
+    for (int k0 = 0; k0 < NP; k0 += 8) {
+      FragA fa;
+      load_a<PP>(fa, Pm, 16 * mt, k0, g, t);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        FragB fb;
+        load_b<VP>(fb, V, k0, 16 * ng + 8 * u, g, t);
+        mma3(acc[u], fa, fb);
+      }
+    }
+    store_rows(a.o, acc);
+  }
+
+  float lap_acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+  float tvsum[TS][4], s3sum[TS][4];
+#pragma unroll
+  for (int s = 0; s < TS; ++s)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { tvsum[s][e] = 0.f; s3sum[s][e] = 0.f; }
+
+  // ---------------- stream the Laplacian row (it == 0) and the R Jacobian rows -------------------
+  for (int it = 0; it <= a.R; ++it) {
+    const int cur = it & 1;
+    cp_async_wait<0>();
+    __syncthreads();  // tiles visible; every warp has left the previous iteration
+    if (it < a.R) {
+      float* nb = buf + (cur ^ 1) * kBuf;
+      load_tile<NP, DP>(nb, a.qj + (int64_t)it * a.qjs, a, b, h, rowmask_s, true);
+      load_tile<NP, DP>(nb + NP * DP, a.kj + (int64_t)it * a.kjs, a, b, h, rowmask_s, true);
+      load_tile<NP, VP>(nb + 2 * NP * DP, a.vj + (int64_t)it * a.vjs, a, b, h, rowmask_s, true);
+      cp_async_commit();
+    }
+    const float* QR = buf + cur * kBuf;
+    const float* KR = QR + NP * DP;
+    const float* VR = KR + NP * DP;
+    const bool hess = it > 0;
+    // m_r gates the Hessian contribution of coordinate r (reference line 481)
+    const float m = !hess ? 0.f
+                          : (a.input_mask ? (a.input_mask[(int64_t)(it - 1) * a.B + b] ? 1.f : 0.f) : 1.f);
+
+    // ---- score phase: s_r = q_r k^T + q k_r^T (+ e_r) and q_r k_r^T ----
+    float sr[TS][4], s3[TS][4];
+#pragma unroll
+    for (int s = 0; s < TS; ++s) {
+      float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s3[s][e] = 0.f;
+      if constexpr (EDGE) {
+        // e_r of this row; pairs with a masked electron contribute nothing (reference line 806)
+        const float* src = hess ? a.ej + (int64_t)(it - 1) * a.ejs : a.el;
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (unmasked(s, e)) s1[e] = __ldcs(src + edge_index(s, e));
+      }
+#pragma unroll
+      for (int k0 = 0; k0 < DMAX; k0 += 8) {
+        FragA aq, aqr;
+        FragB bk, bkr;
+        load_a<DP>(aq, Q, 16 * mt, k0, g, t);
+        load_a<DP>(aqr, QR, 16 * mt, k0, g, t);
+        load_bt<DP>(bk, Kx, 8 * (ng * TS + s), k0, g, t);
+        load_bt<DP>(bkr, KR, 8 * (ng * TS + s), k0, g, t);
+        // interleaved so that consecutive instructions never touch the same accumulator
+        mma_tf32(s1, aqr.lo, bk.hi);
+        mma_tf32(s2, aq.lo, bkr.hi);
+        mma_tf32(s3[s], aqr.lo, bkr.hi);
+        mma_tf32(s1, aqr.hi, bk.lo);
+        mma_tf32(s2, aq.hi, bkr.lo);
+        mma_tf32(s3[s], aqr.hi, bkr.lo);
+        mma_tf32(s1, aqr.hi, bk.hi);
+        mma_tf32(s2, aq.hi, bkr.hi);
+        mma_tf32(s3[s], aqr.hi, bkr.hi);
+      }
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sr[s][e] = s1[e] + s2[e];
+    }
+    {
+      float q0 = 0.f, q1 = 0.f;
+#pragma unroll
+      for (int s = 0; s < TS; ++s) {
+        q0 += fmaf(p[s][0], sr[s][0], p[s][1] * sr[s][1]);
+        q1 += fmaf(p[s][2], sr[s][2], p[s][3] * sr[s][3]);
+      }
+      q0 = quad_sum(q0);
+      q1 = quad_sum(q1);
+      if (t == 0) { red1[ng * NP + R0] = q0; red1[ng * NP + R1] = q1; }
+    }
+    __syncthreads();
+    const float r1a = sum_groups(red1, R0), r1b = sum_groups(red1, R1);  // rowsum(p s_r)
+    float c[TS][4], pr[TS][4];
+    {
+      float q0 = 0.f, q1 = 0.f;
+#pragma unroll
+      for (int s = 0; s < TS; ++s) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          c[s][e] = sr[s][e] - (e < 2 ? r1a : r1b);
+          pr[s][e] = p[s][e] * c[s][e];
+        }
+        *reinterpret_cast<float2*>(PR + R0 * PP + CS + 8 * s) = make_float2(pr[s][0], pr[s][1]);
+        *reinterpret_cast<float2*>(PR + R1 * PP + CS + 8 * s) = make_float2(pr[s][2], pr[s][3]);
+        q0 += fmaf(pr[s][0], sr[s][0], pr[s][1] * sr[s][1]);
+        q1 += fmaf(pr[s][2], sr[s][2], pr[s][3] * sr[s][3]);
+      }
+      q0 = quad_sum(q0);
+      q1 = quad_sum(q1);
+      if (t == 0) { red2[ng * NP + R0] = q0; red2[ng * NP + R1] = q1; }
+    }
+    __syncthreads();
+    {
+      const float r2a = sum_groups(red2, R0), r2b = sum_groups(red2, R1);  // rowsum(p_r s_r)
+#pragma unroll
+      for (int s = 0; s < TS; ++s)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          tvsum[s][e] = fmaf(m, pr[s][e] * c[s][e] - p[s][e] * (e < 2 ? r2a : r2b), tvsum[s][e]);
+          s3sum[s][e] = fmaf(m, s3[s][e], s3sum[s][e]);
+        }
+    }
+
+    // ---- value phase: o_r = p_r v + p v_r ; per-row Hessian term 2 p_r v_r ----
+    float oj[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // p_r v
+    float ok2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // p v_r
+    float ct[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};   // p_r v_r
+#pragma unroll 4
+    for (int k0 = 0; k0 < NP; k0 += 8) {
+      FragA apr, ap;
+      FragB bv[2], bvr[2];
+      load_a<PP>(apr, PR, 16 * mt, k0, g, t);
+      load_a<PP>(ap, Pm, 16 * mt, k0, g, t);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        load_b<VP>(bv[u], V, k0, 16 * ng + 8 * u, g, t);
+        load_b<VP>(bvr[u], VR, k0, 16 * ng + 8 * u, g, t);
+      }
+      // six independent accumulators, visited round robin
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        mma_tf32(oj[u], apr.lo, bv[u].hi);
+        mma_tf32(ok2[u], ap.lo, bvr[u].hi);
+        mma_tf32(ct[u], apr.lo, bvr[u].hi);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        mma_tf32(oj[u], apr.hi, bv[u].lo);
+        mma_tf32(ok2[u], ap.hi, bvr[u].lo);
+        mma_tf32(ct[u], apr.hi, bvr[u].lo);
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        mma_tf32(oj[u], apr.hi, bv[u].hi);
+        mma_tf32(ok2[u], ap.hi, bvr[u].hi);
+        mma_tf32(ct[u], apr.hi, bvr[u].hi);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oj[u][e] += ok2[u][e];
+    if (!hess) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) lap_acc[u][e] = oj[u][e];
+    } else {
+      const float m2 = 2.0f * m;
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) lap_acc[u][e] = fmaf(m2, ct[u][e], lap_acc[u][e]);
+      store_rows(a.oj + (int64_t)(it - 1) * a.ojs, oj);
+    }
+  }
+
+  // ---------------- the summed weights of v, applied once --------------------------------------
+  // sum_r m_r [p_r c_r - p rowsum(p_r s_r)] + p (2 S3 - rowsum(2 p S3)),  S3 = sum_r m_r q_r k_r^T
+  __syncthreads();  // every warp has finished reading PR and the partial sums
+  {
+    float q0 = 0.f, q1 = 0.f;
+#pragma unroll
+    for (int s = 0; s < TS; ++s) {
+      q0 += 2.0f * fmaf(p[s][0], s3sum[s][0], p[s][1] * s3sum[s][1]);
+      q1 += 2.0f * fmaf(p[s][2], s3sum[s][2], p[s][3] * s3sum[s][3]);
+    }
+    q0 = quad_sum(q0);
+    q1 = quad_sum(q1);
+    if (t == 0) { red1[ng * NP + R0] = q0; red1[ng * NP + R1] = q1; }
+  }
+  __syncthreads();
+  {
+    const float r3a = sum_groups(red1, R0), r3b = sum_groups(red1, R1);  // rowsum(2 p S3)
+#pragma unroll
+    for (int s = 0; s < TS; ++s) {
+      float tv[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        tv[e] = tvsum[s][e] + p[s][e] * (2.0f * s3sum[s][e] - (e < 2 ? r3a : r3b));
+      *reinterpret_cast<float2*>(PR + R0 * PP + CS + 8 * s) = make_float2(tv[0], tv[1]);
+      *reinterpret_cast<float2*>(PR + R1 * PP + CS + 8 * s) = make_float2(tv[2], tv[3]);
+    }
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int k0 = 0; k0 < NP; k0 += 8) {
+    FragA atv;
+    load_a<PP>(atv, PR, 16 * mt, k0, g, t);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      FragB bv;
+      load_b<VP>(bv, V, k0, 16 * ng + 8 * u, g, t);
+      mma3(lap_acc[u], atv, bv);
+    }
+  }
+  store_rows(a.ol, lap_acc);
+}
+
+template <int NP, bool EDGE>
+int32_t launch(const AttentionArgs& a, cudaStream_t st) {
+  constexpr size_t smem = (size_t)Geo<NP>::kSmemFloats * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    FL_CUDA(cudaFuncSetAttribute(mhsa_mma_kernel<NP, EDGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    attr = true;
+  }
+  const int64_t blocks = (int64_t)a.B * a.H;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "attention: too many (walker, head) pairs");
+  mhsa_mma_kernel<NP, EDGE><<<(unsigned)blocks, Geo<NP>::THREADS, smem, st>>>(a);
+  FL_CHECK_LAUNCH("attention (tensor-core kernel) launch");
+  return FL_OK;
+}
+
+}  // namespace
+
+bool attention_mma_supported(int64_t n, int64_t d) {
+  return n > 16 && n <= 64 && d >= 4 && d <= DMAX && d % 4 == 0;
+}
+
+int32_t launch_attention_mma(const AttentionArgs& a, bool edge, cudaStream_t st) {
+  if (a.n <= 32) return edge ? launch<32, true>(a, st) : launch<32, false>(a, st);
+  return edge ? launch<64, true>(a, st) : launch<64, false>(a, st);
+}
+
+}  // namespace fl
