@@ -61,11 +61,73 @@ gemm_ffma_kernel(const float* __restrict__ A, const float* __restrict__ W,
   }
 }
 
+// Short contracted axis (first layers: 4 or 16 input features): the product is a stream -- read
+// Kc floats per row, write N -- so one thread owns four output columns, keeps its Kc x 4 block of W
+// in registers and walks down the rows; a warp writes whole 128-byte lines.  HBM-bound:
+// 4 M (Kc + N) bytes.
+template <int KC>
+__global__ void __launch_bounds__(256)
+gemm_smallk_kernel(const float* __restrict__ A, const float* __restrict__ W,
+                   const float* __restrict__ bias, float* __restrict__ Y, int64_t M, int N,
+                   int64_t bias_rows) {
+  const int cg_count = N / 4;              // column groups of 4 (N % 4 == 0, N <= 1024)
+  const int rows_per_pass = 256 / cg_count;
+  const int cg = threadIdx.x % cg_count, r_off = threadIdx.x / cg_count;
+  if (r_off >= rows_per_pass) return;
+  float4 w[KC];
+#pragma unroll
+  for (int k = 0; k < KC; ++k) w[k] = __ldg(reinterpret_cast<const float4*>(W + (int64_t)k * N) + cg);
+  const float4 bv = bias ? __ldg(reinterpret_cast<const float4*>(bias) + cg) : make_float4(0.f, 0.f, 0.f, 0.f);
+  const int64_t stride = (int64_t)gridDim.x * rows_per_pass;
+  for (int64_t row = (int64_t)blockIdx.x * rows_per_pass + r_off; row < M; row += stride) {
+    float a[KC];
+    if constexpr (KC % 4 == 0) {
+#pragma unroll
+      for (int k4 = 0; k4 < KC / 4; ++k4) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(A + row * KC) + k4);
+        a[4 * k4] = v.x; a[4 * k4 + 1] = v.y; a[4 * k4 + 2] = v.z; a[4 * k4 + 3] = v.w;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < KC; ++k) a[k] = __ldg(A + row * KC + k);
+    }
+    float4 acc = row < bias_rows ? bv : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k = 0; k < KC; ++k) {
+      acc.x = fmaf(a[k], w[k].x, acc.x); acc.y = fmaf(a[k], w[k].y, acc.y);
+      acc.z = fmaf(a[k], w[k].z, acc.z); acc.w = fmaf(a[k], w[k].w, acc.w);
+    }
+    __stcs(reinterpret_cast<float4*>(Y + row * N) + cg, acc);
+  }
+}
+
+template <int KC>
+int32_t launch_smallk(const float* A, int64_t M, int64_t N, const float* W, const float* bias,
+                      int64_t bias_rows, float* Y, cudaStream_t st) {
+  const int rows_per_pass = 256 / (int)(N / 4);
+  int64_t blocks = (M + rows_per_pass - 1) / rows_per_pass;
+  const int64_t cap = (int64_t)sm_count() * 16;  // a few passes per block amortise the W registers
+  if (blocks > cap) blocks = cap;
+  gemm_smallk_kernel<KC><<<(unsigned)blocks, 256, 0, st>>>(A, W, bias, Y, M, (int)N, bias_rows);
+  FL_CHECK_LAUNCH("gemm_smallk launch");
+  return FL_OK;
+}
+
 }  // namespace
 
 int32_t gemm_ffma(const float* A, int64_t M, int64_t Kc, int64_t N, const float* W,
                   const float* bias, int64_t bias_rows, float* Y, cudaStream_t st) {
   if (M == 0 || N == 0) return FL_OK;
+  // streaming kernel for a short contracted axis
+  if (Kc <= 16 && N % 4 == 0 && N <= 1024 && aligned16(W) && aligned16(Y) &&
+      (bias == nullptr || aligned16(bias)) && (Kc % 4 != 0 || aligned16(A))) {
+    switch ((int)Kc) {
+#define FL_SK(K) case K: return launch_smallk<K>(A, M, N, W, bias, bias_rows, Y, st);
+      FL_SK(1) FL_SK(2) FL_SK(3) FL_SK(4) FL_SK(5) FL_SK(6) FL_SK(7) FL_SK(8) FL_SK(12) FL_SK(16)
+#undef FL_SK
+      default: break;
+    }
+  }
   int64_t gx = (M + BM - 1) / BM;
   int64_t gy = (N + BN - 1) / BN;
   FL_REQUIRE(gx < (1ll << 31) && gy < 65536, FL_EBADSHAPE, "gemm: grid too large");
