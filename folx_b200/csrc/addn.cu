@@ -1,4 +1,4 @@
-// Sum of up to four triplets followed by an elementwise function, in one pass:
+// Sum of up to five triplets followed by an elementwise function, in one pass:
 //     s = sum_t c_t a_t            (c_t = +1 / -1; a term may be broadcast or a constant)
 //     y = f(s_x),  J_y[k] = f'(s_x) s_J[k],  lap_y = f'(s_x) s_lap + f''(s_x) sum_k s_J[k]^2
 // The reference evaluates such an expression as a chain of `add` rules and one elementwise rule
@@ -49,74 +49,104 @@ __device__ __forceinline__ D3 act(int op, float x) {
   return r;
 }
 
+template <bool RES>
 __global__ void __launch_bounds__(256)
-addn_vec4(int op, Terms t, float4* __restrict__ y, float4* __restrict__ jy, float4* __restrict__ ly,
+addn_vec4(int fop, Terms t, float4* __restrict__ y, float4* __restrict__ jy, float4* __restrict__ ly,
           int64_t jys, int K, int64_t n4) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n4) return;
+  // RES: the last term stays outside the function, y = f(sum of the others) + last
+  const int nf = RES ? t.n - 1 : t.n;
   int64_t pos[kMaxTerms];
-  float4 sx = make_float4(0.f, 0.f, 0.f, 0.f), sl = sx;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 sx = zero, sl = zero, rx = zero, rl = zero;
 #pragma unroll
   for (int q = 0; q < kMaxTerms; ++q) {
     if (q < t.n) {
       pos[q] = (t.mid[q] == 1) ? i : (i / (t.inner[q] * t.mid[q])) * t.inner[q] + i % t.inner[q];
       const float c = t.scale[q];
       float4 v = __ldg(reinterpret_cast<const float4*>(t.x[q]) + pos[q]);
-      sx.x = fmaf(c, v.x, sx.x); sx.y = fmaf(c, v.y, sx.y); sx.z = fmaf(c, v.z, sx.z); sx.w = fmaf(c, v.w, sx.w);
-      if (t.lap[q]) {
-        float4 w = __ldg(reinterpret_cast<const float4*>(t.lap[q]) + pos[q]);
+      float4 w = t.lap[q] ? __ldg(reinterpret_cast<const float4*>(t.lap[q]) + pos[q]) : zero;
+      if (!RES || q < nf) {
+        sx.x = fmaf(c, v.x, sx.x); sx.y = fmaf(c, v.y, sx.y); sx.z = fmaf(c, v.z, sx.z); sx.w = fmaf(c, v.w, sx.w);
         sl.x = fmaf(c, w.x, sl.x); sl.y = fmaf(c, w.y, sl.y); sl.z = fmaf(c, w.z, sl.z); sl.w = fmaf(c, w.w, sl.w);
+      } else {
+        rx = make_float4(c * v.x, c * v.y, c * v.z, c * v.w);
+        rl = make_float4(c * w.x, c * w.y, c * w.z, c * w.w);
       }
     }
   }
-  const D3 a = act(op, sx.x), b = act(op, sx.y), c = act(op, sx.z), d = act(op, sx.w);
-  st_stream(y + i, make_float4(a.y, b.y, c.y, d.y));
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int k = 0; k < K; ++k) {
-    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  const D3 a = act(fop, sx.x), b = act(fop, sx.y), c = act(fop, sx.z), d = act(fop, sx.w);
+  st_stream(y + i, make_float4(a.y + rx.x, b.y + rx.y, c.y + rx.z, d.y + rx.w));
+  float4 acc = zero;
+  // two Jacobian rows per trip: all their loads are issued before the first use
+  for (int k = 0; k < K; k += 2) {
+    float4 v[2][kMaxTerms];
 #pragma unroll
-    for (int q = 0; q < kMaxTerms; ++q) {
-      if (q < t.n && k < t.K[q]) {
-        const float cq = t.scale[q];
-        float4 v = __ldcs(reinterpret_cast<const float4*>(t.jac[q]) + (int64_t)k * t.js[q] + pos[q]);
-        s.x = fmaf(cq, v.x, s.x); s.y = fmaf(cq, v.y, s.y); s.z = fmaf(cq, v.z, s.z); s.w = fmaf(cq, v.w, s.w);
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+      for (int q = 0; q < kMaxTerms; ++q)
+        v[u][q] = (q < t.n && k + u < t.K[q])
+                      ? __ldcs(reinterpret_cast<const float4*>(t.jac[q]) + (int64_t)(k + u) * t.js[q] + pos[q])
+                      : zero;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (k + u < K) {
+        float4 s = zero, r = zero;
+#pragma unroll
+        for (int q = 0; q < kMaxTerms; ++q) {
+          const float cq = t.scale[q];  // 0 for the unused slots
+          const float4 w = v[u][q];
+          if (!RES || q < nf) {
+            s.x = fmaf(cq, w.x, s.x); s.y = fmaf(cq, w.y, s.y); s.z = fmaf(cq, w.z, s.z); s.w = fmaf(cq, w.w, s.w);
+          } else if (q < t.n) {
+            r = make_float4(cq * w.x, cq * w.y, cq * w.z, cq * w.w);
+          }
+        }
+        acc.x = fmaf(s.x, s.x, acc.x); acc.y = fmaf(s.y, s.y, acc.y);
+        acc.z = fmaf(s.z, s.z, acc.z); acc.w = fmaf(s.w, s.w, acc.w);
+        st_stream(jy + (int64_t)(k + u) * jys + i, make_float4(fmaf(a.d1, s.x, r.x), fmaf(b.d1, s.y, r.y),
+                                                               fmaf(c.d1, s.z, r.z), fmaf(d.d1, s.w, r.w)));
       }
     }
-    acc.x = fmaf(s.x, s.x, acc.x); acc.y = fmaf(s.y, s.y, acc.y);
-    acc.z = fmaf(s.z, s.z, acc.z); acc.w = fmaf(s.w, s.w, acc.w);
-    st_stream(jy + (int64_t)k * jys + i, make_float4(a.d1 * s.x, b.d1 * s.y, c.d1 * s.z, d.d1 * s.w));
   }
-  st_stream(ly + i, make_float4(fmaf(a.d2, acc.x, a.d1 * sl.x), fmaf(b.d2, acc.y, b.d1 * sl.y),
-                                fmaf(c.d2, acc.z, c.d1 * sl.z), fmaf(d.d2, acc.w, d.d1 * sl.w)));
+  st_stream(ly + i, make_float4(fmaf(a.d2, acc.x, fmaf(a.d1, sl.x, rl.x)), fmaf(b.d2, acc.y, fmaf(b.d1, sl.y, rl.y)),
+                                fmaf(c.d2, acc.z, fmaf(c.d1, sl.z, rl.z)), fmaf(d.d2, acc.w, fmaf(d.d1, sl.w, rl.w))));
 }
 
+template <bool RES>
 __global__ void __launch_bounds__(256)
-addn_scalar(int op, Terms t, float* __restrict__ y, float* __restrict__ jy, float* __restrict__ ly,
+addn_scalar(int fop, Terms t, float* __restrict__ y, float* __restrict__ jy, float* __restrict__ ly,
             int64_t jys, int K, int64_t n) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
+  const int nf = RES ? t.n - 1 : t.n;
   int64_t pos[kMaxTerms];
-  float sx = 0.f, sl = 0.f;
+  float sx = 0.f, sl = 0.f, rx = 0.f, rl = 0.f;
 #pragma unroll
   for (int q = 0; q < kMaxTerms; ++q) {
     if (q < t.n) {
       pos[q] = (t.mid[q] == 1) ? i : (i / (t.inner[q] * t.mid[q])) * t.inner[q] + i % t.inner[q];
-      sx = fmaf(t.scale[q], t.x[q][pos[q]], sx);
-      if (t.lap[q]) sl = fmaf(t.scale[q], t.lap[q][pos[q]], sl);
+      const float v = t.scale[q] * t.x[q][pos[q]];
+      const float w = t.lap[q] ? t.scale[q] * t.lap[q][pos[q]] : 0.f;
+      if (q < nf) { sx += v; sl += w; } else { rx = v; rl = w; }
     }
   }
-  const D3 a = act(op, sx);
-  y[i] = a.y;
+  const D3 a = act(fop, sx);
+  y[i] = a.y + rx;
   float acc = 0.f;
   for (int k = 0; k < K; ++k) {
-    float s = 0.f;
+    float s = 0.f, r = 0.f;
 #pragma unroll
     for (int q = 0; q < kMaxTerms; ++q)
-      if (q < t.n && k < t.K[q]) s = fmaf(t.scale[q], t.jac[q][(int64_t)k * t.js[q] + pos[q]], s);
+      if (q < t.n && k < t.K[q]) {
+        const float v = t.scale[q] * t.jac[q][(int64_t)k * t.js[q] + pos[q]];
+        if (q < nf) s += v; else r = v;
+      }
     acc = fmaf(s, s, acc);
-    jy[(int64_t)k * jys + i] = a.d1 * s;
+    jy[(int64_t)k * jys + i] = fmaf(a.d1, s, r);
   }
-  ly[i] = fmaf(a.d2, acc, a.d1 * sl);
+  ly[i] = fmaf(a.d2, acc, fmaf(a.d1, sl, rl));
 }
 
 }  // namespace
@@ -126,10 +156,12 @@ extern "C" int32_t fl_addn_elementwise(int32_t op, int32_t n_terms, const FlAddn
                                        float* jac_y, float* lap_y, int64_t K, int64_t N,
                                        int64_t jac_y_stride, void* stream) {
   using namespace fl;
-  FL_REQUIRE(op >= FL_ADDN_IDENTITY && op <= FL_ADDN_EXP, FL_EUNSUPPORTED,
+  FL_REQUIRE(op >= FL_ADDN_IDENTITY && op <= FL_ADDN_EXP_RESIDUAL, FL_EUNSUPPORTED,
              "fl_addn_elementwise: unknown op %d", op);
   FL_REQUIRE(n_terms >= 1 && n_terms <= kMaxTerms && terms, FL_EBADSHAPE,
              "fl_addn_elementwise: between 1 and %d terms", kMaxTerms);
+  FL_REQUIRE(op <= FL_ADDN_EXP || n_terms >= 2, FL_EBADSHAPE,
+             "fl_addn_elementwise: a residual form needs at least two terms");
   FL_REQUIRE(K >= 0 && N >= 0 && K < (1ll << 31) && (N + 255) / 256 < (1ll << 31), FL_EBADSHAPE,
              "fl_addn_elementwise: bad sizes");
   if (N == 0) return FL_OK;
@@ -154,14 +186,22 @@ extern "C" int32_t fl_addn_elementwise(int32_t op, int32_t n_terms, const FlAddn
     t.inner[q] = 1; t.mid[q] = 1; t.scale[q] = 0.f;
   }
   cudaStream_t st = (cudaStream_t)stream;
+  const bool res = op > FL_ADDN_EXP;
+  const int fop = res ? op - FL_ADDN_EXP : op;
   if (vec) {
     for (int q = 0; q < n_terms; ++q) { t.js[q] /= 4; t.inner[q] /= 4; }
     const int64_t n4 = N / 4;
-    addn_vec4<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(op, t, (float4*)y, (float4*)jac_y,
-                                                             (float4*)lap_y, jac_y_stride / 4, (int)K, n4);
+    const unsigned blocks = (unsigned)((n4 + 255) / 256);
+    if (res)
+      addn_vec4<true><<<blocks, 256, 0, st>>>(fop, t, (float4*)y, (float4*)jac_y, (float4*)lap_y,
+                                              jac_y_stride / 4, (int)K, n4);
+    else
+      addn_vec4<false><<<blocks, 256, 0, st>>>(fop, t, (float4*)y, (float4*)jac_y, (float4*)lap_y,
+                                               jac_y_stride / 4, (int)K, n4);
   } else {
-    addn_scalar<<<(unsigned)((N + 255) / 256), 256, 0, st>>>(op, t, y, jac_y, lap_y, jac_y_stride,
-                                                             (int)K, N);
+    const unsigned blocks = (unsigned)((N + 255) / 256);
+    if (res) addn_scalar<true><<<blocks, 256, 0, st>>>(fop, t, y, jac_y, lap_y, jac_y_stride, (int)K, N);
+    else addn_scalar<false><<<blocks, 256, 0, st>>>(fop, t, y, jac_y, lap_y, jac_y_stride, (int)K, N);
   }
   FL_CHECK_LAUNCH("fl_addn_elementwise launch");
   return FL_OK;

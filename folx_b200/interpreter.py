@@ -48,9 +48,9 @@ _CHAINABLE = frozenset({'tanh', 'silu', 'exp', 'log', 'sqrt', 'rsqrt', 'square',
 class LaplTensor:
     """A tensor seen by the traced function: value, Jacobian and Laplacian travel together."""
 
-    __slots__ = ('_arr', 'nb', 'thr', '_terms', '_chain')
+    __slots__ = ('_arr', 'nb', 'thr', '_terms', '_chain', '_act')
 
-    def __init__(self, arr: FwdLaplArray | None, nb: int, thr: int, terms=None, chain=None):
+    def __init__(self, arr: FwdLaplArray | None, nb: int, thr: int, terms=None, chain=None, act=None):
         # `terms` is a pending sum [(dense triplet or constant, +1 / -1), ...] that has not been
         # written out yet: a chain of additions is evaluated in one pass, together with the
         # elementwise function that consumes it if there is one (what XLA's fusion does for the
@@ -58,14 +58,18 @@ class LaplTensor:
         # `chain` is a pending chain of elementwise functions (source triplet, [(name, param), ...]):
         # consecutive scalar functions are evaluated by one pass over the triplet when the value is
         # first needed
-        self._arr, self.nb, self.thr, self._terms, self._chain = arr, nb, thr, terms, chain
+        # `act` = (name, residual) says that a function is applied to the pending sum; with
+        # `residual` the last term is added after the function (h + tanh(...)), all in one kernel
+        self._arr, self.nb, self.thr, self._terms, self._chain, self._act = arr, nb, thr, terms, chain, act
 
     @property
     def arr(self) -> FwdLaplArray:
         if self._arr is None:
             if self._terms is not None:
-                self._arr = kernels.addn(self._terms, 'identity')
+                key, residual = self._act or ('identity', False)
+                self._arr = kernels.addn(self._terms, key, residual=residual)
                 self._terms = None
+                self._act = None
             else:
                 src, ops = self._chain
                 if len(ops) == 1:  # a single function goes through its registered rule as usual
@@ -141,7 +145,7 @@ class LaplTensor:
     # ---- arithmetic ----
     def _dense_terms(self):
         """This tensor as a list of sum terms, or None if its Jacobian is sparse."""
-        if self._terms is not None:
+        if self._terms is not None and self._act is None:
             return list(self._terms)
         arr = self.arr
         return None if arr.jacobian.weak else [(arr, 1.0)]
@@ -150,6 +154,17 @@ class LaplTensor:
         """`a + b` / `a - b` of dense operands becomes a pending sum instead of a kernel launch."""
         if op not in ('add', 'sub') or reverse or not registry.is_builtin(op):
             return None
+        if (self._terms is not None and self._act is not None and not self._act[1]
+                and len(self._terms) < 5 and isinstance(other, LaplTensor) and other.nb == self.nb
+                and other.ndim == self.ndim):
+            # f(pending sum) + residual: the residual joins the same kernel as its last term
+            theirs = other._dense_terms()
+            if (theirs is not None and len(theirs) == 1
+                    and tuple(theirs[0][0].x.shape) == tuple(self._x_like().shape)):
+                t, s0 = theirs[0]
+                sign = s0 if op == 'add' else -s0
+                return LaplTensor(None, self.nb, self.thr, terms=self._terms + [(t, sign)],
+                                  act=(self._act[0], True))
         mine = self._dense_terms()
         if mine is None:
             return None
@@ -258,9 +273,11 @@ class LaplTensor:
         return self._wrap(_call('dot_general', (W, self.arr), {}, self.thr))
 
     def _unary(self, key: str):
-        if self._terms is not None and key in ('tanh', 'silu', 'exp') and registry.is_builtin(key):
-            # pending sum + elementwise function: one fused pass
-            return LaplTensor(kernels.addn(self._terms, key), self.nb, self.thr)
+        if (self._terms is not None and self._act is None and key in ('tanh', 'silu', 'exp')
+                and registry.is_builtin(key)):
+            # pending sum + elementwise function: one fused pass, still pending so that a residual
+            # connection added next can join it
+            return LaplTensor(None, self.nb, self.thr, terms=self._terms, act=(key, False))
         if key in _CHAINABLE and registry.is_builtin(key):
             # scalar functions stay pending so that a run of them becomes one pass
             if self._arr is None and self._chain is not None and len(self._chain[1]) < 4:
@@ -486,7 +503,7 @@ def _solve(A, b):
 def _layer_norm(x, normalized_shape, weight=None, bias=None, eps=1e-5):
     if len(tuple(normalized_shape)) != 1:
         raise NotImplementedError('layer_norm on triplets normalises the last axis only')
-    terms = x._terms if x._arr is None and x._terms is not None else None
+    terms = x._terms if x._arr is None and x._terms is not None and x._act is None else None
     if (terms is not None and len(terms) == 2 and registry.is_builtin('layer_norm')
             and all(isinstance(t, FwdLaplArray) and t.x.shape == terms[0][0].x.shape for t, _ in terms)
             and terms[0][1] == 1.0 and x.shape[-1] % 128 == 0 and x.shape[-1] <= 1024

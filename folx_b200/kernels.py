@@ -395,8 +395,9 @@ def local_energy(lap: torch.Tensor, jac: torch.Tensor, pot: torch.Tensor | None 
     return energy, sums
 
 
-def addn(terms, op: str = 'identity') -> FwdLaplArray:
+def addn(terms, op: str = 'identity', residual: bool = False) -> FwdLaplArray:
     """``f(sum_t scale_t * a_t)`` in one pass; ``terms`` is a list of ``(operand, scale)``.
+    With ``residual`` the last term stays outside the function: ``f(sum of the others) + last``.
 
     Operands are dense triplets or plain tensors (constants).  The first operand must have the
     output shape; the others may be smaller along one run of axes (see ``binary``).  Triplets may
@@ -437,7 +438,10 @@ def addn(terms, op: str = 'identity') -> FwdLaplArray:
             keep.append(x)
             arr[q] = lib.FlAddnTerm(x.data_ptr(), 0, 0, 0, 0, run[0], run[1], float(scale))
     out = alloc_triplet(K, shape, dev, None)
-    lib.call('fl_addn_elementwise', lib.ADDN_OPS[op], len(terms), arr, _ptr(out.x),
+    code = lib.ADDN_OPS[op] + (3 if residual else 0)
+    if residual and (op == 'identity' or len(terms) < 2):
+        raise ValueError('addn: a residual form needs a function and at least two terms')
+    lib.call('fl_addn_elementwise', code, len(terms), arr, _ptr(out.x),
              _ptr(out.jacobian.data), _ptr(out.laplacian), K, N, _jac_stride(out.jacobian.data),
              _stream(dev))
     return out

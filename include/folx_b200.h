@@ -116,9 +116,14 @@ int32_t fl_binary(int32_t op,
  * output (rows >= K are zero: a dense Jacobian truncated at its highest input,
  * folx/api.py:182-196) and may be broadcast like operand b of fl_binary (inner, mid).
  * `terms` is a HOST array; its pointers are device pointers.
+ * The *_RESIDUAL forms keep the LAST term outside the function, y = f(sum of the others) + last:
+ * the residual connection h + tanh(...) of a layer, one more `add` rule in the reference.
  * ------------------------------------------------------------------------------------------- */
-#define FL_ADDN_MAX_TERMS 4
-enum { FL_ADDN_IDENTITY = 0, FL_ADDN_TANH = 1, FL_ADDN_SILU = 2, FL_ADDN_EXP = 3 };
+#define FL_ADDN_MAX_TERMS 5
+enum {
+  FL_ADDN_IDENTITY = 0, FL_ADDN_TANH = 1, FL_ADDN_SILU = 2, FL_ADDN_EXP = 3,
+  FL_ADDN_TANH_RESIDUAL = 4, FL_ADDN_SILU_RESIDUAL = 5, FL_ADDN_EXP_RESIDUAL = 6
+};
 
 typedef struct FlAddnTerm {
   const float* x;

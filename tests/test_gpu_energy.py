@@ -35,7 +35,8 @@ def test_harness_chunking_is_transparent(cuda_device):
     e_all, s_all = harness.local_energy_sums(f, r, pot, sparsity_threshold=6)
     e_chk, s_chk = harness.local_energy_sums(f, r, pot, sparsity_threshold=6, chunk=3)
     torch.testing.assert_close(e_all, e_chk, rtol=1e-5, atol=1e-5)
-    torch.testing.assert_close(s_all, s_chk, rtol=1e-6, atol=1e-6)
+    # different chunk sizes may take differently tiled kernels (fp32 round-off at the 1e-6 level)
+    torch.testing.assert_close(s_all, s_chk, rtol=1e-5, atol=1e-5)
     mean, var, n = harness.reduce_energy(s_all)
     assert int(n) == 10
     torch.testing.assert_close(mean, e_all.double().mean(), rtol=1e-6, atol=1e-6)

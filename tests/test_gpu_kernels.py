@@ -259,6 +259,22 @@ def test_addn_fused_sum_and_activation(cuda_device, op):
     assert_close(to_host(got), want)
 
 
+@pytest.mark.parametrize('op', ['tanh', 'silu', 'exp'])
+@pytest.mark.parametrize('shape,sign', [((3, 6, 8), 1.0), ((5, 7), -1.0)])
+def test_addn_with_residual(cuda_device, op, shape, sign):
+    """f(a + b + bias) + sign * h in one pass: the residual stays outside the function."""
+    a = seeded_triplet(7, shape, seed=25, scale=0.3)
+    b = seeded_triplet(4, shape, seed=26, scale=0.3)
+    h = seeded_triplet(6, shape, seed=27)
+    bias = seeded_triplet(0, shape[-1:], seed=28)[0]
+    got = kernels.addn([(to_device(a, cuda_device), 1.0), (to_device(b, cuda_device), 1.0),
+                        (bias.float().to(cuda_device), 1.0), (to_device(h, cuda_device), sign)], op, residual=True)
+    pad = lambda t: (t[0], torch.cat([t[1], torch.zeros(7 - t[1].shape[0], *t[1].shape[1:], dtype=t[1].dtype)]), t[2])
+    s = rules.binary('add', rules.binary('add', a, pad(b)), rules.constant(torch.broadcast_to(bias, shape), 7))
+    want = rules.binary('add' if sign > 0 else 'sub', rules.elementwise(op, s), pad(h))
+    assert_close(to_host(got), want)
+
+
 @pytest.mark.parametrize('K,K2,P,F,scale', [(6, 6, 9, 256, 1.0), (7, 3, 5, 128, -1.0), (0, 0, 4, 384, 1.0),
                                             (19, 6, 7, 256, 1.0), (10, 10, 3, 512, -1.0)])
 def test_add_layernorm_fused(cuda_device, K, K2, P, F, scale):
