@@ -8,6 +8,14 @@ synthetic triplets; `value` is samples (walker-Laplacians) per second over all r
 inputs already in HBM; `e2e` is the same through host buffers (H2D of the inputs and D2H of the
 result inside the timed region).  `--impl reference` times the CPU restatement of the reference's
 rules (the reference itself is pure Python on JAX, which is not installed on these machines).
+
+Workloads: `operators` (default; the operator microbench: dot_general, tanh, silu, LayerNorm as
+single launches on a dense and on a sparse Jacobian), `mlp`, `ferminet`, `psiformer`, `psiformer64`
+(whole wavefunctions through the front end with CUDA-graph replay), and the single-kernel profiling
+cases `attention`, `slogdet`, `gather`.  Environment switches, all off by default:
+FOLX_B200_CHAIN=1 (tanh + silu as one launch), FOLX_B200_NO_GRAPH=1 (no graph replay in the model
+workloads), FOLX_B200_E2E_SLICES=n (sample slices of the end-to-end pipeline),
+FOLX_B200_MEASURE_TF32=1 (time a library TF32 GEMM beside the run).
 """
 
 from __future__ import annotations
