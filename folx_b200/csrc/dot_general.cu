@@ -65,8 +65,63 @@ extern "C" int32_t fl_dot_general(const float* x, const float* jac, const float*
       FL_REQUIRE(tc_ok, FL_EUNSUPPORTED,
                  "fl_dot_general: tensor-core kernel forced but shape/workspace unsuitable");
     int32_t rc = use_tc ? gemm_tc(p.a, p.rows, F_in, F_out, workspace, bias, p.bias_rows, p.o,
-                                  status, g_mode == 3 ? 1 : (g_mode == 4 ? 2 : 0), st)
+                                  status, g_mode == 3 ? 1 : (g_mode == 4 ? 2 : 0), 0, 0, st)
                         : gemm_ffma(p.a, p.rows, F_in, F_out, W, bias, p.bias_rows, p.o, st);
+    if (rc != FL_OK) return rc;
+  }
+  return FL_OK;
+}
+
+// The same product for a triplet that is a SLICE of a larger one (say the spin-up electrons of
+// every walker): x, every Jacobian row and lap consist of P / group_rows groups of group_rows
+// contiguous rows, group_stride elements apart, and are read in place through a 3-D tensor map.
+// Tensor-core kernel only: FL_EUNSUPPORTED tells the caller to make the triplet contiguous and use
+// fl_dot_general.
+extern "C" int32_t fl_dot_general_grouped(const float* x, const float* jac, const float* lap,
+                                          int64_t P, int64_t K, int64_t jac_stride, int64_t F_in,
+                                          int64_t F_out, int64_t group_rows, int64_t group_stride,
+                                          const float* bias, const void* workspace,
+                                          int64_t workspace_bytes, float* y, float* jac_y,
+                                          float* lap_y, int32_t* status, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(P >= 0 && K >= 0 && F_in > 0 && F_out > 0 && group_rows > 0, FL_EBADSHAPE,
+             "fl_dot_general_grouped: bad sizes P=%lld K=%lld F_in=%lld F_out=%lld group_rows=%lld",
+             (long long)P, (long long)K, (long long)F_in, (long long)F_out, (long long)group_rows);
+  if (P == 0) return FL_OK;
+  FL_REQUIRE(x && lap && y && lap_y && (K == 0 || (jac && jac_y)), FL_EBADSHAPE,
+             "fl_dot_general_grouped: null pointer");
+  FL_REQUIRE(P % group_rows == 0 && 128 % group_rows == 0 && group_stride >= group_rows * F_in,
+             FL_EUNSUPPORTED, "fl_dot_general_grouped: groups of %lld rows are not supported",
+             (long long)group_rows);
+  const int64_t groups = P / group_rows;
+  FL_REQUIRE(K <= 1 || jac_stride == groups * group_stride, FL_EUNSUPPORTED,
+             "fl_dot_general_grouped: Jacobian rows must continue the group pattern");
+  FL_REQUIRE(workspace != nullptr && workspace_bytes >= wsplit_geom(F_in, F_out).bytes && F_in >= 16 &&
+                 F_out >= 16 && g_mode != 1,
+             FL_EUNSUPPORTED, "fl_dot_general_grouped: needs the tensor-core path");
+  cudaStream_t st = (cudaStream_t)stream;
+  // pieces x, J, lap; adjacent pieces that continue the group pattern (and whose outputs are
+  // adjacent) run as one launch -- the usual stacked layout is a single product
+  struct Piece { const float* a; float* o; int64_t groups; int64_t bias_rows; };
+  Piece pieces[3] = {{x, y, groups, bias ? P : 0}, {jac, jac_y, K * groups, 0}, {lap, lap_y, groups, 0}};
+  Piece merged[3];
+  int n = 0;
+  for (int i = 0; i < 3; ++i) {
+    if (pieces[i].groups == 0) continue;
+    if (n > 0 && merged[n - 1].a + merged[n - 1].groups * group_stride == pieces[i].a &&
+        merged[n - 1].o + merged[n - 1].groups * group_rows * F_out == pieces[i].o) {
+      merged[n - 1].groups += pieces[i].groups;
+    } else {
+      merged[n++] = pieces[i];
+    }
+  }
+  for (int i = 0; i < n; ++i) {
+    const Piece& p = merged[i];
+    const int64_t rows = p.groups * group_rows;
+    FL_REQUIRE(gemm_tc_supported(p.a, rows, F_in, F_out, p.o), FL_EUNSUPPORTED,
+               "fl_dot_general_grouped: shape or alignment does not fit the tensor-core kernel");
+    int32_t rc = gemm_tc(p.a, rows, F_in, F_out, workspace, bias, p.bias_rows, p.o, status,
+                         g_mode == 3 ? 1 : (g_mode == 4 ? 2 : 0), group_rows, group_stride, st);
     if (rc != FL_OK) return rc;
   }
   return FL_OK;

@@ -24,10 +24,11 @@ int32_t gemm_ffma(const float* A, int64_t M, int64_t Kc, int64_t N, const float*
 bool gemm_tc_supported(const float* A, int64_t M, int64_t Kc, int64_t N, const float* Y);
 
 // tcgen05 3xTF32 kernel reading the split W from `workspace`.  ctas: 0 = pick (CTA pairs sharing W
-// when there are at least two row tiles), 1 = one CTA per tile, 2 = require pairs.
+// when there are at least two row tiles), 1 = one CTA per tile, 2 = require pairs.  group_rows > 0:
+// the rows of A are groups of group_rows contiguous rows, group_stride elements apart.
 int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* workspace,
                 const float* bias, int64_t bias_rows, float* Y, int32_t* status, int ctas,
-                cudaStream_t st);
+                int64_t group_rows, int64_t group_stride, cudaStream_t st);
 
 // Splits W into TF32 head/tail, transposed and padded, into `workspace`.
 int32_t gemm_tc_prepare(const float* W, int64_t Kc, int64_t N, void* workspace, cudaStream_t st);

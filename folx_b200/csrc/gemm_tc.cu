@@ -122,6 +122,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+// A given as groups of rows: coordinates (column, row inside the group, group)
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
                "r"(src), "r"(x), "r"(y)
@@ -277,7 +287,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmWlo, const __grid_constant__ CUtensorMap tmY,
                const float* __restrict__ bias, int64_t bias_rows, int num_m_tiles, int num_k_steps,
                int n_tile, int n_chunks, int n_total, float* __restrict__ Y, int64_t M_rows,
-               int32_t* __restrict__ status) {
+               int32_t* __restrict__ status, int a_groups_per_tile) {
+  // a_groups_per_tile > 0: A is a 3-D map (columns, rows of a group, groups) whose groups of
+  // 128 / a_groups_per_tile contiguous rows lie a fixed stride apart (a slice of a larger
+  // triplet read in place); 0: A is a plain 2-D map.
   using G = Geom<CTAS>;
   constexpr int STAGES = G::STAGES;
   constexpr int STAGE_BYTES = G::STAGE_BYTES;
@@ -351,7 +364,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint8_t* sb = smem + stage * STAGE_BYTES;
           const uint32_t bar = smem_u32(&ctrl->full[stage]);
           mbar_expect_tx(bar, stage_bytes_tx);
-          tma_load_2d(smem_u32(sb), &tmA, ks * BLOCK_K, m_tile * BLOCK_M, bar);
+          if (a_groups_per_tile > 0)
+            tma_load_3d(smem_u32(sb), &tmA, ks * BLOCK_K, 0, m_tile * a_groups_per_tile, bar);
+          else
+            tma_load_2d(smem_u32(sb), &tmA, ks * BLOCK_K, m_tile * BLOCK_M, bar);
           const int w_row0 = n_chunk * n_tile + (int)rank * w_rows;
           tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES), &tmWhi, ks * BLOCK_K, w_row0, bar);
           tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES), &tmWlo, ks * BLOCK_K, w_row0,
@@ -614,6 +630,24 @@ int32_t make_map(CUtensorMap* m, const void* base, int64_t rows, int64_t cols, i
   return FL_OK;
 }
 
+// A as n_groups groups of group_rows contiguous rows of `cols` fp32, group_stride elements apart:
+// 3-D map (cols, group_rows, n_groups) with a box of (16, group_rows, 128 / group_rows), which
+// lands in shared memory as the same 128 x 16 tile the 2-D map produces.
+int32_t make_map_grouped(CUtensorMap* m, const void* base, int64_t n_groups, int64_t group_rows,
+                         int64_t cols, int64_t group_stride) {
+  EncodeTiledFn enc = get_encode();
+  FL_REQUIRE(enc != nullptr, FL_ECUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[3] = {(cuuint64_t)cols, (cuuint64_t)group_rows, (cuuint64_t)n_groups};
+  cuuint64_t gstride[2] = {(cuuint64_t)cols * 4, (cuuint64_t)group_stride * 4};
+  cuuint32_t box[3] = {(cuuint32_t)BLOCK_K, (cuuint32_t)group_rows, (cuuint32_t)(BLOCK_M / group_rows)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), gdim, gstride, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  FL_REQUIRE(r == CUDA_SUCCESS, FL_ECUDA, "cuTensorMapEncodeTiled(A, grouped) failed with %d", (int)r);
+  return FL_OK;
+}
+
 }  // namespace
 
 WSplitGeom wsplit_geom(int64_t F_in, int64_t F_out) {
@@ -685,7 +719,13 @@ int max_pair_clusters() {
 
 int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* workspace,
                 const float* bias, int64_t bias_rows, float* Y, int32_t* status, int ctas,
-                cudaStream_t st) {
+                int64_t group_rows, int64_t group_stride, cudaStream_t st) {
+  // group_rows > 0: the M rows of A come in groups of group_rows contiguous rows, group_stride
+  // elements apart (group_rows divides 128 and M); 0: A is contiguous
+  FL_REQUIRE(group_rows == 0 || (group_rows > 0 && BLOCK_M % group_rows == 0 && M % group_rows == 0 &&
+                                 group_stride >= group_rows * Kc && group_stride % 4 == 0),
+             FL_EUNSUPPORTED, "tensor-core GEMM: row groups of %lld rows (stride %lld) are not supported",
+             (long long)group_rows, (long long)group_stride);
   FL_REQUIRE(gemm_tc_supported(A, M, Kc, N, Y), FL_EUNSUPPORTED,
              "tensor-core GEMM needs F_in %% 4 == 0, F_out %% 4 == 0 and 16-byte aligned buffers");
   FL_REQUIRE(aligned16(workspace), FL_EBADSHAPE, "dot_general workspace must be 16-byte aligned");
@@ -711,7 +751,12 @@ int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* wo
   const int w_box_rows = (int)g.n_tile / (pair ? 2 : 1);
   CUtensorMap tmA, tmWhi, tmWlo, tmY;
   int32_t rc;
-  if ((rc = make_map(&tmA, A, M, Kc, Kc, BLOCK_M, BLOCK_K, "A")) != FL_OK) return rc;
+  if (group_rows > 0)
+    rc = make_map_grouped(&tmA, A, M / group_rows, group_rows, Kc, group_stride);
+  else
+    rc = make_map(&tmA, A, M, Kc, Kc, BLOCK_M, BLOCK_K, "A");
+  if (rc != FL_OK) return rc;
+  const int a_groups_per_tile = group_rows > 0 ? (int)(BLOCK_M / group_rows) : 0;
   if ((rc = make_map(&tmWhi, whi, wrows, g.k_pad, g.k_pad, w_box_rows, BLOCK_K, "W_hi")) != FL_OK) return rc;
   if ((rc = make_map(&tmWlo, wlo, wrows, g.k_pad, g.k_pad, w_box_rows, BLOCK_K, "W_lo")) != FL_OK) return rc;
   if ((rc = make_map(&tmY, Y, M, N, N, 32, 32, "Y")) != FL_OK) return rc;
@@ -734,13 +779,13 @@ int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* wo
     cfg.numAttrs = 1;
     FL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<2>, tmA, tmWhi, tmWlo, tmY, bias, bias_rows,
                                groups, num_k_steps, (int)g.n_tile, (int)g.n_chunks, (int)N, Y, M,
-                               status));
+                               status, a_groups_per_tile));
   } else {
     const int64_t tiles = (int64_t)num_m_tiles * g.n_chunks;
     int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     gemm_tc_kernel<1><<<grid, NUM_THREADS, Geom<1>::SMEM_BYTES, st>>>(
         tmA, tmWhi, tmWlo, tmY, bias, bias_rows, num_m_tiles, num_k_steps, (int)g.n_tile,
-        (int)g.n_chunks, (int)N, Y, M, status);
+        (int)g.n_chunks, (int)N, Y, M, status, a_groups_per_tile);
   }
   FL_CHECK_LAUNCH("gemm_tc launch");
   return FL_OK;

@@ -218,9 +218,75 @@ def check_gemm_status(device) -> None:
         raise lib.FolxB200Error('fl_dot_general', code, 'a bounded wait inside the kernel ran out')
 
 
+def _row_groups(x: torch.Tensor, j: torch.Tensor, l: torch.Tensor, F_in: int):
+    """``(group_rows, group_stride, n_groups)`` if ``x`` -- and, with the same strides, every
+    Jacobian row and ``l`` -- is a non-contiguous view made of equally spaced groups of contiguous
+    rows (a slice along one leading axis of a contiguous tensor), else None."""
+    if x.ndim < 2 or x.stride(-1) != 1 or x.is_contiguous() or x.numel() == 0:
+        return None
+    lead, st = list(x.shape[:-1]), list(x.stride()[:-1])
+    g, d = 1, len(lead) - 1
+    while d >= 0 and (lead[d] == 1 or st[d] == g * F_in):
+        g *= lead[d]
+        d -= 1
+    if d < 0:
+        return None
+    gs, n, e = st[d], lead[d], d - 1
+    while e >= 0:
+        if lead[e] != 1 and st[e] != gs * n:
+            return None
+        n *= lead[e]
+        e -= 1
+    if 128 % g or gs % 4 or gs < g * F_in:
+        return None
+    same = lambda shape, strides: tuple(shape) == tuple(x.shape) and all(
+        a == b or m == 1 for a, b, m in zip(strides, x.stride(), x.shape))
+    if not same(l.shape, l.stride()) or not same(j.shape[1:], j.stride()[1:]):
+        return None
+    if j.shape[0] > 1 and j.stride(0) != n * gs:
+        return None
+    return g, gs, n
+
+
+def _dot_general_in_place(a: FwdLaplArray, W, bias, x0_idx):
+    """The product of a sliced triplet read where it lies (``fl_dot_general_grouped``), or None
+    when the view, the shape or the library mode does not allow it."""
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    if not (x.is_cuda and W.ndim == 2):
+        return None
+    F_in, F_out = W.shape
+    if x.shape[-1] != F_in or F_in < 16 or F_out < 16 or F_in % 4 or F_out % 4:
+        return None
+    pattern = _row_groups(x, j, l, F_in)
+    if pattern is None:
+        return None
+    g, gs, n = pattern
+    W = W.contiguous()
+    _require_cuda(x, j, l, W, bias)
+    K = j.shape[0]
+    P = n * g
+    out = alloc_triplet(K, (*x.shape[:-1], F_out), x.device, x0_idx)
+    ws = _weights.get(W)
+    try:
+        lib.call(
+            'fl_dot_general_grouped', _ptr(x), _ptr(j), _ptr(l), P, K, n * gs, F_in, F_out, g, gs,
+            _ptr(bias.contiguous() if bias is not None else None), _ptr(ws), ws.numel(),
+            _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), _ptr(gemm_status(x.device)),
+            _stream(x.device),
+        )
+    except lib.FolxB200Error as e:
+        if e.code == lib.FL_EUNSUPPORTED:
+            return None
+        raise
+    return out
+
+
 def dot_general(a: FwdLaplArray, W: torch.Tensor, bias: torch.Tensor | None = None,
                 x0_idx: np.ndarray | None = None) -> FwdLaplArray:
     """y = x @ W (+ bias) over the last axis of a triplet (folx/wrapped_functions.py:71-171)."""
+    sliced = _dot_general_in_place(a, W, bias, x0_idx)
+    if sliced is not None:
+        return sliced
     a = as_contiguous(a)
     x, j, l = a.x, a.jacobian.data, a.laplacian
     W = W.contiguous()

@@ -173,6 +173,25 @@ int32_t fl_dot_general(const float* x, const float* jac, const float* lap,
                        float* y, float* jac_y, float* lap_y,
                        int32_t* status, void* stream);
 
+/* fl_dot_general for a triplet that is a SLICE of a larger one (the reference slices with
+ * ordinary indexing rules, folx/wrapped_functions.py:457-508, and XLA fuses the slice into the
+ * product): x, every Jacobian row and lap consist of P / group_rows groups of group_rows
+ * contiguous rows of F_in values, group_stride elements apart (e.g. the first 8 of 16 electrons of
+ * every walker: group_rows = 8, group_stride = 16 F_in); jac_stride is the distance between
+ * Jacobian rows and must continue the pattern (jac_stride = (P / group_rows) group_stride).
+ * The operand is read in place through a 3-D tensor map; outputs are dense ([P][F_out] per row).
+ * Tensor-core path only (group_rows divides 128, F_in, F_out >= 16 and multiples of 4, prepared
+ * workspace): FL_EUNSUPPORTED otherwise, and the caller falls back to a contiguous copy and
+ * fl_dot_general. */
+int32_t fl_dot_general_grouped(const float* x, const float* jac, const float* lap,
+                               int64_t P, int64_t K, int64_t jac_stride,
+                               int64_t F_in, int64_t F_out,
+                               int64_t group_rows, int64_t group_stride,
+                               const float* bias,
+                               const void* workspace, int64_t workspace_bytes,
+                               float* y, float* jac_y, float* lap_y,
+                               int32_t* status, void* stream);
+
 /* Selects the GEMM implementation: 0 = automatic (tensor-core path when the shape allows),
  * 1 = force the CUDA-core fp32 kernel, 2 = force the tensor-core kernel (FL_EUNSUPPORTED if the
  * shape does not fit), 3 = tensor-core kernel with one CTA per row tile, 4 = tensor-core kernel

@@ -4,6 +4,7 @@ contiguous triplets and over slices / permutations of one, against the oracle.""
 import pytest
 import torch
 
+from folx_b200 import kernels, lib
 from folx_b200 import rules as dev_rules
 from folx_b200.api import FwdJacobian, FwdLaplArray
 from oracle import rules
@@ -58,3 +59,24 @@ def test_dot_general_of_two_triplets(cuda_device, K, sa, sb):
     a, b = seeded_triplet(K, sa, seed=51), seeded_triplet(K, sb, seed=52)
     got = dev_rules.dot_general_pair(to_device(a, cuda_device), to_device(b, cuda_device))
     assert_close(to_host(got), rules.dot_general_pair(a, b))
+
+
+@pytest.mark.parametrize('stacked', [True, False])
+@pytest.mark.parametrize('n_el,lo,hi,F_in,F_out', [(16, 0, 8, 64, 48), (16, 8, 16, 64, 48), (12, 4, 8, 32, 256),
+                                                  (32, 16, 32, 256, 64), (10, 0, 5, 64, 32)])
+def test_dot_general_reads_a_slice_in_place(cuda_device, stacked, n_el, lo, hi, F_in, F_out):
+    """The product of `h[:, lo:hi]` (a spin block of every walker) without a staging copy; group
+    sizes that do not divide 128 (the last case) fall back to the contiguous path."""
+    K, B = 7, 6
+    t = seeded_triplet(K, (B, n_el, F_in), seed=61)
+    g = torch.Generator().manual_seed(62)
+    W = (torch.randn(F_in, F_out, generator=g, dtype=torch.float64) / F_in**0.5).float().double()
+    bias = (torch.randn(F_out, generator=g, dtype=torch.float64) * 0.1).float().double()
+    index = (slice(None), slice(lo, hi), slice(None))
+    a = view_of(to_device(t, cuda_device, stacked=stacked), index)
+    before = lib.LAUNCH_COUNTS.get('fl_dot_general_grouped', 0)
+    got = kernels.dot_general(a, W.float().to(cuda_device), bias.float().to(cuda_device))
+    kernels.check_gemm_status(cuda_device)
+    assert_close(to_host(got), rules.dot_general(host_view(t, index), W, bias))
+    in_place = 128 % (hi - lo) == 0
+    assert lib.LAUNCH_COUNTS.get('fl_dot_general_grouped', 0) == before + (1 if in_place else 0)
