@@ -34,13 +34,22 @@ __device__ __forceinline__ void group_sync() {
   }
 }
 
+// Where matrix m of the batch starts and how far its rows are apart: matrix m = (o, i) with
+// i = m mod inner sits at o * outer_stride + i * inner_stride, rows row_stride apart.  Contiguous
+// matrices are inner = 1, outer_stride = n * n, row_stride = n; a view such as the
+// (walker, determinant, electron, orbital) permutation of a (walker, electron, determinant x
+// orbital) product is read in place.
+struct MatLayout {
+  int64_t inner, outer_stride, inner_stride, row_stride;
+};
+
 // N: padded matrix size, TR x TC: per-thread tile of M (TR * TC == 8), G = N*N/8 threads per matrix.
 template <int N, int TR, int TC>
 __global__ void __launch_bounds__(kBlock)
 slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
                const float* __restrict__ lapA, int64_t n_mat, int K, int64_t js, int n,
                float* __restrict__ sign_out, float* __restrict__ logdet_out,
-               float* __restrict__ J_out, int64_t jos, float* __restrict__ lap_out) {
+               float* __restrict__ J_out, int64_t jos, float* __restrict__ lap_out, MatLayout lay) {
   constexpr int G = N * N / 8;
   constexpr int MPB = kBlock / G;  // matrices per block
   constexpr int P = N + 4;         // smem pitch (keeps rows 16-byte aligned)
@@ -57,15 +66,19 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
   const int64_t m = (int64_t)blockIdx.x * MPB + g;
   const bool live = m < n_mat;  // dead groups still take part in block-wide syncs
   const int64_t mm = live ? m : 0;
-  const int nn = n * n;
+  const int64_t rs = lay.row_stride;
+  // offset of this group's matrix inside x / one Jacobian row / lap
+  const int64_t mat_off = (mm / lay.inner) * lay.outer_stride + (mm % lay.inner) * lay.inner_stride;
   const bool vec = (n == N) && ((js & 3) == 0) &&
+                   (((rs | lay.outer_stride | lay.inner_stride) & 3) == 0) &&
                    ((reinterpret_cast<uintptr_t>(J) | reinterpret_cast<uintptr_t>(A) |
                      reinterpret_cast<uintptr_t>(lapA)) & 15) == 0;
 
   // The 8 matrix elements e = 8 t .. 8 t + 7 of the PADDED N x N matrix this thread moves.
   auto load8 = [&](const float* base, float (&r)[8], float diag_fill) {
     if (vec) {
-      const float4* p = reinterpret_cast<const float4*>(base) + 2 * t;
+      const int e = 8 * t, i = e / N, j = e % N;  // the 8 elements stay inside one row (N % 8 == 0)
+      const float4* p = reinterpret_cast<const float4*>(base + i * rs + j);
       float4 a = __ldcs(p), b = __ldcs(p + 1);
       r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
       r[4] = b.x; r[5] = b.y; r[6] = b.z; r[7] = b.w;
@@ -73,7 +86,7 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
         int e = 8 * t + q, i = e / N, j = e % N;
-        r[q] = (i < n && j < n) ? base[i * n + j] : (i == j ? diag_fill : 0.f);
+        r[q] = (i < n && j < n) ? base[i * rs + j] : (i == j ? diag_fill : 0.f);
       }
     }
   };
@@ -86,7 +99,7 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
 
   // ---------------- phase 1: A^-1, sign, log|det| by Gauss-Jordan with partial pivoting --------
   float r8[8];
-  load8(A + mm * nn, r8, 1.f);
+  load8(A + mat_off, r8, 1.f);
   store8(buf, r8);
   {
     float id[8];
@@ -170,14 +183,14 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
   float lap_part = 0.f;
   {
     float l8[8];
-    load8(lapA + mm * nn, l8, 0.f);
+    load8(lapA + mat_off, l8, 0.f);
 #pragma unroll
     for (int q = 0; q < 8; ++q) lap_part = fmaf(w[q], l8[q], lap_part);
   }
 
   float trmm = 0.f;  // this thread's share of sum_k tr(M_k M_k)
   float pre[2][8];
-  const float* Jm = J + mm * nn;
+  const float* Jm = J + mat_off;
   if (K > 0) load8(Jm, pre[0], 0.f);
   if (K > 1) load8(Jm + js, pre[1], 0.f);
 
@@ -266,7 +279,7 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
 template <int N, int TR, int TC>
 int32_t launch(const float* A, const float* J, const float* lapA, int64_t n_mat, int64_t K,
                int64_t js, int n, float* sign, float* logdet, float* J_out, int64_t jos,
-               float* lap_out, cudaStream_t st) {
+               float* lap_out, MatLayout lay, cudaStream_t st) {
   constexpr int G = N * N / 8;
   constexpr int MPB = kBlock / G;
   constexpr int P = N + 4;
@@ -280,11 +293,20 @@ int32_t launch(const float* A, const float* J, const float* lapA, int64_t n_mat,
   int64_t blocks = (n_mat + MPB - 1) / MPB;
   FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_slogdet: too many matrices");
   slogdet_kernel<N, TR, TC><<<(unsigned)blocks, kBlock, smem, st>>>(
-      A, J, lapA, n_mat, (int)K, js, n, sign, logdet, J_out, jos, lap_out);
+      A, J, lapA, n_mat, (int)K, js, n, sign, logdet, J_out, jos, lap_out, lay);
   FL_CHECK_LAUNCH("fl_slogdet launch");
   return FL_OK;
 }
 
+}  // namespace
+}  // namespace fl
+
+namespace fl {
+namespace {
+int32_t run_slogdet(const char* who, const float* A, const float* jac, const float* lap,
+                    int64_t n_mat, int64_t n, int64_t K, int64_t jac_stride, float* sign,
+                    float* logdet, float* jac_out, int64_t jac_out_stride, float* lap_out,
+                    MatLayout lay, cudaStream_t st);
 }  // namespace
 }  // namespace fl
 
@@ -293,22 +315,50 @@ extern "C" int32_t fl_slogdet(const float* A, const float* jac, const float* lap
                               float* logdet, float* jac_out, int64_t jac_out_stride,
                               float* lap_out, void* stream) {
   using namespace fl;
+  FL_REQUIRE(K <= 1 || jac_stride >= n_mat * n * n, FL_EBADSHAPE,
+             "fl_slogdet: Jacobian row stride too small");
+  return run_slogdet("fl_slogdet", A, jac, lap, n_mat, n, K, jac_stride, sign, logdet, jac_out,
+                     jac_out_stride, lap_out, MatLayout{1, n * n, 0, n}, (cudaStream_t)stream);
+}
+
+extern "C" int32_t fl_slogdet_strided(const float* A, const float* jac, const float* lap,
+                                      int64_t n_mat, int64_t n, int64_t K, int64_t jac_stride,
+                                      int64_t inner, int64_t outer_stride, int64_t inner_stride,
+                                      int64_t row_stride, float* sign, float* logdet,
+                                      float* jac_out, int64_t jac_out_stride, float* lap_out,
+                                      void* stream) {
+  using namespace fl;
+  FL_REQUIRE(inner >= 1 && outer_stride >= 0 && inner_stride >= 0 && row_stride >= n, FL_EBADSHAPE,
+             "fl_slogdet_strided: bad matrix layout (inner %lld, strides %lld / %lld / %lld)",
+             (long long)inner, (long long)outer_stride, (long long)inner_stride, (long long)row_stride);
+  return run_slogdet("fl_slogdet_strided", A, jac, lap, n_mat, n, K, jac_stride, sign, logdet,
+                     jac_out, jac_out_stride, lap_out,
+                     MatLayout{inner, outer_stride, inner_stride, row_stride}, (cudaStream_t)stream);
+}
+
+namespace fl {
+namespace {
+int32_t run_slogdet(const char* who, const float* A, const float* jac, const float* lap,
+                    int64_t n_mat, int64_t n, int64_t K, int64_t jac_stride, float* sign,
+                    float* logdet, float* jac_out, int64_t jac_out_stride, float* lap_out,
+                    MatLayout lay, cudaStream_t st) {
   FL_REQUIRE(n_mat >= 0 && n >= 1 && K >= 0 && K < (1ll << 31), FL_EBADSHAPE,
-             "fl_slogdet: bad sizes n_mat=%lld n=%lld K=%lld", (long long)n_mat, (long long)n,
+             "%s: bad sizes n_mat=%lld n=%lld K=%lld", who, (long long)n_mat, (long long)n,
              (long long)K);
-  FL_REQUIRE(n <= 32, FL_EUNSUPPORTED, "fl_slogdet: n=%lld > 32 is not supported", (long long)n);
+  FL_REQUIRE(n <= 32, FL_EUNSUPPORTED, "%s: n=%lld > 32 is not supported", who, (long long)n);
   if (n_mat == 0) return FL_OK;
   FL_REQUIRE(A && lap && sign && logdet && lap_out && (K == 0 || (jac && jac_out)), FL_EBADSHAPE,
-             "fl_slogdet: null pointer");
-  FL_REQUIRE(K <= 1 || (jac_stride >= n_mat * n * n && jac_out_stride >= n_mat), FL_EBADSHAPE,
-             "fl_slogdet: Jacobian row stride too small");
-  cudaStream_t st = (cudaStream_t)stream;
+             "%s: null pointer", who);
+  FL_REQUIRE(K <= 1 || jac_out_stride >= n_mat, FL_EBADSHAPE,
+             "%s: output Jacobian row stride too small", who);
   if (n <= 8)
     return launch<8, 4, 2>(A, jac, lap, n_mat, K, jac_stride, (int)n, sign, logdet, jac_out,
-                           jac_out_stride, lap_out, st);
+                           jac_out_stride, lap_out, lay, st);
   if (n <= 16)
     return launch<16, 4, 2>(A, jac, lap, n_mat, K, jac_stride, (int)n, sign, logdet, jac_out,
-                            jac_out_stride, lap_out, st);
+                            jac_out_stride, lap_out, lay, st);
   return launch<32, 2, 4>(A, jac, lap, n_mat, K, jac_stride, (int)n, sign, logdet, jac_out,
-                          jac_out_stride, lap_out, st);
+                          jac_out_stride, lap_out, lay, st);
 }
+}  // namespace
+}  // namespace fl

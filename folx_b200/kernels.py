@@ -330,31 +330,76 @@ def layernorm(a: FwdLaplArray, gamma: torch.Tensor | None, beta: torch.Tensor | 
     return out
 
 
+def _matrix_view_layout(x: torch.Tensor, j: torch.Tensor, l: torch.Tensor):
+    """``(inner, outer_stride, inner_stride, row_stride)`` if the square matrices in the last two
+    axes of ``x`` (and, with the same strides, of every Jacobian row and of ``l``) form a view the
+    slogdet kernel can read in place: contiguous matrix rows, the last batch axis strided freely,
+    the remaining batch axes collapsing to one stride.  None for other views."""
+    if x.ndim < 3 or x.stride(-1) != 1 or x.numel() == 0:
+        return None
+    n = x.shape[-1]
+    rs = x.stride(-2)
+    lead, st = list(x.shape[:-2]), list(x.stride()[:-2])
+    inner, inner_stride = lead[-1], st[-1]
+    outer_stride, count = None, 1
+    for d in range(len(lead) - 2, -1, -1):
+        if lead[d] == 1:
+            continue
+        if outer_stride is None:
+            outer_stride, count = st[d], lead[d]
+        elif st[d] == outer_stride * count:
+            count *= lead[d]
+        else:
+            return None
+    if outer_stride is None:
+        outer_stride = 0
+    if rs < n or min(inner_stride, outer_stride) < 0:
+        return None
+    same = lambda shape, strides: tuple(shape) == tuple(x.shape) and all(
+        a == b or m == 1 for a, b, m in zip(strides, x.stride(), x.shape))
+    if not same(l.shape, l.stride()) or not same(j.shape[1:], j.stride()[1:]):
+        return None
+    return inner, outer_stride, inner_stride, rs
+
+
 def slogdet(a: FwdLaplArray):
     """``(sign, triplet of log|det|)`` for matrices in the last two axes (folx/slogdet.py:296-358).
 
     The Jacobian must be dense (the rule densifies, as the reference does: the determinant
-    depends on every coordinate its matrix depends on, folx/slogdet.py:247, 344).
+    depends on every coordinate its matrix depends on, folx/slogdet.py:247, 344).  A permuted /
+    reshaped view of a product (the usual way orbital matrices are formed) is read in place.
     """
     if a.jacobian.weak:
         a = a.dense
-    a = as_contiguous(a)
     x, j, l = a.x, a.jacobian.data, a.laplacian
-    _require_cuda(x, j, l)
     n = x.shape[-1]
-    if x.shape[-2] != n:
+    if x.ndim < 2 or x.shape[-2] != n:
         raise ValueError(f'slogdet: matrices must be square, got {tuple(x.shape[-2:])}')
+    layout = None
+    if x.is_cuda and not (x.is_contiguous() and l.is_contiguous() and _rows_contiguous(j)):
+        layout = _matrix_view_layout(x, j, l)
+    if layout is None:
+        a = as_contiguous(a)
+        x, j, l = a.x, a.jacobian.data, a.laplacian
+    _require_cuda(x, j, l)
     batch = tuple(x.shape[:-2])
     n_mat = x.numel() // (n * n) if n else 0
     K = j.shape[0]
-    if K > 1 and j.stride(0) < x.numel():
+    if layout is None and K > 1 and j.stride(0) < x.numel():
         j = j.contiguous()
     sign = torch.empty(batch, dtype=torch.float32, device=x.device)
     out = alloc_triplet(K, batch, x.device, None)
-    lib.call(
-        'fl_slogdet', _ptr(x), _ptr(j), _ptr(l), n_mat, n, K, _jac_stride(j), _ptr(sign),
-        _ptr(out.x), _ptr(out.jacobian.data), max(n_mat, 1), _ptr(out.laplacian), _stream(x.device),
-    )
+    if layout is None:
+        lib.call(
+            'fl_slogdet', _ptr(x), _ptr(j), _ptr(l), n_mat, n, K, _jac_stride(j), _ptr(sign),
+            _ptr(out.x), _ptr(out.jacobian.data), max(n_mat, 1), _ptr(out.laplacian), _stream(x.device),
+        )
+    else:
+        lib.call(
+            'fl_slogdet_strided', _ptr(x), _ptr(j), _ptr(l), n_mat, n, K, _jac_stride(j), *layout,
+            _ptr(sign), _ptr(out.x), _ptr(out.jacobian.data), max(n_mat, 1), _ptr(out.laplacian),
+            _stream(x.device),
+        )
     return sign, out
 
 

@@ -77,6 +77,9 @@ _SIGNATURES = {
                                         c_int64, c_void_p, c_void_p]),
     'fl_slogdet': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                              c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
+    'fl_slogdet_strided': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                     c_int64, c_int64, c_int64, c_int64,
+                                     c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     'fl_inv': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                          c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     'fl_mhsa': (c_int32, [c_void_p] * 14 + [c_int64] * 9 + [c_void_p]),

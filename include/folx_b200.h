@@ -293,6 +293,20 @@ int32_t fl_slogdet(const float* A, const float* jac, const float* lap,
                    float* sign, float* logdet, float* jac_out, int64_t jac_out_stride,
                    float* lap_out, void* stream);
 
+/* fl_slogdet for matrices that are a strided VIEW (the reference permutes and reshapes with
+ * ordinary rules, folx/wrapped_functions.py:457-508, before slogdet): matrix m = (o, i) with
+ * i = m mod inner starts o * outer_stride + i * inner_stride elements into A / one Jacobian row /
+ * lap, its rows are row_stride elements apart and contiguous.  Example: the (walker, determinant,
+ * electron, orbital) view of a (walker, electron, determinant x orbital) product with n_det
+ * determinants of n x n: inner = n_det, inner_stride = n, outer_stride = n n_det n,
+ * row_stride = n_det n.  Outputs are dense as for fl_slogdet. */
+int32_t fl_slogdet_strided(const float* A, const float* jac, const float* lap,
+                           int64_t n_mat, int64_t n, int64_t K, int64_t jac_stride,
+                           int64_t inner, int64_t outer_stride, int64_t inner_stride,
+                           int64_t row_stride,
+                           float* sign, float* logdet, float* jac_out, int64_t jac_out_stride,
+                           float* lap_out, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Matrix inverse of a triplet of small square matrices.  Replaces inv_wrapper
  * (folx/linear_solve.py:114-145).  With C = A^-1 and M_k = C dA_k:

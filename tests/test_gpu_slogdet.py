@@ -3,7 +3,8 @@
 import pytest
 import torch
 
-from folx_b200 import kernels
+from folx_b200 import kernels, lib
+from folx_b200.api import FwdJacobian, FwdLaplArray
 from oracle import rules
 
 from gpu_util import assert_close, seeded_triplet, to_device, to_host
@@ -68,3 +69,23 @@ def test_slogdet_config_shapes_properties(cuda_device, n, K, walkers, dets):
     torch.testing.assert_close(out2.x, out.x + n * 0.6931471805599453, rtol=1e-5, atol=1e-4)
     torch.testing.assert_close(out2.jacobian.data, out.jacobian.data, rtol=1e-4, atol=1e-4)
     torch.testing.assert_close(out2.laplacian, out.laplacian, rtol=1e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize('n,n_det,K,B', [(8, 16, 5, 6), (16, 4, 7, 3), (5, 3, 4, 4), (32, 2, 3, 2)])
+def test_slogdet_reads_a_permuted_view_in_place(cuda_device, n, n_det, K, B):
+    """Orbital matrices as models form them: a (walker, electron, determinant x orbital) product
+    viewed as (walker, determinant, electron, orbital); no staging copy."""
+    x, J, lap = seeded_triplet(K, (B, n, n_det * n), seed=n + n_det)
+    eye = torch.eye(n, dtype=torch.float64).repeat(1, n_det)           # keeps every block well conditioned
+    x = (x / n**0.5 + 1.5 * eye).float().double()
+    t = (x, J, lap)
+    view = lambda u, lead: u.reshape(*lead, B, n, n_det, n).permute(*range(len(lead)), len(lead), len(lead) + 2,
+                                                                     len(lead) + 1, len(lead) + 3)
+    d = to_device(t, cuda_device)
+    a = FwdLaplArray(view(d.x, ()), FwdJacobian(view(d.jacobian.data, (K,)), None), view(d.laplacian, ()))
+    before = lib.LAUNCH_COUNTS.get('fl_slogdet_strided', 0)
+    sign, out = kernels.slogdet(a)
+    assert lib.LAUNCH_COUNTS.get('fl_slogdet_strided', 0) == before + 1
+    want_sign, want = rules.slogdet((view(x, ()), view(J, (K,)), view(lap, ())))
+    torch.testing.assert_close(sign.double().cpu(), want_sign)
+    assert_close(to_host(out), want, rtol=2e-4, atol_scale=2e-5)
