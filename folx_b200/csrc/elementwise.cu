@@ -99,13 +99,82 @@ __device__ __forceinline__ D eval(float x, float param) {
     r.y = inv;
     r.d1 = -inv * inv;
     r.d2 = 2.0f * inv * inv * inv;
+  } else if constexpr (OP == FL_OP_LOG1P) {
+    float inv = 1.0f / (1.0f + x);
+    r.y = log1pf(x);
+    r.d1 = inv;
+    r.d2 = -inv * inv;
+  } else if constexpr (OP == FL_OP_EXPM1) {
+    r.y = expm1f(x);
+    r.d1 = expf(x);
+    r.d2 = r.d1;
+  } else if constexpr (OP == FL_OP_TAN) {
+    r.y = tanf(x);
+    r.d1 = 1.0f + r.y * r.y;
+    r.d2 = 2.0f * r.y * r.d1;
+  } else if constexpr (OP == FL_OP_SINH) {
+    r.y = sinhf(x); r.d1 = coshf(x); r.d2 = r.y;
+  } else if constexpr (OP == FL_OP_COSH) {
+    r.y = coshf(x); r.d1 = sinhf(x); r.d2 = r.y;
+  } else if constexpr (OP == FL_OP_ASIN || OP == FL_OP_ACOS) {
+    float q = 1.0f / (1.0f - x * x);   // 1 / (1 - x^2)
+    float s = sqrtf(q);
+    r.y = OP == FL_OP_ASIN ? asinf(x) : acosf(x);
+    r.d1 = OP == FL_OP_ASIN ? s : -s;
+    r.d2 = r.d1 * x * q;
+  } else if constexpr (OP == FL_OP_ATAN) {
+    float q = 1.0f / (1.0f + x * x);
+    r.y = atanf(x);
+    r.d1 = q;
+    r.d2 = -2.0f * x * q * q;
+  } else if constexpr (OP == FL_OP_ASINH) {
+    float q = 1.0f / (1.0f + x * x);
+    r.y = asinhf(x);
+    r.d1 = sqrtf(q);
+    r.d2 = -x * q * r.d1;
+  } else if constexpr (OP == FL_OP_ACOSH) {
+    float q = 1.0f / (x * x - 1.0f);
+    r.y = acoshf(x);
+    r.d1 = sqrtf(q);
+    r.d2 = -x * q * r.d1;
+  } else if constexpr (OP == FL_OP_ATANH) {
+    float q = 1.0f / (1.0f - x * x);
+    r.y = atanhf(x);
+    r.d1 = q;
+    r.d2 = 2.0f * x * q * q;
+  } else if constexpr (OP == FL_OP_ERF || OP == FL_OP_ERFC) {
+    float gauss = 1.1283791670955126f * expf(-x * x);  // 2 / sqrt(pi) e^{-x^2}
+    r.y = OP == FL_OP_ERF ? erff(x) : erfcf(x);
+    r.d1 = OP == FL_OP_ERF ? gauss : -gauss;
+    r.d2 = -2.0f * x * r.d1;
+  } else if constexpr (OP == FL_OP_CBRT) {
+    float inv = 1.0f / x;
+    r.y = cbrtf(x);
+    r.d1 = r.y * inv * (1.0f / 3.0f);
+    r.d2 = -2.0f * r.y * inv * inv * (1.0f / 9.0f);
+  } else if constexpr (OP == FL_OP_POW) {
+    float inv = 1.0f / x;
+    r.y = powf(x, param);
+    r.d1 = param * r.y * inv;
+    r.d2 = (param - 1.0f) * r.d1 * inv;
+  } else if constexpr (OP == FL_OP_RELU) {
+    r.y = fmaxf(x, 0.0f);
+    r.d1 = x > 0.0f ? 1.0f : 0.0f;
+    r.d2 = 0.0f;
+  } else if constexpr (OP == FL_OP_GELU) {
+    float cdf = 0.5f * (1.0f + erff(x * 0.7071067811865476f));
+    float pdf = 0.3989422804014327f * expf(-0.5f * x * x);
+    r.y = x * cdf;
+    r.d1 = fmaf(x, pdf, cdf);
+    r.d2 = pdf * (2.0f - x * x);
   }
   return r;
 }
 
 template <int OP>
 constexpr bool is_linear() {
-  return OP == FL_OP_NEG || OP == FL_OP_ABS || OP == FL_OP_SCALE || OP == FL_OP_SHIFT;
+  return OP == FL_OP_NEG || OP == FL_OP_ABS || OP == FL_OP_SCALE || OP == FL_OP_SHIFT ||
+         OP == FL_OP_RELU;
 }
 
 constexpr int kUnroll = 8;
@@ -217,7 +286,11 @@ __device__ __forceinline__ D eval_dyn(int op, float x, float param) {
     FL_EV(FL_OP_TANH) FL_EV(FL_OP_SILU) FL_EV(FL_OP_EXP) FL_EV(FL_OP_LOG) FL_EV(FL_OP_SQRT)
     FL_EV(FL_OP_RSQRT) FL_EV(FL_OP_SQUARE) FL_EV(FL_OP_SIGMOID) FL_EV(FL_OP_SOFTPLUS)
     FL_EV(FL_OP_INTEGER_POW) FL_EV(FL_OP_SIN) FL_EV(FL_OP_COS) FL_EV(FL_OP_NEG) FL_EV(FL_OP_ABS)
-    FL_EV(FL_OP_SCALE) FL_EV(FL_OP_SHIFT) FL_EV(FL_OP_RECIPROCAL)
+    FL_EV(FL_OP_SCALE) FL_EV(FL_OP_SHIFT) FL_EV(FL_OP_RECIPROCAL) FL_EV(FL_OP_LOG1P)
+    FL_EV(FL_OP_EXPM1) FL_EV(FL_OP_TAN) FL_EV(FL_OP_SINH) FL_EV(FL_OP_COSH) FL_EV(FL_OP_ASIN)
+    FL_EV(FL_OP_ACOS) FL_EV(FL_OP_ATAN) FL_EV(FL_OP_ASINH) FL_EV(FL_OP_ACOSH) FL_EV(FL_OP_ATANH)
+    FL_EV(FL_OP_ERF) FL_EV(FL_OP_ERFC) FL_EV(FL_OP_CBRT) FL_EV(FL_OP_POW) FL_EV(FL_OP_RELU)
+    FL_EV(FL_OP_GELU)
 #undef FL_EV
   }
   return D{x, 1.f, 0.f};
@@ -372,6 +445,23 @@ extern "C" int32_t fl_elementwise(int32_t op, float param, const float* x, const
     FL_CASE(FL_OP_SCALE)
     FL_CASE(FL_OP_SHIFT)
     FL_CASE(FL_OP_RECIPROCAL)
+    FL_CASE(FL_OP_LOG1P)
+    FL_CASE(FL_OP_EXPM1)
+    FL_CASE(FL_OP_TAN)
+    FL_CASE(FL_OP_SINH)
+    FL_CASE(FL_OP_COSH)
+    FL_CASE(FL_OP_ASIN)
+    FL_CASE(FL_OP_ACOS)
+    FL_CASE(FL_OP_ATAN)
+    FL_CASE(FL_OP_ASINH)
+    FL_CASE(FL_OP_ACOSH)
+    FL_CASE(FL_OP_ATANH)
+    FL_CASE(FL_OP_ERF)
+    FL_CASE(FL_OP_ERFC)
+    FL_CASE(FL_OP_CBRT)
+    FL_CASE(FL_OP_POW)
+    FL_CASE(FL_OP_RELU)
+    FL_CASE(FL_OP_GELU)
   }
 #undef FL_CASE
   return FL_EUNSUPPORTED;

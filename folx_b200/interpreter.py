@@ -42,7 +42,8 @@ class BatchedConst(torch.Tensor):
 
 
 _CHAINABLE = frozenset({'tanh', 'silu', 'exp', 'log', 'sqrt', 'rsqrt', 'square', 'sigmoid', 'softplus',
-                        'sin', 'cos', 'neg', 'abs', 'reciprocal'})
+                        'sin', 'cos', 'neg', 'abs', 'reciprocal', 'log1p', 'expm1', 'tan', 'sinh', 'cosh',
+                        'asin', 'acos', 'atan', 'asinh', 'acosh', 'atanh', 'erf', 'erfc', 'relu', 'gelu'})
 
 
 class LaplTensor:
@@ -245,7 +246,10 @@ class LaplTensor:
             return self._unary('sqrt')
         if p == -0.5:
             return self._unary('rsqrt')
-        raise NotImplementedError(f'power {p} of a triplet is not supported')
+        if isinstance(p, (int, float)):
+            # a real constant exponent (jax.lax.pow with a constant, folx/wrapped_functions.py:384)
+            return self._wrap(_call('pow', (self.arr,), {'param': float(p)}, self.thr))
+        raise NotImplementedError('a power whose exponent is a tensor is not supported on triplets')
 
     def __matmul__(self, W):
         if isinstance(W, LaplTensor):
@@ -299,6 +303,20 @@ class LaplTensor:
     def neg(self): return self._unary('neg')
     def reciprocal(self): return self._unary('reciprocal')
     def pow(self, p): return self.__pow__(p)
+    def log1p(self): return self._unary('log1p')
+    def expm1(self): return self._unary('expm1')
+    def tan(self): return self._unary('tan')
+    def sinh(self): return self._unary('sinh')
+    def cosh(self): return self._unary('cosh')
+    def asin(self): return self._unary('asin')
+    def acos(self): return self._unary('acos')
+    def atan(self): return self._unary('atan')
+    def asinh(self): return self._unary('asinh')
+    def acosh(self): return self._unary('acosh')
+    def atanh(self): return self._unary('atanh')
+    def erf(self): return self._unary('erf')
+    def erfc(self): return self._unary('erfc')
+    def relu(self): return self._unary('relu')
 
     def detach(self):
         return self._wrap(_call('stop_gradient', (self.arr,), {}, self.thr))
@@ -532,6 +550,12 @@ def _pow(x, p):
     return x.__pow__(p)
 
 
+def _gelu(x, approximate):
+    if approximate != 'none':
+        raise NotImplementedError("only the exact (erf) form of gelu has a rule on triplets")
+    return x._unary('gelu')
+
+
 def _like(fn):
     def h(x, **k):
         return fn(x.arr.x[(0,) * x.nb], **k)
@@ -546,6 +570,15 @@ _TORCH_TABLE: dict[Any, Callable] = {
     torch.nn.functional.sigmoid: _method('sigmoid'), torch.sin: _method('sin'), torch.cos: _method('cos'),
     torch.abs: _method('abs'), torch.neg: _method('neg'), torch.negative: _method('neg'),
     torch.reciprocal: _method('reciprocal'),
+    torch.log1p: _method('log1p'), torch.expm1: _method('expm1'), torch.tan: _method('tan'),
+    torch.sinh: _method('sinh'), torch.cosh: _method('cosh'), torch.asin: _method('asin'),
+    torch.arcsin: _method('asin'), torch.acos: _method('acos'), torch.arccos: _method('acos'),
+    torch.atan: _method('atan'), torch.arctan: _method('atan'), torch.asinh: _method('asinh'),
+    torch.arcsinh: _method('asinh'), torch.acosh: _method('acosh'), torch.arccosh: _method('acosh'),
+    torch.atanh: _method('atanh'), torch.arctanh: _method('atanh'), torch.erf: _method('erf'),
+    torch.special.erf: _method('erf'), torch.erfc: _method('erfc'), torch.special.erfc: _method('erfc'),
+    torch.relu: _method('relu'), torch.nn.functional.relu: lambda x, inplace=False: x._unary('relu'),
+    torch.nn.functional.gelu: lambda x, approximate='none': _gelu(x, approximate),
     torch.nn.functional.silu: lambda x, inplace=False: x._unary('silu'),
     torch.nn.functional.softplus: lambda x, beta=1.0, threshold=20.0: x._unary('softplus'),
     torch.add: _binary_fn('add'), torch.sub: _binary_fn('sub'), torch.subtract: _binary_fn('sub'),

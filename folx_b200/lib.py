@@ -23,7 +23,9 @@ FL_ECUDA = 4
 ELEMENTWISE_OPS = {
     'tanh': 0, 'silu': 1, 'exp': 2, 'log': 3, 'sqrt': 4, 'rsqrt': 5, 'square': 6,
     'sigmoid': 7, 'softplus': 8, 'integer_pow': 9, 'sin': 10, 'cos': 11, 'neg': 12,
-    'abs': 13, 'scale': 14, 'shift': 15, 'reciprocal': 16,
+    'abs': 13, 'scale': 14, 'shift': 15, 'reciprocal': 16, 'log1p': 17, 'expm1': 18, 'tan': 19,
+    'sinh': 20, 'cosh': 21, 'asin': 22, 'acos': 23, 'atan': 24, 'asinh': 25, 'acosh': 26,
+    'atanh': 27, 'erf': 28, 'erfc': 29, 'cbrt': 30, 'pow': 31, 'relu': 32, 'gelu': 33,
 }
 BINARY_OPS = {'add': 0, 'sub': 1, 'mul': 2, 'div': 3}
 ADDN_OPS = {'identity': 0, 'tanh': 1, 'silu': 2, 'exp': 3}

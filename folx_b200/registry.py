@@ -281,7 +281,8 @@ def _mhsea(args, kwargs, sparsity_threshold):
 
 
 for _op in ('tanh', 'exp', 'log', 'sqrt', 'rsqrt', 'square', 'sigmoid', 'softplus', 'silu', 'sin',
-            'cos', 'neg', 'abs', 'reciprocal'):
+            'cos', 'neg', 'abs', 'reciprocal', 'log1p', 'expm1', 'tan', 'sinh', 'cosh', 'asin', 'acos',
+            'atan', 'asinh', 'acosh', 'atanh', 'erf', 'erfc', 'cbrt', 'pow', 'relu', 'gelu'):
     register_function(_op, _unary(_op))
 register_function('logistic', _unary('sigmoid'))
 register_function('integer_pow', _integer_pow)

@@ -96,15 +96,22 @@ _TORCH_UNARY = {
     'tanh': torch.tanh, 'silu': torch.nn.functional.silu, 'exp': torch.exp, 'log': torch.log,
     'sqrt': torch.sqrt, 'rsqrt': torch.rsqrt, 'square': torch.square, 'sigmoid': torch.sigmoid,
     'softplus': torch.nn.functional.softplus, 'sin': torch.sin, 'cos': torch.cos, 'neg': torch.neg,
-    'abs': torch.abs, 'reciprocal': torch.reciprocal,
+    'abs': torch.abs, 'reciprocal': torch.reciprocal, 'log1p': torch.log1p, 'expm1': torch.expm1,
+    'tan': torch.tan, 'sinh': torch.sinh, 'cosh': torch.cosh, 'asin': torch.asin, 'acos': torch.acos,
+    'atan': torch.atan, 'asinh': torch.asinh, 'acosh': torch.acosh, 'atanh': torch.atanh,
+    'erf': torch.erf, 'erfc': torch.erfc,
+    'cbrt': lambda x: torch.sign(x) * torch.abs(x) ** (1.0 / 3.0), 'relu': torch.relu,
+    'gelu': torch.nn.functional.gelu,
 }
-_LINEAR_UNARY = {'neg', 'abs', 'scale', 'shift'}
+_LINEAR_UNARY = {'neg', 'abs', 'scale', 'shift', 'relu'}
 
 
 def elementwise(op: str, a, param: float = 0.0, sparsity_threshold: int = 0):
     if not is_triplet(a):
         if op == 'integer_pow':
             return a ** int(param)
+        if op == 'pow':
+            return a ** float(param)
         if op == 'scale':
             return a * param
         if op == 'shift':

@@ -45,8 +45,11 @@ const char* fl_last_error(void);
  * scalar function registered with in_axes=() (folx/wrapped_functions.py:384-431, 553-556):
  *     y = f(x), J_y[k] = f'(x) J[k], lap_y = f'(x) lap + f''(x) sum_k J[k]^2.
  * One pass: every input element is read once and every output element written once.
- * `param` is the exponent of FL_OP_INTEGER_POW and the factor / offset of FL_OP_SCALE /
- * FL_OP_SHIFT, ignored otherwise.
+ * `param` is the exponent of FL_OP_INTEGER_POW / FL_OP_POW and the factor / offset of
+ * FL_OP_SCALE / FL_OP_SHIFT, ignored otherwise.  FL_OP_LOG1P .. FL_OP_CBRT are the remaining
+ * scalar functions of the reference's registry (folx/wrapped_functions.py:404-431); FL_OP_RELU
+ * (piecewise linear, like clamp there) and FL_OP_GELU (exact, erf form) are the activations torch
+ * models spell as single calls.
  * ------------------------------------------------------------------------------------------- */
 enum {
   FL_OP_TANH = 0,
@@ -66,7 +69,24 @@ enum {
   FL_OP_SCALE = 14, /* y = param * x (mul by a constant, folx/hessian.py:563-564) */
   FL_OP_SHIFT = 15, /* y = x + param (add of a constant, folx/wrapped_functions.py:364-366) */
   FL_OP_RECIPROCAL = 16,
-  FL_OP_COUNT_ = 17
+  FL_OP_LOG1P = 17,
+  FL_OP_EXPM1 = 18,
+  FL_OP_TAN = 19,
+  FL_OP_SINH = 20,
+  FL_OP_COSH = 21,
+  FL_OP_ASIN = 22,
+  FL_OP_ACOS = 23,
+  FL_OP_ATAN = 24,
+  FL_OP_ASINH = 25,
+  FL_OP_ACOSH = 26,
+  FL_OP_ATANH = 27,
+  FL_OP_ERF = 28,
+  FL_OP_ERFC = 29,
+  FL_OP_CBRT = 30,
+  FL_OP_POW = 31,   /* y = x^param for x > 0 (pow with a constant exponent) */
+  FL_OP_RELU = 32,  /* max(x, 0): linear a.e. */
+  FL_OP_GELU = 33,  /* x Phi(x) */
+  FL_OP_COUNT_ = 34
 };
 
 int32_t fl_elementwise(int32_t op, float param,

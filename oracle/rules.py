@@ -63,6 +63,53 @@ def _derivs(op: str, x: torch.Tensor, param: float = 0.0):
     if op == 'reciprocal':
         inv = 1 / x
         return inv, -inv * inv, 2 * inv**3
+    # the remaining scalar functions of the reference's registry (folx/wrapped_functions.py:404-431)
+    if op == 'log1p':
+        return torch.log1p(x), 1 / (1 + x), -1 / (1 + x) ** 2
+    if op == 'expm1':
+        return torch.expm1(x), torch.exp(x), torch.exp(x)
+    if op == 'tan':
+        y = torch.tan(x)
+        return y, 1 + y * y, 2 * y * (1 + y * y)
+    if op == 'sinh':
+        return torch.sinh(x), torch.cosh(x), torch.sinh(x)
+    if op == 'cosh':
+        return torch.cosh(x), torch.sinh(x), torch.cosh(x)
+    if op == 'asin':
+        q = 1 / (1 - x * x)
+        return torch.asin(x), q.sqrt(), x * q * q.sqrt()
+    if op == 'acos':
+        q = 1 / (1 - x * x)
+        return torch.acos(x), -q.sqrt(), -x * q * q.sqrt()
+    if op == 'atan':
+        q = 1 / (1 + x * x)
+        return torch.atan(x), q, -2 * x * q * q
+    if op == 'asinh':
+        q = 1 / (1 + x * x)
+        return torch.asinh(x), q.sqrt(), -x * q * q.sqrt()
+    if op == 'acosh':
+        q = 1 / (x * x - 1)
+        return torch.acosh(x), q.sqrt(), -x * q * q.sqrt()
+    if op == 'atanh':
+        q = 1 / (1 - x * x)
+        return torch.atanh(x), q, 2 * x * q * q
+    if op == 'erf':
+        g = 2 / math.sqrt(math.pi) * torch.exp(-x * x)
+        return torch.erf(x), g, -2 * x * g
+    if op == 'erfc':
+        g = -2 / math.sqrt(math.pi) * torch.exp(-x * x)
+        return torch.erfc(x), g, -2 * x * g
+    if op == 'cbrt':
+        y = torch.sign(x) * torch.abs(x) ** (1 / 3)
+        return y, y / (3 * x), -2 * y / (9 * x * x)
+    if op == 'pow':
+        return x**param, param * x ** (param - 1), param * (param - 1) * x ** (param - 2)
+    if op == 'relu':  # piecewise linear (like clamp in the reference): no Hessian term
+        return torch.relu(x), (x > 0).to(x.dtype), torch.zeros_like(x)
+    if op == 'gelu':
+        cdf = 0.5 * (1 + torch.erf(x / math.sqrt(2)))
+        pdf = torch.exp(-0.5 * x * x) / math.sqrt(2 * math.pi)
+        return x * cdf, cdf + x * pdf, pdf * (2 - x * x)
     raise KeyError(op)
 
 

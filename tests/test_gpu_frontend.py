@@ -229,6 +229,26 @@ def test_runs_of_scalar_functions_are_fused(cuda_device, thr):
     assert lib.LAUNCH_COUNTS.get('fl_elementwise_chain', 0) - before.get('fl_elementwise_chain', 0) >= 2
 
 
+@pytest.mark.parametrize('thr', [0, 4])
+def test_scalar_functions_of_the_registry_through_torch(cuda_device, thr):
+    """torch spellings of the scalar functions the reference registers (log1p, expm1, the
+    trigonometric / hyperbolic families, erf, gelu, relu, a real power) reach the fused kernel."""
+    g = torch.Generator().manual_seed(41)
+    W = torch.randn(4, 6, generator=g) * 0.4
+
+    def f(Wm, x):
+        h = torch.tanh(x @ Wm) * 0.8                 # values in (-0.8, 0.8): inside every domain used below
+        a = torch.asin(h) + torch.atanh(h) * torch.acos(h) + torch.atan(h) + torch.tan(h)
+        b = torch.sinh(h) * torch.cosh(h) + torch.asinh(h) + torch.acosh(h * h + 1.5)
+        c = torch.erf(h) + torch.erfc(h) * torch.expm1(h) + torch.log1p(h * h)
+        d = F.gelu(h) + F.relu(h) + (h * h + 0.5) ** 1.3
+        return (a + b + c + d).sum()
+
+    x = torch.randn(3, 5, 4, generator=g).to(cuda_device)
+    Wd, W64 = W.to(cuda_device), W.double()
+    check_against_brute(lambda z: f(Wd, z), lambda z: f(W64, z), x, thr, samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

@@ -13,19 +13,31 @@ from gpu_util import assert_close, seeded_triplet, to_device, to_host
 
 pytestmark = pytest.mark.gpu
 
-POSITIVE = {'log', 'sqrt', 'rsqrt', 'reciprocal'}
+POSITIVE = {'log', 'sqrt', 'rsqrt', 'reciprocal', 'log1p', 'cbrt'}
+UNIT_INTERVAL = {'asin', 'acos', 'atanh'}   # inputs mapped into (-0.9, 0.9)
+ABOVE_ONE = {'acosh'}                       # inputs mapped above 1.5
 
 
-@pytest.mark.parametrize('op', sorted(set(lib.ELEMENTWISE_OPS) - {'integer_pow', 'scale', 'shift'}))
+def in_domain(op, t):
+    x, J, lap = t
+    if op in UNIT_INTERVAL:
+        x = (0.9 * torch.tanh(x)).float().double()
+    elif op in ABOVE_ONE:
+        x = (x.abs() + 1.5).float().double()
+    return x, J, lap
+
+
+@pytest.mark.parametrize('op', sorted(set(lib.ELEMENTWISE_OPS) - {'integer_pow', 'scale', 'shift', 'pow'}))
 @pytest.mark.parametrize('K,shape', [(0, (5,)), (1, (7, 3)), (9, (4, 8)), (17, (3, 5, 16))])
 def test_elementwise(cuda_device, op, K, shape):
-    t = seeded_triplet(K, shape, seed=1, positive=op in POSITIVE)
+    t = in_domain(op, seeded_triplet(K, shape, seed=1, positive=op in POSITIVE))
     got = kernels.elementwise(op, to_device(t, cuda_device))
     assert_close(to_host(got), rules.elementwise(op, t))
 
 
 @pytest.mark.parametrize('op,param', [('integer_pow', 2), ('integer_pow', 3), ('integer_pow', -1),
-                                      ('integer_pow', -2), ('scale', 0.37), ('shift', -1.5)])
+                                      ('integer_pow', -2), ('scale', 0.37), ('shift', -1.5),
+                                      ('pow', 1.7), ('pow', -0.3)])
 def test_elementwise_param(cuda_device, op, param):
     t = seeded_triplet(6, (10, 12), seed=2, positive=True)
     got = kernels.elementwise(op, to_device(t, cuda_device), param)

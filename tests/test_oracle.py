@@ -35,6 +35,16 @@ ELEMENTWISE = {
     'sigmoid': (torch.sigmoid, False), 'softplus': (torch.nn.functional.softplus, False),
     'sin': (torch.sin, False), 'cos': (torch.cos, False), 'neg': (torch.neg, False),
     'abs': (torch.abs, False), 'reciprocal': (torch.reciprocal, True),
+    'log1p': (torch.log1p, True), 'expm1': (torch.expm1, False), 'tan': (torch.tan, False),
+    'sinh': (torch.sinh, False), 'cosh': (torch.cosh, False), 'atan': (torch.atan, False),
+    'asinh': (torch.asinh, False), 'erf': (torch.erf, False), 'erfc': (torch.erfc, False),
+    'cbrt': (lambda x: torch.sign(x) * torch.abs(x) ** (1 / 3), True), 'relu': (torch.relu, False),
+    'gelu': (torch.nn.functional.gelu, False),
+}
+# functions with a restricted domain: the inputs are mapped into it first
+RESTRICTED = {
+    'asin': (torch.asin, lambda x: 0.9 * torch.tanh(x)), 'acos': (torch.acos, lambda x: 0.9 * torch.tanh(x)),
+    'atanh': (torch.atanh, lambda x: 0.9 * torch.tanh(x)), 'acosh': (torch.acosh, lambda x: x.abs() + 1.5),
 }
 
 
@@ -43,6 +53,19 @@ def test_elementwise_matches_brute_force(op):
     fn, positive = ELEMENTWISE[op]
     t = rand_triplet(5, (3, 4), positive)
     assert_triplet_close(rules.elementwise(op, t), brute.propagate(fn, [t]))
+
+
+@pytest.mark.parametrize('op', sorted(RESTRICTED))
+def test_restricted_domain_elementwise_matches_brute_force(op):
+    fn, into_domain = RESTRICTED[op]
+    x, J, lap = rand_triplet(5, (3, 4))
+    t = (into_domain(x), J, lap)
+    assert_triplet_close(rules.elementwise(op, t), brute.propagate(fn, [t]))
+
+
+def test_pow_with_constant_exponent():
+    t = rand_triplet(4, (6,), positive=True)
+    assert_triplet_close(rules.elementwise('pow', t, 1.7), brute.propagate(lambda x: x**1.7, [t]))
 
 
 @pytest.mark.parametrize('n', [-2, -1, 2, 3])
