@@ -7,6 +7,8 @@
 //        lap = la / b - a lb / b^2 - (2 / b^2) sum_k Ja_k Jb_k + (2 a / b^3) sum_k Jb_k^2
 //        (reference: folx/wrapped_functions.py:378-383, folx/custom_hessian.py:35-59)
 //   add/sub: linear in both operands, no Hessian term (folx/wrapped_functions.py:364-369).
+//   max/min: piecewise linear, the selected operand's J and lap pass through
+//        (folx/wrapped_functions.py:509-514).
 //
 // Either operand may be a constant array (its lap pointer, and jac pointer, are NULL): then its
 // Jacobian and Laplacian are zero.  Operand b may be broadcast: seen as (outer, mid, inner)
@@ -28,6 +30,14 @@ __device__ __forceinline__ void coeffs(float a, float b, float& y, float& ca, fl
     y = a - b; ca = 1.f; cb = -1.f; hab = 0.f; hbb = 0.f;
   } else if constexpr (OP == FL_BIN_MUL) {
     y = a * b; ca = b; cb = a; hab = 2.f; hbb = 0.f;
+  } else if constexpr (OP == FL_BIN_MAX || OP == FL_BIN_MIN) {
+    // piecewise linear (reference: max / min with the LINEAR flag, folx/wrapped_functions.py:
+    // 509-514): the derivatives of the selected operand pass through, ties share them equally
+    const bool first = OP == FL_BIN_MAX ? a > b : a < b;
+    y = OP == FL_BIN_MAX ? fmaxf(a, b) : fminf(a, b);
+    ca = first ? 1.f : (a == b ? 0.5f : 0.f);
+    cb = 1.f - ca;
+    hab = 0.f; hbb = 0.f;
   } else {
     float inv = 1.0f / b;
     y = a * inv;
@@ -170,7 +180,7 @@ extern "C" int32_t fl_binary(int32_t op, const float* a, const float* jac_a, con
                              float* lap_y, int64_t jac_y_stride, int64_t K, int64_t N,
                              int64_t b_inner, int64_t b_mid, void* stream) {
   using namespace fl;
-  FL_REQUIRE(op >= FL_BIN_ADD && op <= FL_BIN_DIV, FL_EUNSUPPORTED, "fl_binary: unknown op %d", op);
+  FL_REQUIRE(op >= FL_BIN_ADD && op <= FL_BIN_MIN, FL_EUNSUPPORTED, "fl_binary: unknown op %d", op);
   FL_REQUIRE(K >= 0 && N >= 0 && K < (1ll << 31) && (N + 255) / 256 < (1ll << 31), FL_EBADSHAPE,
              "fl_binary: bad sizes K=%lld N=%lld", (long long)K, (long long)N);
   if (N == 0) return FL_OK;
@@ -193,6 +203,12 @@ extern "C" int32_t fl_binary(int32_t op, const float* a, const float* jac_a, con
                                   jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
     case FL_BIN_MUL:
       return dispatch<FL_BIN_MUL>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,
+                                  jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
+    case FL_BIN_MAX:
+      return dispatch<FL_BIN_MAX>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,
+                                  jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
+    case FL_BIN_MIN:
+      return dispatch<FL_BIN_MIN>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,
                                   jac_y, lap_y, jac_y_stride, K, N, b_inner, b_mid, st);
     default:
       return dispatch<FL_BIN_DIV>(a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b, jac_b_stride, y,

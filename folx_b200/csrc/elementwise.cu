@@ -167,6 +167,13 @@ __device__ __forceinline__ D eval(float x, float param) {
     r.y = x * cdf;
     r.d1 = fmaf(x, pdf, cdf);
     r.d2 = pdf * (2.0f - x * x);
+  } else if constexpr (OP == FL_OP_CLAMP_MIN || OP == FL_OP_CLAMP_MAX) {
+    // the two halves of clamp (folx/wrapped_functions.py:435-437): the derivative passes only
+    // strictly inside the bound, as in the jvp of jax.lax.clamp
+    const bool inside = OP == FL_OP_CLAMP_MIN ? x > param : x < param;
+    r.y = OP == FL_OP_CLAMP_MIN ? fmaxf(x, param) : fminf(x, param);
+    r.d1 = inside ? 1.0f : 0.0f;
+    r.d2 = 0.0f;
   }
   return r;
 }
@@ -174,7 +181,7 @@ __device__ __forceinline__ D eval(float x, float param) {
 template <int OP>
 constexpr bool is_linear() {
   return OP == FL_OP_NEG || OP == FL_OP_ABS || OP == FL_OP_SCALE || OP == FL_OP_SHIFT ||
-         OP == FL_OP_RELU;
+         OP == FL_OP_RELU || OP == FL_OP_CLAMP_MIN || OP == FL_OP_CLAMP_MAX;
 }
 
 constexpr int kUnroll = 8;
@@ -290,7 +297,7 @@ __device__ __forceinline__ D eval_dyn(int op, float x, float param) {
     FL_EV(FL_OP_EXPM1) FL_EV(FL_OP_TAN) FL_EV(FL_OP_SINH) FL_EV(FL_OP_COSH) FL_EV(FL_OP_ASIN)
     FL_EV(FL_OP_ACOS) FL_EV(FL_OP_ATAN) FL_EV(FL_OP_ASINH) FL_EV(FL_OP_ACOSH) FL_EV(FL_OP_ATANH)
     FL_EV(FL_OP_ERF) FL_EV(FL_OP_ERFC) FL_EV(FL_OP_CBRT) FL_EV(FL_OP_POW) FL_EV(FL_OP_RELU)
-    FL_EV(FL_OP_GELU)
+    FL_EV(FL_OP_GELU) FL_EV(FL_OP_CLAMP_MIN) FL_EV(FL_OP_CLAMP_MAX)
 #undef FL_EV
   }
   return D{x, 1.f, 0.f};
@@ -462,6 +469,8 @@ extern "C" int32_t fl_elementwise(int32_t op, float param, const float* x, const
     FL_CASE(FL_OP_POW)
     FL_CASE(FL_OP_RELU)
     FL_CASE(FL_OP_GELU)
+    FL_CASE(FL_OP_CLAMP_MIN)
+    FL_CASE(FL_OP_CLAMP_MAX)
   }
 #undef FL_CASE
   return FL_EUNSUPPORTED;

@@ -1,0 +1,209 @@
+// Batched slogdet forward-Laplacian rule for matrices whose Jacobian is sparse (n <= 32).
+//
+// When every input coordinate c touches only a few rows (or columns, or entries) of A, dA/dx_c is
+// a sum of a few rank-one factors e_{i_s} w_s^T and both outputs follow from the small matrices
+//   W_c[s][t] = sum_l w_s[j_l] A^-1[j_l][i_t]
+//   d_c log|det A|   = tr(W_c)
+//   lap log|det A|   = tr(A^-1 lapA) - sum_c sum_st W_c[s][t] W_c[t][s]
+// (reference: sparse_slogdet .. _pack_slogdet, folx/slogdet.py:76-293; the dense rule contracts
+// A^-1 with all n^2 entries of every tangent instead).  The factors come as static tables built on
+// the host from the index map: take[c][s][l] addresses entry l of factor s of coordinate c in the
+// matrix's (slot, row, column) Jacobian, cols[c][s][l] is its column j_l, rows[c][s] its row i_s.
+// With `transposed` the tables describe A^T (coordinates that touch few columns): take already
+// addresses A's own layout and A^-1 is read transposed.
+//
+// A group of N lanes owns one matrix (N = n padded to 8, 16 or 32): Gauss-Jordan elimination with
+// partial pivoting in shared memory gives A^-1, the sign and log|det|; the lanes then share the
+// coordinates.  HBM traffic per matrix: 4 (k + 2) n^2 bytes for k stored Jacobian slots.
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kBlock = 128;
+
+template <int N>
+__device__ __forceinline__ unsigned lanes_of_group() {
+  if constexpr (N == 32) return 0xffffffffu;
+  const unsigned lane = threadIdx.x & 31u;
+  return ((1u << N) - 1u) << (lane / N * N);
+}
+
+struct Tables {
+  const int32_t* take;    // [n_coords][rank][width], -1 = unused
+  const int32_t* cols;    // [n_coords][rank][width]
+  const int32_t* rows;    // [n_coords][rank]
+  const int32_t* coords;  // [n_coords] output Jacobian row of every coordinate
+  int n_coords, rank, width, transposed;
+};
+
+template <int N>
+__global__ void __launch_bounds__(kBlock)
+slogdet_sparse_kernel(const float* __restrict__ A, const float* __restrict__ J,
+                      const float* __restrict__ lapA, int64_t n_mat, int64_t js, int n, Tables tb,
+                      float* __restrict__ sign_out, float* __restrict__ logdet_out,
+                      float* __restrict__ J_out, int64_t jos, float* __restrict__ lap_out) {
+  constexpr int P = N + 1;         // pitch: lane-per-row accesses hit distinct banks
+  constexpr int MPB = kBlock / N;  // matrices per block
+  extern __shared__ float smem[];
+  const int g = threadIdx.x / N;   // matrix slot in the block
+  const int i = threadIdx.x % N;   // this lane's row
+  const unsigned mask = lanes_of_group<N>();
+  float* Cm = smem + (size_t)g * 2 * N * P;  // becomes A^-1
+  float* D = Cm + N * P;                     // A, reduced to the identity
+  const int64_t m = (int64_t)blockIdx.x * MPB + g;
+  const bool live = m < n_mat;
+  const int64_t mm = live ? m : 0;
+  const int nn = n * n;
+
+  // ---------------- A^-1, sign and log|det| by Gauss-Jordan with partial pivoting ----------------
+  {
+    const float* src = A + mm * nn;
+#pragma unroll 4
+    for (int q = 0; q < N; ++q) {
+      const int e = i + N * q, r = e / N, c = e % N;
+      D[r * P + c] = (r < n && c < n) ? __ldg(src + r * n + c) : (r == c ? 1.f : 0.f);
+      Cm[r * P + c] = (r == c) ? 1.f : 0.f;
+    }
+  }
+  __syncwarp(mask);
+  float sgn = 1.f, logdet = 0.f;
+  for (int c = 0; c < N; ++c) {
+    // pivot row: the first row r >= c with the largest |D[r][c]|
+    float best = i >= c ? fabsf(D[i * P + c]) : -1.f;
+    int piv = i;
+#pragma unroll
+    for (int o = N / 2; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(mask, best, o, N);
+      const int op = __shfl_xor_sync(mask, piv, o, N);
+      if (ob > best || (ob == best && op < piv)) { best = ob; piv = op; }
+    }
+    if (piv != c) {  // lanes swap the two rows, one column pair each
+      float a = D[c * P + i], b = D[piv * P + i];
+      D[c * P + i] = b; D[piv * P + i] = a;
+      a = Cm[c * P + i]; b = Cm[piv * P + i];
+      Cm[c * P + i] = b; Cm[piv * P + i] = a;
+      sgn = -sgn;
+    }
+    __syncwarp(mask);
+    const float pv = D[c * P + c];
+    sgn = pv < 0.f ? -sgn : sgn;
+    logdet += logf(fabsf(pv));
+    const float ipv = 1.0f / pv;
+    __syncwarp(mask);
+    D[c * P + i] *= ipv;
+    Cm[c * P + i] *= ipv;
+    __syncwarp(mask);
+    if (i != c) {
+      const float f = D[i * P + c];
+#pragma unroll 4
+      for (int col = 0; col < N; ++col) {
+        D[i * P + col] = fmaf(-f, D[c * P + col], D[i * P + col]);
+        Cm[i * P + col] = fmaf(-f, Cm[c * P + col], Cm[i * P + col]);
+      }
+      D[i * P + c] = 0.f;
+    }
+    __syncwarp(mask);
+  }
+  if (live && i == 0) {
+    sign_out[m] = sgn;
+    logdet_out[m] = logdet;
+  }
+
+  // ---------------- tr(A^-1 lapA): the lanes stride over the n^2 entries -------------------------
+  float acc = 0.f;
+  {
+    const float* src = lapA + mm * nn;
+    for (int e = i; e < nn; e += N) {
+      const int r = e / n, c = e % n;
+      acc = fmaf(Cm[c * P + r], __ldg(src + e), acc);
+    }
+  }
+
+  // ---------------- the coordinates: W_c from the factor tables ----------------------------------
+  const float* Jm = J + mm * nn;
+  const int rank = tb.rank, width = tb.width;
+  // W_c[s][t] for one ordered pair of factors
+  auto w_entry = [&](int c, int s, int t) {
+    const int32_t* tk = tb.take + ((int64_t)c * rank + s) * width;
+    const int32_t* cl = tb.cols + ((int64_t)c * rank + s) * width;
+    const int it = tb.rows[(int64_t)c * rank + t];
+    float w = 0.f;
+    for (int l = 0; l < width; ++l) {
+      const int32_t at = tk[l];
+      if (at < 0) continue;
+      const int slot = at / nn, e = at - slot * nn;
+      const float v = __ldg(Jm + (int64_t)slot * js + e);
+      const int j = cl[l];
+      w = fmaf(v, tb.transposed ? Cm[it * P + j] : Cm[j * P + it], w);
+    }
+    return w;
+  };
+  for (int c = i; c < tb.n_coords; c += N) {
+    float jc = 0.f;
+    for (int s = 0; s < rank; ++s) {
+      const float wss = w_entry(c, s, s);
+      jc += wss;
+      acc = fmaf(-wss, wss, acc);
+      for (int t = s + 1; t < rank; ++t) acc = fmaf(-2.f * w_entry(c, s, t), w_entry(c, t, s), acc);
+    }
+    if (live) J_out[(int64_t)tb.coords[c] * jos + m] = jc;
+  }
+#pragma unroll
+  for (int o = N / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(mask, acc, o, N);
+  if (live && i == 0) lap_out[m] = acc;
+}
+
+template <int N>
+int32_t launch(const float* A, const float* J, const float* lapA, int64_t n_mat, int64_t js, int n,
+               Tables tb, float* sign, float* logdet, float* J_out, int64_t jos, float* lap_out,
+               cudaStream_t st) {
+  constexpr int MPB = kBlock / N;
+  constexpr size_t smem = (size_t)MPB * 2 * N * (N + 1) * sizeof(float);
+  const int64_t blocks = (n_mat + MPB - 1) / MPB;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_slogdet_sparse: too many matrices");
+  slogdet_sparse_kernel<N><<<(unsigned)blocks, kBlock, smem, st>>>(
+      A, J, lapA, n_mat, js, n, tb, sign, logdet, J_out, jos, lap_out);
+  FL_CHECK_LAUNCH("fl_slogdet_sparse launch");
+  return FL_OK;
+}
+
+}  // namespace
+}  // namespace fl
+
+extern "C" int32_t fl_slogdet_sparse(const float* A, const float* jac, const float* lap,
+                                     int64_t n_mat, int64_t n, int64_t k_slots, int64_t jac_stride,
+                                     const int32_t* take, const int32_t* cols, const int32_t* rows,
+                                     const int32_t* coords, int64_t n_coords, int64_t rank,
+                                     int64_t width, int32_t transposed, float* sign, float* logdet,
+                                     float* jac_out, int64_t jac_out_stride, float* lap_out,
+                                     void* stream) {
+  using namespace fl;
+  FL_REQUIRE(n_mat >= 0 && n >= 1 && k_slots >= 0 && n_coords >= 0 && rank >= 0 && width >= 0 &&
+                 n_coords < (1ll << 31) && rank < (1ll << 15) && width < (1ll << 15) &&
+                 k_slots * n * n < (1ll << 31),
+             FL_EBADSHAPE, "fl_slogdet_sparse: bad sizes n_mat=%lld n=%lld k=%lld coords=%lld",
+             (long long)n_mat, (long long)n, (long long)k_slots, (long long)n_coords);
+  FL_REQUIRE(n <= 32, FL_EUNSUPPORTED, "fl_slogdet_sparse: n=%lld > 32 is not supported",
+             (long long)n);
+  if (n_mat == 0) return FL_OK;
+  FL_REQUIRE(A && lap && sign && logdet && lap_out, FL_EBADSHAPE, "fl_slogdet_sparse: null pointer");
+  const bool any = n_coords > 0 && rank > 0 && width > 0;
+  FL_REQUIRE(!any || (jac && take && cols && rows && coords && jac_out), FL_EBADSHAPE,
+             "fl_slogdet_sparse: null table or Jacobian pointer");
+  FL_REQUIRE(k_slots <= 1 || jac_stride >= n_mat * n * n, FL_EBADSHAPE,
+             "fl_slogdet_sparse: Jacobian row stride too small");
+  FL_REQUIRE(!any || jac_out_stride >= n_mat, FL_EBADSHAPE,
+             "fl_slogdet_sparse: output Jacobian row stride too small");
+  Tables tb{take, cols, rows, coords, any ? (int)n_coords : 0, (int)rank, (int)width,
+            transposed ? 1 : 0};
+  cudaStream_t st = (cudaStream_t)stream;
+  if (n <= 8)
+    return launch<8>(A, jac, lap, n_mat, jac_stride, (int)n, tb, sign, logdet, jac_out,
+                     jac_out_stride, lap_out, st);
+  if (n <= 16)
+    return launch<16>(A, jac, lap, n_mat, jac_stride, (int)n, tb, sign, logdet, jac_out,
+                      jac_out_stride, lap_out, st);
+  return launch<32>(A, jac, lap, n_mat, jac_stride, (int)n, tb, sign, logdet, jac_out,
+                    jac_out_stride, lap_out, st);
+}

@@ -43,7 +43,8 @@ class BatchedConst(torch.Tensor):
 
 _CHAINABLE = frozenset({'tanh', 'silu', 'exp', 'log', 'sqrt', 'rsqrt', 'square', 'sigmoid', 'softplus',
                         'sin', 'cos', 'neg', 'abs', 'reciprocal', 'log1p', 'expm1', 'tan', 'sinh', 'cosh',
-                        'asin', 'acos', 'atan', 'asinh', 'acosh', 'atanh', 'erf', 'erfc', 'relu', 'gelu'})
+                        'asin', 'acos', 'atan', 'asinh', 'acosh', 'atanh', 'erf', 'erfc', 'relu', 'gelu',
+                        'clamp_min', 'clamp_max'})
 
 
 class LaplTensor:
@@ -74,7 +75,8 @@ class LaplTensor:
             else:
                 src, ops = self._chain
                 if len(ops) == 1:  # a single function goes through its registered rule as usual
-                    kw = {'y': int(ops[0][1])} if ops[0][0] == 'integer_pow' else {}
+                    kw = ({'y': int(ops[0][1])} if ops[0][0] == 'integer_pow'
+                          else {'param': ops[0][1]} if ops[0][1] else {})
                     self._arr = _call(ops[0][0], (src,), kw, self.thr)
                 else:
                     self._arr = rules.elementwise_chain(ops, src, self.thr)
@@ -276,7 +278,7 @@ class LaplTensor:
     def __rmatmul__(self, W):
         return self._wrap(_call('dot_general', (W, self.arr), {}, self.thr))
 
-    def _unary(self, key: str):
+    def _unary(self, key: str, param: float = 0.0):
         if (self._terms is not None and self._act is None and key in ('tanh', 'silu', 'exp')
                 and registry.is_builtin(key)):
             # pending sum + elementwise function: one fused pass, still pending so that a residual
@@ -286,9 +288,9 @@ class LaplTensor:
             # scalar functions stay pending so that a run of them becomes one pass
             if self._arr is None and self._chain is not None and len(self._chain[1]) < 4:
                 src, ops = self._chain
-                return LaplTensor(None, self.nb, self.thr, chain=(src, ops + [(key, 0.0)]))
-            return LaplTensor(None, self.nb, self.thr, chain=(self.arr, [(key, 0.0)]))
-        return self._wrap(_call(key, (self.arr,), {}, self.thr))
+                return LaplTensor(None, self.nb, self.thr, chain=(src, ops + [(key, param)]))
+            return LaplTensor(None, self.nb, self.thr, chain=(self.arr, [(key, param)]))
+        return self._wrap(_call(key, (self.arr,), {'param': param} if param else {}, self.thr))
 
     def tanh(self): return self._unary('tanh')
     def exp(self): return self._unary('exp')
@@ -317,6 +319,22 @@ class LaplTensor:
     def erf(self): return self._unary('erf')
     def erfc(self): return self._unary('erfc')
     def relu(self): return self._unary('relu')
+    def maximum(self, o): return self._binary('max', o)
+    def minimum(self, o): return self._binary('min', o)
+
+    def clamp(self, min=None, max=None):
+        """Scalar bounds are the two fused halves of clamp; array bounds go through max / min."""
+        out = self
+        for bound, scalar_op, array_op in ((min, 'clamp_min', 'max'), (max, 'clamp_max', 'min')):
+            if bound is None:
+                continue
+            if isinstance(bound, (int, float)):
+                out = out._unary(scalar_op, float(bound))
+            else:
+                out = out._binary(array_op, bound)
+        return out
+
+    clip = clamp
 
     def detach(self):
         return self._wrap(_call('stop_gradient', (self.arr,), {}, self.thr))
@@ -584,6 +602,15 @@ _TORCH_TABLE: dict[Any, Callable] = {
     torch.add: _binary_fn('add'), torch.sub: _binary_fn('sub'), torch.subtract: _binary_fn('sub'),
     torch.mul: _binary_fn('mul'), torch.multiply: _binary_fn('mul'), torch.div: _binary_fn('div'),
     torch.true_divide: _binary_fn('div'), torch.pow: _pow,
+    torch.maximum: _binary_fn('max'), torch.minimum: _binary_fn('min'),
+    # a plain tensor on the left (`W + t`, `W * t`, `W @ t`) arrives as the Tensor method
+    torch.Tensor.add: _binary_fn('add'), torch.Tensor.__add__: _binary_fn('add'),
+    torch.Tensor.sub: _binary_fn('sub'), torch.Tensor.__sub__: _binary_fn('sub'),
+    torch.Tensor.mul: _binary_fn('mul'), torch.Tensor.__mul__: _binary_fn('mul'),
+    torch.Tensor.div: _binary_fn('div'), torch.Tensor.__truediv__: _binary_fn('div'),
+    torch.Tensor.maximum: _binary_fn('max'), torch.Tensor.minimum: _binary_fn('min'),
+    torch.Tensor.matmul: _matmul, torch.Tensor.__matmul__: _matmul,
+    torch.clamp: _method('clamp'), torch.clip: _method('clamp'),
     torch.matmul: _matmul, torch.nn.functional.linear: _linear,
     torch.sum: _method('sum'), torch.mean: _method('mean'),
     torch.reshape: _method('reshape'), torch.permute: _method('permute'),

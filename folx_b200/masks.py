@@ -258,3 +258,101 @@ def union_rows(masks: Sequence[np.ndarray]):
     cat = np.concatenate(broadcast_except(list(masks), JAC_DIM), axis=JAC_DIM)
     result, inv = np.unique(cat, axis=JAC_DIM, return_inverse=True)
     return result, inv.reshape(-1)
+
+
+# ------------------------------------------------------------------------------------------
+# factor tables of the sparse log-determinant rule (reference: folx/slogdet.py:93-193, 259-293)
+# ------------------------------------------------------------------------------------------
+_MAX_SLOGDET_ENTRIES = 2**24  # size bound of the trace-time analysis, as in folx/slogdet.py:73
+
+
+def slogdet_entry_mask(x0_idx: np.ndarray | None, shape: Sequence[int]) -> np.ndarray | None:
+    """``(slots, n, n)`` input coordinate of every Jacobian entry of a batch of matrices, ``-1``
+    where a slot is unused; ``None`` when the map is dense, differs between the matrices of the
+    batch or is too large to analyse (folx/slogdet.py:93-123)."""
+    if x0_idx is None:
+        return None
+    shape = tuple(shape)
+    k = x0_idx.shape[JAC_DIM]
+    if k * int(np.prod(shape, dtype=np.int64)) > _MAX_SLOGDET_ENTRIES:
+        return None
+    per_matrix = np.broadcast_to(x0_idx, (k, *shape)).reshape(k, -1, *shape[-2:])
+    first = per_matrix[:, 0]
+    if any(s > 1 for s in x0_idx.shape[1:-2]) and not (per_matrix == first[:, None]).all():
+        return None
+    return np.ascontiguousarray(first)
+
+
+def _position_in_run(sorted_keys: np.ndarray):
+    """For a sorted key array: index of every element inside its run of equal keys, the run it
+    belongs to, and the run lengths."""
+    _, start, run, length = np.unique(sorted_keys, return_index=True, return_inverse=True,
+                                      return_counts=True)
+    run = run.reshape(-1)
+    return np.arange(sorted_keys.size) - start[run], run, length
+
+
+def slogdet_factor_tables(mask: np.ndarray, per_entry: bool):
+    """Splits every ``dA/dx_c`` into rank-one factors ``e_i w^T`` (folx/slogdet.py:138-193).
+
+    A factor is one touched row of ``dA/dx_c`` (its supported entries), or with ``per_entry`` one
+    touched entry.  Returns ``(cost, take, cols, rows, coords)``: ``take[c, s, l]`` is the flat
+    ``(slot, row, column)`` address of entry ``l`` of factor ``s`` of coordinate ``coords[c]``
+    (``-1`` = unused), ``cols[c, s, l]`` its column, ``rows[c, s]`` the factor's row; ``cost``
+    counts the multiplications of the contraction the tables describe.  ``None`` if the tables
+    would be too large."""
+    k, n, m = mask.shape
+    slot, row, col = np.nonzero(mask >= 0)
+    coords, c_of = np.unique(mask[slot, row, col], return_inverse=True)
+    c_of = c_of.reshape(-1)
+    factor_key = (c_of * n + row) * m + (col if per_entry else 0)
+    order = np.lexsort((col, factor_key))
+    slot, row, col, c_of, factor_key = slot[order], row[order], col[order], c_of[order], factor_key[order]
+    entry, factor, per_factor = _position_in_run(factor_key)
+    # one representative element per factor gives its coordinate and row; factors are sorted by
+    # coordinate already, so their position inside the coordinate's run is the factor slot
+    _, first = np.unique(factor, return_index=True)
+    f_coord, f_row = c_of[first], row[first]
+    f_slot, _, per_coord = _position_in_run(f_coord)
+    rank, width = int(per_coord.max()), int(per_factor.max())
+    if coords.size * rank * width > _MAX_SLOGDET_ENTRIES:
+        return None
+    take = np.full((coords.size, rank, width), -1, dtype=np.int32)
+    cols = np.zeros((coords.size, rank, width), dtype=np.int32)
+    rows = np.zeros((coords.size, rank), dtype=np.int32)
+    take[c_of, f_slot[factor], entry] = (slot * n + row) * m + col
+    cols[c_of, f_slot[factor], entry] = col
+    rows[f_coord, f_slot] = f_row
+    cost = coords.size * rank * rank * (1 if per_entry else width)
+    return cost, take, cols, rows, coords.astype(np.int32)
+
+
+def plan_sparse_slogdet(x0_idx: np.ndarray | None, shape: Sequence[int], tangents: int):
+    """Cheapest of the four factorisations (rows or entries of ``A``, rows of ``A^T``), if it beats
+    the dense contraction (folx/slogdet.py:259-293).  Returns ``(take, cols, rows, coords,
+    transposed)`` with ``take`` addressing ``A``'s own layout, or ``None`` for the dense rule."""
+    base = slogdet_entry_mask(x0_idx, shape)
+    if base is None or not (base >= 0).any():
+        return None
+    n, m = base.shape[-2:]
+    best = None
+    for transposed in (False, True):
+        mask = np.ascontiguousarray(np.swapaxes(base, -1, -2)) if transposed else base
+        for per_entry in ((False,) if transposed else (False, True)):  # entries are the same either way
+            plan = slogdet_factor_tables(mask, per_entry)
+            if plan is not None and (best is None or plan[0] < best[0]):
+                best = (*plan, transposed)
+    if best is None:
+        return None
+    cost, take, cols, rows, coords, transposed = best
+    # margins of the reference: the gathers cost too, and the tables must not outgrow the
+    # dense intermediate (folx/slogdet.py:286-291)
+    if 4 * cost > tangents * n * m * (n + 1) or cost > 2 * tangents * n * m:
+        return None
+    if transposed:
+        # tables were built on A^T (slot, column, row): address A's (slot, row, column) instead
+        used = take >= 0
+        s, rc = np.divmod(take, n * m)
+        a, b = np.divmod(rc, n)   # (row of A^T = column of A, column of A^T = row of A); A^T is (m, n)
+        take = np.where(used, (s * n + b) * m + a, -1).astype(np.int32)
+    return take, cols, rows, coords, transposed

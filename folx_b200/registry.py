@@ -194,6 +194,20 @@ def _binary(op):
     return rule
 
 
+def _clamp(args, kwargs, sparsity_threshold):
+    """``clamp(lo, x, hi)`` with constant bounds (folx/wrapped_functions.py:435-437): scalar bounds
+    take the fused elementwise halves, array bounds the max / min rules."""
+    lo, x, hi = args
+    for bound, scalar_op, array_op in ((lo, 'clamp_min', 'max'), (hi, 'clamp_max', 'min')):
+        if bound is None:
+            continue
+        if isinstance(bound, (int, float)) or (torch.is_tensor(bound) and bound.numel() == 1):
+            x = rules.elementwise(scalar_op, x, float(bound), sparsity_threshold)
+        else:
+            x = rules.binary(array_op, x, bound, sparsity_threshold)
+    return x
+
+
 def _integer_pow(args, kwargs, sparsity_threshold):
     return rules.elementwise('integer_pow', args[0], kwargs['y'], sparsity_threshold)
 
@@ -282,11 +296,13 @@ def _mhsea(args, kwargs, sparsity_threshold):
 
 for _op in ('tanh', 'exp', 'log', 'sqrt', 'rsqrt', 'square', 'sigmoid', 'softplus', 'silu', 'sin',
             'cos', 'neg', 'abs', 'reciprocal', 'log1p', 'expm1', 'tan', 'sinh', 'cosh', 'asin', 'acos',
-            'atan', 'asinh', 'acosh', 'atanh', 'erf', 'erfc', 'cbrt', 'pow', 'relu', 'gelu'):
+            'atan', 'asinh', 'acosh', 'atanh', 'erf', 'erfc', 'cbrt', 'pow', 'relu', 'gelu',
+            'clamp_min', 'clamp_max'):
     register_function(_op, _unary(_op))
 register_function('logistic', _unary('sigmoid'))
 register_function('integer_pow', _integer_pow)
-for _op in ('add', 'sub', 'mul', 'div'):
+register_function('clamp', _clamp)
+for _op in ('add', 'sub', 'mul', 'div', 'max', 'min'):
     register_function(_op, _binary(_op))
 register_function('add_any', _binary('add'))
 register_function('dot_general', _dot_general)

@@ -103,7 +103,7 @@ _TORCH_UNARY = {
     'cbrt': lambda x: torch.sign(x) * torch.abs(x) ** (1.0 / 3.0), 'relu': torch.relu,
     'gelu': torch.nn.functional.gelu,
 }
-_LINEAR_UNARY = {'neg', 'abs', 'scale', 'shift', 'relu'}
+_LINEAR_UNARY = {'neg', 'abs', 'scale', 'shift', 'relu', 'clamp_min', 'clamp_max'}
 
 
 def elementwise(op: str, a, param: float = 0.0, sparsity_threshold: int = 0):
@@ -116,6 +116,10 @@ def elementwise(op: str, a, param: float = 0.0, sparsity_threshold: int = 0):
             return a * param
         if op == 'shift':
             return a + param
+        if op == 'clamp_min':
+            return torch.clamp(a, min=param)
+        if op == 'clamp_max':
+            return torch.clamp(a, max=param)
         return _TORCH_UNARY[op](a)
     out = kernels.elementwise(op, a, param)
     if op not in _LINEAR_UNARY and a.jacobian.weak and masks.has_duplicate_x0_idx(_mask_nd(a)):
@@ -149,7 +153,9 @@ def elementwise_chain(ops, a, sparsity_threshold: int = 0):
 # ------------------------------------------------------------------------------------------
 def _const_binary(op: str, a: Arr, c, reverse: bool, threshold: int):
     """triplet (op) constant, or constant (op) triplet when ``reverse``."""
-    if not torch.is_tensor(c) or c.numel() == 1:
+    if op in ('max', 'min') and not torch.is_tensor(c):
+        c = torch.full((1,) * max(a.x.ndim, 1), float(c), dtype=a.x.dtype, device=a.x.device)
+    if op not in ('max', 'min') and (not torch.is_tensor(c) or c.numel() == 1):
         s = float(c)
         if op == 'add':
             return elementwise('shift', a, s)
@@ -185,6 +191,13 @@ def _align_rows(a: Arr, row_of: np.ndarray, n_rows: int, shape) -> Arr:
 def binary(op: str, a, b, sparsity_threshold: int = 0):
     ta, tb = is_triplet(a), is_triplet(b)
     if not ta and not tb:
+        if op in ('max', 'min'):
+            fn = torch.maximum if op == 'max' else torch.minimum
+            if not torch.is_tensor(a):
+                a = torch.as_tensor(a, dtype=b.dtype, device=b.device)
+            if not torch.is_tensor(b):
+                b = torch.as_tensor(b, dtype=a.dtype, device=a.device)
+            return fn(a, b)
         return {'add': torch.add, 'sub': torch.sub, 'mul': torch.mul, 'div': torch.div}[op](a, b)
     if ta != tb:
         return _const_binary(op, a if ta else b, b if ta else a, reverse=tb, threshold=sparsity_threshold)
@@ -194,7 +207,7 @@ def binary(op: str, a, b, sparsity_threshold: int = 0):
         a, b = densify(a), densify(b)
         rows = max(a.jacobian.data.shape[0], b.jacobian.data.shape[0])
         a, b = _with_rows(a, rows), _with_rows(b, rows)
-        if op in ('add', 'mul') and tuple(a.x.shape) != shape and tuple(b.x.shape) == shape:
+        if op in ('add', 'mul', 'max', 'min') and tuple(a.x.shape) != shape and tuple(b.x.shape) == shape:
             a, b = b, a  # commutative: keep the full-size operand first, broadcast the other in-kernel
         return kernels.binary(op, broadcast_triplet(a, shape), b)
     # both sparse: rows with identical index maps are merged, the others are kept side by side
@@ -459,21 +472,38 @@ def broadcast_to(a, shape):
 
 
 def getitem(a, index, batch_dims: int = 0):
-    """Basic (static) indexing: ints, slices, ``None`` and ``Ellipsis``."""
+    """Static indexing: ints, slices, ``None``, ``Ellipsis`` and integer arrays (the reference's
+    slice / gather rules, INDEXING flag, folx/wrapped_functions.py:460-462, 497-499: the index map
+    is indexed exactly like the values, folx/jvp.py:378-385)."""
     if not is_triplet(a):
         return a[index]
     if not isinstance(index, tuple):
         index = (index,)
+
+    def is_array(it):
+        return (isinstance(it, (np.ndarray, list))
+                or (torch.is_tensor(it) and not it.dtype.is_floating_point and it.dtype != torch.bool))
+
+    where = [i for i, it in enumerate(index) if is_array(it)]
     for it in index:
-        if not (isinstance(it, (int, slice)) or it is None or it is Ellipsis):
-            raise NotImplementedError('only static basic indexing is supported on triplets')
+        if not (isinstance(it, (int, slice)) or it is None or it is Ellipsis or is_array(it)):
+            raise NotImplementedError('only static indexing (ints, slices, None, ..., integer arrays) '
+                                      'is supported on triplets')
+    if where and where[-1] - where[0] + 1 != len(where):
+        # numpy moves the indexed axes to the front in that case, ahead of the Jacobian axis
+        raise NotImplementedError('integer array indices must be adjacent')
+    host_index = tuple(it.detach().cpu().numpy() if torch.is_tensor(it) else
+                       (np.asarray(it) if isinstance(it, list) else it) for it in index)
+    if where:
+        index = tuple(torch.as_tensor(h, device=a.x.device) if i in where else it
+                      for i, (it, h) in enumerate(zip(index, host_index)))
     m = _full_mask_keep_batch(a, batch_dims)
     jidx = (slice(None), *index)
     if m is not None:
         # an index that selects inside a batch axis does not change the (batch-constant) map
         midx = []
         d = 0
-        for it in index:
+        for it in host_index:
             if it is Ellipsis:
                 midx.append(it)
                 d = a.x.ndim  # everything after an ellipsis counts from the right: never batch
@@ -482,6 +512,8 @@ def getitem(a, index, batch_dims: int = 0):
                 midx.append(it)
                 continue
             if d < batch_dims:
+                if is_array(it):
+                    raise NotImplementedError('integer array index on a walker axis')
                 midx.append(0 if isinstance(it, int) else slice(None))
             else:
                 midx.append(it)
@@ -567,6 +599,12 @@ def slogdet(a, sparsity_threshold: int = 0):
     if not is_triplet(a):
         s, l = torch.linalg.slogdet(a)
         return s, l
+    if a.jacobian.weak and a.x.shape[-1] <= 32:
+        # inputs that touch few rows, columns or entries: the factorised rule on the stored slots
+        # (sparse_slogdet, folx/slogdet.py:259-293); otherwise the dense contraction
+        plan = sparse.plan_slogdet(a)
+        if plan is not None:
+            return sparse.slogdet_sparse(a, plan)
     return kernels.slogdet(a)
 
 

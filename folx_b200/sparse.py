@@ -165,3 +165,50 @@ def index_intersection_device(parts: list[np.ndarray], device) -> np.ndarray:
              _ptr(d_cnt), _stream(device))
     M = int(d_cnt.max().item()) if S else 0
     return d_out[:, :M].cpu().numpy().astype(parts[0].dtype).reshape(*lead, M)
+
+
+_slogdet_plans: dict[tuple, tuple | None] = {}
+
+
+def plan_slogdet(a) -> tuple | None:
+    """Factor tables of the sparse log-determinant rule for this triplet's index map, or ``None``
+    when the dense rule is the cheaper one (folx/slogdet.py:259-293).  Cached per map."""
+    idx = a.jacobian.x0_idx
+    if idx is None:
+        return None
+    shape = tuple(a.x.shape)
+    idx = np.asarray(idx)
+    if idx.ndim != len(shape) + 1:
+        return None
+    key = (hashlib.blake2b(np.ascontiguousarray(idx).tobytes(), digest_size=16).digest(), idx.shape, shape)
+    if key not in _slogdet_plans:
+        _slogdet_plans[key] = masks.plan_sparse_slogdet(idx, shape, a.jacobian.max_n + 1)
+    return _slogdet_plans[key]
+
+
+def slogdet_sparse(a, plan):
+    """``(sign, triplet of log|det|)`` from the stored Jacobian slots and the factor tables of
+    ``plan_slogdet``; the output Jacobian is dense over ``max_n + 1`` inputs, as the reference
+    materialises it (folx/slogdet.py:244-250)."""
+    from .kernels import alloc_triplet, as_contiguous, _jac_stride
+
+    take, cols, rows, coords, transposed = plan
+    a = as_contiguous(a)
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    _require_cuda(x, j, l)
+    n = x.shape[-1]
+    batch = tuple(x.shape[:-2])
+    n_mat = x.numel() // (n * n)
+    k = j.shape[0]
+    K_out = a.jacobian.max_n + 1
+    sign = torch.empty(batch, dtype=torch.float32, device=x.device)
+    out = alloc_triplet(K_out, batch, x.device, None)
+    out.jacobian.data.zero_()
+    dev = x.device
+    lib.call(
+        'fl_slogdet_sparse', _ptr(x), _ptr(j), _ptr(l), n_mat, n, k, _jac_stride(j),
+        _ptr(_device_table(take, dev)), _ptr(_device_table(cols, dev)), _ptr(_device_table(rows, dev)),
+        _ptr(_device_table(coords, dev)), take.shape[0], take.shape[1], take.shape[2], int(transposed),
+        _ptr(sign), _ptr(out.x), _ptr(out.jacobian.data), max(n_mat, 1), _ptr(out.laplacian), _stream(dev),
+    )
+    return sign, out

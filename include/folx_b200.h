@@ -86,7 +86,11 @@ enum {
   FL_OP_POW = 31,   /* y = x^param for x > 0 (pow with a constant exponent) */
   FL_OP_RELU = 32,  /* max(x, 0): linear a.e. */
   FL_OP_GELU = 33,  /* x Phi(x) */
-  FL_OP_COUNT_ = 34
+  /* the two halves of clamp (folx/wrapped_functions.py:435-437): max(x, param) / min(x, param),
+   * derivative 1 strictly inside the bound and 0 elsewhere (the jvp of jax.lax.clamp) */
+  FL_OP_CLAMP_MIN = 34,
+  FL_OP_CLAMP_MAX = 35,
+  FL_OP_COUNT_ = 36
 };
 
 int32_t fl_elementwise(int32_t op, float param,
@@ -118,8 +122,11 @@ int32_t fl_elementwise_chain(int32_t n_ops, const int32_t* ops, const float* par
  * (outer, 1, b_inner): position i of b is (i / (b_inner * b_mid)) * b_inner + i % b_inner.
  * b_mid == 1 means no broadcast; outer == 1 is a bias over the trailing b_inner positions;
  * b_mid == electrons is a per-walker row shared by all electrons.
+ * FL_BIN_MAX / FL_BIN_MIN are the piecewise-linear rules of jax.lax.max / min
+ * (folx/wrapped_functions.py:509-514): value, Jacobian and Laplacian of the selected operand,
+ * shared equally at ties; with a constant operand they give clamp and relu-like functions.
  * ------------------------------------------------------------------------------------------- */
-enum { FL_BIN_ADD = 0, FL_BIN_SUB = 1, FL_BIN_MUL = 2, FL_BIN_DIV = 3 };
+enum { FL_BIN_ADD = 0, FL_BIN_SUB = 1, FL_BIN_MUL = 2, FL_BIN_DIV = 3, FL_BIN_MAX = 4, FL_BIN_MIN = 5 };
 
 int32_t fl_binary(int32_t op,
                   const float* a, const float* jac_a, const float* lap_a, int64_t jac_a_stride,
@@ -326,6 +333,24 @@ int32_t fl_slogdet_strided(const float* A, const float* jac, const float* lap,
                            int64_t row_stride,
                            float* sign, float* logdet, float* jac_out, int64_t jac_out_stride,
                            float* lap_out, void* stream);
+
+/* slogdet of matrices whose Jacobian is SPARSE: every input coordinate touches a few rows,
+ * columns or entries of A.  Replaces sparse_slogdet / _sparse_slogdet / _pack_slogdet
+ * (folx/slogdet.py:196-293).  jac holds the k_slots stored slots (k_slots, n_mat, n, n), rows
+ * jac_stride apart.  The static tables (folx/slogdet.py:138-193, built by the caller from the index
+ * map, shared by all matrices) split dA/dx_c of coordinate c into `rank` factors of `width`
+ * entries: take[c][s][l] = (slot n + row) n + column of entry l of factor s (-1 = unused),
+ * cols[c][s][l] its column, rows[c][s] the factor's row, coords[c] the row of jac_out that
+ * coordinate c writes.  With transposed != 0 the tables describe A^T (cols / rows name rows /
+ * columns of A; take still addresses A).  jac_out rows that no coordinate names are left
+ * untouched: the caller zero-fills jac_out (rows jac_out_stride >= n_mat apart). */
+int32_t fl_slogdet_sparse(const float* A, const float* jac, const float* lap,
+                          int64_t n_mat, int64_t n, int64_t k_slots, int64_t jac_stride,
+                          const int32_t* take, const int32_t* cols, const int32_t* rows,
+                          const int32_t* coords, int64_t n_coords, int64_t rank, int64_t width,
+                          int32_t transposed,
+                          float* sign, float* logdet, float* jac_out, int64_t jac_out_stride,
+                          float* lap_out, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Matrix inverse of a triplet of small square matrices.  Replaces inv_wrapper

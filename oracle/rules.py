@@ -106,6 +106,13 @@ def _derivs(op: str, x: torch.Tensor, param: float = 0.0):
         return x**param, param * x ** (param - 1), param * (param - 1) * x ** (param - 2)
     if op == 'relu':  # piecewise linear (like clamp in the reference): no Hessian term
         return torch.relu(x), (x > 0).to(x.dtype), torch.zeros_like(x)
+    if op in ('clamp_min', 'clamp_max'):
+        # halves of clamp (folx/wrapped_functions.py:435-437): derivative only strictly inside the
+        # bound, as in the jvp of jax.lax.clamp
+        bound = torch.as_tensor(param, dtype=x.dtype)
+        if op == 'clamp_min':
+            return torch.maximum(x, bound), (x > bound).to(x.dtype), torch.zeros_like(x)
+        return torch.minimum(x, bound), (x < bound).to(x.dtype), torch.zeros_like(x)
     if op == 'gelu':
         cdf = 0.5 * (1 + torch.erf(x / math.sqrt(2)))
         pdf = torch.exp(-0.5 * x * x) / math.sqrt(2 * math.pi)
@@ -140,6 +147,14 @@ def binary(op: str, a: Triplet, b: Triplet) -> Triplet:
         lap = (al / bx - ax * bl / bx**2 - 2 / bx**2 * (aJ * bJ).sum(0)
                + 2 * ax / bx**3 * (bJ * bJ).sum(0))
         return y, J, lap
+    if op in ('max', 'min'):
+        # piecewise linear (folx/wrapped_functions.py:509-514): the selected operand's derivatives,
+        # shared equally at ties (the balanced rule of the jvp of jax.lax.max)
+        first = (ax > bx) if op == 'max' else (ax < bx)
+        ca = torch.where(first, 1.0, torch.where(ax == bx, 0.5, 0.0)).to(ax.dtype)
+        cb = 1 - ca
+        y = torch.maximum(ax, bx) if op == 'max' else torch.minimum(ax, bx)
+        return y, ca * aJ + cb * bJ, ca * al + cb * bl
     raise KeyError(op)
 
 
@@ -235,6 +250,30 @@ def slogdet(t: Triplet):
 # (folx/experimental/pallas/attention/utils.py:210-220).
 # q, k, v: (B, n, H, d); *_J: (R, B, n, H, d); mask: (B, n) bool; input_mask: (R, B) bool.
 # --------------------------------------------------------------------------------------------
+def slogdet_sparse(A, J_slots, lap, mask, n_inputs: int):
+    """The sparse log-determinant rule (reference: _sparse_slogdet + _pack_slogdet,
+    folx/slogdet.py:196-256), written per input coordinate without tables: with
+    ``dA_c = sum over slots whose map names c`` restricted to the entries it is supported on,
+    ``W_c = A^-1 dA_c`` restricted to the touched rows,
+    ``J_c = tr(W_c)`` and ``lap = tr(A^-1 lapA) - sum_c tr(W_c W_c)``.
+
+    ``A, lap: (..., n, n)``; ``J_slots: (k, ..., n, n)``; ``mask: (k, n, n)`` input coordinate of
+    every stored entry (-1 = unused).  Returns ``sign, (logdet, J: (n_inputs, ...), lap)``."""
+    sign, logdet = torch.linalg.slogdet(A)
+    A_inv = torch.linalg.inv(A)
+    m = torch.as_tensor(mask)
+    jac = A.new_zeros((n_inputs, *A.shape[:-2]))
+    lapl = torch.einsum('...ji,...ij->...', A_inv, lap)
+    for c in sorted(set(int(v) for v in m.reshape(-1).tolist() if v >= 0)):
+        dA = (J_slots * (m == c).reshape(m.shape[0], *((1,) * (A.ndim - 2)), *m.shape[1:])).sum(0)
+        touched = torch.nonzero((m == c).any(0).any(-1)).reshape(-1)  # rows of A this input moves
+        # the small matrix W_c[s, t] = sum_j dA_c[i_s, j] A^-1[j, i_t]
+        W = dA[..., touched, :] @ A_inv[..., :, touched]
+        jac[c] = torch.einsum('...ss->...', W)
+        lapl = lapl - torch.einsum('...st,...ts->...', W, W)
+    return sign, (logdet, jac, lapl)
+
+
 def det(t: Triplet) -> Triplet:
     """``det A`` from the log-determinant rule (reference: det_wrapper, folx/slogdet.py:361-395):
     ``J = det J_log``, ``lap = det (lap_log + sum_k J_log_k^2)``."""

@@ -249,6 +249,79 @@ def test_scalar_functions_of_the_registry_through_torch(cuda_device, thr):
     check_against_brute(lambda z: f(Wd, z), lambda z: f(W64, z), x, thr, samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
 
 
+@pytest.mark.parametrize('thr', [0, 4])
+def test_max_min_and_clamp_through_torch(cuda_device, thr):
+    """The piecewise linear rules (max, min, clamp; folx/wrapped_functions.py:435-437, 509-514):
+    between triplets, against constants, and with scalar bounds (the fused clamp halves)."""
+    g = torch.Generator().manual_seed(43)
+    W = torch.randn(4, 6, generator=g) * 0.7
+    c = torch.randn(6, generator=g) * 0.3
+
+    def f(p, x):
+        Wm, cm = p
+        h = torch.tanh(x @ Wm)
+        a = torch.maximum(h, torch.sin(h * 3.0)) * torch.minimum(h, cm)
+        b = torch.clamp(h * h, 0.1, 0.6) + h.clamp(min=-0.2) * torch.clamp(h, max=0.3)
+        return (a + b * torch.exp(h)).sum()
+
+    x = torch.randn(3, 5, 4, generator=g).to(cuda_device)
+    pd, p64 = (W.to(cuda_device), c.to(cuda_device)), (W.double(), c.double())
+    check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), x, thr, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+
+
+@pytest.mark.parametrize('mode,expect_fast', [('row_sparse', True), ('two_rows', True), ('columns', True),
+                                              ('two_columns', True), ('shared_rows', False), ('batched', True)])
+def test_slogdet_of_sparse_orbitals(cuda_device, mode, expect_fast):
+    """The cases of the reference's sparse log-determinant test (test/test_layers.py:340-396): every
+    row (column) of the orbital matrix depends on one particle, on two, or on all of them; the
+    factorised kernel runs exactly when the structure pays off and the result equals brute force."""
+    from folx_b200 import lib
+    n = 6
+    g = torch.Generator().manual_seed(53)
+    w = torch.randn(n, 3, n, generator=g)
+    x = torch.randn(2, n, 3, generator=g).to(cuda_device)
+
+    def f(wm, z):
+        A = (z[:, :, None] * wm).sum(1)                      # A[i, j] = sum_d z[i, d] w[i, d, j]
+        if mode in ('columns', 'two_columns'):
+            A = A.transpose(0, 1)
+            if mode == 'two_columns':
+                A = A + torch.cat([A[:, -1:], A[:, :-1]], dim=1)
+        elif mode == 'two_rows':
+            A = A + torch.cat([A[-1:], A[:-1]], dim=0)
+        elif mode == 'shared_rows':
+            A = A + z.sum()
+        eye = 1.5 * torch.eye(n, dtype=z.dtype, device=z.device)   # keeps fp32 elimination well conditioned
+        if mode == 'batched':
+            orb = torch.stack([torch.tanh(A) + eye, torch.sin(A) + eye])[None]   # (mol, det, elec, orb)
+        else:
+            orb = torch.tanh(A) + eye
+        return torch.linalg.slogdet(orb)[1].sum()
+
+    wd, w64 = w.to(cuda_device), w.double()
+    for thr in (0, 3 * n):
+        before = lib.LAUNCH_COUNTS.get('fl_slogdet_sparse', 0)
+        check_against_brute(lambda z: f(wd, z), lambda z: f(w64, z), x, thr, samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
+        fast = lib.LAUNCH_COUNTS.get('fl_slogdet_sparse', 0) > before
+        assert fast == (expect_fast and thr > 0)
+
+
+def test_slogdet_of_entry_sparse_matrix(cuda_device):
+    """Every input touches one entry per row (test/test_layers.py:398-420): neither orientation has
+    low rank, so the factors are single entries -- n factors of one entry per input."""
+    from folx_b200 import masks
+    n = 6
+    perm = torch.stack([torch.roll(torch.arange(n), s) for s in range(n)])
+    x = torch.randn(2, n, generator=torch.Generator().manual_seed(59)).to(cuda_device)
+
+    def f(z):
+        return torch.linalg.slogdet(2 * torch.eye(n, dtype=z.dtype, device=z.device) + 0.5 * torch.tanh(z)[perm.to(z.device)])[1]
+
+    check_against_brute(f, f, x, n, samples=(0, 1), rtol=2e-4, lap_rtol=1e-3)
+    plan = masks.plan_sparse_slogdet(perm.numpy()[None], (n, n), n)
+    assert plan is not None and plan[0].shape == (n, n, 1)
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

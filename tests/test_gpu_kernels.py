@@ -37,7 +37,8 @@ def test_elementwise(cuda_device, op, K, shape):
 
 @pytest.mark.parametrize('op,param', [('integer_pow', 2), ('integer_pow', 3), ('integer_pow', -1),
                                       ('integer_pow', -2), ('scale', 0.37), ('shift', -1.5),
-                                      ('pow', 1.7), ('pow', -0.3)])
+                                      ('pow', 1.7), ('pow', -0.3), ('clamp_min', 0.6),
+                                      ('clamp_max', 1.1)])
 def test_elementwise_param(cuda_device, op, param):
     t = seeded_triplet(6, (10, 12), seed=2, positive=True)
     got = kernels.elementwise(op, to_device(t, cuda_device), param)
@@ -89,7 +90,7 @@ def test_elementwise_bench_shape_properties(cuda_device):
     torch.testing.assert_close(out2.jacobian.data, 2 * out.jacobian.data, rtol=1e-6, atol=1e-6)
 
 
-@pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div'])
+@pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div', 'max', 'min'])
 @pytest.mark.parametrize('K,shape', [(0, (4,)), (5, (6, 7)), (12, (3, 4, 8))])
 def test_binary(cuda_device, op, K, shape):
     a = seeded_triplet(K, shape, seed=4)
@@ -98,7 +99,19 @@ def test_binary(cuda_device, op, K, shape):
     assert_close(to_host(got), rules.binary(op, a, b))
 
 
-@pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div'])
+@pytest.mark.parametrize('op', ['max', 'min'])
+def test_max_min_share_derivatives_at_ties(cuda_device, op):
+    """Equal operands: both Jacobians and Laplacians enter with weight one half."""
+    a = seeded_triplet(4, (6, 8), seed=21)
+    b = seeded_triplet(4, (6, 8), seed=22)
+    b = (torch.where(a[0] > 0, a[0], b[0]), b[1], b[2])   # ties wherever a is positive
+    got = to_host(kernels.binary(op, to_device(a, cuda_device), to_device(b, cuda_device)))
+    assert_close(got, rules.binary(op, a, b))
+    tie = a[0] > 0
+    torch.testing.assert_close(got[1][:, tie].double(), 0.5 * (a[1] + b[1])[:, tie], rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div', 'max', 'min'])
 def test_binary_constant_and_broadcast(cuda_device, op):
     K, shape = 5, (6, 8)
     a = seeded_triplet(K, shape, seed=6, positive=True)

@@ -4,6 +4,7 @@ The reference has no stored float vectors; its tests assert exactly this identit
 (test/laplacian_testcase.py:22-49), so this is the float-path pin of the oracle.
 """
 
+import numpy as np
 import pytest
 import torch
 
@@ -66,6 +67,17 @@ def test_restricted_domain_elementwise_matches_brute_force(op):
 def test_pow_with_constant_exponent():
     t = rand_triplet(4, (6,), positive=True)
     assert_triplet_close(rules.elementwise('pow', t, 1.7), brute.propagate(lambda x: x**1.7, [t]))
+
+
+@pytest.mark.parametrize('op,bound', [('clamp_min', 0.2), ('clamp_max', -0.1)])
+def test_clamp_halves(op, bound):
+    t = rand_triplet(4, (3, 6))
+    fn = (lambda x: torch.clamp(x, min=bound)) if op == 'clamp_min' else (lambda x: torch.clamp(x, max=bound))
+    assert_triplet_close(rules.elementwise(op, t, bound), brute.propagate(fn, [t]))
+    # on the bound itself the derivative is dropped (the jvp of jax.lax.clamp)
+    x = torch.full((2,), bound, dtype=torch.float64)
+    _, J, lap = rules.elementwise(op, (x, torch.ones(3, 2, dtype=torch.float64), torch.ones(2, dtype=torch.float64)), bound)
+    assert float(J.abs().sum()) == 0.0 and float(lap.abs().sum()) == 0.0
 
 
 @pytest.mark.parametrize('n', [-2, -1, 2, 3])
@@ -219,6 +231,45 @@ def test_mhsa_input_mask_drops_hessian_terms_of_masked_coordinates():
     a = rules.mhsa(q, k, v, mask, input_mask)
     b = rules.mhsa(z(q), z(k), z(v), mask, torch.ones(R, B, dtype=torch.bool))
     torch.testing.assert_close(a[2], b[2], rtol=1e-10, atol=1e-12)
+
+
+@pytest.mark.parametrize('op,fn', [('max', torch.maximum), ('min', torch.minimum)])
+def test_max_min_match_brute_force(op, fn):
+    a = rand_triplet(4, (3, 5), seed=41)
+    b = rand_triplet(4, (3, 5), seed=42)
+    assert_triplet_close(rules.binary(op, a, b), brute.propagate(fn, [a, b]))
+
+
+@pytest.mark.parametrize('mode', ['rows', 'two_rows', 'columns', 'entries'])
+def test_sparse_slogdet_equals_dense_rule(mode):
+    """The per-coordinate form (folx/slogdet.py:196-256) against the dense rule on the densified
+    Jacobian, on the index maps of the reference's test/test_layers.py:340-420."""
+    g = torch.Generator().manual_seed(7)
+    n, B = 5, 3
+    if mode == 'entries':
+        mask = np.stack([np.roll(np.arange(n), s) for s in range(n)])[None]      # (1, n, n)
+    else:
+        mask = np.zeros((3, n, n), dtype=np.int64)
+        for k in range(3):
+            mask[k] = (3 * np.arange(n) + k)[:, None]
+        if mode == 'two_rows':
+            mask = np.concatenate([mask, np.roll(mask, 1, axis=1)], axis=0)      # 6 slots
+        if mode == 'columns':
+            mask = np.swapaxes(mask, -1, -2).copy()
+    k = mask.shape[0]
+    A = torch.randn(B, n, n, dtype=torch.float64, generator=g) + 2 * torch.eye(n, dtype=torch.float64)
+    J = torch.randn(k, B, n, n, dtype=torch.float64, generator=g)
+    lap = torch.randn(B, n, n, dtype=torch.float64, generator=g)
+    n_in = int(mask.max()) + 1
+    dense = torch.zeros(n_in, B, n, n, dtype=torch.float64)
+    for s in range(k):
+        for i in range(n):
+            for j in range(n):
+                dense[mask[s, i, j], :, i, j] += J[s, :, i, j]
+    sign_d, want = rules.slogdet((A, dense, lap))
+    sign_s, got = rules.slogdet_sparse(A, J, lap, mask, n_in)
+    torch.testing.assert_close(sign_s, sign_d)
+    assert_triplet_close(got, want)
 
 
 def test_dot_general_pair_matches_brute_force():
