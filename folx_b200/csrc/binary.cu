@@ -171,8 +171,71 @@ int32_t dispatch(const float* a, const float* ja, const float* la, int64_t jas, 
   return launch<OP, float>(a, ja, la, jas, b, jb, lb, jbs, y, jy, ly, jys, K, N, inner, mid, st);
 }
 
+// y = cond ? a : b on every field of the triplet (select_n / where: an indexing rule, the
+// derivatives of the chosen operand pass through; folx/wrapped_functions.py:494-496).  Grid:
+// (positions, K + 2 rows); a constant operand has zero Jacobian and Laplacian.
+template <typename V>
+__global__ void __launch_bounds__(256)
+select_kernel(const uint8_t* __restrict__ cond, const V* __restrict__ a, const V* __restrict__ ja,
+              const V* __restrict__ la, int64_t jas, const V* __restrict__ b,
+              const V* __restrict__ jb, const V* __restrict__ lb, int64_t jbs, V* __restrict__ y,
+              V* __restrict__ jy, V* __restrict__ ly, int64_t jys, int K, int64_t N) {
+  using L = Lanes<V>;
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= N) return;
+  const int row = blockIdx.y;  // 0: x, 1 .. K: Jacobian rows, K + 1: lap
+  const V* pa = row == 0 ? a : row <= K ? (ja ? ja + (int64_t)(row - 1) * jas : nullptr) : la;
+  const V* pb = row == 0 ? b : row <= K ? (jb ? jb + (int64_t)(row - 1) * jbs : nullptr) : lb;
+  V* py = row == 0 ? y : row <= K ? jy + (int64_t)(row - 1) * jys : ly;
+  V va, vb, out;
+#pragma unroll
+  for (int l = 0; l < L::n; ++l) { L::set(va, l, 0.f); L::set(vb, l, 0.f); }
+  if (pa) va = __ldcs(pa + i);
+  if (pb) vb = __ldcs(pb + i);
+#pragma unroll
+  for (int l = 0; l < L::n; ++l)
+    L::set(out, l, cond[i * L::n + l] ? L::get(va, l) : L::get(vb, l));
+  __stcs(py + i, out);
+}
+
 }  // namespace
 }  // namespace fl
+
+extern "C" int32_t fl_select(const uint8_t* cond, const float* a, const float* jac_a,
+                             const float* lap_a, int64_t jac_a_stride, const float* b,
+                             const float* jac_b, const float* lap_b, int64_t jac_b_stride, float* y,
+                             float* jac_y, float* lap_y, int64_t jac_y_stride, int64_t K, int64_t N,
+                             void* stream) {
+  using namespace fl;
+  FL_REQUIRE(K >= 0 && N >= 0 && K + 2 < 65536 && (N + 255) / 256 < (1ll << 31), FL_EBADSHAPE,
+             "fl_select: bad sizes K=%lld N=%lld", (long long)K, (long long)N);
+  if (N == 0) return FL_OK;
+  FL_REQUIRE(cond && a && b && y && lap_y && (K == 0 || jac_y), FL_EBADSHAPE,
+             "fl_select: null pointer");
+  FL_REQUIRE((lap_a != nullptr || jac_a == nullptr) && (lap_b != nullptr || jac_b == nullptr) &&
+                 (K == 0 || ((lap_a == nullptr) == (jac_a == nullptr) &&
+                             (lap_b == nullptr) == (jac_b == nullptr))),
+             FL_EBADSHAPE, "fl_select: jac and lap of an operand must both be given or both NULL");
+  cudaStream_t st = (cudaStream_t)stream;
+  auto al = [](const void* p) { return p == nullptr || aligned16(p); };
+  const bool vec = N % 4 == 0 && jac_a_stride % 4 == 0 && jac_b_stride % 4 == 0 &&
+                   jac_y_stride % 4 == 0 && al(a) && al(jac_a) && al(lap_a) && al(b) && al(jac_b) &&
+                   al(lap_b) && al(y) && al(jac_y) && al(lap_y);
+  if (vec) {
+    const int64_t n = N / 4;
+    dim3 grid((unsigned)((n + 255) / 256), (unsigned)(K + 2));
+    select_kernel<float4><<<grid, 256, 0, st>>>(
+        cond, (const float4*)a, (const float4*)jac_a, (const float4*)lap_a, jac_a_stride / 4,
+        (const float4*)b, (const float4*)jac_b, (const float4*)lap_b, jac_b_stride / 4, (float4*)y,
+        (float4*)jac_y, (float4*)lap_y, jac_y_stride / 4, (int)K, n);
+  } else {
+    dim3 grid((unsigned)((N + 255) / 256), (unsigned)(K + 2));
+    select_kernel<float><<<grid, 256, 0, st>>>(cond, a, jac_a, lap_a, jac_a_stride, b, jac_b, lap_b,
+                                               jac_b_stride, y, jac_y, lap_y, jac_y_stride, (int)K, N);
+  }
+  FL_CHECK_LAUNCH("fl_select launch");
+  return FL_OK;
+}
 
 extern "C" int32_t fl_binary(int32_t op, const float* a, const float* jac_a, const float* lap_a,
                              int64_t jac_a_stride, const float* b, const float* jac_b,

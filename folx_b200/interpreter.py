@@ -356,6 +356,24 @@ class LaplTensor:
         axes = tuple(self._axis(d) for d in dims)
         return self._wrap(_call('reduce_sum', (self.arr,), {'axes': axes, 'keepdim': keepdim}, self.thr))
 
+    def _reduce(self, key, dim, keepdim):
+        if dim is None:
+            dim = tuple(range(self.ndim))
+        dims = (dim,) if isinstance(dim, int) else tuple(dim)
+        axes = tuple(self._axis(d) for d in dims)
+        return self._wrap(_call(key, (self.arr,), {'axes': axes, 'keepdim': keepdim}, self.thr))
+
+    def amax(self, dim=None, keepdim=False): return self._reduce('reduce_max', dim, keepdim)
+    def amin(self, dim=None, keepdim=False): return self._reduce('reduce_min', dim, keepdim)
+    def prod(self, dim=None, keepdim=False): return self._reduce('reduce_prod', dim, keepdim)
+
+    def cumsum(self, dim):
+        return self._wrap(_call('cumsum', (self.arr,), {'axis': self._axis(dim)}, self.thr))
+
+    def flip(self, *dims):
+        dims = dims[0] if len(dims) == 1 and isinstance(dims[0], (tuple, list)) else dims
+        return self._wrap(_call('rev', (self.arr,), {'dimensions': tuple(self._axis(d) for d in dims)}, self.thr))
+
     def mean(self, dim=None, keepdim=False):
         if dim is None:
             dim = tuple(range(self.ndim))
@@ -558,6 +576,48 @@ def _logsumexp(x, dim, keepdim=False):
     return out if keepdim else out.squeeze(dim)
 
 
+def _where(cond, a, b):
+    """``torch.where`` with triplets among the branches: all three operands are brought to one
+    per-walker rank with the walker axes in front, then the select rule runs."""
+    parts = [cond, a, b]
+    if not any(isinstance(v, LaplTensor) for v in (a, b)):
+        # only the condition was traced: nothing differentiable is selected
+        strip = lambda v: v._wrap(v.arr.x) if isinstance(v, LaplTensor) else v
+        return torch.where(strip(cond), a, b)
+    lt = _first((a, b))
+    nb = lt.nb
+
+    def rank_of(v):
+        if isinstance(v, LaplTensor):
+            return v.ndim
+        if isinstance(v, BatchedConst):
+            return v.ndim - nb
+        return v.ndim if torch.is_tensor(v) else 0
+
+    rank = max(rank_of(v) for v in parts)
+
+    def phys(v):
+        if isinstance(v, LaplTensor):
+            return v._rank_to(rank).arr
+        if isinstance(v, BatchedConst):
+            t = v.as_subclass(torch.Tensor)
+            return t.reshape(*t.shape[:nb], *((1,) * (rank - (t.ndim - nb))), *t.shape[nb:])
+        return v
+
+    c = phys(cond)
+    c = c.x if isinstance(c, FwdLaplArray) else c
+    return lt._wrap(_call('where', (c, phys(a), phys(b)), {}, lt.thr))
+
+
+def _pad(x, pad, mode='constant', value=None):
+    if mode != 'constant':
+        raise NotImplementedError('only constant padding has a rule on triplets')
+    if len(pad) // 2 > x.ndim:
+        raise ValueError('padding reaches into the walker axes')
+    kw = {'padding': tuple(pad), 'value': 0.0 if value is None else float(value), 'batch_dims': x.nb}
+    return x._wrap(_call('pad', (x.arr,), kw, x.thr))
+
+
 def _softmax_unsupported(*a, **k):
     raise NotImplementedError(
         'softmax on triplets is only available inside the fused attention rule '
@@ -611,6 +671,9 @@ _TORCH_TABLE: dict[Any, Callable] = {
     torch.Tensor.maximum: _binary_fn('max'), torch.Tensor.minimum: _binary_fn('min'),
     torch.Tensor.matmul: _matmul, torch.Tensor.__matmul__: _matmul,
     torch.clamp: _method('clamp'), torch.clip: _method('clamp'),
+    torch.where: _where, torch.Tensor.where: _where,
+    torch.amax: _method('amax'), torch.amin: _method('amin'), torch.prod: _method('prod'),
+    torch.cumsum: _method('cumsum'), torch.flip: _method('flip'), torch.nn.functional.pad: _pad,
     torch.matmul: _matmul, torch.nn.functional.linear: _linear,
     torch.sum: _method('sum'), torch.mean: _method('mean'),
     torch.reshape: _method('reshape'), torch.permute: _method('permute'),

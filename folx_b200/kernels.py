@@ -175,6 +175,42 @@ def binary(op: str, a, b, x0_idx: np.ndarray | None = None) -> FwdLaplArray:
     return out
 
 
+def select(cond: torch.Tensor, a, b, x0_idx: np.ndarray | None = None) -> FwdLaplArray:
+    """``where(cond, a, b)`` on every field (folx/wrapped_functions.py:494-496).  ``cond``, ``a`` and
+    ``b`` have the output shape; two triplets have aligned Jacobian rows, a plain tensor is a
+    constant."""
+    a_t, b_t = isinstance(a, FwdLaplArray), isinstance(b, FwdLaplArray)
+    assert a_t or b_t
+    if a_t:
+        a = as_contiguous(a)
+    if b_t:
+        b = as_contiguous(b)
+    ax = a.x if a_t else a.contiguous()
+    bx = b.x if b_t else b.contiguous()
+    cond = cond.to(torch.bool).contiguous()
+    _require_cuda(ax, bx)
+    if not cond.is_cuda:
+        raise RuntimeError('select: the condition must be a CUDA tensor')
+    if not (tuple(ax.shape) == tuple(bx.shape) == tuple(cond.shape)):
+        raise ValueError('select: cond, a and b must share one shape')
+    K = a.jacobian.data.shape[0] if a_t else b.jacobian.data.shape[0]
+    if a_t and b_t and b.jacobian.data.shape[0] != K:
+        raise ValueError('select: operands have different numbers of Jacobian rows')
+    if x0_idx is None:
+        x0_idx = a.jacobian.x0_idx if a_t else b.jacobian.x0_idx
+    out = alloc_triplet(K, ax.shape, ax.device, x0_idx)
+    ja = a.jacobian.data if a_t else None
+    jb = b.jacobian.data if b_t else None
+    lib.call(
+        'fl_select', _ptr(cond),
+        _ptr(ax), _ptr(ja), _ptr(a.laplacian if a_t else None), _jac_stride(ja) if a_t else 0,
+        _ptr(bx), _ptr(jb), _ptr(b.laplacian if b_t else None), _jac_stride(jb) if b_t else 0,
+        _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), _jac_stride(out.jacobian.data),
+        K, ax.numel(), _stream(ax.device),
+    )
+    return out
+
+
 class _WeightCache:
     """Split-W workspaces keyed by the weight tensor (redone when the tensor is modified)."""
 

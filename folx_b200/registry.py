@@ -235,6 +235,39 @@ def _reduce_sum(args, kwargs, sparsity_threshold):
     return rules.reduce_sum(args[0], kwargs['axes'], kwargs.get('keepdim', False), sparsity_threshold)
 
 
+def _prod_over(x, axes, keepdim):
+    axes = sorted((axes,) if isinstance(axes, int) else axes, reverse=True)
+    for ax in axes:
+        x = torch.prod(x, dim=ax, keepdim=keepdim)
+    return x
+
+
+def _reduce_extreme(op):
+    def rule(args, kwargs, sparsity_threshold):
+        return rules.reduce_extreme(op, args[0], kwargs['axes'], kwargs.get('keepdim', False), sparsity_threshold)
+
+    rule.__name__ = f'reduce_{op}'
+    return rule
+
+
+def _select_n(args, kwargs, sparsity_threshold):
+    """``select_n(which, case_false, case_true)`` in the operand order of jax.lax.select_n."""
+    which, if_false, if_true = args
+    return rules.where(which, if_true, if_false, sparsity_threshold)
+
+
+def _where(args, kwargs, sparsity_threshold):
+    return rules.where(args[0], args[1], args[2], sparsity_threshold)
+
+
+def _rev(args, kwargs, sparsity_threshold):
+    return rules.flip(args[0], kwargs['dimensions'])
+
+
+def _pad(args, kwargs, sparsity_threshold):
+    return rules.pad(args[0], kwargs['padding'], kwargs.get('value', 0.0), kwargs.get('batch_dims', 0))
+
+
 def _reshape(args, kwargs, sparsity_threshold):
     return rules.reshape(args[0], kwargs['new_sizes'], kwargs.get('batch_dims', 0))
 
@@ -307,6 +340,29 @@ for _op in ('add', 'sub', 'mul', 'div', 'max', 'min'):
 register_function('add_any', _binary('add'))
 register_function('dot_general', _dot_general)
 register_function('reduce_sum', _reduce_sum)
+register_function('reduce_max', _reduce_extreme('max'))
+register_function('reduce_min', _reduce_extreme('min'))
+register_function('select_n', _select_n)
+register_function('where', _where)
+register_function('rev', _rev)
+register_function('pad', _pad)
+# functions without a kernel of their own: the dense autodiff rule (the generic path of
+# folx/wrapper.py:73-138 for the registry entries of folx/wrapped_functions.py:402-456)
+register_function('reduce_prod', wrap_forward_laplacian(
+    lambda x, axes, keepdim=False: _prod_over(x, axes, keepdim), name='reduce_prod'))
+register_function('cumsum', wrap_forward_laplacian(
+    lambda x, axis=0: torch.cumsum(x, dim=axis), flags=FunctionFlags.LINEAR, name='cumsum'))
+register_function('cumprod', wrap_forward_laplacian(
+    lambda x, axis=0: torch.cumprod(x, dim=axis), name='cumprod'))
+register_function('cummax', wrap_forward_laplacian(
+    lambda x, axis=0: torch.cummax(x, dim=axis).values, flags=FunctionFlags.LINEAR, name='cummax'))
+register_function('cummin', wrap_forward_laplacian(
+    lambda x, axis=0: torch.cummin(x, dim=axis).values, flags=FunctionFlags.LINEAR, name='cummin'))
+register_function('atan2', wrap_forward_laplacian(torch.atan2, in_axes=(), name='atan2'))
+register_function('rem', wrap_forward_laplacian(torch.fmod, in_axes=(), flags=FunctionFlags.LINEAR, name='rem'))
+register_function('erf_inv', wrap_forward_laplacian(torch.erfinv, in_axes=(), name='erf_inv'))
+register_function('lgamma', wrap_forward_laplacian(torch.lgamma, in_axes=(), name='lgamma'))
+register_function('digamma', wrap_forward_laplacian(torch.digamma, in_axes=(), name='digamma'))
 register_function('reshape', _reshape)
 register_function('transpose', _transpose)
 register_function('broadcast_in_dim', _broadcast_in_dim)
@@ -324,7 +380,8 @@ register_function('_multi_head_self_edge_attention', _mhsea)
 register_function('stop_gradient', warp_without_fwd_laplacian(lambda x: x))
 for _name, _fn in (('eq', torch.eq), ('lt', torch.lt), ('le', torch.le), ('gt', torch.gt),
                    ('ge', torch.ge), ('ne', torch.ne), ('sign', torch.sign), ('floor', torch.floor),
-                   ('ceil', torch.ceil), ('round', torch.round), ('is_finite', torch.isfinite)):
+                   ('ceil', torch.ceil), ('round', torch.round), ('is_finite', torch.isfinite),
+                   ('argmax', torch.argmax), ('argmin', torch.argmin)):
     register_function(_name, warp_without_fwd_laplacian(_fn))
 
 # The rules above, as shipped.  The front end fuses chains of additions with a following

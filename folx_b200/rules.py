@@ -212,6 +212,20 @@ def binary(op: str, a, b, sparsity_threshold: int = 0):
         return kernels.binary(op, broadcast_triplet(a, shape), b)
     # both sparse: rows with identical index maps are merged, the others are kept side by side
     a, b = broadcast_triplet(a, shape), broadcast_triplet(b, shape)
+    aa, bb, result_mask = _union_aligned(a, b, shape)
+    out = kernels.binary(op, aa, bb, x0_idx=result_mask)
+    if op in ('mul', 'div') and masks.has_duplicate_x0_idx(result_mask):
+        # two rows of the union may name the same input at a position (e.g. the i == j pairs of
+        # r_i - r_j); the Hessian term then needs the per-position frame (folx/hessian.py:472-501)
+        am, bm = _merged_pair(a, b)
+        fix = kernels.binary(op, am, bm)
+        out = FwdLaplArray(out.x, out.jacobian, fix.laplacian)
+    return out
+
+
+def _union_aligned(a: Arr, b: Arr, shape):
+    """Two sparse triplets of the same shape on one row frame: rows with identical index maps are
+    merged, the others are kept side by side (FwdJacobian.__add__, folx/api.py:230-249)."""
     ma, mb = masks.broadcast_except([_mask_nd(a), _mask_nd(b)], JAC_DIM)
     result_mask, inv = masks.union_rows([ma, mb])
     Ka = ma.shape[0]
@@ -221,14 +235,95 @@ def binary(op: str, a, b, sparsity_threshold: int = 0):
     # equal, already ordered index maps: rows correspond one to one and nothing has to move
     aa = a if in_place else _align_rows(a, inv[:Ka], n_rows, shape)
     bb = b if in_place else _align_rows(b, inv[Ka:], n_rows, shape)
-    out = kernels.binary(op, aa, bb, x0_idx=result_mask)
-    if op in ('mul', 'div') and masks.has_duplicate_x0_idx(result_mask):
-        # two rows of the union may name the same input at a position (e.g. the i == j pairs of
-        # r_i - r_j); the Hessian term then needs the per-position frame (folx/hessian.py:472-501)
-        am, bm = _merged_pair(a, b)
-        fix = kernels.binary(op, am, bm)
-        out = FwdLaplArray(out.x, out.jacobian, fix.laplacian)
-    return out
+    return aa, bb, result_mask
+
+
+def where(cond, a, b, sparsity_threshold: int = 0):
+    """``where(cond, a, b)`` (reference: select_n, an INDEXING rule, folx/wrapped_functions.py:
+    494-496): the chosen operand's value, Jacobian and Laplacian pass through.  Two sparse operands
+    are first put on the union of their row frames, so the result stays sparse whatever ``cond``
+    holds."""
+    ta, tb = is_triplet(a), is_triplet(b)
+    if is_triplet(cond):
+        cond = cond.x
+    if not ta and not tb:
+        return torch.where(cond, a, b)
+    ref = (a if ta else b).x
+    as_const = lambda c: (c if torch.is_tensor(c) else torch.as_tensor(c)).to(device=ref.device, dtype=ref.dtype)
+    if not ta:
+        a = as_const(a)
+    if not tb:
+        b = as_const(b)
+    shape = tuple(torch.broadcast_shapes(cond.shape, (a.x if ta else a).shape, (b.x if tb else b).shape))
+    cond = cond.to(ref.device).expand(shape)
+    a = broadcast_triplet(a, shape) if ta else a.expand(shape)
+    b = broadcast_triplet(b, shape) if tb else b.expand(shape)
+    if ta and tb:
+        if a.jacobian.weak and b.jacobian.weak:
+            aa, bb, result_mask = _union_aligned(a, b, shape)
+            return kernels.select(cond, aa, bb, x0_idx=result_mask)
+        a, b = densify(a), densify(b)
+        rows = max(a.jacobian.data.shape[0], b.jacobian.data.shape[0])
+        a, b = _with_rows(a, rows), _with_rows(b, rows)
+    return kernels.select(cond, a, b)
+
+
+def reduce_extreme(op: str, a, axes, keepdim: bool = False, sparsity_threshold: int = 0):
+    """``max`` / ``min`` over ``axes`` (reference: reduce_max / reduce_min, REDUCTION | LINEAR,
+    folx/wrapped_functions.py:392-401): the derivatives of the extreme element pass through, ties
+    share them equally (the jvp of jax.lax.reduce_max).  Evaluated as a weighted sum with the
+    constant weights ``[x == extreme] / #ties``."""
+    pick = torch.amax if op == 'max' else torch.amin
+    if not is_triplet(a):
+        return pick(a, dim=axes, keepdim=keepdim)
+    nd = a.x.ndim
+    axes = tuple(sorted({ax % nd for ax in (axes if isinstance(axes, (tuple, list)) else (axes,))}))
+    if not axes:
+        return a
+    ext = pick(a.x, dim=axes, keepdim=True)
+    hit = (a.x == ext).to(a.x.dtype)
+    out = reduce_sum(binary('mul', a, hit / hit.sum(dim=axes, keepdim=True), sparsity_threshold),
+                     axes, keepdim, sparsity_threshold)
+    # the weighted sum of the values is the extreme itself; keep it free of rounding
+    return FwdLaplArray(ext if keepdim else ext.reshape(out.x.shape), out.jacobian, out.laplacian)
+
+
+def flip(a, dims):
+    """Reverses axes (reference: rev, INDEXING, folx/wrapped_functions.py:506-508): values,
+    Jacobian rows, Laplacian and the index map are reversed alike."""
+    dims = (dims,) if isinstance(dims, int) else tuple(dims)
+    if not is_triplet(a):
+        return torch.flip(a, dims)
+    nd = a.x.ndim
+    dims = tuple(d % nd for d in dims)
+    m = a.jacobian.x0_idx
+    if m is not None:
+        m = _mask_nd(a)
+        m = np.ascontiguousarray(np.flip(m, axis=tuple(d + 1 for d in dims if m.shape[d + 1] > 1)))
+    return FwdLaplArray(torch.flip(a.x, dims),
+                        FwdJacobian(torch.flip(a.jacobian.data, [d + 1 for d in dims]), m),
+                        torch.flip(a.laplacian, dims))
+
+
+def pad(a, padding, value: float = 0.0, batch_dims: int = 0):
+    """Constant padding in ``torch.nn.functional.pad`` order (last axis first) (reference: pad,
+    INDEXING, folx/wrapped_functions.py:480-487): padded positions are constants, so their
+    Jacobian and Laplacian are zero and their index-map entries ``-1``."""
+    if not is_triplet(a):
+        return torch.nn.functional.pad(a, tuple(padding), value=value)
+    padding = tuple(int(p) for p in padding)
+    if any(p < 0 for p in padding):
+        raise NotImplementedError('pad: negative padding (cropping) is not supported on triplets')
+    m = a.jacobian.x0_idx
+    if m is not None:
+        m = _full_mask_keep_batch(a, batch_dims)
+        widths = [(0, 0)] * m.ndim
+        for i in range(len(padding) // 2):
+            widths[m.ndim - 1 - i] = (padding[2 * i], padding[2 * i + 1])
+        m = np.pad(m, widths, constant_values=-1)
+    F = torch.nn.functional
+    return FwdLaplArray(F.pad(a.x, padding, value=value),
+                        FwdJacobian(F.pad(a.jacobian.data, padding), m), F.pad(a.laplacian, padding))
 
 
 def _merged_pair(a: Arr, b: Arr):

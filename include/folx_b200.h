@@ -134,6 +134,16 @@ int32_t fl_binary(int32_t op,
                   float* y, float* jac_y, float* lap_y, int64_t jac_y_stride,
                   int64_t K, int64_t N, int64_t b_inner, int64_t b_mid, void* stream);
 
+/* y = cond ? a : b on x, every Jacobian row and the Laplacian (select_n / where: an INDEXING rule
+ * of the reference, folx/wrapped_functions.py:494-496, the chosen operand's derivatives pass
+ * through).  cond: N bytes, nonzero = take a.  a and b: N positions each with aligned Jacobian
+ * rows; an operand is a constant when its jac and lap pointers are NULL (as in fl_binary). */
+int32_t fl_select(const uint8_t* cond,
+                  const float* a, const float* jac_a, const float* lap_a, int64_t jac_a_stride,
+                  const float* b, const float* jac_b, const float* lap_b, int64_t jac_b_stride,
+                  float* y, float* jac_y, float* lap_y, int64_t jac_y_stride,
+                  int64_t K, int64_t N, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Sum of up to FL_ADDN_MAX_TERMS triplets followed by an elementwise function, one pass:
  *     s = sum_t scale_t a_t,   y = f(s)   with the elementwise rule applied to the summed triplet.

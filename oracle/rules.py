@@ -158,6 +158,23 @@ def binary(op: str, a: Triplet, b: Triplet) -> Triplet:
     raise KeyError(op)
 
 
+def where(cond: torch.Tensor, a: Triplet, b: Triplet) -> Triplet:
+    """select_n / where (INDEXING, folx/wrapped_functions.py:494-496): every field of the chosen
+    operand passes through."""
+    return tuple(torch.where(cond, u, v) for u, v in zip(a, b))
+
+
+def reduce_extreme(op: str, t: Triplet, axes) -> Triplet:
+    """reduce_max / reduce_min (REDUCTION | LINEAR, folx/wrapped_functions.py:392-401): the extreme
+    element's derivatives, averaged over ties (the jvp of jax.lax.reduce_max)."""
+    x, J, lap = t
+    axes = tuple(axes)
+    ext = (torch.amax if op == 'max' else torch.amin)(x, dim=axes, keepdim=True)
+    w = (x == ext).to(x.dtype)
+    w = w / w.sum(dim=axes, keepdim=True)
+    return ext.squeeze(axes), (J * w).sum(dim=tuple(a + 1 for a in axes)), (lap * w).sum(dim=axes)
+
+
 def constant(x: torch.Tensor, K: int) -> Triplet:
     """A constant seen as a triplet: zero Jacobian and Laplacian."""
     return x, torch.zeros((K, *x.shape), dtype=x.dtype), torch.zeros_like(x)

@@ -322,6 +322,28 @@ def test_slogdet_of_entry_sparse_matrix(cuda_device):
     assert plan is not None and plan[0].shape == (n, n, 1)
 
 
+@pytest.mark.parametrize('thr', [0, 6])
+def test_where_reductions_and_data_movement(cuda_device, thr):
+    """select (where), max / min reductions, flip, pad, cumsum and prod through their torch
+    spellings (registry entries of folx/wrapped_functions.py:392-408, 480-508), sparse and dense."""
+    g = torch.Generator().manual_seed(67)
+    W = torch.randn(3, 5, generator=g) * 0.8
+    keep = torch.tensor([True, False, True, True])
+
+    def f(p, z):                                         # z: (4, 3)
+        Wm, km = p
+        h = torch.tanh(z @ Wm)                           # (4, 5), sparse rows per particle
+        a = torch.where(h > 0.1, h * h, torch.sin(h))    # condition traced from the values
+        b = torch.where(km[:, None], h, 0.5)             # constant condition and branch
+        c = a.amax(dim=1) + b.amin(dim=0).sum() + torch.amax(h)
+        d = torch.flip(h, (1,)) * h + F.pad(h, (1, 2))[:, 2:7] + torch.cumsum(h, 1)
+        return c.sum() + d.sum() + (1.0 + 0.1 * h).prod(dim=1).sum()
+
+    x = torch.randn(3, 4, 3, generator=g).to(cuda_device)
+    pd, p64 = (W.to(cuda_device), keep.to(cuda_device)), (W.double(), keep)
+    check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), x, thr, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

@@ -111,6 +111,22 @@ def test_max_min_share_derivatives_at_ties(cuda_device, op):
     torch.testing.assert_close(got[1][:, tie].double(), 0.5 * (a[1] + b[1])[:, tie], rtol=1e-6, atol=1e-6)
 
 
+@pytest.mark.parametrize('K,shape', [(0, (4,)), (5, (6, 7)), (12, (3, 4, 8))])
+def test_select(cuda_device, K, shape):
+    """where(cond, a, b): two triplets, and a constant on either side."""
+    a = seeded_triplet(K, shape, seed=31)
+    b = seeded_triplet(K, shape, seed=32)
+    cond = a[0] > b[0]
+    cd = cond.to(cuda_device)
+    got = kernels.select(cd, to_device(a, cuda_device), to_device(b, cuda_device))
+    assert_close(to_host(got), rules.where(cond, a, b))
+    c = b[0].float()
+    got = kernels.select(cd, to_device(a, cuda_device), c.to(cuda_device))
+    assert_close(to_host(got), rules.where(cond, a, rules.constant(c.double(), K)))
+    got = kernels.select(cd, c.to(cuda_device), to_device(a, cuda_device))
+    assert_close(to_host(got), rules.where(cond, rules.constant(c.double(), K), a))
+
+
 @pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div', 'max', 'min'])
 def test_binary_constant_and_broadcast(cuda_device, op):
     K, shape = 5, (6, 8)

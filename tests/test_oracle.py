@@ -272,6 +272,16 @@ def test_sparse_slogdet_equals_dense_rule(mode):
     assert_triplet_close(got, want)
 
 
+def test_where_and_reduce_extreme_match_brute_force():
+    a = rand_triplet(4, (3, 5), seed=61)
+    b = rand_triplet(4, (3, 5), seed=62)
+    cond = a[0] > b[0]
+    assert_triplet_close(rules.where(cond, a, b), brute.propagate(lambda u, v: torch.where(cond, u, v), [a, b]))
+    for op, fn in (('max', torch.amax), ('min', torch.amin)):
+        assert_triplet_close(rules.reduce_extreme(op, a, (1,)), brute.propagate(lambda u: fn(u, dim=1), [a]))
+        assert_triplet_close(rules.reduce_extreme(op, a, (0, 1)), brute.propagate(lambda u: fn(u, dim=(0, 1)), [a]))
+
+
 def test_dot_general_pair_matches_brute_force():
     a = rand_triplet(4, (2, 3, 5), seed=21)
     b = rand_triplet(4, (2, 5, 4), seed=22)
