@@ -15,7 +15,8 @@ single launches on a dense and on a sparse Jacobian), `mlp`, `ferminet`, `psifor
 cases `attention`, `slogdet`, `gather`.  Environment switches, all off by default:
 FOLX_B200_CHAIN=1 (tanh + silu as one launch), FOLX_B200_NO_GRAPH=1 (no graph replay in the model
 workloads), FOLX_B200_E2E_SLICES=n (sample slices of the end-to-end pipeline),
-FOLX_B200_MEASURE_TF32=1 (time a library TF32 GEMM beside the run).
+FOLX_B200_MEASURE_TF32=1 (time a library TF32 GEMM beside the run), FOLX_B200_SLOGDET_N=8|16|32
+(matrix size of the `slogdet` case; 16 by default).
 """
 
 from __future__ import annotations
@@ -585,12 +586,17 @@ def run_kernel_case(args, device):
             return dev_rules.reduce_sum(FwdLaplArray(a.x, FwdJacobian(d, None), a.laplacian), (1,))
         nbytes = 4 * n * F * (3 + 96) + 4 * n * F * 98 + 4 * n * 98
         desc = f'gather kernel: densify (3 -> 96 rows) + feature sum of the dense triplet, {n} samples x 256'
-    else:  # PsiFormer determinants: 32 matrices of 16 x 16 per walker, K = 96
-        a = rand(96, (walkers, 32, 16, 16))
-        a.x.div_(4.0).add_(1.5 * torch.eye(16, device=device))
+    else:
+        # determinants of the model configs: 32 matrices per walker of 16 x 16 with K = 96
+        # (PsiFormer, the default), 8 x 8 with K = 48 (FermiNet) or 32 x 32 with K = 192 (scaled
+        # PsiFormer), chosen by FOLX_B200_SLOGDET_N
+        n = int(os.environ.get('FOLX_B200_SLOGDET_N', '16'))
+        K = 6 * n
+        a = rand(K, (walkers, 32, n, n))
+        a.x.div_(n ** 0.5).add_(1.5 * torch.eye(n, device=device))
         fn = lambda: kernels.slogdet(a)
-        nbytes = 4 * walkers * 32 * 98 * 256
-        desc = f'slogdet kernel, {walkers} walkers x 32 matrices of 16x16, K=96'
+        nbytes = 4 * walkers * 32 * (K + 2) * n * n
+        desc = f'slogdet kernel, {walkers} walkers x 32 matrices of {n}x{n}, K={K}'
     for _ in range(max(args.warmup, 3)):
         fn()
     torch.cuda.synchronize(device)

@@ -12,10 +12,14 @@
 // tr(A^-1 dA_k) is a plain dot product with (A^-1)^T; tr(M_k M_k) = sum_ij M_ij M_ji pairs each
 // thread's tile with the transposed tile read back from shared memory.
 // Roofline: HBM traffic 4 (K + 2) n^2 bytes per matrix against 2 K n^3 flops on the CUDA cores.
-#include "common.cuh"
+// This kernel serves n <= 8; larger matrices take the tensor-core variant (slogdet_mma.cu) unless
+// fl_slogdet_set_mode(1) asks for this one.
+#include "slogdet.cuh"
 
 namespace fl {
 namespace {
+
+int g_slogdet_mode = 0;  // 0 auto, 1 CUDA cores, 2 tensor cores wherever n > 8
 
 constexpr int kBlock = 128;
 constexpr int kJBatch = 32;  // J_k partial sums are reduced 32 rows at a time
@@ -33,15 +37,6 @@ __device__ __forceinline__ void group_sync() {
     __syncthreads();
   }
 }
-
-// Where matrix m of the batch starts and how far its rows are apart: matrix m = (o, i) with
-// i = m mod inner sits at o * outer_stride + i * inner_stride, rows row_stride apart.  Contiguous
-// matrices are inner = 1, outer_stride = n * n, row_stride = n; a view such as the
-// (walker, determinant, electron, orbital) permutation of a (walker, electron, determinant x
-// orbital) product is read in place.
-struct MatLayout {
-  int64_t inner, outer_stride, inner_stride, row_stride;
-};
 
 // N: padded matrix size, TR x TC: per-thread tile of M (TR * TC == 8), G = N*N/8 threads per matrix.
 template <int N, int TR, int TC>
@@ -321,6 +316,12 @@ extern "C" int32_t fl_slogdet(const float* A, const float* jac, const float* lap
                      jac_out_stride, lap_out, MatLayout{1, n * n, 0, n}, (cudaStream_t)stream);
 }
 
+extern "C" int32_t fl_slogdet_set_mode(int32_t mode) {
+  FL_REQUIRE(mode >= 0 && mode <= 2, FL_EUNSUPPORTED, "fl_slogdet_set_mode: unknown mode %d", mode);
+  fl::g_slogdet_mode = mode;
+  return FL_OK;
+}
+
 extern "C" int32_t fl_slogdet_strided(const float* A, const float* jac, const float* lap,
                                       int64_t n_mat, int64_t n, int64_t K, int64_t jac_stride,
                                       int64_t inner, int64_t outer_stride, int64_t inner_stride,
@@ -351,6 +352,9 @@ int32_t run_slogdet(const char* who, const float* A, const float* jac, const flo
              "%s: null pointer", who);
   FL_REQUIRE(K <= 1 || jac_out_stride >= n_mat, FL_EBADSHAPE,
              "%s: output Jacobian row stride too small", who);
+  if (n > 8 && g_slogdet_mode != 1)
+    return launch_slogdet_mma(A, jac, lap, n_mat, K, jac_stride, (int)n, sign, logdet, jac_out,
+                              jac_out_stride, lap_out, lay, st);
   if (n <= 8)
     return launch<8, 4, 2>(A, jac, lap, n_mat, K, jac_stride, (int)n, sign, logdet, jac_out,
                            jac_out_stride, lap_out, lay, st);

@@ -1,0 +1,23 @@
+// Shared between the two batched slogdet kernels (CUDA-core: slogdet.cu, tensor-core:
+// slogdet_mma.cu): the matrix layout descriptor and the launch entry of the tensor-core variant.
+#pragma once
+
+#include "common.cuh"
+
+namespace fl {
+
+// Where matrix m of the batch starts and how far its rows are apart: matrix m = (o, i) with
+// i = m mod inner sits at o * outer_stride + i * inner_stride, rows row_stride apart.  Contiguous
+// matrices are inner = 1, outer_stride = n * n, row_stride = n; a view such as the
+// (walker, determinant, electron, orbital) permutation of a (walker, electron, determinant x
+// orbital) product is read in place.
+struct MatLayout {
+  int64_t inner, outer_stride, inner_stride, row_stride;
+};
+
+// Tensor-core kernel for 8 < n <= 32 (slogdet_mma.cu).
+int32_t launch_slogdet_mma(const float* A, const float* J, const float* lapA, int64_t n_mat,
+                           int64_t K, int64_t js, int n, float* sign, float* logdet, float* J_out,
+                           int64_t jos, float* lap_out, MatLayout lay, cudaStream_t st);
+
+}  // namespace fl

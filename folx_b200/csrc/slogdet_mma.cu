@@ -1,0 +1,416 @@
+// Tensor-core variant of the batched slogdet forward-Laplacian rule for 8 < n <= 32.
+//
+// Same rule and the same walk as slogdet_kernel (slogdet.cu; reference: _dense_log_det /
+// dense_slogdet, folx/slogdet.py:296-344): A^-1 once per matrix by Gauss-Jordan elimination in
+// shared memory, then the K Jacobian matrices stream through shared memory once.  The n^3 product
+// per Jacobian row, which keeps the CUDA-core kernel on its shared-memory pipe, runs on mma.sync
+// (m16n8k8, split-fp32 TF32: fp32 accuracy, see mma_tf32.cuh).  It is taken as M'_k = dA_k A^-1
+// (same traces as A^-1 dA_k: tr(M') = tr(A^-1 dA_k), tr(M' M') = tr(M_k M_k)): A^-1 is then the B
+// operand, split once and kept in registers, and dA_k the A operand, read from its tile in
+// shared memory.  That tile is unpadded and XOR-swizzled in units of four floats, which makes both
+// the 16-byte row stores and the fragment reads free of bank conflicts.  tr(M' M') = sum_ij
+// M'_ij M'_ji pairs each accumulator element with its transposed partner read back from shared
+// memory.  One warp owns a matrix of n <= 16; two warps (16 columns of M' each) own one of
+// n <= 32.  HBM traffic 4 (K + 2) n^2 bytes per matrix against 3 x 2 K n^3 tensor-core flops.
+#include "mma_tf32.cuh"
+#include "slogdet.cuh"
+
+namespace fl {
+namespace {
+
+constexpr int kBlock = 128;
+constexpr int kJBatch = 32;  // J_k partial sums are reduced 32 rows at a time
+
+template <int N>
+struct Geo {
+  static constexpr int W = N / 16;         // warps per matrix
+  static constexpr int G = 32 * W;         // threads per matrix
+  static constexpr int MPB = kBlock / G;   // matrices per block
+  static constexpr int PI = N + 4;         // pitch of A^-1 and of the M' tile
+  static constexpr int CH = N * N / G / 8; // 8-element chunks every thread moves per matrix
+  static constexpr int MT = N / 16;        // row tiles of M'
+  static constexpr int NTW = 2;            // column tiles of M' per warp (16 columns)
+  static constexpr int KS = N / 8;         // k steps
+  static constexpr bool PAIR = N == 16;    // two Jacobian rows in flight per iteration (registers allow)
+  static constexpr int kPerMat = (PAIR ? 3 : 2) * N * PI + 2 * N * N + kJBatch * (G + 1);
+};
+
+// Offset of element (i, j) in the swizzled, unpadded N x N tile of dA_k: the group of four
+// columns j / 4 is XORed with row bits, so that the eight rows of a fragment read and the
+// 16-byte stores of eight consecutive threads land in 32 distinct banks.
+template <int N>
+__device__ __forceinline__ int swz(int i, int j) {
+  const int key = N == 16 ? ((i >> 1) & 3) : (i & 7);
+  return i * N + ((((j >> 2) ^ key) << 2) | (j & 3));
+}
+
+// A fragment (16 x 8) of the swizzled tile: rows m0 .., columns k0 ..
+template <int N>
+__device__ __forceinline__ void load_a_swz(FragA& f, const float* X, int m0, int k0, int g, int t) {
+  split_tf32(X[swz<N>(m0 + g, k0 + t)], f.hi[0], f.lo[0]);
+  split_tf32(X[swz<N>(m0 + g + 8, k0 + t)], f.hi[1], f.lo[1]);
+  split_tf32(X[swz<N>(m0 + g, k0 + t + 4)], f.hi[2], f.lo[2]);
+  split_tf32(X[swz<N>(m0 + g + 8, k0 + t + 4)], f.hi[3], f.lo[3]);
+}
+
+// Barrier over the threads that own one matrix: a warp, or two warps on a named barrier.
+template <int G>
+__device__ __forceinline__ void group_sync(int slot) {
+  if constexpr (G == 32) {
+    __syncwarp();
+  } else {
+    asm volatile("bar.sync %0, %1;" ::"r"(slot + 1), "n"(G) : "memory");
+  }
+}
+
+template <int N>
+__global__ void __launch_bounds__(kBlock, N == 32 ? 4 : 5)
+slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
+                   const float* __restrict__ lapA, int64_t n_mat, int K, int64_t js, int n,
+                   float* __restrict__ sign_out, float* __restrict__ logdet_out,
+                   float* __restrict__ J_out, int64_t jos, float* __restrict__ lap_out,
+                   MatLayout lay) {
+  using Ge = Geo<N>;
+  constexpr int G = Ge::G, PI = Ge::PI, CH = Ge::CH, MT = Ge::MT, NTW = Ge::NTW, KS = Ge::KS;
+  extern __shared__ __align__(16) float smem[];
+  const int slot = threadIdx.x / G;  // matrix slot in the block
+  const int t = threadIdx.x % G;     // thread in the group
+  float* inv = smem + (size_t)slot * Ge::kPerMat;  // [N][PI]  A^-1
+  float* mt = inv + N * PI;                        // [N][PI]  A during the elimination, then M'_k
+  float* buf = mt + (Ge::PAIR ? 2 : 1) * N * PI;   // 2 x [N][N]  dA_k (swizzled), double buffered
+  float* dp = buf + 2 * N * N;                     // [kJBatch][G + 1]
+  const int lane = threadIdx.x & 31, wi = t >> 5, g = lane >> 2, q4 = lane & 3;
+  const int64_t m = (int64_t)blockIdx.x * Ge::MPB + slot;
+  const bool live = m < n_mat;  // dead groups run along on matrix 0 and write nothing
+  const int64_t mm = live ? m : 0;
+  const int64_t rs = lay.row_stride;
+  const int64_t mat_off = (mm / lay.inner) * lay.outer_stride + (mm % lay.inner) * lay.inner_stride;
+  const bool vec = (n == N) && ((js & 3) == 0) &&
+                   (((rs | lay.outer_stride | lay.inner_stride) & 3) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(J) | reinterpret_cast<uintptr_t>(A) |
+                     reinterpret_cast<uintptr_t>(lapA)) & 15) == 0;
+
+  // Chunk c of this thread: the 8 elements e0 .. e0 + 7 of the PADDED N x N matrix (one row).
+  auto load_chunk = [&](const float* base, int c, float (&r)[8], float diag_fill) {
+    const int e0 = 8 * (c * G + t), i = e0 / N, j = e0 % N;
+    if (vec) {
+      const float4* p = reinterpret_cast<const float4*>(base + i * rs + j);
+      float4 a = __ldcs(p), b = __ldcs(p + 1);
+      r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
+      r[4] = b.x; r[5] = b.y; r[6] = b.z; r[7] = b.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        r[q] = (i < n && j + q < n) ? base[i * rs + j + q] : (i == j + q ? diag_fill : 0.f);
+    }
+  };
+  auto store_chunk = [&](float* dst, int pitch, int c, const float (&r)[8]) {
+    const int e0 = 8 * (c * G + t), i = e0 / N, j = e0 % N;
+    float4* d = reinterpret_cast<float4*>(dst + i * pitch + j);
+    d[0] = make_float4(r[0], r[1], r[2], r[3]);
+    d[1] = make_float4(r[4], r[5], r[6], r[7]);
+  };
+
+  // ---------------- phase 1: A^-1, sign, log|det| by Gauss-Jordan with partial pivoting --------
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    float r8[8], id[8];
+    load_chunk(A + mat_off, c, r8, 1.f);
+    store_chunk(mt, PI, c, r8);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int e = 8 * (c * G + t) + q;
+      id[q] = (e / N == e % N) ? 1.f : 0.f;
+    }
+    store_chunk(inv, PI, c, id);
+  }
+  group_sync<G>(slot);
+  float sgn = 1.f, logdet = 0.f;
+  for (int c = 0; c < N; ++c) {
+    // every thread finds the same pivot row (first maximum, as in LAPACK's pivot search)
+    int piv = c;
+    float best = fabsf(mt[c * PI + c]);
+    for (int r = c + 1; r < N; ++r) {
+      const float v = fabsf(mt[r * PI + c]);
+      if (v > best) { best = v; piv = r; }
+    }
+    group_sync<G>(slot);
+    if (piv != c) {
+      for (int e = t; e < 2 * N; e += G) {
+        float* base = e < N ? mt : inv;
+        const int col = e < N ? e : e - N;
+        const float a = base[c * PI + col], b = base[piv * PI + col];
+        base[c * PI + col] = b;
+        base[piv * PI + col] = a;
+      }
+      sgn = -sgn;
+      group_sync<G>(slot);
+    }
+    const float pv = mt[c * PI + c];
+    sgn = pv < 0.f ? -sgn : sgn;
+    logdet += logf(fabsf(pv));
+    const float ipv = 1.0f / pv;
+    group_sync<G>(slot);
+    for (int e = t; e < 2 * N; e += G) {  // scale the pivot row
+      float* base = e < N ? mt : inv;
+      const int col = e < N ? e : e - N;
+      base[c * PI + col] *= ipv;
+    }
+    group_sync<G>(slot);
+    // eliminate column c from every other row: thread handles (row, column-of-[A|I]) pairs
+    for (int e = t; e < 2 * N * N; e += G) {
+      const int r = e / (2 * N), cc = e % (2 * N);
+      if (r == c || cc == c) continue;  // column c of A is cleared after the sweep
+      const float f = mt[r * PI + c];
+      float* base = cc < N ? mt : inv;
+      const int col = cc < N ? cc : cc - N;
+      base[r * PI + col] = fmaf(-f, base[c * PI + col], base[r * PI + col]);
+    }
+    group_sync<G>(slot);
+    for (int r = t; r < N; r += G)
+      if (r != c) mt[r * PI + c] = 0.f;
+    group_sync<G>(slot);
+  }
+  if (live && t == 0) {
+    sign_out[m] = sgn;
+    logdet_out[m] = logdet;
+  }
+
+  // ---------------- phase 2: stream lapA and the K Jacobian matrices ----------------------------
+  // columns 16 wi .. 16 wi + 15 of A^-1 as B fragments, split once
+  FragB bf[KS][NTW];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) load_b<PI>(bf[ks][nt], inv, 8 * ks, 16 * wi + 8 * nt, g, q4);
+  // the swizzled store of chunk c of a dA_k tile: two groups of four floats of one row
+  auto store_swz = [&](float* dst, int c, const float (&r)[8]) {
+    const int e0 = 8 * (c * G + t), i = e0 / N, j = e0 % N;
+    *reinterpret_cast<float4*>(dst + swz<N>(i, j)) = make_float4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<float4*>(dst + swz<N>(i, j + 4)) = make_float4(r[4], r[5], r[6], r[7]);
+  };
+  // weights of this thread's loaded elements in tr(A^-1 X) = sum_ij A^-1[j][i] X[i][j]
+  float w[CH][8];
+#pragma unroll
+  for (int c = 0; c < CH; ++c)
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const int e = 8 * (c * G + t) + q, i = e / N, j = e % N;
+      w[c][q] = inv[j * PI + i];
+    }
+
+  float lap_part = 0.f;
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    float l8[8];
+    load_chunk(lapA + mat_off, c, l8, 0.f);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) lap_part = fmaf(w[c][q], l8[q], lap_part);
+  }
+
+  float trmm = 0.f;  // this thread's share of sum_k tr(M_k M_k)
+  float pre[2][CH][8];
+  const float* Jm = J + mat_off;
+  auto fetch = [&](int k, float (&dst)[CH][8]) {
+#pragma unroll
+    for (int c = 0; c < CH; ++c) load_chunk(Jm + (int64_t)k * js, c, dst[c], 0.f);
+  };
+  if (K > 0) fetch(0, pre[0]);
+  if (K > 1) fetch(1, pre[1]);
+
+  auto iteration = [&](int k, float (&cur)[CH][8]) {
+    float* b = buf + (k & 1) * N * N;
+    float d = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      store_swz(b, c, cur[c]);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) d = fmaf(w[c][q], cur[c][q], d);
+    }
+    dp[(k % kJBatch) * (G + 1) + t] = d;
+    if (k + 2 < K) fetch(k + 2, cur);
+    group_sync<G>(slot);
+    // M'_k (all rows, this warp's 16 columns) = dA_k A^-1
+    float acc[MT][NTW][4];
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt) { acc[mi][nt][0] = 0.f; acc[mi][nt][1] = 0.f; acc[mi][nt][2] = 0.f; acc[mi][nt][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+      for (int mi = 0; mi < MT; ++mi) {
+        FragA fa;
+        load_a_swz<N>(fa, b, 16 * mi, 8 * ks, g, q4);
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) mma3(acc[mi][nt], fa, bf[ks][nt]);
+      }
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt) {
+        const int r = 16 * mi + g, c = 16 * wi + 8 * nt + 2 * q4;
+        *reinterpret_cast<float2*>(mt + r * PI + c) = make_float2(acc[mi][nt][0], acc[mi][nt][1]);
+        *reinterpret_cast<float2*>(mt + (r + 8) * PI + c) = make_float2(acc[mi][nt][2], acc[mi][nt][3]);
+      }
+    group_sync<G>(slot);
+    // tr(M' M'): every element with its transposed partner
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = 16 * mi + g + (e >= 2 ? 8 : 0), c = 16 * wi + 8 * nt + 2 * q4 + (e & 1);
+          trmm = fmaf(acc[mi][nt][e], mt[c * PI + r], trmm);
+        }
+    // every kJBatch rows (and at the end) reduce the J_k partial sums: the syncs above have made
+    // all dp entries of this batch visible
+    if ((k % kJBatch) == kJBatch - 1 || k == K - 1) {
+      const int k_base = k - (k % kJBatch);
+      const int cnt = k - k_base + 1;
+      for (int kk = t; kk < cnt; kk += G) {
+        float s = 0.f;
+        for (int u = 0; u < G; ++u) s += dp[kk * (G + 1) + u];
+        if (live) J_out[(int64_t)(k_base + kk) * jos + m] = s;
+      }
+      group_sync<G>(slot);
+    }
+  };
+
+  // Two rows k, k + 1 (k even) as two independent instruction streams: twice the work between
+  // barriers and two accumulator chains on the tensor pipe.
+  auto iteration2 = [&](int k) {
+    float* b0 = buf;
+    float* b1 = buf + N * N;
+    float* mt1 = mt + N * PI;
+    float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      store_swz(b0, c, pre[0][c]);
+      store_swz(b1, c, pre[1][c]);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        d0 = fmaf(w[c][q], pre[0][c][q], d0);
+        d1 = fmaf(w[c][q], pre[1][c][q], d1);
+      }
+    }
+    dp[(k % kJBatch) * (G + 1) + t] = d0;
+    dp[((k + 1) % kJBatch) * (G + 1) + t] = d1;
+    if (k + 2 < K) fetch(k + 2, pre[0]);
+    if (k + 3 < K) fetch(k + 3, pre[1]);
+    group_sync<G>(slot);
+    float acc0[MT][NTW][4], acc1[MT][NTW][4];
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { acc0[mi][nt][e] = 0.f; acc1[mi][nt][e] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+      for (int mi = 0; mi < MT; ++mi) {
+        FragA fa0, fa1;
+        load_a_swz<N>(fa0, b0, 16 * mi, 8 * ks, g, q4);
+        load_a_swz<N>(fa1, b1, 16 * mi, 8 * ks, g, q4);
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+          // interleaved so that consecutive instructions never touch the same accumulator
+          mma_tf32(acc0[mi][nt], fa0.lo, bf[ks][nt].hi);
+          mma_tf32(acc1[mi][nt], fa1.lo, bf[ks][nt].hi);
+          mma_tf32(acc0[mi][nt], fa0.hi, bf[ks][nt].lo);
+          mma_tf32(acc1[mi][nt], fa1.hi, bf[ks][nt].lo);
+          mma_tf32(acc0[mi][nt], fa0.hi, bf[ks][nt].hi);
+          mma_tf32(acc1[mi][nt], fa1.hi, bf[ks][nt].hi);
+        }
+      }
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt) {
+        const int r = 16 * mi + g, c = 16 * wi + 8 * nt + 2 * q4;
+        *reinterpret_cast<float2*>(mt + r * PI + c) = make_float2(acc0[mi][nt][0], acc0[mi][nt][1]);
+        *reinterpret_cast<float2*>(mt + (r + 8) * PI + c) = make_float2(acc0[mi][nt][2], acc0[mi][nt][3]);
+        *reinterpret_cast<float2*>(mt1 + r * PI + c) = make_float2(acc1[mi][nt][0], acc1[mi][nt][1]);
+        *reinterpret_cast<float2*>(mt1 + (r + 8) * PI + c) = make_float2(acc1[mi][nt][2], acc1[mi][nt][3]);
+      }
+    group_sync<G>(slot);
+    float tr1 = 0.f;
+#pragma unroll
+    for (int mi = 0; mi < MT; ++mi)
+#pragma unroll
+      for (int nt = 0; nt < NTW; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = 16 * mi + g + (e >= 2 ? 8 : 0), c = 16 * wi + 8 * nt + 2 * q4 + (e & 1);
+          trmm = fmaf(acc0[mi][nt][e], mt[c * PI + r], trmm);
+          tr1 = fmaf(acc1[mi][nt][e], mt1[c * PI + r], tr1);
+        }
+    trmm += tr1;
+    const int kl = k + 1;  // batches end on odd rows (kJBatch is even)
+    if ((kl % kJBatch) == kJBatch - 1 || kl == K - 1) {
+      const int k_base = kl - (kl % kJBatch);
+      const int cnt = kl - k_base + 1;
+      for (int kk = t; kk < cnt; kk += G) {
+        float s = 0.f;
+        for (int u = 0; u < G; ++u) s += dp[kk * (G + 1) + u];
+        if (live) J_out[(int64_t)(k_base + kk) * jos + m] = s;
+      }
+      group_sync<G>(slot);
+    }
+  };
+
+  int k = 0;
+  for (; k + 1 < K; k += 2) {
+    if constexpr (Ge::PAIR) {
+      iteration2(k);
+    } else {
+      iteration(k, pre[0]);
+      iteration(k + 1, pre[1]);
+    }
+  }
+  if (k < K) iteration(k, pre[0]);
+
+  // ---------------- final reductions over the group --------------------------------------------
+  group_sync<G>(slot);
+  dp[t] = lap_part - trmm;
+  group_sync<G>(slot);
+  if (live && t == 0) {
+    float s = 0.f;
+    for (int u = 0; u < G; ++u) s += dp[u];
+    lap_out[m] = s;
+  }
+}
+
+template <int N>
+int32_t launch(const float* A, const float* J, const float* lapA, int64_t n_mat, int64_t K,
+               int64_t js, int n, float* sign, float* logdet, float* J_out, int64_t jos,
+               float* lap_out, MatLayout lay, cudaStream_t st) {
+  using Ge = Geo<N>;
+  constexpr size_t smem = (size_t)Ge::MPB * Ge::kPerMat * sizeof(float);
+  static bool attr = false;
+  if (!attr && smem > 48 * 1024) {
+    FL_CUDA(cudaFuncSetAttribute(slogdet_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)smem));
+    attr = true;
+  }
+  const int64_t blocks = (n_mat + Ge::MPB - 1) / Ge::MPB;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_slogdet: too many matrices");
+  slogdet_mma_kernel<N><<<(unsigned)blocks, kBlock, smem, st>>>(
+      A, J, lapA, n_mat, (int)K, js, n, sign, logdet, J_out, jos, lap_out, lay);
+  FL_CHECK_LAUNCH("fl_slogdet launch");
+  return FL_OK;
+}
+
+}  // namespace
+
+int32_t launch_slogdet_mma(const float* A, const float* J, const float* lapA, int64_t n_mat,
+                           int64_t K, int64_t js, int n, float* sign, float* logdet, float* J_out,
+                           int64_t jos, float* lap_out, MatLayout lay, cudaStream_t st) {
+  if (n <= 16)
+    return launch<16>(A, J, lapA, n_mat, K, js, n, sign, logdet, J_out, jos, lap_out, lay, st);
+  return launch<32>(A, J, lapA, n_mat, K, js, n, sign, logdet, J_out, jos, lap_out, lay, st);
+}
+
+}  // namespace fl

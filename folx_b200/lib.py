@@ -72,6 +72,7 @@ _SIGNATURES = {
                                          c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     'fl_dot_general_set_mode': (None, [c_int32]),
     'fl_mhsa_set_mode': (None, [c_int32]),
+    'fl_slogdet_set_mode': (c_int32, [c_int32]),
     'fl_layernorm': (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                c_int64, c_void_p]),

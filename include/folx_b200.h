@@ -344,6 +344,11 @@ int32_t fl_slogdet_strided(const float* A, const float* jac, const float* lap,
                            float* sign, float* logdet, float* jac_out, int64_t jac_out_stride,
                            float* lap_out, void* stream);
 
+/* Which kernel fl_slogdet / fl_slogdet_strided run (process-wide; for tests and measurements):
+ * 0 = automatic (tensor-core kernel for n > 8, CUDA-core kernel below), 1 = CUDA-core kernel
+ * always, 2 = same as 0.  Both compute the same rule in fp32 accuracy. */
+int32_t fl_slogdet_set_mode(int32_t mode);
+
 /* slogdet of matrices whose Jacobian is SPARSE: every input coordinate touches a few rows,
  * columns or entries of A.  Replaces sparse_slogdet / _sparse_slogdet / _pack_slogdet
  * (folx/slogdet.py:196-293).  jac holds the k_slots stored slots (k_slots, n_mat, n, n), rows

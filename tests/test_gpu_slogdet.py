@@ -12,6 +12,14 @@ from gpu_util import assert_close, seeded_triplet, to_device, to_host
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[0, 1], ids=['auto', 'cuda-core'])
+def slogdet_mode(request):
+    """0: the kernel the library picks (tensor cores for n > 8), 1: the CUDA-core kernel."""
+    lib.load().fl_slogdet_set_mode(request.param)
+    yield request.param
+    lib.load().fl_slogdet_set_mode(0)
+
+
 def well_conditioned(K, batch, n, seed):
     x, J, lap = seeded_triplet(K, (*batch, n, n), seed=seed)
     # keep the condition number moderate so that fp32 elimination stays well inside rtol 1e-4
@@ -21,7 +29,7 @@ def well_conditioned(K, batch, n, seed):
 
 @pytest.mark.parametrize('n', [1, 2, 3, 5, 8, 9, 12, 16, 17, 24, 32])
 @pytest.mark.parametrize('K,batch', [(0, (3,)), (5, (7,)), (37, (2, 3))])
-def test_slogdet_matches_oracle(cuda_device, n, K, batch):
+def test_slogdet_matches_oracle(cuda_device, slogdet_mode, n, K, batch):
     t = well_conditioned(K, batch, n, seed=n + K)
     sign, out = kernels.slogdet(to_device(t, cuda_device))
     want_sign, want = rules.slogdet(t)
@@ -29,7 +37,7 @@ def test_slogdet_matches_oracle(cuda_device, n, K, batch):
     assert_close(to_host(out), want, rtol=2e-4, atol_scale=2e-5)
 
 
-def test_slogdet_negative_determinants_and_pivoting(cuda_device):
+def test_slogdet_negative_determinants_and_pivoting(cuda_device, slogdet_mode):
     g = torch.Generator().manual_seed(5)
     n, K = 8, 6
     x = torch.randn(64, n, n, generator=g, dtype=torch.float64)
@@ -47,7 +55,7 @@ def test_slogdet_negative_determinants_and_pivoting(cuda_device):
 
 
 @pytest.mark.parametrize('n,K,walkers,dets', [(8, 48, 256, 32), (16, 96, 64, 32), (32, 192, 8, 32)])
-def test_slogdet_config_shapes_properties(cuda_device, n, K, walkers, dets):
+def test_slogdet_config_shapes_properties(cuda_device, slogdet_mode, n, K, walkers, dets):
     """Determinant shapes of the FermiNet / PsiFormer configs (fewer walkers): sampled oracle
     check plus scaling property  slogdet(c A): J and lap unchanged, logdet shifted by n log c."""
     g = torch.Generator(device=cuda_device).manual_seed(0)
@@ -72,7 +80,7 @@ def test_slogdet_config_shapes_properties(cuda_device, n, K, walkers, dets):
 
 
 @pytest.mark.parametrize('n,n_det,K,B', [(8, 16, 5, 6), (16, 4, 7, 3), (5, 3, 4, 4), (32, 2, 3, 2)])
-def test_slogdet_reads_a_permuted_view_in_place(cuda_device, n, n_det, K, B):
+def test_slogdet_reads_a_permuted_view_in_place(cuda_device, slogdet_mode, n, n_det, K, B):
     """Orbital matrices as models form them: a (walker, electron, determinant x orbital) product
     viewed as (walker, determinant, electron, orbital); no staging copy."""
     x, J, lap = seeded_triplet(K, (B, n, n_det * n), seed=n + n_det)
