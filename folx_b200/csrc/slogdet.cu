@@ -93,6 +93,60 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
   };
 
   // ---------------- phase 1: A^-1, sign, log|det| by Gauss-Jordan with partial pivoting --------
+  float sgn = 1.f, logdet = 0.f;
+  if constexpr (N == 8) {
+    // In registers, without row exchanges: the 8 lanes of the group hold one row of [A | I] each.
+    // Column c takes as pivot the largest entry among the rows not used so far; that row is
+    // scaled and subtracted from all others.  The row that served column c ends up holding row c
+    // of A^-1, and the sign of the pivot order enters the determinant's sign.
+    const unsigned lane = threadIdx.x & 31u;
+    const unsigned gm = 0xffu << (lane & 24u);  // the lanes of this group
+    float a[8], ci[8];
+    load8(A + mat_off, a, 1.f);  // thread t loads the elements 8 t .. 8 t + 7: row t
+#pragma unroll
+    for (int q = 0; q < 8; ++q) ci[q] = (q == t) ? 1.f : 0.f;
+    bool used = false;
+    int crow = 0, myp = 0;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      float best = used ? -1.f : fabsf(a[c]);
+      int piv = t;
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(gm, best, o, 8);
+        const int op = __shfl_xor_sync(gm, piv, o, 8);
+        if (ob > best || (ob == best && op < piv)) { best = ob; piv = op; }
+      }
+      const float pv = __shfl_sync(gm, a[c], piv, 8);
+      sgn = pv < 0.f ? -sgn : sgn;
+      logdet += logf(fabsf(pv));
+      const float ipv = 1.0f / pv;
+      const float f = a[c];
+      const bool is_piv = t == piv;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float pa = __shfl_sync(gm, a[q], piv, 8) * ipv;
+        const float pc = __shfl_sync(gm, ci[q], piv, 8) * ipv;
+        a[q] = is_piv ? pa : fmaf(-f, pa, a[q]);
+        ci[q] = is_piv ? pc : fmaf(-f, pc, ci[q]);
+      }
+      if (is_piv) { used = true; crow = c; }
+      if (t == c) myp = piv;
+    }
+    int inversions = 0;  // parity of the pivot order (p_0 .. p_7)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int pj = __shfl_sync(gm, myp, j, 8);
+      inversions += (j > t && pj < myp) ? 1 : 0;
+    }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) inversions += __shfl_xor_sync(gm, inversions, o, 8);
+    if (inversions & 1) sgn = -sgn;
+    float4* dst = reinterpret_cast<float4*>(inv + crow * P);
+    dst[0] = make_float4(ci[0], ci[1], ci[2], ci[3]);
+    dst[1] = make_float4(ci[4], ci[5], ci[6], ci[7]);
+    group_sync<G>();
+  } else {
   float r8[8];
   load8(A + mat_off, r8, 1.f);
   store8(buf, r8);
@@ -106,7 +160,6 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
     store8(inv, id);
   }
   group_sync<G>();
-  float sgn = 1.f, logdet = 0.f;
   for (int c = 0; c < N; ++c) {
     // every thread finds the same pivot row (first maximum, as in LAPACK's pivot search)
     int piv = c;
@@ -153,6 +206,7 @@ slogdet_kernel(const float* __restrict__ A, const float* __restrict__ J,
     for (int r = t; r < N; r += G)
       if (r != c) buf[r * P + c] = 0.f;
     group_sync<G>();
+  }
   }
   if (live && t == 0) {
     sign_out[m] = sgn;

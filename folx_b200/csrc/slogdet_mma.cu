@@ -112,64 +112,135 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
   };
 
   // ---------------- phase 1: A^-1, sign, log|det| by Gauss-Jordan with partial pivoting --------
-#pragma unroll
-  for (int c = 0; c < CH; ++c) {
-    float r8[8], id[8];
-    load_chunk(A + mat_off, c, r8, 1.f);
-    store_chunk(mt, PI, c, r8);
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const int e = 8 * (c * G + t) + q;
-      id[q] = (e / N == e % N) ? 1.f : 0.f;
-    }
-    store_chunk(inv, PI, c, id);
-  }
-  group_sync<G>(slot);
   float sgn = 1.f, logdet = 0.f;
-  for (int c = 0; c < N; ++c) {
-    // every thread finds the same pivot row (first maximum, as in LAPACK's pivot search)
-    int piv = c;
-    float best = fabsf(mt[c * PI + c]);
-    for (int r = c + 1; r < N; ++r) {
-      const float v = fabsf(mt[r * PI + c]);
-      if (v > best) { best = v; piv = r; }
+  if constexpr (N == 16) {
+    // In registers, without row exchanges: lane holds half a row of [A | I] (row r = lane % 16,
+    // columns 8 h .. 8 h + 7 of both, h = lane / 16).  Column c takes as pivot the largest entry
+    // among the rows not used so far; that row is scaled and subtracted from all others.  The
+    // row that served column c ends up holding row c of A^-1, and the sign of the pivot order
+    // enters the determinant's sign.
+    constexpr unsigned kFull = 0xffffffffu;
+    const int r = lane & 15, h = lane >> 4;
+    float a[8], ci[8];
+    {
+      const float* base = A + mat_off;
+      if (vec) {
+        const float4* p = reinterpret_cast<const float4*>(base + r * rs + 8 * h);
+        const float4 u = __ldg(p), v = __ldg(p + 1);
+        a[0] = u.x; a[1] = u.y; a[2] = u.z; a[3] = u.w;
+        a[4] = v.x; a[5] = v.y; a[6] = v.z; a[7] = v.w;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int j = 8 * h + q;
+          a[q] = (r < n && j < n) ? base[r * rs + j] : (r == j ? 1.f : 0.f);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) ci[q] = (8 * h + q == r) ? 1.f : 0.f;
+    }
+    bool used = false;
+    int crow = 0, myp = 0;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const int hc = c >> 3, jc = c & 7;
+      float best = (h == hc && !used) ? fabsf(a[jc]) : -1.f;
+      int piv = r;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(kFull, best, o);
+        const int op = __shfl_xor_sync(kFull, piv, o);
+        if (ob > best || (ob == best && op < piv)) { best = ob; piv = op; }
+      }
+      const float pv = __shfl_sync(kFull, a[jc], piv + 16 * hc);
+      sgn = pv < 0.f ? -sgn : sgn;
+      logdet += logf(fabsf(pv));
+      const float ipv = 1.0f / pv;
+      const float f = __shfl_sync(kFull, a[jc], r + 16 * hc);  // this row's entry in column c
+      const bool is_piv = r == piv;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float pa = __shfl_sync(kFull, a[q], piv + 16 * h) * ipv;
+        const float pc = __shfl_sync(kFull, ci[q], piv + 16 * h) * ipv;
+        a[q] = is_piv ? pa : fmaf(-f, pa, a[q]);
+        ci[q] = is_piv ? pc : fmaf(-f, pc, ci[q]);
+      }
+      if (is_piv) { used = true; crow = c; }
+      if (r == c) myp = piv;
+    }
+    // parity of the pivot order (p_0 .. p_15): number of inversions
+    int inversions = 0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int pj = __shfl_sync(kFull, myp, j);
+      inversions += (h == 0 && j > r && pj < myp) ? 1 : 0;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) inversions += __shfl_xor_sync(kFull, inversions, o);
+    if (inversions & 1) sgn = -sgn;
+    float4* dst = reinterpret_cast<float4*>(inv + crow * PI + 8 * h);
+    dst[0] = make_float4(ci[0], ci[1], ci[2], ci[3]);
+    dst[1] = make_float4(ci[4], ci[5], ci[6], ci[7]);
+    group_sync<G>(slot);
+  } else {
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      float r8[8], id[8];
+      load_chunk(A + mat_off, c, r8, 1.f);
+      store_chunk(mt, PI, c, r8);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int e = 8 * (c * G + t) + q;
+        id[q] = (e / N == e % N) ? 1.f : 0.f;
+      }
+      store_chunk(inv, PI, c, id);
     }
     group_sync<G>(slot);
-    if (piv != c) {
-      for (int e = t; e < 2 * N; e += G) {
+    for (int c = 0; c < N; ++c) {
+      // every thread finds the same pivot row (first maximum, as in LAPACK's pivot search)
+      int piv = c;
+      float best = fabsf(mt[c * PI + c]);
+      for (int r = c + 1; r < N; ++r) {
+        const float v = fabsf(mt[r * PI + c]);
+        if (v > best) { best = v; piv = r; }
+      }
+      group_sync<G>(slot);
+      if (piv != c) {
+        for (int e = t; e < 2 * N; e += G) {
+          float* base = e < N ? mt : inv;
+          const int col = e < N ? e : e - N;
+          const float a = base[c * PI + col], b = base[piv * PI + col];
+          base[c * PI + col] = b;
+          base[piv * PI + col] = a;
+        }
+        sgn = -sgn;
+        group_sync<G>(slot);
+      }
+      const float pv = mt[c * PI + c];
+      sgn = pv < 0.f ? -sgn : sgn;
+      logdet += logf(fabsf(pv));
+      const float ipv = 1.0f / pv;
+      group_sync<G>(slot);
+      for (int e = t; e < 2 * N; e += G) {  // scale the pivot row
         float* base = e < N ? mt : inv;
         const int col = e < N ? e : e - N;
-        const float a = base[c * PI + col], b = base[piv * PI + col];
-        base[c * PI + col] = b;
-        base[piv * PI + col] = a;
+        base[c * PI + col] *= ipv;
       }
-      sgn = -sgn;
+      group_sync<G>(slot);
+      // eliminate column c from every other row: thread handles (row, column-of-[A|I]) pairs
+      for (int e = t; e < 2 * N * N; e += G) {
+        const int r = e / (2 * N), cc = e % (2 * N);
+        if (r == c || cc == c) continue;  // column c of A is cleared after the sweep
+        const float f = mt[r * PI + c];
+        float* base = cc < N ? mt : inv;
+        const int col = cc < N ? cc : cc - N;
+        base[r * PI + col] = fmaf(-f, base[c * PI + col], base[r * PI + col]);
+      }
+      group_sync<G>(slot);
+      for (int r = t; r < N; r += G)
+        if (r != c) mt[r * PI + c] = 0.f;
       group_sync<G>(slot);
     }
-    const float pv = mt[c * PI + c];
-    sgn = pv < 0.f ? -sgn : sgn;
-    logdet += logf(fabsf(pv));
-    const float ipv = 1.0f / pv;
-    group_sync<G>(slot);
-    for (int e = t; e < 2 * N; e += G) {  // scale the pivot row
-      float* base = e < N ? mt : inv;
-      const int col = e < N ? e : e - N;
-      base[c * PI + col] *= ipv;
-    }
-    group_sync<G>(slot);
-    // eliminate column c from every other row: thread handles (row, column-of-[A|I]) pairs
-    for (int e = t; e < 2 * N * N; e += G) {
-      const int r = e / (2 * N), cc = e % (2 * N);
-      if (r == c || cc == c) continue;  // column c of A is cleared after the sweep
-      const float f = mt[r * PI + c];
-      float* base = cc < N ? mt : inv;
-      const int col = cc < N ? cc : cc - N;
-      base[r * PI + col] = fmaf(-f, base[c * PI + col], base[r * PI + col]);
-    }
-    group_sync<G>(slot);
-    for (int r = t; r < N; r += G)
-      if (r != c) mt[r * PI + c] = 0.f;
-    group_sync<G>(slot);
   }
   if (live && t == 0) {
     sign_out[m] = sgn;
