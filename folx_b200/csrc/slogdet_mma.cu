@@ -1,8 +1,10 @@
 // Tensor-core variant of the batched slogdet forward-Laplacian rule for 8 < n <= 32.
 //
 // Same rule and the same walk as slogdet_kernel (slogdet.cu; reference: _dense_log_det /
-// dense_slogdet, folx/slogdet.py:296-344): A^-1 once per matrix by Gauss-Jordan elimination in
-// shared memory, then the K Jacobian matrices stream through shared memory once.  The n^3 product
+// dense_slogdet, folx/slogdet.py:296-344): A^-1 once per matrix by Gauss-Jordan elimination with
+// partial pivoting, held in registers (a row, or half a row, of [A | I] per lane; the pivot row
+// travels by warp shuffles and rows are never exchanged: the row that served column c ends up as
+// row c of A^-1), then the K Jacobian matrices stream through shared memory once.  The n^3 product
 // per Jacobian row, which keeps the CUDA-core kernel on its shared-memory pipe, runs on mma.sync
 // (m16n8k8, split-fp32 TF32: fp32 accuracy, see mma_tf32.cuh).  It is taken as M'_k = dA_k A^-1
 // (same traces as A^-1 dA_k: tr(M') = tr(A^-1 dA_k), tr(M' M') = tr(M_k M_k)): A^-1 is then the B
@@ -64,7 +66,7 @@ __device__ __forceinline__ void group_sync(int slot) {
 }
 
 template <int N>
-__global__ void __launch_bounds__(kBlock, N == 32 ? 4 : 5)
+__global__ void __launch_bounds__(kBlock, N == 32 ? 3 : 5)
 slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
                    const float* __restrict__ lapA, int64_t n_mat, int K, int64_t js, int n,
                    float* __restrict__ sign_out, float* __restrict__ logdet_out,
@@ -76,7 +78,7 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
   const int slot = threadIdx.x / G;  // matrix slot in the block
   const int t = threadIdx.x % G;     // thread in the group
   float* inv = smem + (size_t)slot * Ge::kPerMat;  // [N][PI]  A^-1
-  float* mt = inv + N * PI;                        // [N][PI]  A during the elimination, then M'_k
+  float* mt = inv + N * PI;                        // [N][PI]  M'_k (two tiles when rows go in pairs)
   float* buf = mt + (Ge::PAIR ? 2 : 1) * N * PI;   // 2 x [N][N]  dA_k (swizzled), double buffered
   float* dp = buf + 2 * N * N;                     // [kJBatch][G + 1]
   const int lane = threadIdx.x & 31, wi = t >> 5, g = lane >> 2, q4 = lane & 3;
@@ -103,12 +105,6 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
       for (int q = 0; q < 8; ++q)
         r[q] = (i < n && j + q < n) ? base[i * rs + j + q] : (i == j + q ? diag_fill : 0.f);
     }
-  };
-  auto store_chunk = [&](float* dst, int pitch, int c, const float (&r)[8]) {
-    const int e0 = 8 * (c * G + t), i = e0 / N, j = e0 % N;
-    float4* d = reinterpret_cast<float4*>(dst + i * pitch + j);
-    d[0] = make_float4(r[0], r[1], r[2], r[3]);
-    d[1] = make_float4(r[4], r[5], r[6], r[7]);
   };
 
   // ---------------- phase 1: A^-1, sign, log|det| by Gauss-Jordan with partial pivoting --------
@@ -183,64 +179,71 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
     dst[1] = make_float4(ci[4], ci[5], ci[6], ci[7]);
     group_sync<G>(slot);
   } else {
+    // n <= 32: the same elimination by the first warp of the pair, one row of [A | I] per lane.
+    if (wi == 0) {
+      constexpr unsigned kFull = 0xffffffffu;
+      const int r = lane;
+      float a[32], ci[32];
+      {
+        const float* base = A + mat_off;
+        if (vec) {
+          const float4* p = reinterpret_cast<const float4*>(base + r * rs);
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      float r8[8], id[8];
-      load_chunk(A + mat_off, c, r8, 1.f);
-      store_chunk(mt, PI, c, r8);
+          for (int q = 0; q < 8; ++q) {
+            const float4 u = __ldg(p + q);
+            a[4 * q] = u.x; a[4 * q + 1] = u.y; a[4 * q + 2] = u.z; a[4 * q + 3] = u.w;
+          }
+        } else {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int e = 8 * (c * G + t) + q;
-        id[q] = (e / N == e % N) ? 1.f : 0.f;
+          for (int q = 0; q < 32; ++q) a[q] = (r < n && q < n) ? base[r * rs + q] : (r == q ? 1.f : 0.f);
+        }
+#pragma unroll
+        for (int q = 0; q < 32; ++q) ci[q] = (q == r) ? 1.f : 0.f;
       }
-      store_chunk(inv, PI, c, id);
+      bool used = false;
+      int crow = 0, myp = 0;
+#pragma unroll
+      for (int c = 0; c < 32; ++c) {
+        float best = used ? -1.f : fabsf(a[c]);
+        int piv = r;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ob = __shfl_xor_sync(kFull, best, o);
+          const int op = __shfl_xor_sync(kFull, piv, o);
+          if (ob > best || (ob == best && op < piv)) { best = ob; piv = op; }
+        }
+        const float pv = __shfl_sync(kFull, a[c], piv);
+        sgn = pv < 0.f ? -sgn : sgn;
+        logdet += logf(fabsf(pv));
+        const float ipv = 1.0f / pv;
+        const float f = a[c];
+        const bool is_piv = r == piv;
+#pragma unroll
+        for (int q = 0; q < 32; ++q) {
+          if (q > c) {  // columns up to c of A are unit vectors from here on and never read again
+            const float pa = __shfl_sync(kFull, a[q], piv) * ipv;
+            a[q] = is_piv ? pa : fmaf(-f, pa, a[q]);
+          }
+          const float pc = __shfl_sync(kFull, ci[q], piv) * ipv;
+          ci[q] = is_piv ? pc : fmaf(-f, pc, ci[q]);
+        }
+        if (is_piv) { used = true; crow = c; }
+        if (r == c) myp = piv;
+      }
+      int inversions = 0;  // parity of the pivot order (p_0 .. p_31)
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int pj = __shfl_sync(kFull, myp, j);
+        inversions += (j > r && pj < myp) ? 1 : 0;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) inversions += __shfl_xor_sync(kFull, inversions, o);
+      if (inversions & 1) sgn = -sgn;
+      float4* dst = reinterpret_cast<float4*>(inv + crow * PI);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) dst[q] = make_float4(ci[4 * q], ci[4 * q + 1], ci[4 * q + 2], ci[4 * q + 3]);
     }
     group_sync<G>(slot);
-    for (int c = 0; c < N; ++c) {
-      // every thread finds the same pivot row (first maximum, as in LAPACK's pivot search)
-      int piv = c;
-      float best = fabsf(mt[c * PI + c]);
-      for (int r = c + 1; r < N; ++r) {
-        const float v = fabsf(mt[r * PI + c]);
-        if (v > best) { best = v; piv = r; }
-      }
-      group_sync<G>(slot);
-      if (piv != c) {
-        for (int e = t; e < 2 * N; e += G) {
-          float* base = e < N ? mt : inv;
-          const int col = e < N ? e : e - N;
-          const float a = base[c * PI + col], b = base[piv * PI + col];
-          base[c * PI + col] = b;
-          base[piv * PI + col] = a;
-        }
-        sgn = -sgn;
-        group_sync<G>(slot);
-      }
-      const float pv = mt[c * PI + c];
-      sgn = pv < 0.f ? -sgn : sgn;
-      logdet += logf(fabsf(pv));
-      const float ipv = 1.0f / pv;
-      group_sync<G>(slot);
-      for (int e = t; e < 2 * N; e += G) {  // scale the pivot row
-        float* base = e < N ? mt : inv;
-        const int col = e < N ? e : e - N;
-        base[c * PI + col] *= ipv;
-      }
-      group_sync<G>(slot);
-      // eliminate column c from every other row: thread handles (row, column-of-[A|I]) pairs
-      for (int e = t; e < 2 * N * N; e += G) {
-        const int r = e / (2 * N), cc = e % (2 * N);
-        if (r == c || cc == c) continue;  // column c of A is cleared after the sweep
-        const float f = mt[r * PI + c];
-        float* base = cc < N ? mt : inv;
-        const int col = cc < N ? cc : cc - N;
-        base[r * PI + col] = fmaf(-f, base[c * PI + col], base[r * PI + col]);
-      }
-      group_sync<G>(slot);
-      for (int r = t; r < N; r += G)
-        if (r != c) mt[r * PI + c] = 0.f;
-      group_sync<G>(slot);
-    }
   }
   if (live && t == 0) {
     sign_out[m] = sgn;
