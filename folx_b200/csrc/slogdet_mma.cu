@@ -4,16 +4,21 @@
 // dense_slogdet, folx/slogdet.py:296-344): A^-1 once per matrix by Gauss-Jordan elimination with
 // partial pivoting, held in registers (a row, or half a row, of [A | I] per lane; the pivot row
 // travels by warp shuffles and rows are never exchanged: the row that served column c ends up as
-// row c of A^-1), then the K Jacobian matrices stream through shared memory once.  The n^3 product
-// per Jacobian row, which keeps the CUDA-core kernel on its shared-memory pipe, runs on mma.sync
-// (m16n8k8, split-fp32 TF32: fp32 accuracy, see mma_tf32.cuh).  It is taken as M'_k = dA_k A^-1
-// (same traces as A^-1 dA_k: tr(M') = tr(A^-1 dA_k), tr(M' M') = tr(M_k M_k)): A^-1 is then the B
-// operand, split once and kept in registers, and dA_k the A operand, read from its tile in
-// shared memory.  That tile is unpadded and XOR-swizzled in units of four floats, which makes both
-// the 16-byte row stores and the fragment reads free of bank conflicts.  tr(M' M') = sum_ij
-// M'_ij M'_ji pairs each accumulator element with its transposed partner read back from shared
-// memory.  One warp owns a matrix of n <= 16; two warps (16 columns of M' each) own one of
-// n <= 32.  HBM traffic 4 (K + 2) n^2 bytes per matrix against 3 x 2 K n^3 tensor-core flops.
+// row c of A^-1), then the K Jacobian matrices are read once.  The n^3 product per Jacobian row,
+// which keeps the CUDA-core kernel on its shared-memory pipe, runs on mma.sync (m16n8k8,
+// split-fp32 TF32: fp32 accuracy, see mma_tf32.cuh).  It is taken as M'_k = dA_k A^-1 (same traces
+// as A^-1 dA_k: tr(M') = tr(A^-1 dA_k), tr(M' M') = tr(M_k M_k)): A^-1 is then the B operand,
+// split once and kept in registers, and dA_k the A operand.
+//   n <= 16, one warp per matrix: dA_k goes from global memory straight into the A fragments
+//   (the contraction index is permuted so that a lane's entries are four consecutive floats: two
+//   coalesced 16-byte loads per lane and row, prefetched two rows ahead); nothing of dA_k touches
+//   shared memory.
+//   n <= 32, two warps per matrix (16 columns of M' each): dA_k is staged in an unpadded tile,
+//   XOR-swizzled in units of four floats, which keeps both the 16-byte row stores and the fragment
+//   reads free of bank conflicts.
+// tr(M' M') = sum_ij M'_ij M'_ji pairs each accumulator element with its transposed partner read
+// back from a shared-memory tile.  HBM traffic 4 (K + 2) n^2 bytes per matrix against
+// 3 x 2 K n^3 tensor-core flops.
 #include "mma_tf32.cuh"
 #include "slogdet.cuh"
 
@@ -33,8 +38,9 @@ struct Geo {
   static constexpr int MT = N / 16;        // row tiles of M'
   static constexpr int NTW = 2;            // column tiles of M' per warp (16 columns)
   static constexpr int KS = N / 8;         // k steps
-  static constexpr bool PAIR = N == 16;    // two Jacobian rows in flight per iteration (registers allow)
-  static constexpr int kPerMat = (PAIR ? 3 : 2) * N * PI + 2 * N * N + kJBatch * (G + 1);
+  static constexpr bool PAIR = N == 16;    // one warp per matrix, two Jacobian rows per barrier
+  static constexpr int kPerMat = PAIR ? 5 * N * PI + kJBatch * (G + 1)
+                                      : 2 * N * PI + 2 * N * N + kJBatch * (G + 1);
 };
 
 // Offset of element (i, j) in the swizzled, unpadded N x N tile of dA_k: the group of four
@@ -79,8 +85,8 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
   const int t = threadIdx.x % G;     // thread in the group
   float* inv = smem + (size_t)slot * Ge::kPerMat;  // [N][PI]  A^-1
   float* mt = inv + N * PI;                        // [N][PI]  M'_k (two tiles when rows go in pairs)
-  float* buf = mt + (Ge::PAIR ? 2 : 1) * N * PI;   // 2 x [N][N]  dA_k (swizzled), double buffered
-  float* dp = buf + 2 * N * N;                     // [kJBatch][G + 1]
+  float* buf = mt + N * PI;                        // n > 16: 2 x [N][N]  dA_k (swizzled), double buffered
+  float* dp = Ge::PAIR ? mt + 4 * N * PI : buf + 2 * N * N;  // [kJBatch][G + 1]
   const int lane = threadIdx.x & 31, wi = t >> 5, g = lane >> 2, q4 = lane & 3;
   const int64_t m = (int64_t)blockIdx.x * Ge::MPB + slot;
   const bool live = m < n_mat;  // dead groups run along on matrix 0 and write nothing
@@ -250,7 +256,137 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
     logdet_out[m] = logdet;
   }
 
-  // ---------------- phase 2: stream lapA and the K Jacobian matrices ----------------------------
+  // ---------------- phase 2, n <= 16: dA_k goes from global memory straight into fragments -----
+  if constexpr (N == 16) {
+    // The contraction index of an MMA may be permuted as long as both operands agree: lane (g, q4)
+    // reads the four consecutive floats dA_k[g][4 q4 ..] and dA_k[g + 8][4 q4 ..] (two coalesced
+    // 16-byte loads) and uses them as the k = q4 and k = q4 + 4 entries of the two k steps; the
+    // constant B fragments of A^-1 are gathered with the same permutation.  Element q of a
+    // thread: row g + 8 (q / 4), column 4 q4 + q % 4.
+    auto load_frag = [&](const float* base, float (&r)[8], float diag_fill) {
+      if (vec) {
+        const float4 u = __ldcs(reinterpret_cast<const float4*>(base + g * rs + 4 * q4));
+        const float4 v = __ldcs(reinterpret_cast<const float4*>(base + (g + 8) * rs + 4 * q4));
+        r[0] = u.x; r[1] = u.y; r[2] = u.z; r[3] = u.w;
+        r[4] = v.x; r[5] = v.y; r[6] = v.z; r[7] = v.w;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int i = g + 8 * (q >> 2), j = 4 * q4 + (q & 3);
+          r[q] = (i < n && j < n) ? base[i * rs + j] : (i == j ? diag_fill : 0.f);
+        }
+      }
+    };
+    FragB bp[2][2];  // [k step][column tile]
+    float w[8];      // weights of the thread's elements in tr(A^-1 X) = sum_ij A^-1[j][i] X[i][j]
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const float* p0 = inv + (4 * q4 + 2 * ks) * PI + 8 * nt + g;
+        split_tf32(p0[0], bp[ks][nt].hi[0], bp[ks][nt].lo[0]);
+        split_tf32(p0[PI], bp[ks][nt].hi[1], bp[ks][nt].lo[1]);
+      }
+#pragma unroll
+    for (int q = 0; q < 8; ++q) w[q] = inv[(4 * q4 + (q & 3)) * PI + g + 8 * (q >> 2)];
+    float lap_part = 0.f;
+    {
+      float l8[8];
+      load_frag(lapA + mat_off, l8, 0.f);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) lap_part = fmaf(w[q], l8[q], lap_part);
+    }
+    // M' = dA_k A^-1 for one row of the Jacobian: tr(M') partial and the accumulators
+    auto product = [&](const float (&cur)[8], float (&acc)[2][4], float& d) {
+      FragA f0, f1;
+      split_tf32(cur[0], f0.hi[0], f0.lo[0]); split_tf32(cur[4], f0.hi[1], f0.lo[1]);
+      split_tf32(cur[1], f0.hi[2], f0.lo[2]); split_tf32(cur[5], f0.hi[3], f0.lo[3]);
+      split_tf32(cur[2], f1.hi[0], f1.lo[0]); split_tf32(cur[6], f1.hi[1], f1.lo[1]);
+      split_tf32(cur[3], f1.hi[2], f1.lo[2]); split_tf32(cur[7], f1.hi[3], f1.lo[3]);
+      d = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) d = fmaf(w[q], cur[q], d);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) { acc[nt][0] = 0.f; acc[nt][1] = 0.f; acc[nt][2] = 0.f; acc[nt][3] = 0.f; }
+      mma_tf32(acc[0], f0.lo, bp[0][0].hi); mma_tf32(acc[1], f0.lo, bp[0][1].hi);
+      mma_tf32(acc[0], f0.hi, bp[0][0].lo); mma_tf32(acc[1], f0.hi, bp[0][1].lo);
+      mma_tf32(acc[0], f0.hi, bp[0][0].hi); mma_tf32(acc[1], f0.hi, bp[0][1].hi);
+      mma_tf32(acc[0], f1.lo, bp[1][0].hi); mma_tf32(acc[1], f1.lo, bp[1][1].hi);
+      mma_tf32(acc[0], f1.hi, bp[1][0].lo); mma_tf32(acc[1], f1.hi, bp[1][1].lo);
+      mma_tf32(acc[0], f1.hi, bp[1][0].hi); mma_tf32(acc[1], f1.hi, bp[1][1].hi);
+    };
+    auto put = [&](float* tile, const float (&acc)[2][4]) {
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        *reinterpret_cast<float2*>(tile + g * PI + 8 * nt + 2 * q4) = make_float2(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<float2*>(tile + (g + 8) * PI + 8 * nt + 2 * q4) = make_float2(acc[nt][2], acc[nt][3]);
+      }
+    };
+    // tr(M' M'): every accumulator element with its transposed partner
+    auto trace = [&](const float* tile, const float (&acc)[2][4]) {
+      float s = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          s = fmaf(acc[nt][e], tile[(8 * nt + 2 * q4 + (e & 1)) * PI + g + (e >= 2 ? 8 : 0)], s);
+      return s;
+    };
+    auto reduce_rows = [&](int k_last) {  // J_k of the batch that ends with row k_last
+      const int k_base = k_last - (k_last % kJBatch);
+      const int cnt = k_last - k_base + 1;
+      for (int kk = t; kk < cnt; kk += G) {
+        float s = 0.f;
+        for (int u = 0; u < G; ++u) s += dp[kk * (G + 1) + u];
+        if (live) J_out[(int64_t)(k_base + kk) * jos + m] = s;
+      }
+      group_sync<G>(slot);
+    };
+
+    float trmm = 0.f;
+    float pre[2][8];
+    const float* Jm = J + mat_off;
+    if (K > 0) load_frag(Jm, pre[0], 0.f);
+    if (K > 1) load_frag(Jm + js, pre[1], 0.f);
+    float* tiles = mt;  // four M' tiles: pairs of rows alternate between two sets
+    int k = 0;
+    for (; k + 1 < K; k += 2) {
+      float acc0[2][4], acc1[2][4], d0, d1;
+      product(pre[0], acc0, d0);
+      product(pre[1], acc1, d1);
+      if (k + 2 < K) load_frag(Jm + (int64_t)(k + 2) * js, pre[0], 0.f);
+      if (k + 3 < K) load_frag(Jm + (int64_t)(k + 3) * js, pre[1], 0.f);
+      dp[(k % kJBatch) * (G + 1) + t] = d0;
+      dp[((k + 1) % kJBatch) * (G + 1) + t] = d1;
+      float* t0 = tiles + ((k >> 1) & 1) * 2 * N * PI;
+      float* t1 = t0 + N * PI;
+      put(t0, acc0);
+      put(t1, acc1);
+      group_sync<G>(slot);
+      trmm += trace(t0, acc0) + trace(t1, acc1);
+      // batches end on odd rows (kJBatch is even)
+      if (((k + 1) % kJBatch) == kJBatch - 1 || k + 1 == K - 1) reduce_rows(k + 1);
+    }
+    if (k < K) {
+      float acc0[2][4], d0;
+      product(pre[0], acc0, d0);
+      dp[(k % kJBatch) * (G + 1) + t] = d0;
+      float* t0 = tiles + ((k >> 1) & 1) * 2 * N * PI;
+      put(t0, acc0);
+      group_sync<G>(slot);
+      trmm += trace(t0, acc0);
+      reduce_rows(k);
+    }
+    group_sync<G>(slot);
+    dp[t] = lap_part - trmm;
+    group_sync<G>(slot);
+    if (live && t == 0) {
+      float s = 0.f;
+      for (int u = 0; u < G; ++u) s += dp[u];
+      lap_out[m] = s;
+    }
+  } else {
+  // ---------------- phase 2, n <= 32: dA_k is staged in shared memory -----------------------------
   // columns 16 wi .. 16 wi + 15 of A^-1 as B fragments, split once
   FragB bf[KS][NTW];
 #pragma unroll
@@ -352,97 +488,10 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
     }
   };
 
-  // Two rows k, k + 1 (k even) as two independent instruction streams: twice the work between
-  // barriers and two accumulator chains on the tensor pipe.
-  auto iteration2 = [&](int k) {
-    float* b0 = buf;
-    float* b1 = buf + N * N;
-    float* mt1 = mt + N * PI;
-    float d0 = 0.f, d1 = 0.f;
-#pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      store_swz(b0, c, pre[0][c]);
-      store_swz(b1, c, pre[1][c]);
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        d0 = fmaf(w[c][q], pre[0][c][q], d0);
-        d1 = fmaf(w[c][q], pre[1][c][q], d1);
-      }
-    }
-    dp[(k % kJBatch) * (G + 1) + t] = d0;
-    dp[((k + 1) % kJBatch) * (G + 1) + t] = d1;
-    if (k + 2 < K) fetch(k + 2, pre[0]);
-    if (k + 3 < K) fetch(k + 3, pre[1]);
-    group_sync<G>(slot);
-    float acc0[MT][NTW][4], acc1[MT][NTW][4];
-#pragma unroll
-    for (int mi = 0; mi < MT; ++mi)
-#pragma unroll
-      for (int nt = 0; nt < NTW; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { acc0[mi][nt][e] = 0.f; acc1[mi][nt][e] = 0.f; }
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks)
-#pragma unroll
-      for (int mi = 0; mi < MT; ++mi) {
-        FragA fa0, fa1;
-        load_a_swz<N>(fa0, b0, 16 * mi, 8 * ks, g, q4);
-        load_a_swz<N>(fa1, b1, 16 * mi, 8 * ks, g, q4);
-#pragma unroll
-        for (int nt = 0; nt < NTW; ++nt) {
-          // interleaved so that consecutive instructions never touch the same accumulator
-          mma_tf32(acc0[mi][nt], fa0.lo, bf[ks][nt].hi);
-          mma_tf32(acc1[mi][nt], fa1.lo, bf[ks][nt].hi);
-          mma_tf32(acc0[mi][nt], fa0.hi, bf[ks][nt].lo);
-          mma_tf32(acc1[mi][nt], fa1.hi, bf[ks][nt].lo);
-          mma_tf32(acc0[mi][nt], fa0.hi, bf[ks][nt].hi);
-          mma_tf32(acc1[mi][nt], fa1.hi, bf[ks][nt].hi);
-        }
-      }
-#pragma unroll
-    for (int mi = 0; mi < MT; ++mi)
-#pragma unroll
-      for (int nt = 0; nt < NTW; ++nt) {
-        const int r = 16 * mi + g, c = 16 * wi + 8 * nt + 2 * q4;
-        *reinterpret_cast<float2*>(mt + r * PI + c) = make_float2(acc0[mi][nt][0], acc0[mi][nt][1]);
-        *reinterpret_cast<float2*>(mt + (r + 8) * PI + c) = make_float2(acc0[mi][nt][2], acc0[mi][nt][3]);
-        *reinterpret_cast<float2*>(mt1 + r * PI + c) = make_float2(acc1[mi][nt][0], acc1[mi][nt][1]);
-        *reinterpret_cast<float2*>(mt1 + (r + 8) * PI + c) = make_float2(acc1[mi][nt][2], acc1[mi][nt][3]);
-      }
-    group_sync<G>(slot);
-    float tr1 = 0.f;
-#pragma unroll
-    for (int mi = 0; mi < MT; ++mi)
-#pragma unroll
-      for (int nt = 0; nt < NTW; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int r = 16 * mi + g + (e >= 2 ? 8 : 0), c = 16 * wi + 8 * nt + 2 * q4 + (e & 1);
-          trmm = fmaf(acc0[mi][nt][e], mt[c * PI + r], trmm);
-          tr1 = fmaf(acc1[mi][nt][e], mt1[c * PI + r], tr1);
-        }
-    trmm += tr1;
-    const int kl = k + 1;  // batches end on odd rows (kJBatch is even)
-    if ((kl % kJBatch) == kJBatch - 1 || kl == K - 1) {
-      const int k_base = kl - (kl % kJBatch);
-      const int cnt = kl - k_base + 1;
-      for (int kk = t; kk < cnt; kk += G) {
-        float s = 0.f;
-        for (int u = 0; u < G; ++u) s += dp[kk * (G + 1) + u];
-        if (live) J_out[(int64_t)(k_base + kk) * jos + m] = s;
-      }
-      group_sync<G>(slot);
-    }
-  };
-
   int k = 0;
   for (; k + 1 < K; k += 2) {
-    if constexpr (Ge::PAIR) {
-      iteration2(k);
-    } else {
-      iteration(k, pre[0]);
-      iteration(k + 1, pre[1]);
-    }
+    iteration(k, pre[0]);
+    iteration(k + 1, pre[1]);
   }
   if (k < K) iteration(k, pre[0]);
 
@@ -455,6 +504,7 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
     for (int u = 0; u < G; ++u) s += dp[u];
     lap_out[m] = s;
   }
+  }  // n <= 32
 }
 
 template <int N>
