@@ -11,7 +11,7 @@
 // split once and kept in registers, and dA_k the A operand.
 //   n <= 16, one warp per matrix: dA_k goes from global memory straight into the A fragments
 //   (the contraction index is permuted so that a lane's entries are four consecutive floats: two
-//   coalesced 16-byte loads per lane and row, prefetched two rows ahead); nothing of dA_k touches
+//   coalesced 16-byte loads per lane and row, prefetched four rows ahead); nothing of dA_k touches
 //   shared memory.
 //   n <= 32, two warps per matrix (16 columns of M' each): dA_k is staged in an unpadded tile,
 //   XOR-swizzled in units of four floats, which keeps both the 16-byte row stores and the fragment
@@ -72,7 +72,7 @@ __device__ __forceinline__ void group_sync(int slot) {
 }
 
 template <int N>
-__global__ void __launch_bounds__(kBlock, N == 32 ? 3 : 5)
+__global__ void __launch_bounds__(kBlock, N == 32 ? 3 : 4)
 slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
                    const float* __restrict__ lapA, int64_t n_mat, int K, int64_t js, int n,
                    float* __restrict__ sign_out, float* __restrict__ logdet_out,
@@ -344,21 +344,21 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
     };
 
     float trmm = 0.f;
-    float pre[2][8];
+    float pre[4][8];  // the next four rows: two pairs in flight
     const float* Jm = J + mat_off;
-    if (K > 0) load_frag(Jm, pre[0], 0.f);
-    if (K > 1) load_frag(Jm + js, pre[1], 0.f);
-    float* tiles = mt;  // four M' tiles: pairs of rows alternate between two sets
-    int k = 0;
-    for (; k + 1 < K; k += 2) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (u < K) load_frag(Jm + (int64_t)u * js, pre[u], 0.f);
+    // rows k, k + 1 (k even) from pa, pb; their registers are refilled with rows k + 4, k + 5.
+    // Consecutive pairs alternate between two sets of M' tiles, so one barrier per pair suffices.
+    auto pair = [&](int k, float (&pa)[8], float (&pb)[8], float* t0) {
       float acc0[2][4], acc1[2][4], d0, d1;
-      product(pre[0], acc0, d0);
-      product(pre[1], acc1, d1);
-      if (k + 2 < K) load_frag(Jm + (int64_t)(k + 2) * js, pre[0], 0.f);
-      if (k + 3 < K) load_frag(Jm + (int64_t)(k + 3) * js, pre[1], 0.f);
+      product(pa, acc0, d0);
+      product(pb, acc1, d1);
+      if (k + 4 < K) load_frag(Jm + (int64_t)(k + 4) * js, pa, 0.f);
+      if (k + 5 < K) load_frag(Jm + (int64_t)(k + 5) * js, pb, 0.f);
       dp[(k % kJBatch) * (G + 1) + t] = d0;
       dp[((k + 1) % kJBatch) * (G + 1) + t] = d1;
-      float* t0 = tiles + ((k >> 1) & 1) * 2 * N * PI;
       float* t1 = t0 + N * PI;
       put(t0, acc0);
       put(t1, acc1);
@@ -366,16 +366,28 @@ slogdet_mma_kernel(const float* __restrict__ A, const float* __restrict__ J,
       trmm += trace(t0, acc0) + trace(t1, acc1);
       // batches end on odd rows (kJBatch is even)
       if (((k + 1) % kJBatch) == kJBatch - 1 || k + 1 == K - 1) reduce_rows(k + 1);
-    }
-    if (k < K) {
+    };
+    auto single = [&](int k, const float (&pa)[8], float* t0) {
       float acc0[2][4], d0;
-      product(pre[0], acc0, d0);
+      product(pa, acc0, d0);
       dp[(k % kJBatch) * (G + 1) + t] = d0;
-      float* t0 = tiles + ((k >> 1) & 1) * 2 * N * PI;
       put(t0, acc0);
       group_sync<G>(slot);
       trmm += trace(t0, acc0);
       reduce_rows(k);
+    };
+    float* set0 = mt;
+    float* set1 = mt + 2 * N * PI;
+    int k = 0;
+    for (; k + 3 < K; k += 4) {
+      pair(k, pre[0], pre[1], set0);
+      pair(k + 2, pre[2], pre[3], set1);
+    }
+    if (k + 1 < K) {
+      pair(k, pre[0], pre[1], set0);
+      if (k + 2 < K) single(k + 2, pre[2], set1);
+    } else if (k < K) {
+      single(k, pre[0], set0);
     }
     group_sync<G>(slot);
     dp[t] = lap_part - trmm;
