@@ -215,7 +215,7 @@ def psiformer(cfg: PsiFormerConfig, p, r):
     h = F.linear(feats, p['W_in'].t(), p['b_in']) + p['spin']
     scale = 1.0 / math.sqrt(dh)
     for layer in p['layers']:
-        q = ((h @ layer['Wq']) * scale).reshape(N, H, dh)
+        q = (h @ (layer['Wq'] * scale)).reshape(N, H, dh)   # 1 / sqrt(d_h) folded into the projection
         k = (h @ layer['Wk']).reshape(N, H, dh)
         v = (h @ layer['Wv']).reshape(N, H, dh)
         a = multi_head_self_attention(q, k, v).reshape(N, cfg.dim)
