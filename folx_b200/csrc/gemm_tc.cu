@@ -32,6 +32,7 @@
 // arrive on the even CTA's barriers through the cluster shared window, and the even CTA relays
 // "stage free" and "accumulator full" to the odd CTA with one remote arrive each.
 #include <cuda.h>
+#include <cuda_bf16.h>
 
 #include "gemm.cuh"
 
@@ -52,6 +53,17 @@ constexpr bool kHwTruncates = true;
 // against 0.277 ms on the 401 408 x 256 x 256 case: a warp store then touches 32 lines with 16
 // bytes each), so the staged TMA store stays the default.
 constexpr bool kDirectStore = false;
+// The two correction products A_lo W_hi + A W_lo are 2^-11 of the result, so their operands need
+// only ~11 bits themselves: with this switch on they run as ONE bf16 product at twice the TF32
+// rate.  Per 16-wide K block the converters write the row [bf16(A_lo) x 16 | bf16(A) x 16] (the
+// same 64 bytes as an fp32 row, so the tile, its swizzle and its descriptor stay as they are) and
+// the prepared workspace holds [bf16(W_hi) x 16 | bf16(W_lo) x 16] in place of the fp32 W_lo row;
+// the MMA warp issues 2 TF32 MMAs (A W_hi, K = 8 each) and 2 bf16 MMAs (K = 16 each) per stage
+// into the same fp32 accumulator instead of 6 TF32 MMAs.  Measured on the 401 408 x 256 x 256 case:
+// 0.202 ms against 0.218 ms (the kernel is bound by shared-memory traffic more than by the tensor
+// pipe), but the 8-bit correction operands raise the rms relative error from 2.9e-7 (the level of
+// an fp32 FFMA GEMM) to 1.7e-6.  fp32 accuracy is the contract of this path, so the switch is off.
+constexpr bool kBf16Corrections = false;
 constexpr int MAX_N = 256;
 constexpr int A_TILE_BYTES = BLOCK_M * BLOCK_K * 4;
 constexpr int EPI_WARPS = 4;
@@ -159,6 +171,16 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -258,6 +280,16 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t desc_a,
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                               uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
@@ -392,6 +424,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       // M = 128 per CTA, N = n_tile.
       const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n_tile >> 3) << 17) |
                              ((uint32_t)((BLOCK_M * CTAS) >> 4) << 24);
+      // kind::f16 descriptor of the correction product: D = fp32, A = B = BF16, both K-major
+      const uint32_t idesc_bf = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_tile >> 3) << 17) |
+                                ((uint32_t)((BLOCK_M * CTAS) >> 4) << 24);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -414,10 +449,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             tc_fence_after();
 #pragma unroll
             for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
+              // 32 bytes further inside the swizzle row: 8 fp32, or the second 16 bf16
               const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
               umma_tf32_pair(tmem_d, d_ahi + off, d_whi + off, idesc, (ks | kk) != 0);
-              umma_tf32_pair(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
-              umma_tf32_pair(tmem_d, d_alo + off, d_whi + off, idesc, 1);
+              if (kBf16Corrections) {
+                umma_bf16_pair(tmem_d, d_alo + off, d_wlo + off, idesc_bf, 1);
+              } else {
+                umma_tf32_pair(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
+                umma_tf32_pair(tmem_d, d_alo + off, d_whi + off, idesc, 1);
+              }
             }
             umma_commit_pair(smem_u32(&ctrl->empty[stage]));
           } else {
@@ -431,7 +471,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               // advance inside the swizzle row: 8 fp32 = 32 bytes = 2 descriptor units
               const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
               umma_tf32(tmem_d, d_ahi + off, d_whi + off, idesc, (ks | kk) != 0);
-              umma_tf32(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
+              if (!kBf16Corrections) umma_tf32(tmem_d, d_ahi + off, d_wlo + off, idesc, 1);
             }
             // the tail of A comes from the converter warps
             if (kHwTruncates &&
@@ -440,7 +480,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int kk = 0; kk < BLOCK_K / UMMA_K; ++kk) {
               const uint64_t off = (uint64_t)(kk * UMMA_K * 4 / 16);
-              umma_tf32(tmem_d, d_alo + off, d_whi + off, idesc, 1);
+              if (kBf16Corrections) umma_bf16(tmem_d, d_alo + off, d_wlo + off, idesc_bf, 1);
+              else umma_tf32(tmem_d, d_alo + off, d_whi + off, idesc, 1);
             }
             umma_commit(smem_u32(&ctrl->empty[stage]));
           }
@@ -463,6 +504,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (!mbar_wait(smem_u32(&ctrl->full[stage]), phase, abort_flag)) { ok = false; break; }
         float4* a4 = (float4*)(smem + stage * STAGE_BYTES);
         float4* lo4 = (float4*)(smem + stage * STAGE_BYTES + A_TILE_BYTES);
+        if (kBf16Corrections) {
+          // thread ct owns row ct: the 16 fp32 of the row become 16 bf16 of A_lo and 16 bf16 of A.
+          // 16-byte chunk c of a row sits at chunk c ^ ((row / 2) % 4) of its 64-byte line
+          // (SWIZZLE_64B), in the A tile as in the correction tile.
+          const int key = (ct >> 1) & 3;
+          const float4* arow = a4 + ct * 4;
+          uint4* crow = (uint4*)(lo4 + ct * 4);
+          float4 v[4];
+#pragma unroll
+          for (int c = 0; c < 4; ++c) v[c] = arow[c ^ key];
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const float x[8] = {v[2 * half].x, v[2 * half].y, v[2 * half].z, v[2 * half].w,
+                                v[2 * half + 1].x, v[2 * half + 1].y, v[2 * half + 1].z, v[2 * half + 1].w};
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float a0 = x[2 * e], a1 = x[2 * e + 1];
+              __nv_bfloat162 l2 = __floats2bfloat162_rn(a0 - tf32_trunc(a0), a1 - tf32_trunc(a1));
+              __nv_bfloat162 h2 = __floats2bfloat162_rn(a0, a1);
+              lo[e] = *reinterpret_cast<uint32_t*>(&l2);
+              hi[e] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            crow[half ^ key] = make_uint4(lo[0], lo[1], lo[2], lo[3]);        // A_lo, k = 8 half ..
+            crow[(2 + half) ^ key] = make_uint4(hi[0], hi[1], hi[2], hi[3]);  // A,    k = 8 half ..
+          }
+        } else {
 #pragma unroll
         for (int j = 0; j < A_TILE_BYTES / 16 / 128; ++j) {
           const int i = ct + 128 * j;
@@ -477,6 +545,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           l.x = tf32_rna(v.x - h.x); l.y = tf32_rna(v.y - h.y);
           l.z = tf32_rna(v.z - h.z); l.w = tf32_rna(v.w - h.w);
           lo4[i] = l;
+        }
         }
         if (CTAS == 2) {
           // one arrive per CTA: remote arrives are expensive, so the four warps meet first
@@ -590,7 +659,15 @@ __global__ void wsplit_kernel(const float* __restrict__ W, int Kc, int N, float*
   float v = (n < N && k < Kc) ? W[(int64_t)k * N + n] : 0.f;
   float h = tf32_rna(v);
   whi[i] = h;
-  wlo[i] = tf32_rna(v - h);
+  if (kBf16Corrections) {
+    // row n of the second array: per 16-wide K block 16 bf16 of W_hi, then 16 bf16 of W_lo
+    __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(wlo + (int64_t)n * k_pad);
+    const int kb = k / BLOCK_K, j = k % BLOCK_K;
+    row[kb * 2 * BLOCK_K + j] = __float2bfloat16_rn(h);
+    row[kb * 2 * BLOCK_K + BLOCK_K + j] = __float2bfloat16_rn(v - h);
+  } else {
+    wlo[i] = tf32_rna(v - h);
+  }
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
