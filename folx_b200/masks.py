@@ -274,11 +274,14 @@ def slogdet_entry_mask(x0_idx: np.ndarray | None, shape: Sequence[int]) -> np.nd
         return None
     shape = tuple(shape)
     k = x0_idx.shape[JAC_DIM]
-    if k * int(np.prod(shape, dtype=np.int64)) > _MAX_SLOGDET_ENTRIES:
+    # the map's own batch extents: axes along which it is stored once (size 1: the walker axes,
+    # and any axis it does not vary along) need neither expansion nor comparison
+    batch = tuple(x0_idx.shape[1:-2])
+    if k * int(np.prod(batch + shape[-2:], dtype=np.int64)) > _MAX_SLOGDET_ENTRIES:
         return None
-    per_matrix = np.broadcast_to(x0_idx, (k, *shape)).reshape(k, -1, *shape[-2:])
+    per_matrix = np.broadcast_to(x0_idx, (k, *batch, *shape[-2:])).reshape(k, -1, *shape[-2:])
     first = per_matrix[:, 0]
-    if any(s > 1 for s in x0_idx.shape[1:-2]) and not (per_matrix == first[:, None]).all():
+    if per_matrix.shape[1] > 1 and not (per_matrix == first[:, None]).all():
         return None
     return np.ascontiguousarray(first)
 

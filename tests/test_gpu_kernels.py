@@ -127,6 +127,28 @@ def test_select(cuda_device, K, shape):
     assert_close(to_host(got), rules.where(cond, rules.constant(c.double(), K), a))
 
 
+def test_select_and_max_bench_shape_properties(cuda_device):
+    """Operator-microbench size (B=4096, d=96, F=256): where(c, a, b) + where(~c, a, b) = a + b on
+    every field, max(a, b) + min(a, b) = a + b, and max(a, a) = a."""
+    g = torch.Generator(device=cuda_device).manual_seed(1)
+    K, P, F = 96, 4096, 256
+    a = kernels.alloc_triplet(K, (P, F), cuda_device)
+    b = kernels.alloc_triplet(K, (P, F), cuda_device)
+    for t in (a, b):
+        t.x.normal_(generator=g); t.jacobian.data.normal_(generator=g); t.laplacian.normal_(generator=g)
+    cond = a.x > b.x
+    s1, s2 = kernels.select(cond, a, b), kernels.select(~cond, a, b)
+    total = kernels.binary('add', a, b)
+    for got, other, want in ((s1.x, s2.x, total.x), (s1.jacobian.data, s2.jacobian.data, total.jacobian.data),
+                             (s1.laplacian, s2.laplacian, total.laplacian)):
+        torch.testing.assert_close(got + other, want, rtol=0, atol=0)
+    hi, lo = kernels.binary('max', a, b), kernels.binary('min', a, b)
+    assert torch.equal(hi.x, s1.x) and torch.equal(hi.jacobian.data, s1.jacobian.data)
+    assert torch.equal(lo.laplacian, s2.laplacian)
+    same = kernels.binary('max', a, a)
+    torch.testing.assert_close(same.jacobian.data, a.jacobian.data, rtol=0, atol=0)
+
+
 @pytest.mark.parametrize('op', ['add', 'sub', 'mul', 'div', 'max', 'min'])
 def test_binary_constant_and_broadcast(cuda_device, op):
     K, shape = 5, (6, 8)

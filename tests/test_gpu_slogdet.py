@@ -143,3 +143,32 @@ def test_sparse_slogdet_matches_oracle(cuda_device, mode, n, batch):
     # and the dense kernel on the densified Jacobian agrees with it
     sign_d, dense = kernels.slogdet(dev)
     assert_close(to_host(dense), want, rtol=2e-4, atol_scale=2e-5)
+
+
+def test_sparse_slogdet_at_walker_scale(cuda_device):
+    """4096 walkers x 16 determinants of 16 x 16 orbitals whose rows depend on one electron each
+    (3 stored slots): the factorised kernel against the dense kernel on the densified Jacobian,
+    plus the scaling law slogdet(c A): J and lap unchanged."""
+    import numpy as np
+    from folx_b200 import sparse
+    n, walkers, dets = 16, 4096, 16
+    mask = _sparse_case('rows', n).reshape(3, 1, 1, n, n)
+    g = torch.Generator(device=cuda_device).manual_seed(3)
+    a = kernels.alloc_triplet(3, (walkers, dets, n, n), cuda_device)
+    a.x.normal_(generator=g).div_(n**0.5).add_(1.5 * torch.eye(n, device=cuda_device))
+    a.jacobian.data.normal_(generator=g)
+    a.laplacian.normal_(generator=g)
+    a = FwdLaplArray(a.x, FwdJacobian(a.jacobian.data, mask), a.laplacian)
+    plan = sparse.plan_slogdet(a)
+    assert plan is not None and plan[0].shape == (3 * n, 1, n)
+    sign, out = sparse.slogdet_sparse(a, plan)
+    sign_d, dense = kernels.slogdet(a)
+    assert torch.equal(sign, sign_d)
+    torch.testing.assert_close(out.x, dense.x, rtol=1e-5, atol=1e-5)
+    scale = float(dense.jacobian.data.abs().max())
+    torch.testing.assert_close(out.jacobian.data, dense.jacobian.data, rtol=1e-4, atol=2e-5 * scale)
+    torch.testing.assert_close(out.laplacian, dense.laplacian, rtol=1e-3, atol=2e-4 * float(dense.laplacian.abs().max()))
+    b = FwdLaplArray(2 * a.x, FwdJacobian(2 * a.jacobian.data, mask), 2 * a.laplacian)
+    sign2, out2 = sparse.slogdet_sparse(b, plan)
+    torch.testing.assert_close(out2.x, out.x + n * 0.6931471805599453, rtol=1e-5, atol=1e-4)
+    torch.testing.assert_close(out2.jacobian.data, out.jacobian.data, rtol=1e-4, atol=1e-4)
