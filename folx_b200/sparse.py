@@ -58,7 +58,7 @@ def gather_rows(data: torch.Tensor, take: np.ndarray, out_shape: tuple[int, ...]
     lead = nd - (data.ndim - 1)
     in_strides = [0] * lead + [0 if data.shape[1 + d] == 1 else data.stride(1 + d)
                                for d in range(data.ndim - 1)]
-    in_row_stride = data.stride(0) if k_in > 1 else 1
+    in_row_stride = data.stride(0) if k_in > 1 else 0  # a single row: never multiplied by a row index
     if any(st < 0 for st in in_strides):
         data = data.contiguous()
         return gather_rows(data, take, out_shape, table_shape, n_reduced, reduced_stride, out)
