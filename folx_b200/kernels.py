@@ -8,8 +8,8 @@ of the dot_general rule is therefore a view, not a copy.
 
 from __future__ import annotations
 
+import collections
 import ctypes
-import weakref
 
 import numpy as np
 import torch
@@ -212,24 +212,30 @@ def select(cond: torch.Tensor, a, b, x0_idx: np.ndarray | None = None) -> FwdLap
 
 
 class _WeightCache:
-    """Split-W workspaces keyed by the weight tensor (redone when the tensor is modified)."""
+    """Split-W workspaces keyed by the weight's storage address, shape and strides, so that views
+    made anew on every call (``W.t().t()``, a slice of a parameter) find their workspace again.
+    An entry keeps its tensor alive (the address cannot be reused for other data while it is
+    cached) and is redone when the tensor's version counter moves; least recently used entries
+    are dropped beyond ``capacity``."""
 
-    def __init__(self):
-        self._entries: dict[int, tuple] = {}
+    def __init__(self, capacity: int = 128):
+        self._entries: collections.OrderedDict = collections.OrderedDict()
+        self._capacity = capacity
 
     def get(self, W: torch.Tensor) -> torch.Tensor:
-        key = id(W)
+        key = (W.data_ptr(), tuple(W.shape), tuple(W.stride()), W.device.index)
         ent = self._entries.get(key)
-        if ent is not None:
-            ref, version, ptr, ws = ent
-            if ref() is W and version == W._version and ptr == W.data_ptr():
-                return ws
+        if ent is not None and ent[1] == W._version:
+            self._entries.move_to_end(key)
+            return ent[2]
         F_in, F_out = W.shape
         nbytes = lib.load().fl_dot_general_workspace_bytes(F_in, F_out)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=W.device)
         lib.call('fl_dot_general_prepare', _ptr(W), F_in, F_out, _ptr(ws), nbytes, _stream(W.device))
-        self._entries[key] = (weakref.ref(W, lambda _: self._entries.pop(key, None)), W._version,
-                              W.data_ptr(), ws)
+        self._entries[key] = (W, W._version, ws)
+        self._entries.move_to_end(key)
+        while len(self._entries) > self._capacity:
+            self._entries.popitem(last=False)
         return ws
 
 

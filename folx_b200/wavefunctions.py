@@ -12,6 +12,7 @@ Every function maps ONE walker's electron coordinates ``r: (N, 3)`` to a scalar.
 from __future__ import annotations
 
 import math
+import weakref
 from dataclasses import dataclass, field
 
 import torch
@@ -204,6 +205,19 @@ def psiformer_params(cfg: PsiFormerConfig):
     return p
 
 
+_scaled_weights: dict = {}   # id(W) -> (weak reference to W, (factor, version), W * factor)
+
+
+def _scaled(W: torch.Tensor, s: float) -> torch.Tensor:
+    """``W * s``, made once per weight tensor (and again when the tensor is modified)."""
+    key = id(W)
+    ent = _scaled_weights.get(key)
+    if ent is None or ent[0]() is not W or ent[1] != (s, W._version):
+        ent = (weakref.ref(W, lambda _, k=key: _scaled_weights.pop(k, None)), (s, W._version), W * s)
+        _scaled_weights[key] = ent
+    return ent[2]
+
+
 def psiformer(cfg: PsiFormerConfig, p, r):
     """``log|psi|(r)`` for ``r: (n_elec, 3)``: embedding of electron-nucleus features, ``layers``
     blocks of multi-head self attention + LayerNorm + tanh MLP + LayerNorm, determinants with
@@ -215,7 +229,7 @@ def psiformer(cfg: PsiFormerConfig, p, r):
     h = F.linear(feats, p['W_in'].t(), p['b_in']) + p['spin']
     scale = 1.0 / math.sqrt(dh)
     for layer in p['layers']:
-        q = (h @ (layer['Wq'] * scale)).reshape(N, H, dh)   # 1 / sqrt(d_h) folded into the projection
+        q = (h @ _scaled(layer['Wq'], scale)).reshape(N, H, dh)   # 1 / sqrt(d_h) folded into the projection
         k = (h @ layer['Wk']).reshape(N, H, dh)
         v = (h @ layer['Wv']).reshape(N, H, dh)
         a = multi_head_self_attention(q, k, v).reshape(N, cfg.dim)
