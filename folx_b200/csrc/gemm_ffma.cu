@@ -101,6 +101,51 @@ gemm_smallk_kernel(const float* __restrict__ A, const float* __restrict__ W,
   }
 }
 
+// Few output columns (a final Dense(1), N <= 8): every row is N dot products of length Kc.  One
+// warp per row, lanes stride over k (coalesced reads of A, W comes from the cache), partial sums
+// meet in a shuffle reduction.  HBM-bound: 4 M Kc bytes.
+template <int NC>
+__global__ void __launch_bounds__(256)
+gemm_smalln_kernel(const float* __restrict__ A, const float* __restrict__ W,
+                   const float* __restrict__ bias, float* __restrict__ Y, int64_t M, int Kc,
+                   int64_t bias_rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * 8;
+  for (int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); row < M; row += warps) {
+    float acc[NC];
+#pragma unroll
+    for (int j = 0; j < NC; ++j) acc[j] = 0.f;
+    const float* a = A + row * Kc;
+    for (int k = lane; k < Kc; k += 32) {
+      const float av = __ldg(a + k);
+#pragma unroll
+      for (int j = 0; j < NC; ++j) acc[j] = fmaf(av, __ldg(W + (int64_t)k * NC + j), acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < NC; ++j)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+    if (lane < NC) {
+      float v = 0.f;
+#pragma unroll
+      for (int j = 0; j < NC; ++j) v = lane == j ? acc[j] : v;
+      if (bias && row < bias_rows) v += bias[lane];
+      Y[row * NC + lane] = v;
+    }
+  }
+}
+
+template <int NC>
+int32_t launch_smalln(const float* A, int64_t M, int64_t Kc, const float* W, const float* bias,
+                      int64_t bias_rows, float* Y, cudaStream_t st) {
+  int64_t blocks = (M + 7) / 8;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  gemm_smalln_kernel<NC><<<(unsigned)blocks, 256, 0, st>>>(A, W, bias, Y, M, (int)Kc, bias_rows);
+  FL_CHECK_LAUNCH("gemm_smalln launch");
+  return FL_OK;
+}
+
 template <int KC>
 int32_t launch_smallk(const float* A, int64_t M, int64_t N, const float* W, const float* bias,
                       int64_t bias_rows, float* Y, cudaStream_t st) {
@@ -125,6 +170,15 @@ int32_t gemm_ffma(const float* A, int64_t M, int64_t Kc, int64_t N, const float*
 #define FL_SK(K) case K: return launch_smallk<K>(A, M, N, W, bias, bias_rows, Y, st);
       FL_SK(1) FL_SK(2) FL_SK(3) FL_SK(4) FL_SK(5) FL_SK(6) FL_SK(7) FL_SK(8) FL_SK(12) FL_SK(16)
 #undef FL_SK
+      default: break;
+    }
+  }
+  // a handful of output columns over a long contracted axis: one warp per row
+  if (N <= 8 && Kc >= 32 && Kc < (1 << 30)) {
+    switch ((int)N) {
+#define FL_SN(C) case C: return launch_smalln<C>(A, M, Kc, W, bias, bias_rows, Y, st);
+      FL_SN(1) FL_SN(2) FL_SN(3) FL_SN(4) FL_SN(5) FL_SN(6) FL_SN(7) FL_SN(8)
+#undef FL_SN
       default: break;
     }
   }

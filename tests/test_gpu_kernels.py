@@ -172,6 +172,7 @@ GEMM_SHAPES = [
     # (K, P, F_in, F_out)
     (0, 1, 4, 4), (3, 5, 8, 12), (2, 130, 32, 16), (7, 33, 64, 48), (5, 200, 100, 100),
     (3, 129, 256, 256), (4, 64, 56, 256), (2, 40, 36, 260), (1, 300, 256, 512), (6, 17, 30, 10),
+    (3, 50, 100, 1), (2, 33, 64, 5), (1, 9, 40, 8), (4, 2000, 100, 1),   # few output columns
 ]
 
 
