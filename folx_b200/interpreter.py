@@ -169,19 +169,29 @@ class LaplTensor:
                 return LaplTensor(None, self.nb, self.thr, terms=self._terms + [(t, sign)],
                                   act=(self._act[0], True))
         mine = self._dense_terms()
-        if mine is None:
-            return None
         sign = 1.0 if op == 'add' else -1.0
         phys = tuple(self._x_like().shape)
         if isinstance(other, LaplTensor):
             if other.ndim > self.ndim or other.nb != self.nb:
                 return None
-            theirs = other._rank_to(self.ndim)._dense_terms()
-            if theirs is None:
+            other = other._rank_to(self.ndim)
+            try:
+                if tuple(torch.broadcast_shapes(phys, tuple(other._x_like().shape))) != phys:
+                    return None
+            except RuntimeError:
+                return None
+            theirs = other._dense_terms()
+            # sparse + dense is dense (any dense operand densifies the sum, folx/api.py:233-236):
+            # the sparse side is densified here and joins the pending sum like a dense term
+            if mine is None and theirs is not None:
+                mine = [(rules.densify(self.arr), 1.0)]
+            elif theirs is None and mine is not None:
+                theirs = [(rules.densify(other.arr), 1.0)]
+            if mine is None or theirs is None:
                 return None
             oshape = tuple(theirs[0][0].x.shape)
             theirs = [(t, sign * s) for t, s in theirs]
-        elif torch.is_tensor(other) and other.ndim >= 1 and other.is_floating_point():
+        elif mine is not None and torch.is_tensor(other) and other.ndim >= 1 and other.is_floating_point():
             c = other.as_subclass(torch.Tensor)
             if isinstance(other, BatchedConst):
                 rank_o = c.ndim - self.nb
