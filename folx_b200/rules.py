@@ -443,8 +443,8 @@ def reduce_sum(a, axes, keepdim: bool = False, sparsity_threshold: int = 0):
     nr, rstride = _adjacent_axes_last_stride(a.x, axes)
     x0 = _mask_nd(a)
 
-    def reduce_rows(data, table, table_shape, n_out):
-        # data: (rows, *shape) contiguous -> (n_out, *kept_shape)
+    def reduce_rows(data, table, table_shape, dst):
+        # data: (rows, *shape) contiguous -> dst: (n_out, *kept_shape)
         rows = data.shape[0]
         view = data.reshape(rows, *a.x.shape)
         # an input row as the kernel sees it: the kept axes only (the reduced run is addressed
@@ -452,17 +452,11 @@ def reduce_sum(a, axes, keepdim: bool = False, sparsity_threshold: int = 0):
         idx = tuple(0 if d in axes else slice(None) for d in range(nd))
         row_view = view[(slice(None), *idx)]
         return sparse.gather_rows(row_view, table, kept_shape, table_shape, n_reduced=nr,
-                                  reduced_stride=rstride)
-
-    # x and the Laplacian are plain sums
-    one = np.arange(nr, dtype=np.int64).reshape(1, nr)
-    y = reduce_rows(a.x.reshape(1, *a.x.shape), one, (), 1)[0]
-    lap = reduce_rows(a.laplacian.reshape(1, *a.x.shape), one, (), 1)[0]
+                                  reduced_stride=rstride, out=dst)
 
     if x0 is None:
-        table = (np.arange(K, dtype=np.int64)[:, None] * nr + np.arange(nr)[None, :])
-        jac = reduce_rows(a.jacobian.data, table, (), K)
-        out_mask = None
+        take = (np.arange(K, dtype=np.int64)[:, None] * nr + np.arange(nr)[None, :])
+        kept_c, n_out, out_mask = (), K, None
     else:
         # along reduced axes the true extent matters (every element is a separate source); the
         # kept axes may stay compact (size 1 where the map is constant)
@@ -486,8 +480,14 @@ def reduce_sum(a, axes, keepdim: bool = False, sparsity_threshold: int = 0):
         t = t.reshape(int(np.prod(kept_c, dtype=np.int64)), K * nr)
         take = masks.gather_table(t, n_out)  # (p, n_out, n_slots), entries k * nr + r
         take = np.transpose(take, (1, 2, 0)).reshape(n_out, take.shape[2], *kept_c)
-        jac = reduce_rows(a.jacobian.data, take, kept_c, n_out)
-    out = FwdLaplArray(y, FwdJacobian(jac, out_mask), lap)
+    # all three fields land in one stacked buffer, so that a product that follows reads it as one
+    # operand; x and the Laplacian are plain sums
+    out = kernels.alloc_triplet(n_out, kept_shape, a.x.device, out_mask)
+    one = np.arange(nr, dtype=np.int64).reshape(1, nr)
+    reduce_rows(a.x.reshape(1, *a.x.shape), one, (), out.x.unsqueeze(0))
+    reduce_rows(a.laplacian.reshape(1, *a.x.shape), one, (), out.laplacian.unsqueeze(0))
+    if n_out > 0:
+        reduce_rows(a.jacobian.data, take, kept_c, out.jacobian.data)
     if keepdim:
         for d in axes:
             out = expand_dims(out, d)
