@@ -146,3 +146,74 @@ def test_union_rows_order_is_lexicographic():
     res, inv = masks.union_rows([m1, m2])
     np.testing.assert_array_equal(res, [[0, 1, 2], [3, 4, 5]])
     assert inv.tolist() == [1, 0]
+
+
+# ---- factor tables of the sparse log-determinant rule (folx/slogdet.py:93-293) ---------------------
+def _slogdet_mask(mode, n):
+    if mode == 'entries':
+        return np.stack([np.roll(np.arange(n), s) for s in range(n)])[None].astype(np.int64)
+    mask = np.zeros((3, n, n), dtype=np.int64)
+    for k in range(3):
+        mask[k] = (3 * np.arange(n) + k)[:, None]
+    if mode == 'two_rows':
+        mask = np.concatenate([mask, np.roll(mask, 1, axis=1)], axis=0)
+    if mode == 'columns':
+        mask = np.swapaxes(mask, -1, -2).copy()
+    if mode == 'shared':
+        mask = np.broadcast_to(np.arange(3 * n).reshape(3 * n, 1, 1), (3 * n, n, n)).copy()
+    return mask
+
+
+@pytest.mark.parametrize('mode,fast,shape', [
+    ('rows', True, (18, 1, 6)), ('two_rows', True, (18, 2, 6)), ('columns', True, (18, 1, 6)),
+    ('entries', True, (6, 6, 1)), ('shared', False, None)])
+def test_sparse_slogdet_plan_follows_the_reference_cases(mode, fast, shape):
+    """Which masks take the factorised rule and with which table shape (the cases of the
+    reference's test/test_layers.py:340-420: rows, two rows, columns, single entries, no structure)."""
+    n = 6
+    mask = _slogdet_mask(mode, n)
+    plan = masks.plan_sparse_slogdet(mask, (n, n), int(mask.max()) + 1)
+    assert (plan is not None) == fast
+    if fast:
+        take, cols, rows, coords, transposed = plan
+        assert take.shape == shape and cols.shape == shape and rows.shape == shape[:2]
+        assert transposed == (mode == 'columns')
+        np.testing.assert_array_equal(coords, np.arange(int(mask.max()) + 1))
+    # the same map stored once for a batch of walkers (size-1 batch axes) plans identically,
+    # whatever the batch extent of the values
+    batched = masks.plan_sparse_slogdet(mask.reshape(mask.shape[0], 1, 1, n, n), (4096, 16, n, n),
+                                        int(mask.max()) + 1)
+    assert (batched is not None) == fast
+
+
+@pytest.mark.parametrize('mode', ['rows', 'two_rows', 'columns', 'entries'])
+def test_sparse_slogdet_tables_reproduce_the_rule(mode):
+    """The contraction the kernel runs on the tables, W_c[s, t] = sum_l dA[take] A^-1[cols, rows]
+    (A^-1 read transposed for column factors), written in NumPy: J_c = tr W_c and
+    lap = tr(A^-1 lapA) - sum_c tr(W_c W_c) must equal the dense rule on the densified Jacobian."""
+    rng = np.random.default_rng(5)
+    n = 5
+    mask = _slogdet_mask(mode, n)
+    k = mask.shape[0]
+    n_in = int(mask.max()) + 1
+    A = rng.normal(size=(n, n)) + 2 * np.eye(n)
+    J = rng.normal(size=(k, n, n))
+    lapA = rng.normal(size=(n, n))
+    take, cols, rows, coords, transposed = masks.plan_sparse_slogdet(mask, (n, n), n_in) or \
+        (*masks.slogdet_factor_tables(mask, False)[1:], False)
+    C = np.linalg.inv(A)
+    flat = np.concatenate([J.reshape(-1), [0.0]])
+    vals = flat[np.where(take >= 0, take, J.size)]                       # (coords, rank, width)
+    Cg = C[rows[:, None, None, :], cols[..., None]] if transposed else C[cols[..., None], rows[:, None, None, :]]
+    W = np.einsum('csl,cslt->cst', vals, Cg)
+    jac = np.zeros(n_in)
+    jac[coords] = np.einsum('css->c', W)
+    lap = np.einsum('ji,ij->', C, lapA) - np.einsum('cst,cts->', W, W)
+    dense = np.zeros((n_in, n, n))
+    for s in range(k):
+        for i in range(n):
+            for j in range(n):
+                dense[mask[s, i, j], i, j] += J[s, i, j]
+    M = C @ dense
+    np.testing.assert_allclose(jac, np.einsum('kii->k', M), rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(lap, np.einsum('ji,ij->', C, lapA) - np.einsum('kij,kji->', M, M), rtol=1e-10)
