@@ -283,7 +283,18 @@ class LaplTensor:
             return out
         if W.ndim == 1:
             return (self @ W[:, None]).squeeze(-1)
-        return self._wrap(_call('dot_general', (self.arr, W), {}, self.thr))
+        arr, W = self._operand_and_weight(W)
+        return self._wrap(_call('dot_general', (arr, W), {}, self.thr))
+
+    def _operand_and_weight(self, W):
+        """The triplet and the constant matrix of ``self @ W``; a pending scalar factor of this
+        tensor (``mean``) moves into the matrix: ``(s a) @ W = a @ (s W)``."""
+        if (self._arr is None and self._terms is not None and self._act is None
+                and len(self._terms) == 1 and isinstance(self._terms[0][0], FwdLaplArray)
+                and torch.is_tensor(W) and W.ndim == 2 and registry.is_builtin('dot_general')):
+            arr, s = self._terms[0]
+            return arr, (W if s == 1.0 else kernels.scaled_weight(W, s))
+        return self.arr, W
 
     def __rmatmul__(self, W):
         return self._wrap(_call('dot_general', (W, self.arr), {}, self.thr))
@@ -389,7 +400,13 @@ class LaplTensor:
             dim = tuple(range(self.ndim))
         dims = (dim,) if isinstance(dim, int) else tuple(dim)
         n = math.prod(self.shape[d] for d in dims)
-        return self.sum(dims, keepdim) * (1.0 / n)
+        total = self.sum(dims, keepdim)
+        if (registry.is_builtin('mul') and registry.is_builtin('dot_general')
+                and not total.arr.jacobian.weak):
+            # the factor 1 / n stays pending: a product with a constant matrix that follows takes
+            # it into the weights, anything else applies it in one pass
+            return LaplTensor(None, total.nb, total.thr, terms=[(total.arr, 1.0 / n)])
+        return total * (1.0 / n)
 
     # ---- indexing ----
     def reshape(self, *shape):
@@ -495,7 +512,8 @@ def _binary_fn(op):
 
 
 def _linear(x, weight, bias=None):
-    return x._wrap(_call('dot_general', (x.arr, weight.t()), {'bias': bias}, x.thr))
+    arr, W = x._operand_and_weight(weight.t())
+    return x._wrap(_call('dot_general', (arr, W), {'bias': bias}, x.thr))
 
 
 def _matmul(a, b):

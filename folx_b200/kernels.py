@@ -240,6 +240,36 @@ class _WeightCache:
 
 
 _weights = _WeightCache()
+
+
+class _ScaledWeights:
+    """``W * s`` made once per weight (same keying and lifetime rules as the workspace cache), so
+    that a scalar factor folded into a product keeps hitting that cache."""
+
+    def __init__(self, capacity: int = 128):
+        self._entries: collections.OrderedDict = collections.OrderedDict()
+        self._capacity = capacity
+
+    def get(self, W: torch.Tensor, s: float) -> torch.Tensor:
+        key = (W.data_ptr(), tuple(W.shape), tuple(W.stride()), W.device.index, W.dtype, float(s))
+        ent = self._entries.get(key)
+        if ent is not None and ent[1] == W._version:
+            self._entries.move_to_end(key)
+            return ent[2]
+        scaled = (W * s).contiguous()
+        self._entries[key] = (W, W._version, scaled)
+        while len(self._entries) > self._capacity:
+            self._entries.popitem(last=False)
+        return scaled
+
+
+_scaled_weights = _ScaledWeights()
+
+
+def scaled_weight(W: torch.Tensor, s: float) -> torch.Tensor:
+    """``W * s`` for a constant weight, cached: ``(s a) @ W = a @ (s W)`` saves the pass that
+    would scale the triplet."""
+    return _scaled_weights.get(W, s)
 _status: dict[torch.device, torch.Tensor] = {}
 
 

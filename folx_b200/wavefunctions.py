@@ -12,13 +12,13 @@ Every function maps ONE walker's electron coordinates ``r: (N, 3)`` to a scalar.
 from __future__ import annotations
 
 import math
-import weakref
 from dataclasses import dataclass, field
 
 import torch
 import torch.nn.functional as F
 
 from .attention import multi_head_self_attention
+from .kernels import scaled_weight as _scaled
 
 
 def _normal(gen, *shape, fan_in=None, scale=None):
@@ -135,19 +135,6 @@ def ferminet_params(cfg: FermiNetConfig):
     return p
 
 
-_scaled_weights: dict = {}   # id(W) -> (weak reference to W, (factor, version), W * factor)
-
-
-def _scaled(W: torch.Tensor, s: float) -> torch.Tensor:
-    """``W * s``, made once per weight tensor (and again when the tensor is modified)."""
-    key = id(W)
-    ent = _scaled_weights.get(key)
-    if ent is None or ent[0]() is not W or ent[1] != (s, W._version):
-        ent = (weakref.ref(W, lambda _, k=key: _scaled_weights.pop(k, None)), (s, W._version), W * s)
-        _scaled_weights[key] = ent
-    return ent[2]
-
-
 def ferminet(cfg: FermiNetConfig, p, r):
     """``log|psi|(r)`` for ``r: (n_elec, 3)``.
 
@@ -162,11 +149,8 @@ def ferminet(cfg: FermiNetConfig, p, r):
     h = torch.cat([r_en.reshape(N, -1), d_en], -1)           # (N, 4 M)
     g = torch.cat([r_ee, d_ee.unsqueeze(-1)], -1)            # (N, N, 4)
     for l, layer in enumerate(p['layers']):
-        # means over electrons: the 1 / n of each mean is folded into the weight it multiplies
-        pooled = (h[:nu].sum(0) @ _scaled(layer['W_up'], 1.0 / nu)
-                  + h[nu:].sum(0) @ _scaled(layer['W_dn'], 1.0 / (N - nu)))               # (width,)
-        pair = (g[:, :nu].sum(1) @ _scaled(layer['W_2u'], 1.0 / nu)
-                + g[:, nu:].sum(1) @ _scaled(layer['W_2d'], 1.0 / (N - nu)))              # (N, width)
+        pooled = (h[:nu].mean(0) @ layer['W_up'] + h[nu:].mean(0) @ layer['W_dn'])  # (width,)
+        pair = g[:, :nu].mean(1) @ layer['W_2u'] + g[:, nu:].mean(1) @ layer['W_2d']  # (N, width)
         new_h = (F.linear(h, layer['W_h'].t(), layer['b']) + pair + pooled).tanh()
         h = new_h + h if new_h.shape == h.shape else new_h
         if 'V' in layer:
