@@ -12,6 +12,7 @@ Every function maps ONE walker's electron coordinates ``r: (N, 3)`` to a scalar.
 from __future__ import annotations
 
 import math
+import weakref
 from dataclasses import dataclass, field
 
 import torch
@@ -135,6 +136,20 @@ def ferminet_params(cfg: FermiNetConfig):
     return p
 
 
+_stacked_weights: dict = {}   # (id(A), id(B)) -> (weak references, versions, cat([A, B]))
+
+
+def _stacked(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
+    """``cat([A, B], 0)``, made once per pair of weight tensors (again when one is modified)."""
+    key = (id(A), id(B))
+    ent = _stacked_weights.get(key)
+    if ent is None or ent[0]() is not A or ent[1]() is not B or ent[2] != (A._version, B._version):
+        drop = lambda _, k=key: _stacked_weights.pop(k, None)
+        ent = (weakref.ref(A, drop), weakref.ref(B, drop), (A._version, B._version), torch.cat([A, B], 0))
+        _stacked_weights[key] = ent
+    return ent[3]
+
+
 def ferminet(cfg: FermiNetConfig, p, r):
     """``log|psi|(r)`` for ``r: (n_elec, 3)``.
 
@@ -150,7 +165,8 @@ def ferminet(cfg: FermiNetConfig, p, r):
     g = torch.cat([r_ee, d_ee.unsqueeze(-1)], -1)            # (N, N, 4)
     for l, layer in enumerate(p['layers']):
         pooled = (h[:nu].mean(0) @ layer['W_up'] + h[nu:].mean(0) @ layer['W_dn'])  # (width,)
-        pair = g[:, :nu].mean(1) @ layer['W_2u'] + g[:, nu:].mean(1) @ layer['W_2d']  # (N, width)
+        # the two pooled pair features share one product: [mean_up g | mean_dn g] @ [W_2u; W_2d]
+        pair = torch.cat([g[:, :nu].mean(1), g[:, nu:].mean(1)], -1) @ _stacked(layer['W_2u'], layer['W_2d'])
         new_h = (F.linear(h, layer['W_h'].t(), layer['b']) + pair + pooled).tanh()
         h = new_h + h if new_h.shape == h.shape else new_h
         if 'V' in layer:
