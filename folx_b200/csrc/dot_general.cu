@@ -126,3 +126,41 @@ extern "C" int32_t fl_dot_general_grouped(const float* x, const float* jac, cons
   }
   return FL_OK;
 }
+
+// The product of a CONCATENATION along the feature axis, [a_1 | a_2 | a_3] W (+ bias), without
+// forming the concatenation (the reference concatenates first: an INDEXING rule followed by
+// dot_general, folx/wrapped_functions.py:474-479, 174-203).  Every operand is a stacked triplet
+// ([x; J_1..J_K; lap]: (K + 2) P contiguous rows of F_in[i] floats) with the same P and K; the
+// output is stacked the same way.  W has sum F_in rows and is prepared as usual.  Tensor-core
+// kernel only: FL_EUNSUPPORTED (operand widths that are not multiples of 16 before the last one,
+// misaligned buffers, a forced CUDA-core mode) tells the caller to concatenate and use
+// fl_dot_general.
+extern "C" int32_t fl_dot_general_cat(int32_t n_operands, const float* const* operands,
+                                      const int64_t* F_in, int64_t P, int64_t K, int64_t F_out,
+                                      const float* bias, const void* workspace,
+                                      int64_t workspace_bytes, float* y, int32_t* status,
+                                      void* stream) {
+  using namespace fl;
+  FL_REQUIRE(n_operands >= 1 && n_operands <= 3 && operands && F_in, FL_EBADSHAPE,
+             "fl_dot_general_cat: 1 to 3 operands, got %d", n_operands);
+  FL_REQUIRE(P >= 0 && K >= 0 && F_out > 0, FL_EBADSHAPE,
+             "fl_dot_general_cat: bad sizes P=%lld K=%lld F_out=%lld", (long long)P, (long long)K,
+             (long long)F_out);
+  int64_t total = 0;
+  for (int i = 0; i < n_operands; ++i) {
+    FL_REQUIRE(operands[i] && F_in[i] > 0, FL_EBADSHAPE, "fl_dot_general_cat: bad operand %d", i);
+    total += F_in[i];
+  }
+  if (P == 0) return FL_OK;
+  FL_REQUIRE(y, FL_EBADSHAPE, "fl_dot_general_cat: null output");
+  FL_REQUIRE(workspace != nullptr && workspace_bytes >= wsplit_geom(total, F_out).bytes &&
+                 total >= 16 && F_out >= 16 && g_mode != 1,
+             FL_EUNSUPPORTED, "fl_dot_general_cat: needs the tensor-core path");
+  const int64_t rows = (K + 2) * P;
+  FL_REQUIRE(gemm_tc_supported(operands[0], rows, F_in[0], F_out, y), FL_EUNSUPPORTED,
+             "fl_dot_general_cat: shape or alignment does not fit the tensor-core kernel");
+  return gemm_tc(operands[0], rows, F_in[0], F_out, workspace, bias, bias ? P : 0, y, status,
+                 g_mode == 3 ? 1 : (g_mode == 4 ? 2 : 0), 0, 0, (cudaStream_t)stream,
+                 n_operands > 1 ? operands[1] : nullptr, n_operands > 1 ? F_in[1] : 0,
+                 n_operands > 2 ? operands[2] : nullptr, n_operands > 2 ? F_in[2] : 0);
+}

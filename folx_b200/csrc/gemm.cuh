@@ -25,10 +25,14 @@ bool gemm_tc_supported(const float* A, int64_t M, int64_t Kc, int64_t N, const f
 
 // tcgen05 3xTF32 kernel reading the split W from `workspace`.  ctas: 0 = pick (CTA pairs sharing W
 // when there are at least two row tiles), 1 = one CTA per tile, 2 = require pairs.  group_rows > 0:
-// the rows of A are groups of group_rows contiguous rows, group_stride elements apart.
+// the rows of A are groups of group_rows contiguous rows, group_stride elements apart.  A2 / A3:
+// further operands with the same rows whose columns continue those of A (the product of their
+// concatenation along K with a W of Kc + Kc2 + Kc3 rows, never formed in memory).
 int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* workspace,
                 const float* bias, int64_t bias_rows, float* Y, int32_t* status, int ctas,
-                int64_t group_rows, int64_t group_stride, cudaStream_t st);
+                int64_t group_rows, int64_t group_stride, cudaStream_t st,
+                const float* A2 = nullptr, int64_t Kc2 = 0, const float* A3 = nullptr,
+                int64_t Kc3 = 0);
 
 // Splits W into TF32 head/tail, transposed and padded, into `workspace`.
 int32_t gemm_tc_prepare(const float* W, int64_t Kc, int64_t N, void* workspace, cudaStream_t st);

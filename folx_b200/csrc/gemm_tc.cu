@@ -319,10 +319,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                const __grid_constant__ CUtensorMap tmWlo, const __grid_constant__ CUtensorMap tmY,
                const float* __restrict__ bias, int64_t bias_rows, int num_m_tiles, int num_k_steps,
                int n_tile, int n_chunks, int n_total, float* __restrict__ Y, int64_t M_rows,
-               int32_t* __restrict__ status, int a_groups_per_tile) {
+               int32_t* __restrict__ status, int a_groups_per_tile,
+               const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmA3,
+               int k_steps_a1, int k_steps_a12) {
   // a_groups_per_tile > 0: A is a 3-D map (columns, rows of a group, groups) whose groups of
   // 128 / a_groups_per_tile contiguous rows lie a fixed stride apart (a slice of a larger
   // triplet read in place); 0: A is a plain 2-D map.
+  // A may be the concatenation [A1 | A2 | A3] along K of up to three row-aligned operands that is
+  // never formed in memory: K steps below k_steps_a1 come from tmA, those below k_steps_a12 from
+  // tmA2, the rest from tmA3 (a single operand has k_steps_a1 = k_steps_a12 = num_k_steps).
   using G = Geom<CTAS>;
   constexpr int STAGES = G::STAGES;
   constexpr int STAGE_BYTES = G::STAGE_BYTES;
@@ -398,8 +403,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           mbar_expect_tx(bar, stage_bytes_tx);
           if (a_groups_per_tile > 0)
             tma_load_3d(smem_u32(sb), &tmA, ks * BLOCK_K, 0, m_tile * a_groups_per_tile, bar);
-          else
+          else if (ks < k_steps_a1)
             tma_load_2d(smem_u32(sb), &tmA, ks * BLOCK_K, m_tile * BLOCK_M, bar);
+          else if (ks < k_steps_a12)
+            tma_load_2d(smem_u32(sb), &tmA2, (ks - k_steps_a1) * BLOCK_K, m_tile * BLOCK_M, bar);
+          else
+            tma_load_2d(smem_u32(sb), &tmA3, (ks - k_steps_a12) * BLOCK_K, m_tile * BLOCK_M, bar);
           const int w_row0 = n_chunk * n_tile + (int)rank * w_rows;
           tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES), &tmWhi, ks * BLOCK_K, w_row0, bar);
           tma_load_2d(smem_u32(sb + 2 * A_TILE_BYTES + W_TILE_BYTES), &tmWlo, ks * BLOCK_K, w_row0,
@@ -796,9 +805,22 @@ int max_pair_clusters() {
 
 int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* workspace,
                 const float* bias, int64_t bias_rows, float* Y, int32_t* status, int ctas,
-                int64_t group_rows, int64_t group_stride, cudaStream_t st) {
+                int64_t group_rows, int64_t group_stride, cudaStream_t st, const float* A2,
+                int64_t Kc2, const float* A3, int64_t Kc3) {
   // group_rows > 0: the M rows of A come in groups of group_rows contiguous rows, group_stride
   // elements apart (group_rows divides 128 and M); 0: A is contiguous
+  // A2 / A3 (optional, Kc2 / Kc3 columns): further operands with the same M rows whose columns
+  // continue those of A, i.e. the product is [A | A2 | A3] W with W of Kc + Kc2 + Kc3 rows; every
+  // operand but the last must have a multiple of 16 columns (a K step never straddles two)
+  if (A2 == nullptr) { Kc2 = 0; A3 = nullptr; }
+  if (A3 == nullptr) Kc3 = 0;
+  FL_REQUIRE(A2 == nullptr ||
+                 (group_rows == 0 && Kc % BLOCK_K == 0 && gemm_tc_supported(A2, M, Kc2, N, Y) &&
+                  (A3 == nullptr || (Kc2 % BLOCK_K == 0 && gemm_tc_supported(A3, M, Kc3, N, Y)))),
+             FL_EUNSUPPORTED, "tensor-core GEMM: concatenated operands need 16-column blocks "
+             "(%lld, %lld, %lld columns) and 16-byte aligned rows", (long long)Kc, (long long)Kc2,
+             (long long)Kc3);
+  const int64_t Kc_total = Kc + Kc2 + Kc3;
   FL_REQUIRE(group_rows == 0 || (group_rows > 0 && BLOCK_M % group_rows == 0 && M % group_rows == 0 &&
                                  group_stride >= group_rows * Kc && group_stride % 4 == 0),
              FL_EUNSUPPORTED, "tensor-core GEMM: row groups of %lld rows (stride %lld) are not supported",
@@ -814,7 +836,7 @@ int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* wo
                                  Geom<2>::SMEM_BYTES));
     attr_set = true;
   }
-  WSplitGeom g = wsplit_geom(Kc, N);
+  WSplitGeom g = wsplit_geom(Kc_total, N);
   const int64_t wrows = g.n_chunks * g.n_tile;
   const float* whi = (const float*)workspace;
   const float* wlo = whi + wrows * g.k_pad;
@@ -834,10 +856,16 @@ int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* wo
     rc = make_map(&tmA, A, M, Kc, Kc, BLOCK_M, BLOCK_K, "A");
   if (rc != FL_OK) return rc;
   const int a_groups_per_tile = group_rows > 0 ? (int)(BLOCK_M / group_rows) : 0;
+  // further operands of a concatenation (a single operand passes its own map again, unused)
+  CUtensorMap tmA2 = tmA, tmA3 = tmA;
+  if (A2 && (rc = make_map(&tmA2, A2, M, Kc2, Kc2, BLOCK_M, BLOCK_K, "A2")) != FL_OK) return rc;
+  if (A3 && (rc = make_map(&tmA3, A3, M, Kc3, Kc3, BLOCK_M, BLOCK_K, "A3")) != FL_OK) return rc;
   if ((rc = make_map(&tmWhi, whi, wrows, g.k_pad, g.k_pad, w_box_rows, BLOCK_K, "W_hi")) != FL_OK) return rc;
   if ((rc = make_map(&tmWlo, wlo, wrows, g.k_pad, g.k_pad, w_box_rows, BLOCK_K, "W_lo")) != FL_OK) return rc;
   if ((rc = make_map(&tmY, Y, M, N, N, 32, 32, "Y")) != FL_OK) return rc;
   const int num_k_steps = (int)(g.k_pad / BLOCK_K);
+  const int k_steps_a1 = A2 ? (int)(Kc / BLOCK_K) : num_k_steps;
+  const int k_steps_a12 = A3 ? k_steps_a1 + (int)(Kc2 / BLOCK_K) : num_k_steps;
   if (pair) {
     const int groups = (num_m_tiles + 1) / 2;
     const int64_t tiles = (int64_t)groups * g.n_chunks;
@@ -856,13 +884,13 @@ int32_t gemm_tc(const float* A, int64_t M, int64_t Kc, int64_t N, const void* wo
     cfg.numAttrs = 1;
     FL_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc_kernel<2>, tmA, tmWhi, tmWlo, tmY, bias, bias_rows,
                                groups, num_k_steps, (int)g.n_tile, (int)g.n_chunks, (int)N, Y, M,
-                               status, a_groups_per_tile));
+                               status, a_groups_per_tile, tmA2, tmA3, k_steps_a1, k_steps_a12));
   } else {
     const int64_t tiles = (int64_t)num_m_tiles * g.n_chunks;
     int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     gemm_tc_kernel<1><<<grid, NUM_THREADS, Geom<1>::SMEM_BYTES, st>>>(
         tmA, tmWhi, tmWlo, tmY, bias, bias_rows, num_m_tiles, num_k_steps, (int)g.n_tile,
-        (int)g.n_chunks, (int)N, Y, M, status, a_groups_per_tile);
+        (int)g.n_chunks, (int)N, Y, M, status, a_groups_per_tile, tmA2, tmA3, k_steps_a1, k_steps_a12);
   }
   FL_CHECK_LAUNCH("gemm_tc launch");
   return FL_OK;

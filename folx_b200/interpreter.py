@@ -50,9 +50,10 @@ _CHAINABLE = frozenset({'tanh', 'silu', 'exp', 'log', 'sqrt', 'rsqrt', 'square',
 class LaplTensor:
     """A tensor seen by the traced function: value, Jacobian and Laplacian travel together."""
 
-    __slots__ = ('_arr', 'nb', 'thr', '_terms', '_chain', '_act')
+    __slots__ = ('_arr', 'nb', 'thr', '_terms', '_chain', '_act', '_parts', '_like')
 
-    def __init__(self, arr: FwdLaplArray | None, nb: int, thr: int, terms=None, chain=None, act=None):
+    def __init__(self, arr: FwdLaplArray | None, nb: int, thr: int, terms=None, chain=None, act=None,
+                 parts=None):
         # `terms` is a pending sum [(dense triplet or constant, +1 / -1), ...] that has not been
         # written out yet: a chain of additions is evaluated in one pass, together with the
         # elementwise function that consumes it if there is one (what XLA's fusion does for the
@@ -62,12 +63,21 @@ class LaplTensor:
         # first needed
         # `act` = (name, residual) says that a function is applied to the pending sum; with
         # `residual` the last term is added after the function (h + tanh(...)), all in one kernel
+        # `parts` is a pending concatenation of dense triplets along the last axis: a product with
+        # a constant matrix that follows reads the parts where they are (fl_dot_general_cat), any
+        # other use forms the concatenation
         self._arr, self.nb, self.thr, self._terms, self._chain, self._act = arr, nb, thr, terms, chain, act
+        self._parts, self._like = parts, None
 
     @property
     def arr(self) -> FwdLaplArray:
         if self._arr is None:
-            if self._terms is not None:
+            if self._parts is not None:
+                ax = self._parts[0].x.ndim - 1
+                self._arr = _call('concatenate', tuple(self._parts), {'dimension': ax, 'batch_dims': self.nb},
+                                  self.thr)
+                self._parts = None
+            elif self._terms is not None:
                 key, residual = self._act or ('identity', False)
                 self._arr = kernels.addn(self._terms, key, residual=residual)
                 self._terms = None
@@ -86,6 +96,12 @@ class LaplTensor:
     def _x_like(self) -> torch.Tensor:
         if self._arr is not None:
             return self._arr.x
+        if self._parts is not None:
+            if self._like is None:  # shape, dtype and device of the concatenation without forming it
+                x0 = self._parts[0].x
+                width = sum(int(p.x.shape[-1]) for p in self._parts)
+                self._like = x0.new_zeros(1).expand(*x0.shape[:-1], width)
+            return self._like
         return self._terms[0][0].x if self._terms is not None else self._chain[0].x
 
     # ---- tensor-like attributes (per walker) ----
@@ -283,8 +299,21 @@ class LaplTensor:
             return out
         if W.ndim == 1:
             return (self @ W[:, None]).squeeze(-1)
+        out = self._product_of_parts(W, None)
+        if out is not None:
+            return out
         arr, W = self._operand_and_weight(W)
         return self._wrap(_call('dot_general', (arr, W), {}, self.thr))
+
+    def _product_of_parts(self, W, bias):
+        """``cat(parts) @ W (+ bias)`` for a pending concatenation, without forming it; None when
+        this tensor is not one or the kernel does not take the operands."""
+        if (self._arr is None and self._parts is not None and torch.is_tensor(W) and W.ndim == 2
+                and not isinstance(W, LaplTensor) and registry.is_builtin('dot_general')):
+            out = kernels.dot_general_cat(self._parts, W, bias)
+            if out is not None:
+                return self._wrap(out)
+        return None
 
     def _operand_and_weight(self, W):
         """The triplet and the constant matrix of ``self @ W``; a pending scalar factor of this
@@ -512,6 +541,9 @@ def _binary_fn(op):
 
 
 def _linear(x, weight, bias=None):
+    out = x._product_of_parts(weight.t(), bias)
+    if out is not None:
+        return out
     arr, W = x._operand_and_weight(weight.t())
     return x._wrap(_call('dot_general', (arr, W), {'bias': bias}, x.thr))
 
@@ -537,6 +569,14 @@ def _cat(tensors, dim=0):
             c = t.reshape((1,) * (t0.nb + rank - t.ndim) + tuple(t.shape))
             parts.append(c.expand(*t0.arr.x.shape[: t0.nb], *c.shape[t0.nb:]))
     ax = (dim % rank) + t0.nb
+    if (dim % rank == rank - 1 and 2 <= len(parts) <= 3 and registry.is_builtin('concatenate')
+            and registry.is_builtin('dot_general')
+            and all(isinstance(p, FwdLaplArray) and not p.jacobian.weak for p in parts)
+            and all(tuple(p.x.shape[:-1]) == tuple(parts[0].x.shape[:-1])
+                    and p.jacobian.data.shape[0] == parts[0].jacobian.data.shape[0] for p in parts)):
+        # dense features side by side (a layer input [h, pooled ...]): stays pending, a product
+        # with a constant matrix reads the parts in place
+        return LaplTensor(None, t0.nb, t0.thr, parts=list(parts))
     return t0._wrap(_call('concatenate', tuple(parts), {'dimension': ax, 'batch_dims': t0.nb}, t0.thr))
 
 

@@ -382,6 +382,57 @@ def dot_general(a: FwdLaplArray, W: torch.Tensor, bias: torch.Tensor | None = No
     return out
 
 
+def _stacked_base(a: FwdLaplArray):
+    """The address of the triplet's buffer if x, the K Jacobian rows and lap lie back to back in
+    one contiguous buffer (the layout ``alloc_triplet`` produces), else None."""
+    x, j, l = a.x, a.jacobian.data, a.laplacian
+    if not (x.is_contiguous() and l.is_contiguous() and j.is_contiguous()):
+        return None
+    n, K = x.numel() * 4, j.shape[0]
+    if K and j.data_ptr() != x.data_ptr() + n:
+        return None
+    if l.data_ptr() != x.data_ptr() + (K + 1) * n:
+        return None
+    return x.data_ptr()
+
+
+def dot_general_cat(parts, W: torch.Tensor, bias: torch.Tensor | None = None):
+    """``cat(parts, -1) @ W (+ bias)`` for dense triplets that share everything but the last axis,
+    without forming the concatenation (``fl_dot_general_cat``).  Returns None when the kernel
+    does not take the operands (the caller then concatenates)."""
+    if not 1 < len(parts) <= 3 or any(p.jacobian.weak for p in parts):
+        return None
+    lead, K = tuple(parts[0].x.shape[:-1]), parts[0].jacobian.data.shape[0]
+    widths = [int(p.x.shape[-1]) for p in parts]
+    if any(tuple(p.x.shape[:-1]) != lead or p.jacobian.data.shape[0] != K for p in parts):
+        return None
+    if any(w % 16 for w in widths[:-1]) or widths[-1] % 4 or W.shape[0] != sum(widths):
+        return None
+    F_out = int(W.shape[1])
+    if F_out < 16 or F_out % 4:
+        return None
+    bases = [_stacked_base(p) for p in parts]
+    if any(b is None or b % 16 for b in bases):
+        return None
+    W = W.contiguous()
+    _require_cuda(*(p.x for p in parts), W, bias)
+    P = parts[0].x.numel() // widths[0]
+    out = alloc_triplet(K, (*lead, F_out), W.device, None)
+    ws = _weights.get(W)
+    ptrs = (ctypes.c_void_p * len(parts))(*bases)
+    f_in = (ctypes.c_int64 * len(parts))(*widths)
+    try:
+        lib.call(
+            'fl_dot_general_cat', len(parts), ptrs, f_in, P, K, F_out,
+            _ptr(bias.contiguous() if bias is not None else None), _ptr(ws), ws.numel(), _ptr(out.x),
+            _ptr(gemm_status(W.device)), _stream(W.device))
+    except lib.FolxB200Error as e:
+        if e.code == lib.FL_EUNSUPPORTED:
+            return None
+        raise
+    return out
+
+
 def layernorm(a: FwdLaplArray, gamma: torch.Tensor | None, beta: torch.Tensor | None,
               eps: float = 1e-6) -> FwdLaplArray:
     """LayerNorm over the last axis of a triplet whose index map is constant along that axis."""

@@ -70,6 +70,8 @@ _SIGNATURES = {
     'fl_dot_general_grouped': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                          c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    'fl_dot_general_cat': (c_int32, [c_int32, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+                                     c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
     'fl_dot_general_set_mode': (None, [c_int32]),
     'fl_mhsa_set_mode': (None, [c_int32]),
     'fl_slogdet_set_mode': (c_int32, [c_int32]),

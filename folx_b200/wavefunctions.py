@@ -136,27 +136,28 @@ def ferminet_params(cfg: FermiNetConfig):
     return p
 
 
-_stacked_weights: dict = {}   # (id(A), id(B)) -> (weak references, versions, cat([A, B]))
+_stacked_weights: dict = {}   # ids of the blocks -> (weak references, versions, cat(blocks))
 
 
-def _stacked(A: torch.Tensor, B: torch.Tensor) -> torch.Tensor:
-    """``cat([A, B], 0)``, made once per pair of weight tensors (again when one is modified)."""
-    key = (id(A), id(B))
+def _stacked(*blocks: torch.Tensor) -> torch.Tensor:
+    """``cat(blocks, 0)``, made once per set of weight tensors (again when one is modified)."""
+    key = tuple(id(b) for b in blocks)
     ent = _stacked_weights.get(key)
-    if ent is None or ent[0]() is not A or ent[1]() is not B or ent[2] != (A._version, B._version):
+    versions = tuple(b._version for b in blocks)
+    if ent is None or any(r() is not b for r, b in zip(ent[0], blocks)) or ent[1] != versions:
         drop = lambda _, k=key: _stacked_weights.pop(k, None)
-        ent = (weakref.ref(A, drop), weakref.ref(B, drop), (A._version, B._version), torch.cat([A, B], 0))
+        ent = (tuple(weakref.ref(b, drop) for b in blocks), versions, torch.cat(list(blocks), 0))
         _stacked_weights[key] = ent
-    return ent[3]
+    return ent[2]
 
 
 def ferminet(cfg: FermiNetConfig, p, r):
     """``log|psi|(r)`` for ``r: (n_elec, 3)``.
 
-    One- and two-electron streams with mean pooling per spin; the layer input
-    ``[h_i, mean_up h, mean_dn h, mean_up g_i., mean_dn g_i.]`` is never concatenated: its weight
-    matrix is kept in blocks and the pooled terms (one row per walker) are added after their own
-    small products.
+    One- and two-electron streams with mean pooling per spin.  Of the layer input
+    ``[h_i, mean_up h, mean_dn h, mean_up g_i., mean_dn g_i.]`` the per-electron features are
+    written as a concatenation (which the front end hands to the product without forming it); the
+    pooled one-electron terms (one row per walker) are added after their own small products.
     """
     N, nu = cfg.n_elec, cfg.n_up
     r_en, d_en = electron_nucleus(r, p['nuclei'])
@@ -165,9 +166,11 @@ def ferminet(cfg: FermiNetConfig, p, r):
     g = torch.cat([r_ee, d_ee.unsqueeze(-1)], -1)            # (N, N, 4)
     for l, layer in enumerate(p['layers']):
         pooled = (h[:nu].mean(0) @ layer['W_up'] + h[nu:].mean(0) @ layer['W_dn'])  # (width,)
-        # the two pooled pair features share one product: [mean_up g | mean_dn g] @ [W_2u; W_2d]
-        pair = torch.cat([g[:, :nu].mean(1), g[:, nu:].mean(1)], -1) @ _stacked(layer['W_2u'], layer['W_2d'])
-        new_h = (F.linear(h, layer['W_h'].t(), layer['b']) + pair + pooled).tanh()
+        # the per-electron part of the layer input, [h_i | mean_up g_i. | mean_dn g_i.], against the
+        # stacked blocks of the weight matrix
+        feats = torch.cat([h, g[:, :nu].mean(1), g[:, nu:].mean(1)], -1)
+        W_feats = _stacked(layer['W_h'], layer['W_2u'], layer['W_2d'])
+        new_h = (F.linear(feats, W_feats.t(), layer['b']) + pooled).tanh()
         h = new_h + h if new_h.shape == h.shape else new_h
         if 'V' in layer:
             new_g = F.linear(g, layer['V'].t(), layer['c']).tanh()

@@ -210,6 +210,20 @@ int32_t fl_dot_general(const float* x, const float* jac, const float* lap,
                        float* y, float* jac_y, float* lap_y,
                        int32_t* status, void* stream);
 
+/* The product of a CONCATENATION along the feature axis, [a_1 | a_2 | a_3] W (+ bias), without
+ * forming the concatenation (the reference concatenates first: concatenate, an INDEXING rule,
+ * folx/wrapped_functions.py:474-479, followed by dot_general, 174-203; the usual form of a
+ * FermiNet layer input [h_i, pooled features]).  operands[i]: a stacked triplet [x; J_1..J_K; lap]
+ * of (K + 2) P contiguous rows of F_in[i] floats, all with the same P and K; y: the output stacked
+ * the same way, (K + 2) P rows of F_out floats; bias is added to the x rows.  workspace: prepared
+ * by fl_dot_general_prepare for the W of sum F_in rows.  Tensor-core path only: every operand but
+ * the last needs F_in[i] % 16 == 0 (all % 4 == 0, 16-byte aligned buffers); FL_EUNSUPPORTED
+ * otherwise, and the caller concatenates and uses fl_dot_general. */
+int32_t fl_dot_general_cat(int32_t n_operands, const float* const* operands, const int64_t* F_in,
+                           int64_t P, int64_t K, int64_t F_out, const float* bias,
+                           const void* workspace, int64_t workspace_bytes, float* y,
+                           int32_t* status, void* stream);
+
 /* fl_dot_general for a triplet that is a SLICE of a larger one (the reference slices with
  * ordinary indexing rules, folx/wrapped_functions.py:457-508, and XLA fuses the slice into the
  * product): x, every Jacobian row and lap consist of P / group_rows groups of group_rows

@@ -344,6 +344,33 @@ def test_where_reductions_and_data_movement(cuda_device, thr):
     check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), x, thr, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
 
 
+def test_product_of_a_concatenation_reads_the_parts_in_place(cuda_device):
+    """cat([a, b, c], -1) @ W of dense features runs as one product over the parts
+    (fl_dot_general_cat) and equals brute force; an odd width falls back to the concatenation."""
+    from folx_b200 import lib
+    g = torch.Generator().manual_seed(71)
+    W0 = torch.randn(4, 64, generator=g) * 0.5
+    Wa, Wb = torch.randn(4, 32, generator=g) * 0.5, torch.randn(4, 20, generator=g) * 0.5
+    Wc = torch.randn(64 + 32 + 20, 24, generator=g) * 0.2
+    bc = torch.randn(24, generator=g) * 0.1
+    Wd = torch.randn(64 + 20, 16, generator=g) * 0.2
+
+    def f(p, x):                                      # x: (6, 4)
+        W0_, Wa_, Wb_, Wc_, bc_, Wd_ = p
+        a, b, c = torch.tanh(x @ W0_), torch.sin(x @ Wa_), torch.tanh(x @ Wb_)
+        y = F.linear(torch.cat([a, b, c], -1), Wc_.t(), bc_)          # widths 64, 32, 20: in place
+        z = torch.cat([a, c], -1) @ Wd_                               # 64, 20: in place as well
+        w = torch.cat([c, a], -1) @ torch.flip(Wd_, (0,))             # 20 first: concatenated
+        return torch.tanh(y).sum() + (z * z).sum() + w.sum()
+
+    x = torch.randn(3, 6, 4, generator=g).to(cuda_device)
+    ps = (W0, Wa, Wb, Wc, bc, Wd)
+    pd, p64 = tuple(t.to(cuda_device) for t in ps), tuple(t.double() for t in ps)
+    before = lib.LAUNCH_COUNTS.get('fl_dot_general_cat', 0)
+    check_against_brute(lambda v: f(pd, v), lambda v: f(p64, v), x, 0, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+    assert lib.LAUNCH_COUNTS.get('fl_dot_general_cat', 0) >= before + 2
+
+
 def test_sparse_and_dense_agree_and_loop_operator(cuda_device):
     """Thresholds 0 and 6 give the same numbers; LoopLaplacianOperator (plain AD) agrees too."""
     cfg = SMALL_FERMI

@@ -127,6 +127,29 @@ def test_select(cuda_device, K, shape):
     assert_close(to_host(got), rules.where(cond, rules.constant(c.double(), K), a))
 
 
+@pytest.mark.parametrize('K,P,widths,F_out', [
+    (3, 40, (32, 16), 24), (5, 300, (256, 32, 32), 256), (0, 7, (16, 20), 16), (2, 130, (64, 36), 260),
+    (4, 200, (48, 16, 4), 64),
+])
+def test_dot_general_of_a_concatenation(cuda_device, K, P, widths, F_out):
+    """[a_1 | a_2 | a_3] W + b over the parts in place against the oracle on the concatenation."""
+    parts = [seeded_triplet(K, (P, w), seed=40 + i) for i, w in enumerate(widths)]
+    g = torch.Generator().manual_seed(7)
+    W = torch.randn(sum(widths), F_out, generator=g, dtype=torch.float64) / sum(widths) ** 0.5
+    b = torch.randn(F_out, generator=g, dtype=torch.float64)
+    W, b = W.float().double(), b.float().double()
+    before = lib.LAUNCH_COUNTS.get('fl_dot_general_cat', 0)
+    got = kernels.dot_general_cat([to_device(t, cuda_device) for t in parts],
+                                  W.float().to(cuda_device), b.float().to(cuda_device))
+    assert got is not None and lib.LAUNCH_COUNTS.get('fl_dot_general_cat', 0) == before + 1
+    kernels.check_gemm_status(cuda_device)
+    whole = tuple(torch.cat([t[i] for t in parts], -1) for i in range(3))
+    assert_close(to_host(got), rules.dot_general(whole, W, b))
+    # not stacked, or a leading width that is no multiple of 16: the caller has to concatenate
+    assert kernels.dot_general_cat([to_device(t, cuda_device, stacked=False) for t in parts],
+                                   W.float().to(cuda_device)) is None
+
+
 def test_select_and_max_bench_shape_properties(cuda_device):
     """Operator-microbench size (B=4096, d=96, F=256): where(c, a, b) + where(~c, a, b) = a + b on
     every field, max(a, b) + min(a, b) = a + b, and max(a, a) = a."""
