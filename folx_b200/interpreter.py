@@ -73,9 +73,9 @@ class LaplTensor:
     def arr(self) -> FwdLaplArray:
         if self._arr is None:
             if self._parts is not None:
-                ax = self._parts[0].x.ndim - 1
-                self._arr = _call('concatenate', tuple(self._parts), {'dimension': ax, 'batch_dims': self.nb},
-                                  self.thr)
+                ax = self._parts[0][0].x.ndim - 1
+                parts = tuple(_scaled_part(a, s, self.thr) for a, s in self._parts)
+                self._arr = _call('concatenate', parts, {'dimension': ax, 'batch_dims': self.nb}, self.thr)
                 self._parts = None
             elif self._terms is not None:
                 key, residual = self._act or ('identity', False)
@@ -98,8 +98,8 @@ class LaplTensor:
             return self._arr.x
         if self._parts is not None:
             if self._like is None:  # shape, dtype and device of the concatenation without forming it
-                x0 = self._parts[0].x
-                width = sum(int(p.x.shape[-1]) for p in self._parts)
+                x0 = self._parts[0][0].x
+                width = sum(int(p.x.shape[-1]) for p, _ in self._parts)
                 self._like = x0.new_zeros(1).expand(*x0.shape[:-1], width)
             return self._like
         return self._terms[0][0].x if self._terms is not None else self._chain[0].x
@@ -310,18 +310,28 @@ class LaplTensor:
         this tensor is not one or the kernel does not take the operands."""
         if (self._arr is None and self._parts is not None and torch.is_tensor(W) and W.ndim == 2
                 and not isinstance(W, LaplTensor) and registry.is_builtin('dot_general')):
-            out = kernels.dot_general_cat(self._parts, W, bias)
+            arrays = [a for a, _ in self._parts]
+            if any(s != 1.0 for _, s in self._parts):
+                # pending factors of the parts (means) go into their blocks of rows of W
+                W = kernels.scaled_weight(W, [(int(a.x.shape[-1]), s) for a, s in self._parts])
+            out = kernels.dot_general_cat(arrays, W, bias)
             if out is not None:
                 return self._wrap(out)
+        return None
+
+    def _scaled_term(self):
+        """``(triplet, s)`` when this tensor is a pending ``s * triplet`` and nothing else."""
+        if (self._arr is None and self._terms is not None and self._act is None
+                and len(self._terms) == 1 and isinstance(self._terms[0][0], FwdLaplArray)):
+            return self._terms[0]
         return None
 
     def _operand_and_weight(self, W):
         """The triplet and the constant matrix of ``self @ W``; a pending scalar factor of this
         tensor (``mean``) moves into the matrix: ``(s a) @ W = a @ (s W)``."""
-        if (self._arr is None and self._terms is not None and self._act is None
-                and len(self._terms) == 1 and isinstance(self._terms[0][0], FwdLaplArray)
-                and torch.is_tensor(W) and W.ndim == 2 and registry.is_builtin('dot_general')):
-            arr, s = self._terms[0]
+        term = self._scaled_term()
+        if term is not None and torch.is_tensor(W) and W.ndim == 2 and registry.is_builtin('dot_general'):
+            arr, s = term
             return arr, (W if s == 1.0 else kernels.scaled_weight(W, s))
         return self.arr, W
 
@@ -554,30 +564,39 @@ def _matmul(a, b):
     return b.__rmatmul__(a)
 
 
+def _scaled_part(a, s: float, thr: int):
+    """A part of a pending concatenation with its pending factor applied."""
+    return a if s == 1.0 else _call('mul', (a, s), {}, thr)
+
+
 def _cat(tensors, dim=0):
     t0 = _first(tensors)
     rank = max(t.ndim for t in tensors)
-    parts = []
+    parts = []   # (triplet or tensor, pending factor)
     for t in tensors:
         if isinstance(t, LaplTensor):
-            parts.append(t._rank_to(rank).arr)
+            t = t._rank_to(rank)
+            parts.append(t._scaled_term() or (t.arr, 1.0))
         elif isinstance(t, BatchedConst):
             c = t.as_subclass(torch.Tensor)
-            parts.append(c.reshape(*c.shape[: t0.nb], *((1,) * (rank - (c.ndim - t0.nb))), *c.shape[t0.nb:]))
+            parts.append((c.reshape(*c.shape[: t0.nb], *((1,) * (rank - (c.ndim - t0.nb))), *c.shape[t0.nb:]), 1.0))
         else:
             # a constant is shared by all walkers: give it the walker axes
             c = t.reshape((1,) * (t0.nb + rank - t.ndim) + tuple(t.shape))
-            parts.append(c.expand(*t0.arr.x.shape[: t0.nb], *c.shape[t0.nb:]))
+            parts.append((c.expand(*t0.arr.x.shape[: t0.nb], *c.shape[t0.nb:]), 1.0))
     ax = (dim % rank) + t0.nb
+    first = parts[0][0]
     if (dim % rank == rank - 1 and 2 <= len(parts) <= 3 and registry.is_builtin('concatenate')
-            and registry.is_builtin('dot_general')
-            and all(isinstance(p, FwdLaplArray) and not p.jacobian.weak for p in parts)
-            and all(tuple(p.x.shape[:-1]) == tuple(parts[0].x.shape[:-1])
-                    and p.jacobian.data.shape[0] == parts[0].jacobian.data.shape[0] for p in parts)):
+            and registry.is_builtin('dot_general') and registry.is_builtin('mul')
+            and all(isinstance(p, FwdLaplArray) and not p.jacobian.weak for p, _ in parts)
+            and all(tuple(p.x.shape[:-1]) == tuple(first.x.shape[:-1])
+                    and p.jacobian.data.shape[0] == first.jacobian.data.shape[0] for p, _ in parts)):
         # dense features side by side (a layer input [h, pooled ...]): stays pending, a product
-        # with a constant matrix reads the parts in place
-        return LaplTensor(None, t0.nb, t0.thr, parts=list(parts))
-    return t0._wrap(_call('concatenate', tuple(parts), {'dimension': ax, 'batch_dims': t0.nb}, t0.thr))
+        # with a constant matrix reads the parts in place and takes their pending factors (means)
+        # into its weights
+        return LaplTensor(None, t0.nb, t0.thr, parts=parts)
+    plain = tuple(_scaled_part(p, s, t0.thr) for p, s in parts)
+    return t0._wrap(_call('concatenate', plain, {'dimension': ax, 'batch_dims': t0.nb}, t0.thr))
 
 
 def _stack(tensors, dim=0):

@@ -250,13 +250,19 @@ class _ScaledWeights:
         self._entries: collections.OrderedDict = collections.OrderedDict()
         self._capacity = capacity
 
-    def get(self, W: torch.Tensor, s: float) -> torch.Tensor:
-        key = (W.data_ptr(), tuple(W.shape), tuple(W.stride()), W.device.index, W.dtype, float(s))
+    def get(self, W: torch.Tensor, s) -> torch.Tensor:
+        # s: one factor, or ((rows, factor), ...) for consecutive blocks of rows
+        s = tuple((int(n), float(f)) for n, f in s) if isinstance(s, (tuple, list)) else float(s)
+        key = (W.data_ptr(), tuple(W.shape), tuple(W.stride()), W.device.index, W.dtype, s)
         ent = self._entries.get(key)
         if ent is not None and ent[1] == W._version:
             self._entries.move_to_end(key)
             return ent[2]
-        scaled = (W * s).contiguous()
+        if isinstance(s, tuple):
+            factors = torch.cat([torch.full((n,), f, dtype=W.dtype) for n, f in s]).to(W.device)
+            scaled = (W * factors[:, None]).contiguous()
+        else:
+            scaled = (W * s).contiguous()
         self._entries[key] = (W, W._version, scaled)
         while len(self._entries) > self._capacity:
             self._entries.popitem(last=False)
@@ -266,9 +272,10 @@ class _ScaledWeights:
 _scaled_weights = _ScaledWeights()
 
 
-def scaled_weight(W: torch.Tensor, s: float) -> torch.Tensor:
+def scaled_weight(W: torch.Tensor, s) -> torch.Tensor:
     """``W * s`` for a constant weight, cached: ``(s a) @ W = a @ (s W)`` saves the pass that
-    would scale the triplet."""
+    would scale the triplet.  ``s`` is one factor or ``((rows, factor), ...)`` for consecutive
+    blocks of rows (the operands of a concatenation, each with its own factor)."""
     return _scaled_weights.get(W, s)
 _status: dict[torch.device, torch.Tensor] = {}
 
