@@ -456,6 +456,12 @@ int32_t run_attention(const char* who, Args a, int64_t B, int64_t n, int64_t H, 
   const bool tc_ok = vec && attention_mma_supported(n, d) && al(a.o) && al(a.ol);
   FL_REQUIRE(g_attention_mode != 2 || tc_ok, FL_EUNSUPPORTED,
              "%s: tensor-core kernel forced but n=%lld / alignment do not fit", who, (long long)n);
+  if (a.slots > 0) {
+    FL_REQUIRE(tc_ok && g_attention_mode != 1 && !edge && R == (int64_t)a.slots * n, FL_EUNSUPPORTED,
+               "%s: slot-structured Jacobians need the tensor-core kernel (16 < n <= 64, aligned "
+               "buffers) and R = slots * n", who);
+    return launch_attention_mma(a, false, st);
+  }
   if (tc_ok && g_attention_mode != 1) return launch_attention_mma(a, edge, st);
   if (edge) {
     if (n <= 16) return launch<16, true>(a, vec, st);
@@ -483,6 +489,29 @@ extern "C" int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_la
          (int)B, (int)n, (int)H, (int)d, (int)R, q_jac_stride, k_jac_stride, v_jac_stride,
          o_jac_stride, nullptr, nullptr, nullptr, 0};
   return run_attention("fl_mhsa", a, B, n, H, d, R, false, (cudaStream_t)stream);
+}
+
+// fl_mhsa for q, k, v whose Jacobians are still SPARSE in the layout of per-electron features:
+// `slots` stored rows, slot s of electron i being input coordinate slots * i + s (R = slots * n
+// inputs).  The kernel reads the stored rows in place instead of a densified copy; the output is
+// dense as always.  Tensor-core kernel only: FL_EUNSUPPORTED otherwise (the caller densifies).
+extern "C" int32_t fl_mhsa_slots(const float* q, const float* q_jac, const float* q_lap,
+                                 const float* k, const float* k_jac, const float* k_lap,
+                                 const float* v, const float* v_jac, const float* v_lap,
+                                 const uint8_t* mask, const uint8_t* input_mask, float* o,
+                                 float* o_jac, float* o_lap, int64_t B, int64_t n, int64_t H,
+                                 int64_t d, int64_t slots, int64_t q_jac_stride,
+                                 int64_t k_jac_stride, int64_t v_jac_stride, int64_t o_jac_stride,
+                                 void* stream) {
+  using namespace fl;
+  FL_REQUIRE(slots >= 1 && slots <= 64, FL_EBADSHAPE, "fl_mhsa_slots: bad slot count %lld",
+             (long long)slots);
+  const int64_t R = slots * n;
+  Args a{q, q_jac, q_lap, k, k_jac, k_lap, v, v_jac, v_lap, mask, input_mask, o, o_jac, o_lap,
+         (int)B, (int)n, (int)H, (int)d, (int)R, q_jac_stride, k_jac_stride, v_jac_stride,
+         o_jac_stride, nullptr, nullptr, nullptr, 0};
+  a.slots = (int)slots;
+  return run_attention("fl_mhsa_slots", a, B, n, H, d, R, false, (cudaStream_t)stream);
 }
 
 extern "C" int32_t fl_mhsea(const float* q, const float* q_jac, const float* q_lap, const float* k,

@@ -19,6 +19,11 @@ struct AttentionArgs {
   // Laplacian; ejs = Jacobian row stride
   const float *e, *ej, *el;
   int64_t ejs;
+  // slots > 0 (tensor-core kernel only): the Jacobians of q, k, v are stored SPARSE with `slots`
+  // rows, slot s of electron i being input coordinate slots * i + s (the layout of an embedding of
+  // per-electron features); Jacobian row r = slots * i + s of the rule then reads stored row s and
+  // is zero on every electron but i.  R = slots * n.
+  int slots = 0;
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {

@@ -47,12 +47,16 @@ struct Geo {
 
 template <int NP, int PITCH>
 __device__ __forceinline__ void load_tile(float* dst, const float* src, const AttentionArgs& a, int b,
-                                          int h, const uint8_t* rowmask, bool zero_masked) {
+                                          int h, const uint8_t* rowmask, bool zero_masked,
+                                          int only_row = -1) {
+  // only_row >= 0: every other electron's row of the tile is zero (a Jacobian row of a
+  // slot-structured sparse operand)
   const int64_t row_stride = (int64_t)a.H * a.d;
   const float* base = src + ((int64_t)b * a.n * a.H + h) * a.d;
   for (int e = threadIdx.x; e < NP * (DMAX / 4); e += Geo<NP>::THREADS) {
     const int i = e / (DMAX / 4), c = (e % (DMAX / 4)) * 4;
-    const bool ok = i < a.n && c < a.d && !(zero_masked && !rowmask[i]);
+    const bool ok = i < a.n && c < a.d && !(zero_masked && !rowmask[i]) &&
+                    (only_row < 0 || i == only_row);
     cp_async16(dst + i * PITCH + c, ok ? base + i * row_stride + c : src, ok);
   }
 }
@@ -223,9 +227,12 @@ mhsa_mma_kernel(AttentionArgs a) {
     __syncthreads();  // tiles visible; every warp has left the previous iteration
     if (it < a.R) {
       float* nb = buf + (cur ^ 1) * kBuf;
-      load_tile<NP, DP>(nb, a.qj + (int64_t)it * a.qjs, a, b, h, rowmask_s, true);
-      load_tile<NP, DP>(nb + NP * DP, a.kj + (int64_t)it * a.kjs, a, b, h, rowmask_s, true);
-      load_tile<NP, VP>(nb + 2 * NP * DP, a.vj + (int64_t)it * a.vjs, a, b, h, rowmask_s, true);
+      // Jacobian row `it`: stored row and, for slot-structured operands, the one electron it lives on
+      const int src_row = a.slots ? it % a.slots : it;
+      const int only = a.slots ? it / a.slots : -1;
+      load_tile<NP, DP>(nb, a.qj + (int64_t)src_row * a.qjs, a, b, h, rowmask_s, true, only);
+      load_tile<NP, DP>(nb + NP * DP, a.kj + (int64_t)src_row * a.kjs, a, b, h, rowmask_s, true, only);
+      load_tile<NP, VP>(nb + 2 * NP * DP, a.vj + (int64_t)src_row * a.vjs, a, b, h, rowmask_s, true, only);
       cp_async_commit();
     }
     const float* QR = buf + cur * kBuf;

@@ -607,6 +607,43 @@ def mhsa(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, mask: torch.Tensor |
     return out
 
 
+def mhsa_slots(q: FwdLaplArray, k: FwdLaplArray, v: FwdLaplArray, slots: int,
+               mask: torch.Tensor | None = None, input_mask: torch.Tensor | None = None):
+    """``mhsa`` for q, k, v whose sparse Jacobians have ``slots`` rows with slot ``s`` of electron
+    ``i`` being input ``slots * i + s``: the stored rows are read in place (``fl_mhsa_slots``)
+    instead of densified copies.  Returns None when the kernel does not take the operands."""
+    trip = [as_contiguous(t) for t in (q, k, v)]
+    B, n, H, d = trip[0].x.shape
+    fixed = []
+    for t in trip:
+        j = t.jacobian.data
+        if tuple(j.shape) != (slots, B, n, H, d):
+            j = j.expand(slots, B, n, H, d)
+        if not _rows_contiguous(j) or (slots > 1 and j.stride(0) < t.x.numel()):
+            j = j.contiguous()
+        fixed.append((t.x, j, t.laplacian))
+    (qx, qj, ql), (kx, kj, kl), (vx, vj, vl) = fixed
+    _require_cuda(qx, qj, ql, kx, kj, kl, vx, vj, vl)
+    R = slots * n
+    out = alloc_triplet(R, (B, n, H, d), qx.device, None)
+    m8 = mask.to(torch.uint8).contiguous() if mask is not None else None
+    im8 = input_mask.to(torch.uint8).contiguous() if input_mask is not None else None
+    if im8 is not None and tuple(im8.shape) != (R, B):
+        raise ValueError(f'mhsa: input_mask must have shape {(R, B)}, got {tuple(im8.shape)}')
+    try:
+        lib.call(
+            'fl_mhsa_slots', _ptr(qx), _ptr(qj), _ptr(ql), _ptr(kx), _ptr(kj), _ptr(kl), _ptr(vx),
+            _ptr(vj), _ptr(vl), _ptr(m8), _ptr(im8), _ptr(out.x), _ptr(out.jacobian.data),
+            _ptr(out.laplacian), B, n, H, d, slots, _jac_stride(qj), _jac_stride(kj), _jac_stride(vj),
+            _jac_stride(out.jacobian.data), _stream(qx.device),
+        )
+    except lib.FolxB200Error as err:
+        if err.code == lib.FL_EUNSUPPORTED:
+            return None
+        raise
+    return out
+
+
 def mhsea(q: FwdLaplArray, k: FwdLaplArray, e: FwdLaplArray, v: FwdLaplArray,
           mask: torch.Tensor | None = None, input_mask: torch.Tensor | None = None) -> FwdLaplArray:
     """Self attention with an edge bias added to the scores (argument order of the reference's

@@ -95,6 +95,7 @@ _SIGNATURES = {
     'fl_inv': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                          c_void_p, c_void_p, c_int64, c_void_p, c_void_p]),
     'fl_mhsa': (c_int32, [c_void_p] * 14 + [c_int64] * 9 + [c_void_p]),
+    'fl_mhsa_slots': (c_int32, [c_void_p] * 14 + [c_int64] * 9 + [c_void_p]),
     'fl_mhsea': (c_int32, [c_void_p] * 17 + [c_int64] * 10 + [c_void_p]),
     'fl_local_energy_workspace_bytes': (c_int64, [c_int64]),
     'fl_local_energy': (c_int32, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_void_p,

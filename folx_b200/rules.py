@@ -750,6 +750,23 @@ def solve(A, b, sparsity_threshold: int = 0):
     return dot_general_pair(C, b, sparsity_threshold)
 
 
+def _per_electron_slots(q, k, v) -> int:
+    """``s`` if q, k, v of shape ``(B, n, H, d)`` are triplets whose sparse Jacobians all have ``s``
+    rows with ``x0_idx[slot, electron] = s * electron + slot`` (constant along walkers, heads and
+    features: what an embedding of per-electron inputs produces), else 0."""
+    if not all(is_triplet(t) and t.jacobian.weak and t.x.ndim == 4 for t in (q, k, v)):
+        return 0
+    s, n = q.jacobian.data.shape[0], q.x.shape[1]
+    want = (s * np.arange(n)[None, :] + np.arange(s)[:, None]).reshape(s, 1, n, 1, 1)
+    for t in (q, k, v):
+        m = _mask_nd(t)
+        if t.jacobian.data.shape[0] != s or t.x.shape[1] != n or m.shape[1] != 1:
+            return 0
+        if m.shape[2] != n or not (m == want).all():  # the map may be stored expanded over heads / features
+            return 0
+    return s
+
+
 def mhsa(q, k, v, mask=None, input_mask=None, sparsity_threshold: int = 0, e=None):
     """Fused attention rule (reference: mhsa_forward_laplacian; with an edge bias ``e`` of shape
     ``(B, n, H, n)`` added to the scores: mhsea_forward_laplacian)."""
@@ -761,6 +778,13 @@ def mhsa(q, k, v, mask=None, input_mask=None, sparsity_threshold: int = 0, e=Non
             sq = mask[:, :, None] & mask[:, None, :]
             s = torch.where(sq[:, None], s, torch.full_like(s, -1e20))
         return torch.einsum('bhij,bjhd->bihd', torch.softmax(s, -1), v)
+    slots = _per_electron_slots(q, k, v) if e is None else 0
+    if slots:
+        # first attention layer: q, k, v still carry the sparse Jacobians of per-electron features;
+        # the kernel reads the stored slots in place instead of densified copies
+        out = kernels.mhsa_slots(q, k, v, slots, mask=mask, input_mask=input_mask)
+        if out is not None:
+            return out
     R = max(t.jacobian.max_n + 1 if t.jacobian.weak else t.jacobian.data.shape[0]
             for t in (q, k, v, e) if is_triplet(t))
     trip = []

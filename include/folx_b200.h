@@ -414,6 +414,23 @@ int32_t fl_mhsa(const float* q, const float* q_jac, const float* q_lap,
                 int64_t q_jac_stride, int64_t k_jac_stride, int64_t v_jac_stride,
                 int64_t o_jac_stride, void* stream);
 
+/* fl_mhsa for q, k, v whose Jacobians are still SPARSE in the layout of per-electron features
+ * (the first attention layer: the reference densifies them first,
+ * folx/experimental/pallas/attention/forward_laplacian.py:164-178): q_jac, k_jac, v_jac hold
+ * `slots` rows of shape (B, n, H, d), slot s of electron i being input coordinate slots * i + s;
+ * the rule runs over R = slots * n inputs, reading stored row r % slots restricted to electron
+ * r / slots, and writes the dense o_jac (R rows).  input_mask: (R, B).  Tensor-core kernel only
+ * (16 < n <= 64, d % 4 == 0, 16-byte aligned buffers): FL_EUNSUPPORTED otherwise, and the caller
+ * densifies and uses fl_mhsa. */
+int32_t fl_mhsa_slots(const float* q, const float* q_jac, const float* q_lap,
+                      const float* k, const float* k_jac, const float* k_lap,
+                      const float* v, const float* v_jac, const float* v_lap,
+                      const uint8_t* mask, const uint8_t* input_mask,
+                      float* o, float* o_jac, float* o_lap,
+                      int64_t B, int64_t n, int64_t H, int64_t d, int64_t slots,
+                      int64_t q_jac_stride, int64_t k_jac_stride, int64_t v_jac_stride,
+                      int64_t o_jac_stride, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Multi-head self EDGE attention on triplets: scores q k^T + e with an edge-bias triplet e.
  * Replaces mhsea_forward_laplacian and its Pallas kernel

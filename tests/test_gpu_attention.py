@@ -9,6 +9,7 @@ import pytest
 import torch
 
 from folx_b200 import kernels, lib
+from folx_b200 import rules as dev_rules
 from oracle import rules
 
 from gpu_util import assert_close, seeded_triplet, to_device, to_host
@@ -134,3 +135,38 @@ def test_mhsea_with_zero_edges_equals_mhsa(cuda_device):
     b = kernels.mhsa(dev(q), dev(k), dev(v))
     for x, y in zip(to_host(a), to_host(b)):
         assert torch.equal(x, y)
+
+
+@pytest.mark.parametrize('B,n,H,d,slots', [(3, 32, 4, 64, 3), (2, 24, 2, 32, 2), (1, 64, 1, 64, 3), (2, 17, 3, 16, 1)])
+def test_mhsa_reads_slot_structured_sparse_jacobians_in_place(cuda_device, B, n, H, d, slots):
+    """First attention layer: q, k, v carry `slots` stored rows per electron (x0_idx = slots * i +
+    slot).  fl_mhsa_slots on the stored rows equals the dense rule on the densified Jacobians."""
+    import numpy as np
+    from folx_b200.api import FwdJacobian, FwdLaplArray
+    idx = (slots * np.arange(n)[None, :] + np.arange(slots)[:, None]).reshape(slots, 1, n, 1, 1).astype(np.int32)
+    R = slots * n
+    trips, dense = [], []
+    for i, scale in enumerate((0.5, 0.5, 1.0)):
+        x, J, lap = seeded_triplet(slots, (B, n, H, d), seed=60 + i, scale=scale)
+        # the map may be stored compact or expanded over heads and features (after a reshape)
+        stored = idx if i < 2 else np.ascontiguousarray(np.broadcast_to(idx, (slots, 1, n, H, d)))
+        trips.append(FwdLaplArray(x.float().to(cuda_device), FwdJacobian(J.float().to(cuda_device), stored),
+                                  lap.float().to(cuda_device)))
+        Jd = torch.zeros(R, B, n, H, d, dtype=torch.float64)
+        for s in range(slots):
+            for e in range(n):
+                Jd[slots * e + s, :, e] = J[s, :, e]
+        dense.append((x, Jd, lap))
+    mask = torch.ones(B, n, dtype=torch.bool)
+    mask[:, n - 3:] = False
+    input_mask = torch.ones(R, B, dtype=torch.bool)
+    input_mask[R - 2:] = False
+    assert dev_rules._per_electron_slots(*trips) == slots
+    before = lib.LAUNCH_COUNTS.get('fl_mhsa_slots', 0)
+    got = dev_rules.mhsa(*trips, mask.to(cuda_device), input_mask.to(cuda_device))
+    assert lib.LAUNCH_COUNTS.get('fl_mhsa_slots', 0) == before + 1
+    assert got.jacobian.x0_idx is None and got.jacobian.data.shape[0] == R
+    want = rules.mhsa(*dense, mask, input_mask)
+    g, w = blank_out(to_host(got), mask), blank_out(want, mask)
+    assert_close(g[:2], w[:2], rtol=1e-4, atol_scale=2e-5)
+    assert_close(g[2:], w[2:], rtol=1e-3, atol_scale=5e-5)
