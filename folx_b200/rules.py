@@ -227,6 +227,10 @@ def _union_aligned(a: Arr, b: Arr, shape):
     """Two sparse triplets of the same shape on one row frame: rows with identical index maps are
     merged, the others are kept side by side (FwdJacobian.__add__, folx/api.py:230-249)."""
     ma, mb = masks.broadcast_except([_mask_nd(a), _mask_nd(b)], JAC_DIM)
+    if ma.shape == mb.shape and np.array_equal(ma, mb):
+        # identical index maps: rows correspond one to one and keep their order
+        # (FwdJacobian.__add__, folx/api.py:237-243)
+        return a, b, ma
     result_mask, inv = masks.union_rows([ma, mb])
     Ka = ma.shape[0]
     n_rows = result_mask.shape[0]
