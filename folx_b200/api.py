@@ -94,8 +94,10 @@ class FwdJacobian(NamedTuple):
         """Dense Jacobian with ``max_n + 1`` rows (reference: folx/api.py:182-190)."""
         if self.x0_idx is None:
             return self.data
-        ext = (slice(None),) + (None,) * len(self.data_shape)
-        return self.construct_jac_for(np.arange(self.max_n + 1)[ext])
+        # the frame 0 .. max_n holds input v in slot v, so the slot of every stored row is its
+        # own map entry (what get_index_mask would find by comparison)
+        return self.materialize_for_idx(np.where(self.x0_idx >= 0, self.x0_idx, -1).astype(np.int64),
+                                        self.max_n + 1)
 
     @property
     def as_dense(self) -> 'FwdJacobian':

@@ -19,6 +19,7 @@ from .api import JAC_DIM, FwdJacobian
 from .kernels import _ptr, _require_cuda, _stream
 
 _table_cache: dict[tuple, torch.Tensor] = {}
+_take_cache: dict[tuple, np.ndarray] = {}   # index map -> gather table of materialize_for_idx
 
 
 def _device_table(take: np.ndarray, device) -> torch.Tensor:
@@ -99,9 +100,18 @@ def materialize_for_idx(jac: FwdJacobian, idx: np.ndarray, max_idx: int | None =
     out_shape = tuple(np.broadcast_shapes(tuple(data.shape[1:]), idx.shape[1:]))
     tshape = idx_c.shape[1:]
     p = int(np.prod(tshape, dtype=np.int64))
-    flat = np.broadcast_to(idx_c, (k, *tshape)).reshape(k, p).T  # (p, k)
-    take = masks.gather_table(flat, max_idx)  # (p, max_idx, n_slots)
-    take = np.transpose(take, (1, 2, 0)).reshape(max_idx, take.shape[2], *tshape)
+    # the table depends on the index map alone: built once per map (eager runs hit this on every
+    # call; graph replay never comes back here)
+    key = (hashlib.blake2b(np.ascontiguousarray(idx_c).tobytes(), digest_size=16).digest(), idx_c.shape,
+           str(idx_c.dtype), k, max_idx)
+    take = _take_cache.get(key)
+    if take is None:
+        flat = np.broadcast_to(idx_c, (k, *tshape)).reshape(k, p).T  # (p, k)
+        take = masks.gather_table(flat, max_idx)  # (p, max_idx, n_slots)
+        take = np.transpose(take, (1, 2, 0)).reshape(max_idx, take.shape[2], *tshape)
+        if len(_take_cache) >= 256:
+            _take_cache.pop(next(iter(_take_cache)))
+        _take_cache[key] = take
     return gather_rows(data, take, out_shape, tshape)
 
 
