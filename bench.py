@@ -370,10 +370,23 @@ def run_ours(args, rank, world, device):
     return result
 
 
+def use_all_host_threads() -> int:
+    """The CPU arm runs on every core this process may use.  (A multi-process launcher sets
+    OMP_NUM_THREADS=1 for its workers; only rank 0 runs the CPU arm, so it takes the cores back.)"""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    if torch.get_num_threads() != n:
+        torch.set_num_threads(n)
+    return n
+
+
 def cpu_baseline(sample: int, repeats: int = 3):
     """Times the CPU restatement (oracle, torch fp32, all host threads) on `sample` samples."""
     from oracle import rules
 
+    use_all_host_threads()
     host = make_host_inputs(seed=0, n_samples=sample)
     W, bias = host['W'], host['bias']
     chain_oracle(rules, host['sparse'], W, bias)  # warm-up
@@ -396,6 +409,7 @@ def cpu_baseline(sample: int, repeats: int = 3):
 def run_reference(args, rank, world):
     if rank != 0:
         return None
+    use_all_host_threads()
     if args.workload != 'operators':
         base = cpu_model_baseline(args.workload, walkers=max(1, min(args.steps, 4)))
         return {
@@ -536,6 +550,7 @@ def cpu_model_baseline(name: str, walkers: int = 2):
     """Brute-force Laplacian of the same wavefunction on the host (torch.func, fp32)."""
     from oracle import brute
 
+    use_all_host_threads()
     f, shape, _ = build_model(name, 'cpu')
     r = torch.randn(walkers, *shape, generator=torch.Generator().manual_seed(0))
     brute.jac_and_laplacian(f, r[0])
