@@ -434,6 +434,12 @@ class LaplTensor:
         dims = dims[0] if len(dims) == 1 and isinstance(dims[0], (tuple, list)) else dims
         return self._wrap(_call('rev', (self.arr,), {'dimensions': tuple(self._axis(d) for d in dims)}, self.thr))
 
+    # scatter family with static indices (folx/wrapped_functions.py:497-499, 525-529)
+    def index_add(self, dim, index, source, *, alpha=1): return _index_add(self, dim, index, source, alpha=alpha)
+    def scatter_add(self, dim, index, src): return _scatter_add(self, dim, index, src)
+    def gather(self, dim, index): return _gather(self, dim, index)
+    def index_select(self, dim, index): return _index_select(self, dim, index)
+
     def mean(self, dim=None, keepdim=False):
         if dim is None:
             dim = tuple(range(self.ndim))
@@ -705,6 +711,58 @@ def _pad(x, pad, mode='constant', value=None):
     return x._wrap(_call('pad', (x.arr,), kw, x.thr))
 
 
+def _scatter_operands(x, source):
+    """Physical operands of a scatter: a triplet as it is, a walker-carrying constant as a plain
+    tensor, any other constant expanded over the walker axes."""
+    lt = _first((x, source))
+    nb = lt.nb
+    batch = tuple(lt.arr.x.shape[:nb])
+
+    def rank_of(v):
+        return v.ndim if isinstance(v, LaplTensor) else v.ndim - (nb if isinstance(v, BatchedConst) else 0)
+
+    def phys(v):
+        if isinstance(v, LaplTensor):
+            return v.arr
+        if isinstance(v, BatchedConst):
+            return v.as_subclass(torch.Tensor)
+        t = v.to(device=lt.arr.x.device, dtype=lt.arr.x.dtype)
+        return t.expand(*batch, *t.shape)
+
+    return lt, rank_of(x), phys(x), phys(source)
+
+
+def _static_index_arg(index, what):
+    if isinstance(index, (LaplTensor, BatchedConst)):
+        raise NotImplementedError(f'{what}: the index must be a constant that is the same for every walker')
+    return index
+
+
+def _index_add(x, dim, index, source, *, alpha=1):
+    lt, rank, a, s = _scatter_operands(x, source)
+    kw = {'axis': lt.nb + dim % rank, 'index': _static_index_arg(index, 'index_add'), 'alpha': float(alpha)}
+    return lt._wrap(_call('index_add', (a, s), kw, lt.thr))
+
+
+def _scatter_add(x, dim, index, src):
+    lt, rank, a, s = _scatter_operands(x, src)
+    kw = {'axis': lt.nb + dim % rank, 'index': _static_index_arg(index, 'scatter_add'), 'batch_dims': lt.nb}
+    return lt._wrap(_call('scatter_add', (a, s), kw, lt.thr))
+
+
+def _gather(x, dim, index, *, sparse_grad=False):
+    if not isinstance(x, LaplTensor):
+        raise NotImplementedError('gather: a traced index has no rule (indices are static)')
+    kw = {'axis': x._axis(dim), 'index': _static_index_arg(index, 'gather'), 'batch_dims': x.nb}
+    return x._wrap(_call('gather', (x.arr,), kw, x.thr))
+
+
+def _index_select(x, dim, index):
+    if not isinstance(x, LaplTensor):
+        raise NotImplementedError('index_select: a traced index has no rule (indices are static)')
+    return x[(slice(None),) * (dim % x.ndim) + (_static_index_arg(index, 'index_select'),)]
+
+
 def _softmax_unsupported(*a, **k):
     raise NotImplementedError(
         'softmax on triplets is only available inside the fused attention rule '
@@ -761,6 +819,10 @@ _TORCH_TABLE: dict[Any, Callable] = {
     torch.where: _where, torch.Tensor.where: _where,
     torch.amax: _method('amax'), torch.amin: _method('amin'), torch.prod: _method('prod'),
     torch.cumsum: _method('cumsum'), torch.flip: _method('flip'), torch.nn.functional.pad: _pad,
+    torch.index_add: _index_add, torch.Tensor.index_add: _index_add,
+    torch.scatter_add: _scatter_add, torch.Tensor.scatter_add: _scatter_add,
+    torch.gather: _gather, torch.Tensor.gather: _gather,
+    torch.index_select: _index_select, torch.Tensor.index_select: _index_select,
     torch.matmul: _matmul, torch.nn.functional.linear: _linear,
     torch.sum: _method('sum'), torch.mean: _method('mean'),
     torch.reshape: _method('reshape'), torch.permute: _method('permute'),

@@ -268,6 +268,18 @@ def _pad(args, kwargs, sparsity_threshold):
     return rules.pad(args[0], kwargs['padding'], kwargs.get('value', 0.0), kwargs.get('batch_dims', 0))
 
 
+def _index_add(args, kwargs, sparsity_threshold):
+    return rules.index_add(args[0], kwargs['axis'], kwargs['index'], args[1], kwargs.get('alpha', 1.0))
+
+
+def _scatter_add(args, kwargs, sparsity_threshold):
+    return rules.scatter_add(args[0], kwargs['axis'], kwargs['index'], args[1], kwargs.get('batch_dims', 0))
+
+
+def _take_along(args, kwargs, sparsity_threshold):
+    return rules.take_along(args[0], kwargs['axis'], kwargs['index'], kwargs.get('batch_dims', 0))
+
+
 def _reshape(args, kwargs, sparsity_threshold):
     return rules.reshape(args[0], kwargs['new_sizes'], kwargs.get('batch_dims', 0))
 
@@ -346,6 +358,9 @@ register_function('select_n', _select_n)
 register_function('where', _where)
 register_function('rev', _rev)
 register_function('pad', _pad)
+register_function('index_add', _index_add)
+register_function('scatter_add', _scatter_add)
+register_function('gather', _take_along)
 # functions without a kernel of their own: the dense autodiff rule (the generic path of
 # folx/wrapper.py:73-138 for the registry entries of folx/wrapped_functions.py:402-456)
 register_function('reduce_prod', wrap_forward_laplacian(

@@ -330,6 +330,104 @@ def pad(a, padding, value: float = 0.0, batch_dims: int = 0):
                         FwdJacobian(F.pad(a.jacobian.data, padding), m), F.pad(a.laplacian, padding))
 
 
+def _dense_pair_for_scatter(a, src):
+    """Operand and updates of a scatter as dense triplets with the same number of Jacobian rows
+    (a constant takes part with zero derivatives; the reference's scatter rules materialise too
+    when the operands' maps differ, folx/jvp.py:416-520)."""
+    t = a if is_triplet(a) else src
+    rows = max(densify(x).jacobian.data.shape[0] for x in (a, src) if is_triplet(x))
+    out = []
+    for x in (a, src):
+        if is_triplet(x):
+            out.append(_with_rows(densify(x), rows))
+        else:
+            c = x.to(device=t.x.device, dtype=t.x.dtype)
+            out.append(_zero_triplet_like(c, rows, tuple(c.shape)))
+    return out[0], out[1]
+
+
+_STATIC_INDEX_CACHE: 'OrderedDict' = None
+
+
+def _static_index(index, device):
+    """A static integer index as ``(tensor on device, NumPy copy)``.  The pair is cached per index
+    tensor (storage, shape, version), so a traced function that is replayed or captured into a
+    CUDA graph does not copy the index between host and device again."""
+    global _STATIC_INDEX_CACHE
+    from collections import OrderedDict
+    if _STATIC_INDEX_CACHE is None:
+        _STATIC_INDEX_CACHE = OrderedDict()
+    if not torch.is_tensor(index):
+        index = torch.as_tensor(np.asarray(index), dtype=torch.int64)
+    key = (index.data_ptr(), tuple(index.shape), tuple(index.stride()), str(index.device), str(device),
+           index._version)
+    hit = _STATIC_INDEX_CACHE.get(key)
+    if hit is not None:
+        _STATIC_INDEX_CACHE.move_to_end(key)
+        return hit[1], hit[2]
+    dev = index.detach().to(device=device, dtype=torch.int64)
+    host = index.detach().cpu().numpy().astype(np.int64)
+    _STATIC_INDEX_CACHE[key] = (index, dev, host)          # the strong reference keeps the key unique
+    while len(_STATIC_INDEX_CACHE) > 64:
+        _STATIC_INDEX_CACHE.popitem(last=False)
+    return dev, host
+
+
+def index_add(a, dim: int, index, src, alpha: float = 1.0):
+    """``a.index_add(dim, index, alpha * src)`` (reference: scatter_add, LINEAR | SCATTER,
+    folx/wrapped_functions.py:525-529): linear in operand and updates, so the same scatter is
+    applied to values, Jacobian rows and Laplacian.  ``index`` is a static 1-D integer tensor."""
+    if not is_triplet(a) and not is_triplet(src):
+        return a.index_add(dim, index, src, alpha=alpha)
+    A, S = _dense_pair_for_scatter(a, src)
+    dim = dim % A.x.ndim
+    index, _ = _static_index(index, A.x.device)
+    return FwdLaplArray(A.x.index_add(dim, index, S.x, alpha=alpha),
+                        FwdJacobian(A.jacobian.data.index_add(dim + 1, index, S.jacobian.data, alpha=alpha)),
+                        A.laplacian.index_add(dim, index, S.laplacian, alpha=alpha))
+
+
+def scatter_add(a, dim: int, index, src, batch_dims: int = 0):
+    """``a.scatter_add(dim, index, src)`` with a static ``index`` that is the same for every walker
+    and has the per-walker rank of ``src`` (reference: scatter_add,
+    folx/wrapped_functions.py:525-529)."""
+    if not is_triplet(a) and not is_triplet(src):
+        return a.scatter_add(dim, index, src)
+    A, S = _dense_pair_for_scatter(a, src)
+    dim = dim % A.x.ndim
+    index, _ = _static_index(index, A.x.device)
+    index = index.reshape((1,) * batch_dims + tuple(index.shape)).expand(*S.x.shape[:batch_dims], *index.shape)
+    K = A.jacobian.data.shape[0]
+    return FwdLaplArray(A.x.scatter_add(dim, index, S.x),
+                        FwdJacobian(A.jacobian.data.scatter_add(dim + 1, index.unsqueeze(0).expand(K, *index.shape),
+                                                                S.jacobian.data)),
+                        A.laplacian.scatter_add(dim, index, S.laplacian))
+
+
+def take_along(a, dim: int, index, batch_dims: int = 0):
+    """``torch.gather(a, dim, index)`` with a static ``index`` that is the same for every walker
+    and has the per-walker rank of ``a`` (reference: gather, INDEXING,
+    folx/wrapped_functions.py:497-499); the index map is gathered like the values."""
+    if not is_triplet(a):
+        return torch.gather(a, dim, index)
+    dim = dim % a.x.ndim
+    if dim < batch_dims:
+        raise NotImplementedError('gather along a walker axis')
+    index, host = _static_index(index, a.x.device)
+    K = a.jacobian.data.shape[0]
+    m = a.jacobian.x0_idx
+    if m is not None:
+        full = _full_mask_keep_batch(a, batch_dims)                     # (K, 1 .., per-walker shape)
+        idx0 = host.reshape((1,) * batch_dims + host.shape)
+        m = np.take_along_axis(full, np.broadcast_to(idx0, (K, *idx0.shape)), axis=dim + 1)
+        m, _ = masks.compact_repeated_dims_except(np.ascontiguousarray(m), JAC_DIM)
+    index = index.reshape((1,) * batch_dims + tuple(index.shape)).expand(*a.x.shape[:batch_dims], *index.shape)
+    j = a.jacobian.data.expand(K, *a.x.shape)
+    return FwdLaplArray(torch.gather(a.x, dim, index),
+                        FwdJacobian(torch.gather(j, dim + 1, index.unsqueeze(0).expand(K, *index.shape)), m),
+                        torch.gather(a.laplacian, dim, index))
+
+
 def _merged_pair(a: Arr, b: Arr):
     ma, mb = masks.broadcast_except([_mask_nd(a), _mask_nd(b)], JAC_DIM)
     both = np.concatenate([ma, mb], axis=0)

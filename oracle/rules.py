@@ -175,6 +175,55 @@ def reduce_extreme(op: str, t: Triplet, axes) -> Triplet:
     return ext.squeeze(axes), (J * w).sum(dim=tuple(a + 1 for a in axes)), (lap * w).sum(dim=axes)
 
 
+def scatter_add(a: Triplet, dim: int, index: torch.Tensor, src: Triplet) -> Triplet:
+    """scatter_add (LINEAR | SCATTER, folx/wrapped_functions.py:525-529): the update at position p
+    of ``src`` is added to the operand at p with its ``dim`` coordinate replaced by ``index[p]``;
+    linear, so values, every Jacobian row and the Laplacian scatter alike.  Written as a loop over
+    the updates (small cases only)."""
+    import itertools
+    x, J, lap = (t.clone() for t in a)
+    sx, sJ, sl = src
+    for p in itertools.product(*(range(n) for n in index.shape)):
+        q = list(p)
+        q[dim] = int(index[p])
+        q = tuple(q)
+        x[q] += sx[p]
+        J[(slice(None), *q)] += sJ[(slice(None), *p)]
+        lap[q] += sl[p]
+    return x, J, lap
+
+
+def index_add(a: Triplet, dim: int, index: torch.Tensor, src: Triplet, alpha: float = 1.0) -> Triplet:
+    """index_add: slice i of ``src`` along ``dim`` is added, times ``alpha``, to slice ``index[i]``
+    of the operand (the scatter_add rule with a one-dimensional index)."""
+    x, J, lap = (t.clone() for t in a)
+    sx, sJ, sl = src
+    for i, tgt in enumerate(index.tolist()):
+        sel = (slice(None),) * dim
+        x[(*sel, tgt)] += alpha * sx[(*sel, i)]
+        J[(slice(None), *sel, tgt)] += alpha * sJ[(slice(None), *sel, i)]
+        lap[(*sel, tgt)] += alpha * sl[(*sel, i)]
+    return x, J, lap
+
+
+def take_along(a: Triplet, dim: int, index: torch.Tensor) -> Triplet:
+    """gather with a static index (INDEXING, folx/wrapped_functions.py:497-499): position p of the
+    result is the operand at p with its ``dim`` coordinate replaced by ``index[p]``."""
+    import itertools
+    x, J, lap = a
+    ox = torch.zeros(tuple(index.shape), dtype=x.dtype)
+    oJ = torch.zeros((J.shape[0], *index.shape), dtype=x.dtype)
+    ol = torch.zeros(tuple(index.shape), dtype=x.dtype)
+    for p in itertools.product(*(range(n) for n in index.shape)):
+        q = list(p)
+        q[dim] = int(index[p])
+        q = tuple(q)
+        ox[p] = x[q]
+        oJ[(slice(None), *p)] = J[(slice(None), *q)]
+        ol[p] = lap[q]
+    return ox, oJ, ol
+
+
 def constant(x: torch.Tensor, K: int) -> Triplet:
     """A constant seen as a triplet: zero Jacobian and Laplacian."""
     return x, torch.zeros((K, *x.shape), dtype=x.dtype), torch.zeros_like(x)

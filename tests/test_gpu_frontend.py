@@ -344,6 +344,49 @@ def test_where_reductions_and_data_movement(cuda_device, thr):
     check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), x, thr, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
 
 
+@pytest.mark.parametrize('thr', [0, 3])
+def test_scatter_family_with_static_indices(cuda_device, thr):
+    """index_add, scatter_add, gather and index_select through their torch spellings (registry
+    entries of folx/wrapped_functions.py:497-499, 525-529): message passing from edges to nodes and
+    back, on sparse and dense Jacobians, with a constant or a traced operand."""
+    g = torch.Generator().manual_seed(73)
+    W = torch.randn(3, 5, generator=g) * 0.8
+    send = torch.tensor([0, 0, 1, 2, 3, 3])
+    recv = torch.tensor([1, 2, 3, 0, 1, 2])
+    along = torch.tensor([[4, 0, 1], [1, 1, 2], [2, 3, 3], [0, 0, 4]])
+
+    def f(p, idx, z):                                    # z: (4, 3)
+        Wm, = p
+        s, r, al = idx
+        h = torch.tanh(z @ Wm)                           # (4, 5): node features, sparse rows per node
+        e = torch.index_select(h, 0, s) * h[r]           # (6, 5): edge features
+        agg = torch.zeros(4, 5, dtype=h.dtype, device=h.device).index_add(0, r, e)   # constant operand
+        agg2 = h.index_add(0, s, torch.sin(e), alpha=0.5)                            # traced operand
+        sc = torch.scatter_add(torch.cos(h), 0, r[:, None].expand(6, 5), e)
+        ga = torch.gather(h, 1, al)                      # (4, 3)
+        return (agg * agg2).sum() + torch.tanh(sc).sum() + (ga * ga).sum()
+
+    x = torch.randn(3, 4, 3, generator=g).to(cuda_device)
+    dev = lambda t: t.to(cuda_device)
+    pd, idxd = (dev(W),), (dev(send), dev(recv), dev(along))
+    p64, idx64 = (W.double(),), (send, recv, along)
+    check_against_brute(lambda z: f(pd, idxd, z), lambda z: f(p64, idx64, z), x, thr,
+                        samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+
+
+def test_gather_keeps_the_index_map(cuda_device):
+    """torch.gather of a sparse triplet moves the index map with the values instead of densifying."""
+    g = torch.Generator().manual_seed(74)
+    W = (torch.randn(3, 5, generator=g) * 0.8).to(cuda_device)
+    along = torch.tensor([[4, 0], [1, 1], [2, 3], [0, 0]], device=cuda_device)
+    x = torch.randn(2, 4, 3, generator=g).to(cuda_device)
+    out = folx.vmap(folx.forward_laplacian(lambda z: torch.gather(torch.tanh(z @ W), 1, along), 3))(x)
+    assert out.jacobian.weak and out.jacobian.data.shape == (3, 2, 4, 2)
+    m = np.broadcast_to(out.jacobian.x0_idx, (3, 1, 4, 2))
+    want = 3 * np.arange(4)[None, :, None] + np.arange(3)[:, None, None]
+    assert (m[:, 0] == np.broadcast_to(want, (3, 4, 2))).all()
+
+
 def test_product_of_a_concatenation_reads_the_parts_in_place(cuda_device):
     """cat([a, b, c], -1) @ W of dense features runs as one product over the parts
     (fl_dot_general_cat) and equals brute force; an odd width falls back to the concatenation."""

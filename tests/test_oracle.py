@@ -282,6 +282,19 @@ def test_where_and_reduce_extreme_match_brute_force():
         assert_triplet_close(rules.reduce_extreme(op, a, (0, 1)), brute.propagate(lambda u: fn(u, dim=(0, 1)), [a]))
 
 
+def test_scatter_family_matches_brute_force():
+    a = rand_triplet(4, (4, 5), seed=71)
+    src = rand_triplet(4, (3, 5), seed=72)
+    idx1 = torch.tensor([2, 0, 2])
+    assert_triplet_close(rules.index_add(a, 0, idx1, src, alpha=0.5),
+                         brute.propagate(lambda u, v: u.index_add(0, idx1, v, alpha=0.5), [a, src]))
+    idx2 = torch.tensor([[0, 1, 2, 3, 3], [3, 3, 0, 0, 1], [1, 1, 1, 1, 1]])
+    assert_triplet_close(rules.scatter_add(a, 0, idx2, src),
+                         brute.propagate(lambda u, v: u.scatter_add(0, idx2, v), [a, src]))
+    idx3 = torch.tensor([[4, 0], [1, 1], [2, 3], [0, 0]])
+    assert_triplet_close(rules.take_along(a, 1, idx3), brute.propagate(lambda u: torch.gather(u, 1, idx3), [a]))
+
+
 def test_dot_general_pair_matches_brute_force():
     a = rand_triplet(4, (2, 3, 5), seed=21)
     b = rand_triplet(4, (2, 5, 4), seed=22)
