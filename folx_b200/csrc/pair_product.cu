@@ -1,0 +1,280 @@
+// Matrix product of two triplets in one pass: y = a b for a: (batch, m, c) and b: (batch, c, n),
+//   J_y[k] = J_a[k] b + a J_b[k]
+//   lap_y  = lap_a b + a lap_b + 2 sum_k J_a[k] J_b[k]
+// (reference: dot_general of two non-constant operands, folx/wrapped_functions.py:205-309, with
+// the Hessian term of folx/hessian.py:177-188).  The reference forms the (batch, m, c, n) product
+// and sums it over c; here a group of matrices stays in shared memory, every Jacobian row pair is
+// read from HBM once (cp.async, double buffered) and each thread keeps a 4 x 4 tile of the
+// Laplacian cross term in registers over all rows.
+//
+// HBM traffic per matrix pair and row: 4 (m c + c n + m n) bytes; arithmetic 6 m c n flops on the
+// fp32 pipe (8 flop / byte at m = c = n = 16).
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace fl {
+namespace {
+
+struct PairArgs {
+  const float *a, *ja, *la, *b, *jb, *lb;
+  float *y, *jy, *ly;
+  int64_t sja, sjb, sjy;   // elements between consecutive Jacobian rows
+  int64_t a_bs, b_bs;      // elements between consecutive matrices of a batch (0: one shared matrix)
+  int64_t batch;
+  int K, m, c, n;
+  int mp, cp, np, cs;      // sizes rounded up to 4; row stride of the a-side tiles in shared memory
+  int G, tiles;            // matrices per block, 4 x 4 output tiles per matrix
+};
+
+template <int V>
+__device__ __forceinline__ void cp_async(float* dst, const float* src) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  if constexpr (V == 4)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Where a thread starts in a run of tile rows and how far one step of blockDim chunks moves it:
+// computed once, so that the copy loops below divide nothing.
+struct Walk {
+  int row, j, drow, dj;   // first (row, chunk); step in rows and chunks
+};
+__device__ __forceinline__ Walk make_walk(int cv) {
+  Walk w;
+  w.row = threadIdx.x / cv, w.j = threadIdx.x - w.row * cv;
+  w.drow = blockDim.x / cv, w.dj = blockDim.x - w.drow * cv;
+  return w;
+}
+
+// Copies `rows x cols` floats per matrix of the block's group into tiles with row stride `ld`.
+// `contig`: the group's matrices follow one another without gaps in global memory and the tiles
+// have no padding rows, so both sides are one run of G * rows rows.
+template <int V>
+__device__ __forceinline__ void fetch(float* dst, int tile_floats, int ld, const float* src,
+                                      int64_t bs, int rows, int cols, int64_t t0, int64_t batch,
+                                      int G, bool contig, const Walk& wk) {
+  const int cv = cols / V;
+  if (contig) {
+    const int64_t left = batch - t0;
+    const int nrows = (int)(left < G ? left : G) * rows;
+    const float* s0 = src + t0 * bs;
+    int row = wk.row, j = wk.j;
+    while (row < nrows) {
+      cp_async<V>(dst + row * ld + j * V, s0 + (int64_t)row * cols + j * V);
+      row += wk.drow, j += wk.dj;
+      if (j >= cv) j -= cv, ++row;
+    }
+    return;
+  }
+  const int per = rows * cv;
+  for (int e = threadIdx.x; e < G * per; e += blockDim.x) {
+    const int g = e / per, w = e - g * per;
+    if (t0 + g >= batch) break;
+    const int i = w / cv, j = (w - i * cv) * V;
+    cp_async<V>(dst + (size_t)g * tile_floats + i * ld + j, src + (t0 + g) * bs + (int64_t)i * cols + j);
+  }
+}
+
+template <int V>
+__global__ void __launch_bounds__(256) pair_product_kernel(const PairArgs p) {
+  extern __shared__ __align__(16) float smem[];
+  const int ta = p.mp * p.cs, tb = p.cp * p.np;       // floats per a-side / b-side tile
+  float* A0 = smem;                                   // [G][mp][cs]
+  float* B0 = A0 + (size_t)p.G * ta;                  // [G][cp][np]
+  float* JA = B0 + (size_t)p.G * tb;                  // [2][G][mp][cs]
+  float* JB = JA + (size_t)2 * p.G * ta;              // [2][G][cp][np]
+  const int total = p.G * (3 * ta + 3 * tb);
+  for (int e = threadIdx.x; e < total; e += blockDim.x) smem[e] = 0.f;   // the padding stays zero
+  __syncthreads();
+
+  const int64_t t0 = (int64_t)blockIdx.x * p.G;
+  const bool contig_a = p.mp == p.m && p.a_bs == (int64_t)p.m * p.c;
+  const bool contig_b = p.cp == p.c && p.np == p.n && p.b_bs == (int64_t)p.c * p.n;
+  const Walk wa = make_walk(p.c / V), wb = make_walk(p.n / V);
+  fetch<V>(A0, ta, p.cs, p.a, p.a_bs, p.m, p.c, t0, p.batch, p.G, contig_a, wa);
+  fetch<V>(B0, tb, p.np, p.b, p.b_bs, p.c, p.n, t0, p.batch, p.G, contig_b, wb);
+  cp_commit();
+  auto fetch_row = [&](int r) {   // r < K: Jacobian row r; r == K: the Laplacians
+    const float* sa = r < p.K ? p.ja + (int64_t)r * p.sja : p.la;
+    const float* sb = r < p.K ? p.jb + (int64_t)r * p.sjb : p.lb;
+    fetch<V>(JA + (size_t)(r & 1) * p.G * ta, ta, p.cs, sa, p.a_bs, p.m, p.c, t0, p.batch, p.G, contig_a, wa);
+    fetch<V>(JB + (size_t)(r & 1) * p.G * tb, tb, p.np, sb, p.b_bs, p.c, p.n, t0, p.batch, p.G, contig_b, wb);
+    cp_commit();
+  };
+  fetch_row(0);
+
+  const int g = threadIdx.x / p.tiles, tile = threadIdx.x - g * p.tiles;
+  const int tpr = p.np / 4;
+  const int i0 = (tile / tpr) * 4, j0 = (tile - (tile / tpr) * tpr) * 4;
+  const bool active = g < p.G && t0 + g < p.batch;
+  const float* a0 = A0 + (size_t)(active ? g : 0) * ta + i0 * p.cs;
+  const float* b0 = B0 + (size_t)(active ? g : 0) * tb + j0;
+  const int64_t out_off = (t0 + g) * (int64_t)p.m * p.n;
+
+  auto store = [&](float* dst, const float (&o)[4][4]) {
+    if (!active) return;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if (i0 + r >= p.m) break;
+      float* row = dst + out_off + (int64_t)(i0 + r) * p.n + j0;
+      if constexpr (V == 4) {
+        __stcs(reinterpret_cast<float4*>(row), make_float4(o[r][0], o[r][1], o[r][2], o[r][3]));
+      } else {
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+          if (j0 + s < p.n) row[s] = o[r][s];
+      }
+    }
+  };
+
+  cp_wait<1>();
+  __syncthreads();
+  {
+    float o[4][4] = {};
+    for (int cc = 0; cc < p.cp; cc += 4) {
+      float4 av[4], bv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) av[r] = *reinterpret_cast<const float4*>(a0 + r * p.cs + cc);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) bv[q] = *reinterpret_cast<const float4*>(b0 + (cc + q) * p.np);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float ar[4] = {av[r].x, av[r].y, av[r].z, av[r].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          o[r][0] = fmaf(ar[q], bv[q].x, o[r][0]);
+          o[r][1] = fmaf(ar[q], bv[q].y, o[r][1]);
+          o[r][2] = fmaf(ar[q], bv[q].z, o[r][2]);
+          o[r][3] = fmaf(ar[q], bv[q].w, o[r][3]);
+        }
+      }
+    }
+    store(p.y, o);
+  }
+
+  float cross[4][4] = {};
+  for (int r = 0; r <= p.K; ++r) {
+    if (r < p.K) {
+      fetch_row(r + 1);
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
+    __syncthreads();
+    const float* ja = JA + (size_t)(r & 1) * p.G * ta + (size_t)(active ? g : 0) * ta + i0 * p.cs;
+    const float* jb = JB + (size_t)(r & 1) * p.G * tb + (size_t)(active ? g : 0) * tb + j0;
+    float o[4][4] = {};
+    auto pass = [&](auto with_cross) {
+      for (int cc = 0; cc < p.cp; cc += 4) {
+        float4 av[4], bv[4], jav[4], jbv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          av[q] = *reinterpret_cast<const float4*>(a0 + q * p.cs + cc);
+          jav[q] = *reinterpret_cast<const float4*>(ja + q * p.cs + cc);
+          bv[q] = *reinterpret_cast<const float4*>(b0 + (cc + q) * p.np);
+          jbv[q] = *reinterpret_cast<const float4*>(jb + (cc + q) * p.np);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float ar[4] = {av[i].x, av[i].y, av[i].z, av[i].w};
+          const float jr[4] = {jav[i].x, jav[i].y, jav[i].z, jav[i].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float bq[4] = {bv[q].x, bv[q].y, bv[q].z, bv[q].w};
+            const float jq[4] = {jbv[q].x, jbv[q].y, jbv[q].z, jbv[q].w};
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+              o[i][s] = fmaf(jr[q], bq[s], o[i][s]);
+              o[i][s] = fmaf(ar[q], jq[s], o[i][s]);
+              if constexpr (decltype(with_cross)::value) cross[i][s] = fmaf(jr[q], jq[s], cross[i][s]);
+            }
+          }
+        }
+      }
+    };
+    if (r < p.K) {
+      pass(std::true_type{});
+      store(p.jy + (int64_t)r * p.sjy, o);
+    } else {
+      pass(std::false_type{});   // the Laplacian rows: linear terms only
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int s = 0; s < 4; ++s) o[i][s] += 2.f * cross[i][s];
+      store(p.ly, o);
+    }
+    __syncthreads();   // the buffer just read is the target of the next but one fetch
+  }
+}
+
+}  // namespace
+}  // namespace fl
+
+// Largest group of matrices per block whose tiles fit `limit` bytes of shared memory (0: none).
+static int pair_group(int mp, int cp, int np, int tiles, size_t limit) {
+  const size_t per = (size_t)3 * ((size_t)mp * (cp + 4) + (size_t)cp * np) * sizeof(float);
+  int G = 128 / tiles;
+  if (G < 1) G = 1;
+  if (G > 16) G = 16;
+  while (G > 1 && G * per > limit) --G;
+  return G * per <= limit ? G : 0;
+}
+
+extern "C" int32_t fl_dot_general_pair(const float* a, const float* jac_a, const float* lap_a,
+                                       int64_t jac_a_stride, int64_t a_batch_stride, const float* b,
+                                       const float* jac_b, const float* lap_b, int64_t jac_b_stride,
+                                       int64_t b_batch_stride, float* y, float* jac_y, float* lap_y,
+                                       int64_t jac_y_stride, int64_t K, int64_t batch, int64_t m,
+                                       int64_t c, int64_t n, void* stream) {
+  using namespace fl;
+  FL_REQUIRE(K >= 0 && batch >= 0 && m >= 0 && c >= 0 && n >= 0 && K < (1ll << 30), FL_EBADSHAPE,
+             "fl_dot_general_pair: bad sizes K=%lld batch=%lld m=%lld c=%lld n=%lld", (long long)K,
+             (long long)batch, (long long)m, (long long)c, (long long)n);
+  if (batch == 0 || m == 0 || n == 0) return FL_OK;
+  FL_REQUIRE(c > 0, FL_EUNSUPPORTED, "fl_dot_general_pair: empty contraction");
+  FL_REQUIRE(a && lap_a && b && lap_b && y && lap_y && (K == 0 || (jac_a && jac_b && jac_y)),
+             FL_EBADSHAPE, "fl_dot_general_pair: null pointer");
+  FL_REQUIRE((a_batch_stride == 0 || a_batch_stride >= m * c) &&
+                 (b_batch_stride == 0 || b_batch_stride >= c * n),
+             FL_EBADSHAPE, "fl_dot_general_pair: matrices of a batch overlap");
+  FL_REQUIRE(m <= 256 && n <= 256 && c <= 4096, FL_EUNSUPPORTED,
+             "fl_dot_general_pair: matrices of %lld x %lld x %lld do not fit one block", (long long)m,
+             (long long)c, (long long)n);
+  PairArgs p{};
+  p.a = a, p.ja = jac_a, p.la = lap_a, p.b = b, p.jb = jac_b, p.lb = lap_b;
+  p.y = y, p.jy = jac_y, p.ly = lap_y;
+  p.sja = jac_a_stride, p.sjb = jac_b_stride, p.sjy = jac_y_stride;
+  p.a_bs = a_batch_stride, p.b_bs = b_batch_stride, p.batch = batch;
+  p.K = (int)K, p.m = (int)m, p.c = (int)c, p.n = (int)n;
+  p.mp = (p.m + 3) & ~3, p.cp = (p.c + 3) & ~3, p.np = (p.n + 3) & ~3, p.cs = p.cp + 4;
+  p.tiles = (p.mp / 4) * (p.np / 4);
+  const size_t limit = 200 * 1024;
+  p.G = p.tiles <= 256 ? pair_group(p.mp, p.cp, p.np, p.tiles, limit) : 0;
+  FL_REQUIRE(p.G > 0, FL_EUNSUPPORTED,
+             "fl_dot_general_pair: matrices of %lld x %lld x %lld do not fit one block", (long long)m,
+             (long long)c, (long long)n);
+  // two blocks per SM when the group allows it
+  while (p.G > 1 && (size_t)p.G * 3 * ((size_t)p.mp * p.cs + (size_t)p.cp * p.np) * 4 > 100 * 1024) --p.G;
+  const size_t smem = (size_t)p.G * 3 * ((size_t)p.mp * p.cs + (size_t)p.cp * p.np) * sizeof(float);
+  const int threads = ((p.G * p.tiles + 31) / 32) * 32;
+  const int64_t blocks = (batch + p.G - 1) / p.G;
+  FL_REQUIRE(blocks < (1ll << 31), FL_EBADSHAPE, "fl_dot_general_pair: batch too large");
+  cudaStream_t st = (cudaStream_t)stream;
+  auto al = [](const void* q) { return q == nullptr || aligned16(q); };
+  const bool vec = c % 4 == 0 && n % 4 == 0 && jac_a_stride % 4 == 0 && jac_b_stride % 4 == 0 &&
+                   jac_y_stride % 4 == 0 && a_batch_stride % 4 == 0 && b_batch_stride % 4 == 0 &&
+                   al(a) && al(jac_a) && al(lap_a) && al(b) && al(jac_b) && al(lap_b) && al(y) &&
+                   al(jac_y) && al(lap_y);
+  auto kern = vec ? pair_product_kernel<4> : pair_product_kernel<1>;
+  FL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
+  kern<<<(unsigned)blocks, threads, smem, st>>>(p);
+  FL_CHECK_LAUNCH("fl_dot_general_pair launch");
+  return FL_OK;
+}

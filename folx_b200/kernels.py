@@ -211,6 +211,44 @@ def select(cond: torch.Tensor, a, b, x0_idx: np.ndarray | None = None) -> FwdLap
     return out
 
 
+def pair_product_fits(m: int, c: int, n: int) -> bool:
+    """Does one matrix pair of ``fl_dot_general_pair`` fit a thread block (256 output tiles of
+    4 x 4, 200 KB of shared memory for three copies of both operands)?"""
+    mp, cp, np_ = (m + 3) & ~3, (c + 3) & ~3, (n + 3) & ~3
+    return (m > 0 and n > 0 and c > 0 and (mp // 4) * (np_ // 4) <= 256
+            and 3 * (mp * (cp + 4) + cp * np_) * 4 <= 200 * 1024)
+
+
+def dot_general_pair(a: FwdLaplArray, b: FwdLaplArray) -> FwdLaplArray:
+    """Matrix product of two dense triplets ``a: (..., m, c)``, ``b: (..., c, n)`` with the same
+    number of Jacobian rows in one kernel (folx/wrapped_functions.py:205-309).  The leading axes
+    are equal, or all of size 1 on one side (that matrix is shared by the batch)."""
+    a, b = as_contiguous(a), as_contiguous(b)
+    _require_cuda(a.x, b.x)
+    K = a.jacobian.data.shape[0]
+    if b.jacobian.data.shape[0] != K:
+        raise ValueError('dot_general_pair: operands have different numbers of Jacobian rows')
+    la, lb = tuple(a.x.shape[:-2]), tuple(b.x.shape[:-2])
+    m, c = a.x.shape[-2:]
+    c2, n = b.x.shape[-2:]
+    na, nb = int(np.prod(la, dtype=np.int64)), int(np.prod(lb, dtype=np.int64))
+    if c != c2 or not (la == lb or na == 1 or nb == 1) or len(la) != len(lb):
+        raise ValueError(f'dot_general_pair: cannot multiply {tuple(a.x.shape)} by {tuple(b.x.shape)}')
+    lead = la if na >= nb else lb
+    batch = max(na, nb)
+    out = alloc_triplet(K, (*lead, m, n), a.x.device, None)
+    lib.call(
+        'fl_dot_general_pair',
+        _ptr(a.x), _ptr(a.jacobian.data), _ptr(a.laplacian), _jac_stride(a.jacobian.data),
+        m * c if na == batch else 0,
+        _ptr(b.x), _ptr(b.jacobian.data), _ptr(b.laplacian), _jac_stride(b.jacobian.data),
+        c * n if nb == batch else 0,
+        _ptr(out.x), _ptr(out.jacobian.data), _ptr(out.laplacian), _jac_stride(out.jacobian.data),
+        K, batch, m, c, n, _stream(a.x.device),
+    )
+    return out
+
+
 class _WeightCache:
     """Split-W workspaces keyed by the weight's storage address, shape and strides, so that views
     made anew on every call (``W.t().t()``, a slice of a parameter) find their workspace again.

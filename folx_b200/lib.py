@@ -62,6 +62,10 @@ _SIGNATURES = {
     'fl_select': (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p,
                             c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                             c_int64, c_void_p]),
+    'fl_dot_general_pair': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                      c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                      c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     'fl_dot_general_workspace_bytes': (c_int64, [c_int64, c_int64]),
     'fl_dot_general_prepare': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     'fl_dot_general': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,

@@ -481,6 +481,15 @@ def dot_general_pair(a: Arr, b: Arr, sparsity_threshold: int = 0) -> Arr:
     nd = a.x.ndim
     if nd < 2 or b.x.ndim != nd or a.x.shape[-1] != b.x.shape[-2]:
         raise ValueError(f'dot_general_pair: cannot multiply {tuple(a.x.shape)} by {tuple(b.x.shape)}')
+    if not a.jacobian.weak and not b.jacobian.weak:
+        # dense rows on both sides: one kernel forms the three products per Jacobian row without
+        # the (..., m, c, n) intermediate
+        la, lb = tuple(a.x.shape[:-2]), tuple(b.x.shape[:-2])
+        shared = la == lb or all(s == 1 for s in la) or all(s == 1 for s in lb)
+        if shared and a.x.numel() and b.x.numel() and kernels.pair_product_fits(
+                a.x.shape[-2], a.x.shape[-1], b.x.shape[-1]):
+            rows = max(a.jacobian.data.shape[0], b.jacobian.data.shape[0])
+            return kernels.dot_general_pair(_with_rows(a, rows), _with_rows(b, rows))
     prod = binary('mul', expand_dims(a, nd), expand_dims(b, nd - 2), sparsity_threshold)  # (..., m, c, n)
     return reduce_sum(prod, (nd - 1,), False, sparsity_threshold)
 

@@ -144,6 +144,20 @@ int32_t fl_select(const uint8_t* cond,
                   float* y, float* jac_y, float* lap_y, int64_t jac_y_stride,
                   int64_t K, int64_t N, void* stream);
 
+/* Batched matrix product of two triplets, a: (batch, m, c) times b: (batch, c, n), in one pass:
+ *     y = a b,   J_y[k] = J_a[k] b + a J_b[k],   lap_y = lap_a b + a lap_b + 2 sum_k J_a[k] J_b[k]
+ * (dot_general of two non-constant operands, folx/wrapped_functions.py:205-309; the cross term is
+ * the Hessian contribution of folx/hessian.py:177-188).  Both operands carry K aligned Jacobian
+ * rows; matrices are row-major and contiguous, `*_batch_stride` elements apart (0: one matrix
+ * shared by the whole batch).  Returns FL_EUNSUPPORTED when one matrix pair does not fit a
+ * thread block (m, n <= 64 with c <= 64 always fit). */
+int32_t fl_dot_general_pair(const float* a, const float* jac_a, const float* lap_a,
+                            int64_t jac_a_stride, int64_t a_batch_stride,
+                            const float* b, const float* jac_b, const float* lap_b,
+                            int64_t jac_b_stride, int64_t b_batch_stride,
+                            float* y, float* jac_y, float* lap_y, int64_t jac_y_stride,
+                            int64_t K, int64_t batch, int64_t m, int64_t c, int64_t n, void* stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Sum of up to FL_ADDN_MAX_TERMS triplets followed by an elementwise function, one pass:
  *     s = sum_t scale_t a_t,   y = f(s)   with the elementwise rule applied to the summed triplet.
