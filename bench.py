@@ -565,7 +565,7 @@ def cpu_model_baseline(name: str, walkers: int = 2):
 
 
 def run_kernel_case(args, device):
-    """Single-kernel cases at BASELINE shapes, for profiling (`--workload attention|slogdet`)."""
+    """Single-kernel cases at BASELINE shapes, for profiling (`--workload attention|slogdet|gather|pair_product`)."""
     from folx_b200 import kernels
 
     g = torch.Generator(device=device).manual_seed(0)
@@ -583,6 +583,15 @@ def run_kernel_case(args, device):
         fn = lambda: kernels.mhsa(q, k, v)
         nbytes = 4 * 4 * walkers * 4 * 98 * 32 * 64
         desc = f'attention-Laplacian kernel, {walkers} walkers x 4 heads, n=32, d=64, R=96'
+    elif args.workload == 'pair_product':
+        # product of two dense triplets, one 16 x 16 x 16 pair per walker and head (attention-like
+        # shapes: 32 matrices per walker), K = 48; FOLX_B200_PAIR_N sets the matrix size
+        n = int(os.environ.get('FOLX_B200_PAIR_N', '16'))
+        K = 48
+        a, b = rand(K, (walkers, 32, n, n)), rand(K, (walkers, 32, n, n))
+        fn = lambda: kernels.dot_general_pair(a, b)
+        nbytes = 4 * walkers * 32 * (K + 2) * 3 * n * n
+        desc = f'two-triplet product kernel, {walkers} walkers x 32 pairs of {n}x{n}x{n}, K={K}'
     elif args.workload == 'gather':
         # the sparse Jacobian of the operator microbench (3 rows per position, row r of sample s
         # belongs to electron s mod 32) scattered into its dense frame of 96 rows, and the sum of
@@ -661,7 +670,7 @@ def main():
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='operators', choices=['operators', 'attention', 'slogdet', 'gather', *MODEL_WORKLOADS])
+    ap.add_argument('--workload', default='operators', choices=['operators', 'attention', 'slogdet', 'gather', 'pair_product', *MODEL_WORKLOADS])
     ap.add_argument('--walkers', type=int, default=None, help='walkers per GPU (model workloads)')
     ap.add_argument('--no-models', action='store_true', help='skip the short model timings of the default run')
     ap.add_argument('--samples', type=int, default=None,
@@ -702,7 +711,7 @@ def main():
             res['models'] = models
         if rank == 0:
             res['cpu_baseline'] = cpu_baseline(sample=1024) if world == 1 else None
-    elif args.workload in ('attention', 'slogdet', 'gather'):
+    elif args.workload in ('attention', 'slogdet', 'gather', 'pair_product'):
         res = run_kernel_case(args, device)
     else:
         res = run_model(args, rank, world, device)

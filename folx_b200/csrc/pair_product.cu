@@ -82,10 +82,13 @@ __device__ __forceinline__ void fetch(float* dst, int tile_floats, int ld, const
   }
 }
 
-template <int V>
+// CPT, NPT: the padded sizes c and n when known at compile time (0: taken from the arguments), so
+// that the inner loops unroll and shared-memory reads use immediate offsets.
+template <int V, int CPT, int NPT>
 __global__ void __launch_bounds__(256) pair_product_kernel(const PairArgs p) {
   extern __shared__ __align__(16) float smem[];
-  const int ta = p.mp * p.cs, tb = p.cp * p.np;       // floats per a-side / b-side tile
+  const int cp = CPT ? CPT : p.cp, cs = CPT ? CPT + 4 : p.cs, np = NPT ? NPT : p.np;
+  const int ta = p.mp * cs, tb = cp * np;             // floats per a-side / b-side tile
   float* A0 = smem;                                   // [G][mp][cs]
   float* B0 = A0 + (size_t)p.G * ta;                  // [G][cp][np]
   float* JA = B0 + (size_t)p.G * tb;                  // [2][G][mp][cs]
@@ -96,25 +99,25 @@ __global__ void __launch_bounds__(256) pair_product_kernel(const PairArgs p) {
 
   const int64_t t0 = (int64_t)blockIdx.x * p.G;
   const bool contig_a = p.mp == p.m && p.a_bs == (int64_t)p.m * p.c;
-  const bool contig_b = p.cp == p.c && p.np == p.n && p.b_bs == (int64_t)p.c * p.n;
+  const bool contig_b = cp == p.c && np == p.n && p.b_bs == (int64_t)p.c * p.n;
   const Walk wa = make_walk(p.c / V), wb = make_walk(p.n / V);
-  fetch<V>(A0, ta, p.cs, p.a, p.a_bs, p.m, p.c, t0, p.batch, p.G, contig_a, wa);
-  fetch<V>(B0, tb, p.np, p.b, p.b_bs, p.c, p.n, t0, p.batch, p.G, contig_b, wb);
+  fetch<V>(A0, ta, cs, p.a, p.a_bs, p.m, p.c, t0, p.batch, p.G, contig_a, wa);
+  fetch<V>(B0, tb, np, p.b, p.b_bs, p.c, p.n, t0, p.batch, p.G, contig_b, wb);
   cp_commit();
   auto fetch_row = [&](int r) {   // r < K: Jacobian row r; r == K: the Laplacians
     const float* sa = r < p.K ? p.ja + (int64_t)r * p.sja : p.la;
     const float* sb = r < p.K ? p.jb + (int64_t)r * p.sjb : p.lb;
-    fetch<V>(JA + (size_t)(r & 1) * p.G * ta, ta, p.cs, sa, p.a_bs, p.m, p.c, t0, p.batch, p.G, contig_a, wa);
-    fetch<V>(JB + (size_t)(r & 1) * p.G * tb, tb, p.np, sb, p.b_bs, p.c, p.n, t0, p.batch, p.G, contig_b, wb);
+    fetch<V>(JA + (size_t)(r & 1) * p.G * ta, ta, cs, sa, p.a_bs, p.m, p.c, t0, p.batch, p.G, contig_a, wa);
+    fetch<V>(JB + (size_t)(r & 1) * p.G * tb, tb, np, sb, p.b_bs, p.c, p.n, t0, p.batch, p.G, contig_b, wb);
     cp_commit();
   };
   fetch_row(0);
 
   const int g = threadIdx.x / p.tiles, tile = threadIdx.x - g * p.tiles;
-  const int tpr = p.np / 4;
+  const int tpr = np / 4;
   const int i0 = (tile / tpr) * 4, j0 = (tile - (tile / tpr) * tpr) * 4;
   const bool active = g < p.G && t0 + g < p.batch;
-  const float* a0 = A0 + (size_t)(active ? g : 0) * ta + i0 * p.cs;
+  const float* a0 = A0 + (size_t)(active ? g : 0) * ta + i0 * cs;
   const float* b0 = B0 + (size_t)(active ? g : 0) * tb + j0;
   const int64_t out_off = (t0 + g) * (int64_t)p.m * p.n;
 
@@ -138,12 +141,13 @@ __global__ void __launch_bounds__(256) pair_product_kernel(const PairArgs p) {
   __syncthreads();
   {
     float o[4][4] = {};
-    for (int cc = 0; cc < p.cp; cc += 4) {
+#pragma unroll 4
+    for (int cc = 0; cc < cp; cc += 4) {
       float4 av[4], bv[4];
 #pragma unroll
-      for (int r = 0; r < 4; ++r) av[r] = *reinterpret_cast<const float4*>(a0 + r * p.cs + cc);
+      for (int r = 0; r < 4; ++r) av[r] = *reinterpret_cast<const float4*>(a0 + r * cs + cc);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) bv[q] = *reinterpret_cast<const float4*>(b0 + (cc + q) * p.np);
+      for (int q = 0; q < 4; ++q) bv[q] = *reinterpret_cast<const float4*>(b0 + (cc + q) * np);
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const float ar[4] = {av[r].x, av[r].y, av[r].z, av[r].w};
@@ -168,18 +172,19 @@ __global__ void __launch_bounds__(256) pair_product_kernel(const PairArgs p) {
       cp_wait<0>();
     }
     __syncthreads();
-    const float* ja = JA + (size_t)(r & 1) * p.G * ta + (size_t)(active ? g : 0) * ta + i0 * p.cs;
+    const float* ja = JA + (size_t)(r & 1) * p.G * ta + (size_t)(active ? g : 0) * ta + i0 * cs;
     const float* jb = JB + (size_t)(r & 1) * p.G * tb + (size_t)(active ? g : 0) * tb + j0;
     float o[4][4] = {};
     auto pass = [&](auto with_cross) {
-      for (int cc = 0; cc < p.cp; cc += 4) {
+#pragma unroll 4
+      for (int cc = 0; cc < cp; cc += 4) {
         float4 av[4], bv[4], jav[4], jbv[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          av[q] = *reinterpret_cast<const float4*>(a0 + q * p.cs + cc);
-          jav[q] = *reinterpret_cast<const float4*>(ja + q * p.cs + cc);
-          bv[q] = *reinterpret_cast<const float4*>(b0 + (cc + q) * p.np);
-          jbv[q] = *reinterpret_cast<const float4*>(jb + (cc + q) * p.np);
+          av[q] = *reinterpret_cast<const float4*>(a0 + q * cs + cc);
+          jav[q] = *reinterpret_cast<const float4*>(ja + q * cs + cc);
+          bv[q] = *reinterpret_cast<const float4*>(b0 + (cc + q) * np);
+          jbv[q] = *reinterpret_cast<const float4*>(jb + (cc + q) * np);
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -272,7 +277,13 @@ extern "C" int32_t fl_dot_general_pair(const float* a, const float* jac_a, const
                    jac_y_stride % 4 == 0 && a_batch_stride % 4 == 0 && b_batch_stride % 4 == 0 &&
                    al(a) && al(jac_a) && al(lap_a) && al(b) && al(jac_b) && al(lap_b) && al(y) &&
                    al(jac_y) && al(lap_y);
-  auto kern = vec ? pair_product_kernel<4> : pair_product_kernel<1>;
+  auto kern = pair_product_kernel<1, 0, 0>;
+  if (vec) {
+    kern = pair_product_kernel<4, 0, 0>;
+    if (p.cp == 16 && p.np == 16) kern = pair_product_kernel<4, 16, 16>;
+    if (p.cp == 32 && p.np == 32) kern = pair_product_kernel<4, 32, 32>;
+    if (p.cp == 64 && p.np == 64) kern = pair_product_kernel<4, 64, 64>;
+  }
   FL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
   kern<<<(unsigned)blocks, threads, smem, st>>>(p);
   FL_CHECK_LAUNCH("fl_dot_general_pair launch");
