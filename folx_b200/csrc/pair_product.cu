@@ -12,6 +12,7 @@
 #include <type_traits>
 
 #include "common.cuh"
+#include "mma_tf32.cuh"
 
 namespace fl {
 namespace {
@@ -219,8 +220,130 @@ __global__ void __launch_bounds__(256) pair_product_kernel(const PairArgs p) {
   }
 }
 
+// The same product on the warp-level tensor-core instruction in split TF32 (three mma.sync per
+// fp32 product, see mma_tf32.cuh) for c = 8 KS and n = 8 NT: one warp owns 16 rows of one
+// matrix pair, keeps the fragments of a (and of b when they fit) in registers over all Jacobian
+// rows and reads the row pair's fragments from shared memory with conflict-free pitches.
+template <int KS, int NT>
+__global__ void __launch_bounds__(256) pair_product_mma_kernel(const PairArgs p) {
+  constexpr int C = 8 * KS, N = 8 * NT, PA = C + 4, PB = N + 8;
+  constexpr bool HOLD = KS * NT <= 4;
+  extern __shared__ __align__(16) float smem[];
+  const int ta = p.m * PA, tb = C * PB;
+  float* A0 = smem;
+  float* B0 = A0 + (size_t)p.G * ta;
+  float* JA = B0 + (size_t)p.G * tb;
+  float* JB = JA + (size_t)2 * p.G * ta;
+
+  const int64_t t0 = (int64_t)blockIdx.x * p.G;
+  const bool contig_a = p.a_bs == (int64_t)p.m * C, contig_b = p.b_bs == (int64_t)C * N;
+  const Walk wa = make_walk(C / 4), wb = make_walk(N / 4);
+  fetch<4>(A0, ta, PA, p.a, p.a_bs, p.m, C, t0, p.batch, p.G, contig_a, wa);
+  fetch<4>(B0, tb, PB, p.b, p.b_bs, C, N, t0, p.batch, p.G, contig_b, wb);
+  cp_commit();
+  auto fetch_row = [&](int r) {
+    const float* sa = r < p.K ? p.ja + (int64_t)r * p.sja : p.la;
+    const float* sb = r < p.K ? p.jb + (int64_t)r * p.sjb : p.lb;
+    fetch<4>(JA + (size_t)(r & 1) * p.G * ta, ta, PA, sa, p.a_bs, p.m, C, t0, p.batch, p.G, contig_a, wa);
+    fetch<4>(JB + (size_t)(r & 1) * p.G * tb, tb, PB, sb, p.b_bs, C, N, t0, p.batch, p.G, contig_b, wb);
+    cp_commit();
+  };
+  fetch_row(0);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, t = lane & 3;
+  const int wpm = p.m / 16;                      // warps per matrix
+  const int g = warp / wpm, m0 = (warp - g * wpm) * 16;
+  const bool active = t0 + g < p.batch;
+  const float* a0 = A0 + (size_t)g * ta;
+  const float* b0 = B0 + (size_t)g * tb;
+  const int64_t out_off = (t0 + g) * (int64_t)p.m * N + (int64_t)(m0 + gq) * N + 2 * t;
+
+  auto store = [&](float* dst, const float (&o)[NT][4]) {
+    if (!active) return;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      float* q = dst + out_off + 8 * nt;
+      __stcs(reinterpret_cast<float2*>(q), make_float2(o[nt][0], o[nt][1]));
+      __stcs(reinterpret_cast<float2*>(q + 8 * N), make_float2(o[nt][2], o[nt][3]));
+    }
+  };
+
+  cp_wait<1>();
+  __syncthreads();
+  FragA fa0[KS];
+  FragB fb0[HOLD ? KS * NT : 1];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks) load_a<PA>(fa0[ks], a0, m0, 8 * ks, gq, t);
+  if constexpr (HOLD) {
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) load_b<PB>(fb0[ks * NT + nt], b0, 8 * ks, 8 * nt, gq, t);
+  }
+  auto b_frag = [&](int ks, int nt) -> FragB {
+    if constexpr (HOLD) {
+      return fb0[ks * NT + nt];
+    } else {
+      FragB f;
+      load_b<PB>(f, b0, 8 * ks, 8 * nt, gq, t);
+      return f;
+    }
+  };
+  {
+    float o[NT][4] = {};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) mma3(o[nt], fa0[ks], b_frag(ks, nt));
+    store(p.y, o);
+  }
+
+  float cross[NT][4] = {};
+  for (int r = 0; r <= p.K; ++r) {
+    if (r < p.K) {
+      fetch_row(r + 1);
+      cp_wait<1>();
+    } else {
+      cp_wait<0>();
+    }
+    __syncthreads();
+    const float* ja = JA + (size_t)(r & 1) * p.G * ta + (size_t)g * ta;
+    const float* jb = JB + (size_t)(r & 1) * p.G * tb + (size_t)g * tb;
+    const bool jac_row = r < p.K;
+    FragA fja[KS];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) load_a<PA>(fja[ks], ja, m0, 8 * ks, gq, t);
+    float o[NT][4] = {};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        FragB fjb;
+        load_b<PB>(fjb, jb, 8 * ks, 8 * nt, gq, t);
+        mma3(o[nt], fja[ks], b_frag(ks, nt));
+        mma3(o[nt], fa0[ks], fjb);
+        if (jac_row) mma3(cross[nt], fja[ks], fjb);
+      }
+    }
+    if (jac_row) {
+      store(p.jy + (int64_t)r * p.sjy, o);
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[nt][e] += 2.f * cross[nt][e];
+      store(p.ly, o);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
 }  // namespace fl
+
+static int g_pair_mode = 0;   // 0: choose by shape, 1: fp32-pipe kernel only
+
+extern "C" void fl_dot_general_pair_set_mode(int32_t mode) { g_pair_mode = mode; }
 
 // Largest group of matrices per block whose tiles fit `limit` bytes of shared memory (0: none).
 static int pair_group(int mp, int cp, int np, int tiles, size_t limit) {
@@ -277,6 +400,32 @@ extern "C" int32_t fl_dot_general_pair(const float* a, const float* jac_a, const
                    jac_y_stride % 4 == 0 && a_batch_stride % 4 == 0 && b_batch_stride % 4 == 0 &&
                    al(a) && al(jac_a) && al(lap_a) && al(b) && al(jac_b) && al(lap_b) && al(y) &&
                    al(jac_y) && al(lap_y);
+  const bool mma_size = (c == 16 || c == 32 || c == 64) && (n == 16 || n == 32 || n == 64);
+  if (vec && g_pair_mode != 1 && m % 16 == 0 && m <= 64 && mma_size &&
+      (a_batch_stride == 0 || a_batch_stride == m * c) && (b_batch_stride == 0 || b_batch_stride == c * n)) {
+    // tensor-core kernel: one warp per 16 rows, four warps per block
+    const int wpm = (int)m / 16, warps = 4;
+    p.G = warps / wpm > 0 ? warps / wpm : 1;
+    const size_t per = (size_t)3 * ((size_t)m * (c + 4) + (size_t)c * (n + 8)) * sizeof(float);
+    while (p.G > 1 && p.G * per > limit) --p.G;
+    void (*mk)(const PairArgs) = nullptr;
+    switch ((int)(c / 8) * 16 + (int)(n / 8)) {
+      case 2 * 16 + 2: mk = pair_product_mma_kernel<2, 2>; break;
+      case 2 * 16 + 4: mk = pair_product_mma_kernel<2, 4>; break;
+      case 2 * 16 + 8: mk = pair_product_mma_kernel<2, 8>; break;
+      case 4 * 16 + 2: mk = pair_product_mma_kernel<4, 2>; break;
+      case 4 * 16 + 4: mk = pair_product_mma_kernel<4, 4>; break;
+      case 4 * 16 + 8: mk = pair_product_mma_kernel<4, 8>; break;
+      case 8 * 16 + 2: mk = pair_product_mma_kernel<8, 2>; break;
+      case 8 * 16 + 4: mk = pair_product_mma_kernel<8, 4>; break;
+      default: mk = pair_product_mma_kernel<8, 8>; break;
+    }
+    FL_CUDA(cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
+    const int64_t nb = (batch + p.G - 1) / p.G;
+    mk<<<(unsigned)nb, p.G * wpm * 32, p.G * per, st>>>(p);
+    FL_CHECK_LAUNCH("fl_dot_general_pair launch");
+    return FL_OK;
+  }
   auto kern = pair_product_kernel<1, 0, 0>;
   if (vec) {
     kern = pair_product_kernel<4, 0, 0>;

@@ -66,6 +66,7 @@ _SIGNATURES = {
                                       c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                       c_void_p, c_void_p, c_void_p, c_int64,
                                       c_int64, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    'fl_dot_general_pair_set_mode': (None, [c_int32]),
     'fl_dot_general_workspace_bytes': (c_int64, [c_int64, c_int64]),
     'fl_dot_general_prepare': (c_int32, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     'fl_dot_general': (c_int32, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,

@@ -150,7 +150,11 @@ int32_t fl_select(const uint8_t* cond,
  * the Hessian contribution of folx/hessian.py:177-188).  Both operands carry K aligned Jacobian
  * rows; matrices are row-major and contiguous, `*_batch_stride` elements apart (0: one matrix
  * shared by the whole batch).  Returns FL_EUNSUPPORTED when one matrix pair does not fit a
- * thread block (m, n <= 64 with c <= 64 always fit). */
+ * thread block (m, n <= 64 with c <= 64 always fit).  Square 16- and 32-wide products (c = n,
+ * m a multiple of 16 up to 64) run on the tensor cores in split TF32, everything else on the fp32
+ * pipe; fl_dot_general_pair_set_mode(1) forces the fp32-pipe kernel (process-wide, for tests),
+ * 0 restores the choice by shape. */
+void fl_dot_general_pair_set_mode(int32_t mode);
 int32_t fl_dot_general_pair(const float* a, const float* jac_a, const float* lap_a,
                             int64_t jac_a_stride, int64_t a_batch_stride,
                             const float* b, const float* jac_b, const float* lap_b,

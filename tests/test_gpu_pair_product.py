@@ -15,8 +15,21 @@ from gpu_util import assert_close, seeded_triplet, to_device, to_host
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[0, 1], ids=['auto', 'fp32-pipe'], autouse=True)
+def pair_mode(request):
+    """Every case runs with the kernel chosen by shape (tensor cores for square 16- and 32-wide
+    products) and with the fp32-pipe kernel forced."""
+    from folx_b200 import lib
+    lib.load().fl_dot_general_pair_set_mode(request.param)
+    yield request.param
+    lib.load().fl_dot_general_pair_set_mode(0)
+
+
 @pytest.mark.parametrize('m,c,n', [(1, 1, 1), (4, 4, 4), (16, 16, 16), (3, 5, 7), (17, 9, 6), (8, 32, 12),
-                                   (32, 32, 32), (64, 64, 64), (5, 130, 3), (64, 3, 64)])
+                                   (32, 32, 32), (64, 64, 64), (5, 130, 3), (64, 3, 64),
+                                   (32, 16, 16), (48, 16, 16), (64, 16, 16), (16, 32, 32), (48, 32, 32),
+                                   (64, 32, 32), (16, 64, 16), (16, 16, 64), (32, 64, 32), (64, 32, 64),
+                                   (48, 64, 64), (16, 32, 16), (32, 16, 32)])
 @pytest.mark.parametrize('K,batch', [(0, (3,)), (5, (7,)), (19, (2, 3))])
 def test_pair_product_matches_oracle(cuda_device, m, c, n, K, batch):
     a = seeded_triplet(K, (*batch, m, c), seed=m + 3 * c + K)
@@ -26,9 +39,10 @@ def test_pair_product_matches_oracle(cuda_device, m, c, n, K, batch):
     assert_close(to_host(got), rules.dot_general_pair(a, b), rtol=1e-4, atol_scale=2e-5)
 
 
+@pytest.mark.parametrize('m,c,n', [(8, 12, 8), (16, 16, 16), (32, 32, 32)])
 @pytest.mark.parametrize('shared', ['a', 'b'])
-def test_pair_product_with_one_matrix_shared_by_the_batch(cuda_device, shared):
-    K, m, c, n = 6, 8, 12, 8
+def test_pair_product_with_one_matrix_shared_by_the_batch(cuda_device, shared, m, c, n):
+    K = 6
     a = seeded_triplet(K, ((1, 1) if shared == 'a' else (3, 5)) + (m, c), seed=1)
     b = seeded_triplet(K, ((1, 1) if shared == 'b' else (3, 5)) + (c, n), seed=2)
     got = kernels.dot_general_pair(to_device(a, cuda_device), to_device(b, cuda_device))
