@@ -434,6 +434,9 @@ class LaplTensor:
         dims = dims[0] if len(dims) == 1 and isinstance(dims[0], (tuple, list)) else dims
         return self._wrap(_call('rev', (self.arr,), {'dimensions': tuple(self._axis(d) for d in dims)}, self.thr))
 
+    def softmax(self, dim): return _softmax(self, dim)
+    def log_softmax(self, dim): return _log_softmax(self, dim)
+
     # scatter family with static indices (folx/wrapped_functions.py:497-499, 525-529)
     def index_add(self, dim, index, source, *, alpha=1): return _index_add(self, dim, index, source, alpha=alpha)
     def scatter_add(self, dim, index, src): return _scatter_add(self, dim, index, src)
@@ -763,10 +766,27 @@ def _index_select(x, dim, index):
     return x[(slice(None),) * (dim % x.ndim) + (_static_index_arg(index, 'index_select'),)]
 
 
-def _softmax_unsupported(*a, **k):
-    raise NotImplementedError(
-        'softmax on triplets is only available inside the fused attention rule '
-        '(folx_b200.multi_head_self_attention)')
+def _shifted_exp(x, dim):
+    """``x - max(x)`` with the maximum taken as a constant, and its exponential: the primitives
+    ``jax.nn.softmax`` traces to (reduce_max under stop_gradient, sub, exp), each with its own rule
+    in the reference (folx/wrapped_functions.py:364-431)."""
+    if dim is None:
+        raise NotImplementedError('softmax on triplets needs an explicit dim')
+    shift = x._wrap(x.arr.x.amax(dim=x._axis(dim), keepdim=True))   # the values only: a constant
+    z = x - shift
+    return z, z.exp()
+
+
+def _softmax(x, dim=None, _stacklevel=3, dtype=None):
+    """softmax as exp / sum(exp) on triplets (the fused attention rules,
+    ``folx_b200.multi_head_self_attention``, are the fast path for attention itself)."""
+    _, e = _shifted_exp(x, dim)
+    return e / e.sum(dim=dim, keepdim=True)
+
+
+def _log_softmax(x, dim=None, _stacklevel=3, dtype=None):
+    z, e = _shifted_exp(x, dim)
+    return z - e.sum(dim=dim, keepdim=True).log()
 
 
 def _pow(x, p):
@@ -834,7 +854,8 @@ _TORCH_TABLE: dict[Any, Callable] = {
     torch.linalg.det: _det, torch.det: _det, torch.linalg.inv: _inv, torch.inverse: _inv,
     torch.linalg.solve: _solve,
     torch.nn.functional.layer_norm: _layer_norm, torch.logsumexp: _logsumexp,
-    torch.softmax: _softmax_unsupported, torch.nn.functional.softmax: _softmax_unsupported,
+    torch.softmax: _softmax, torch.nn.functional.softmax: _softmax, torch.Tensor.softmax: _softmax,
+    torch.log_softmax: _log_softmax, torch.nn.functional.log_softmax: _log_softmax,
     torch.detach: _method('detach'),
     torch.zeros_like: _like(torch.zeros_like), torch.ones_like: _like(torch.ones_like),
 }

@@ -387,6 +387,31 @@ def test_gather_keeps_the_index_map(cuda_device):
     assert (m[:, 0] == np.broadcast_to(want, (3, 4, 2))).all()
 
 
+@pytest.mark.parametrize('thr', [0, 6])
+def test_hand_written_attention_with_softmax(cuda_device, thr):
+    """softmax / log_softmax as exp over sum-of-exp (the primitives jax.nn.softmax traces to,
+    folx/wrapped_functions.py:364-431) around products of two triplets (folx/wrapped_functions.py:
+    205-309, the one-pass kernel once both sides are dense): an attention layer written by hand."""
+    g = torch.Generator().manual_seed(79)
+    n, d = 16, 16
+    W0 = torch.randn(3, d, generator=g) * 0.7
+    Wq, Wk, Wv = (torch.randn(d, d, generator=g) * 0.4 for _ in range(3))
+
+    def f(p, z):                                         # z: (16, 3)
+        W0_, Wq_, Wk_, Wv_ = p
+        h = torch.tanh(z @ W0_)                          # (16, 16)
+        q, k, v = h @ Wq_, h @ Wk_, h @ Wv_
+        s = q @ k.transpose(0, 1) * (d ** -0.5)          # two-triplet product (16 x 16 x 16)
+        a = torch.softmax(s, dim=-1)
+        o = a @ v                                        # and another
+        return torch.tanh(o).sum() + torch.log_softmax(s, -1)[:, 0].sum()
+
+    x = torch.randn(3, n, 3, generator=g).to(cuda_device)
+    pd = tuple(t.to(cuda_device) for t in (W0, Wq, Wk, Wv))
+    p64 = tuple(t.double() for t in (W0, Wq, Wk, Wv))
+    check_against_brute(lambda z: f(pd, z), lambda z: f(p64, z), x, thr, samples=(0, 2), rtol=2e-4, lap_rtol=1e-3)
+
+
 def test_product_of_a_concatenation_reads_the_parts_in_place(cuda_device):
     """cat([a, b, c], -1) @ W of dense features runs as one product over the parts
     (fl_dot_general_cat) and equals brute force; an odd width falls back to the concatenation."""
