@@ -341,6 +341,18 @@ __global__ void __launch_bounds__(256) pair_product_mma_kernel(const PairArgs p)
 }  // namespace
 }  // namespace fl
 
+// Raises the dynamic shared-memory limit of a kernel the first time it is launched (not on every
+// call: launches may be recorded into a CUDA graph).
+static cudaError_t allow_shared(const void* fn, size_t bytes) {
+  static const void* seen[32];
+  static int n_seen = 0;
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i] == fn) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess && n_seen < 32) seen[n_seen++] = fn;
+  return e;
+}
+
 static int g_pair_mode = 0;   // 0: choose by shape, 1: fp32-pipe kernel only
 
 extern "C" void fl_dot_general_pair_set_mode(int32_t mode) { g_pair_mode = mode; }
@@ -420,7 +432,7 @@ extern "C" int32_t fl_dot_general_pair(const float* a, const float* jac_a, const
       case 8 * 16 + 4: mk = pair_product_mma_kernel<8, 4>; break;
       default: mk = pair_product_mma_kernel<8, 8>; break;
     }
-    FL_CUDA(cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
+    FL_CUDA(allow_shared((const void*)mk, limit));
     const int64_t nb = (batch + p.G - 1) / p.G;
     mk<<<(unsigned)nb, p.G * wpm * 32, p.G * per, st>>>(p);
     FL_CHECK_LAUNCH("fl_dot_general_pair launch");
@@ -433,7 +445,7 @@ extern "C" int32_t fl_dot_general_pair(const float* a, const float* jac_a, const
     if (p.cp == 32 && p.np == 32) kern = pair_product_kernel<4, 32, 32>;
     if (p.cp == 64 && p.np == 64) kern = pair_product_kernel<4, 64, 64>;
   }
-  FL_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit));
+  FL_CUDA(allow_shared((const void*)kern, limit));
   kern<<<(unsigned)blocks, threads, smem, st>>>(p);
   FL_CHECK_LAUNCH("fl_dot_general_pair launch");
   return FL_OK;

@@ -59,3 +59,30 @@ def test_cuda_graph_replay_matches_eager(cuda_device):
         e1, s1 = graphed(r)
         torch.testing.assert_close(e1, e0, rtol=1e-6, atol=1e-6)
         torch.testing.assert_close(s1, s0, rtol=1e-9, atol=1e-9)
+
+
+def test_cuda_graph_replay_of_hand_written_attention_and_scatter(cuda_device):
+    """Products of two triplets, softmax and an index_add with a static index are captured and
+    replayed like the fused rules: no host copies or attribute calls are left in the step."""
+    g = torch.Generator().manual_seed(11)
+    n, d = 16, 16
+    W0 = (torch.randn(3, d, generator=g) * 0.7).to(cuda_device)
+    Wq, Wk, Wv = ((torch.randn(d, d, generator=g) * 0.4).to(cuda_device) for _ in range(3))
+    recv = torch.arange(n, device=cuda_device).flip(0) // 2
+
+    def f(z):
+        h = torch.tanh(z @ W0)
+        q, k, v = h @ Wq, h @ Wk, h @ Wv
+        a = torch.softmax(q @ k.transpose(0, 1) * d ** -0.5, dim=-1)
+        o = h.index_add(0, recv, a @ v)
+        return torch.tanh(o).sum()
+
+    pot = lambda rr: (rr * rr).sum((-1, -2))
+    eager = harness.EnergyEvaluator(f, pot, sparsity_threshold=6, chunk=4)
+    graphed = harness.EnergyEvaluator(f, pot, sparsity_threshold=6, chunk=4, graph=True)
+    for seed in (3, 4, 5):
+        r = torch.randn(8, n, 3, generator=torch.Generator().manual_seed(seed)).to(cuda_device)
+        e0, s0 = eager(r)
+        e1, s1 = graphed(r)
+        torch.testing.assert_close(e1, e0, rtol=1e-6, atol=1e-6)
+        torch.testing.assert_close(s1, s0, rtol=1e-9, atol=1e-9)
